@@ -1,0 +1,158 @@
+"""The CPU oracle against the golden vectors recorded from the reference (tests/golden/make_golden.py)."""
+import os
+
+import numpy as np
+import pytest
+
+from oracle import int2_oracle as O
+from oracle import native
+
+from conftest import GOLDEN
+
+
+def _load(name):
+    return np.load(os.path.join(GOLDEN, name))
+
+
+def test_pack_unpack_matches_reference_packers():
+    g = _load("pack.npz")
+    for i in range(5):
+        w = g[f"w{i}"]
+        K = w.shape[1]
+        assert np.array_equal(O.pack_ternary(w, pad_code=1), g[f"helper_packed{i}"])
+        assert np.array_equal(O.pack_ternary(w, pad_code=0), g[f"module_packed{i}"])
+        assert np.array_equal(O.unpack_ternary(g[f"helper_packed{i}"], K).astype(np.float32), g[f"helper_unpacked{i}"])
+        assert np.array_equal(O.unpack_ternary(g[f"module_packed{i}"], K), w)
+    allb = np.arange(256, dtype=np.uint8).reshape(1, 256)
+    dec = O.unpack_ternary(allb, 1024)
+    assert np.array_equal(dec.astype(np.float32), g["all_bytes_unpacked"])
+    assert dec.min() == -1 and dec.max() == 1          # the reserved code never decodes to +2
+
+
+def test_counter_roundtrip_and_sign_extension():
+    rng = np.random.default_rng(3)
+    for K in (1, 2, 7, 64):
+        h = rng.integers(-8, 8, (5, K)).astype(np.int8)
+        assert np.array_equal(O.unpack_counters(O.pack_counters(h), K), h)
+    assert O.unpack_counters(np.array([[0x8F]], dtype=np.uint8), 2).tolist() == [[-1, -8]]
+
+
+def test_ternarize_matches_init_from_float_and_legacy_weight_quant():
+    g = _load("ternarize.npz")
+    for i in range(3):
+        W = g[f"W{i}"]
+        gamma = float(g[f"gamma{i}"])
+        q = O.ternarize(W, gamma)
+        assert np.array_equal(O.pack_ternary(q, pad_code=0), g[f"W_packed{i}"])
+        lg = np.float32(g[f"legacy_gamma{i}"])
+        # the legacy layer returns w + (w_quant - w): equal to q*gamma up to one float32 rounding
+        wq = O.ternarize(W, lg).astype(np.float32) * lg
+        assert np.abs(wq - g[f"legacy_wq{i}"]).max() <= 2e-7 * max(1.0, np.abs(W).max())
+        assert np.array_equal(np.rint(g[f"legacy_wq{i}"] / lg).astype(np.int8), O.ternarize(W, lg))
+        assert abs(O.absmean_scale(W) - gamma) <= 1e-6 * gamma
+
+
+def test_quantize_rows_matches_legacy_activation_quant():
+    g = _load("legacy_layer.npz")
+    for i in range(3):
+        x = g[f"x{i}"]
+        q, a = O.quantize_rows(x)
+        s = (np.float32(127.0) / a).astype(np.float32)
+        xq = (q.astype(np.float32) / s[:, None]).astype(np.float32)
+        ref = g[f"xq{i}"]
+        # the legacy layer returns x + (x_quant - x) in the input dtype, one rounding away from q/s
+        if bool(g[f"is_bf16_{i}"]):
+            assert np.abs(O.to_bf16(xq) - ref).max() <= 2.0 ** -7 * np.abs(ref).max()
+        else:
+            assert np.array_equal(np.rint(ref * s[:, None]).astype(np.int8), q)
+            assert np.abs(xq - ref).max() <= 2e-7 * np.abs(x).max()
+        assert q.min() >= -128 and q.max() <= 127
+
+
+def test_layer_forward_and_dx_within_tolerance_of_legacy_layer():
+    g = _load("legacy_layer.npz")
+    for i in range(3):
+        x, W, dY = g[f"x{i}"], g[f"W{i}"], g[f"dY{i}"]
+        K = x.shape[1]
+        gamma = np.float32(max(np.abs(W).mean(dtype=np.float32), 1e-5))
+        Wp = O.pack_ternary(O.ternarize(W, gamma))
+        bf16 = bool(g[f"is_bf16_{i}"])
+        y, Xq, a = O.bitlinear_forward(x, Wp, gamma, K, out="bf16" if bf16 else "f32")
+        ref = g[f"y{i}"]
+        tol = 1e-2 if bf16 else 1e-5
+        assert np.abs(y - ref).max() <= tol * np.abs(ref).max()
+        # dX: the legacy layer back-propagates the unquantised dY; ours quantises it per token to int8
+        dx = O.bitlinear_backward_dx(dY, Wp, gamma, K, out="f32")
+        refdx = g[f"dx{i}"]
+        assert np.abs(dx - refdx).max() <= 1e-2 * np.abs(refdx).max()
+        # dW: integer definition vs the legacy float gradient (dY^T . fake-quantised x)
+        dw, acc, gmax = O.bitlinear_dw(dY, Xq, a)
+        refdw = g[f"dw{i}"]
+        assert np.abs(dw - refdw).max() <= 2e-2 * np.abs(refdw).max()
+
+
+@pytest.mark.parametrize("impl", ["numpy", "c"])
+def test_hysteresis_matches_reference_kernel_source(impl):
+    g = _load("hysteresis.npz")
+    step_fn = O.hysteresis_step if impl == "numpy" else native.c_hysteresis_step
+    for i in range(6):
+        N, K, thr, lr, ls, dec, step = g[f"params{i}"]
+        N, K, thr, step = int(N), int(K), int(thr), int(step)
+        W1, H1 = step_fn(g[f"dW{i}"], g[f"W0_{i}"], g[f"H0_{i}"], lr, ls, thr, dec, step, K)
+        assert np.array_equal(W1, g[f"W1_{i}"]) and np.array_equal(H1, g[f"H1_{i}"])
+        W2, H2 = step_fn(g[f"dW{i}"], W1, H1, lr, ls, thr, dec, step + 1, K)
+        assert np.array_equal(W2, g[f"W2_{i}"]) and np.array_equal(H2, g[f"H2_{i}"])
+        assert not np.array_equal(W1, g[f"W0_{i}"]) or thr >= 7       # the cases do flip weights
+
+
+def test_hysteresis_row_shards_equal_the_whole_matrix():
+    rng = np.random.default_rng(5)
+    N, K = 24, 52
+    Wp = O.pack_ternary(rng.integers(-1, 2, (N, K)).astype(np.int8))
+    Hp = O.pack_counters(rng.integers(-3, 4, (N, K)).astype(np.int8))
+    dW = (rng.standard_normal((N, K)) * 0.05).astype(np.float32)
+    Wf, Hf = O.hysteresis_step(dW, Wp, Hp, 1e-2, 5.0, 3, 0.1, 9, K)
+    for g in (2, 3, 4):
+        rows = N // g
+        Ws, Hs = [], []
+        for r in range(g):
+            sl = slice(r * rows, (r + 1) * rows)
+            w, h = native.c_hysteresis_step(dW[sl], Wp[sl], Hp[sl], 1e-2, 5.0, 3, 0.1, 9, K, idx_base=r * rows * K)
+            Ws.append(w); Hs.append(h)
+        assert np.array_equal(np.concatenate(Ws), Wf) and np.array_equal(np.concatenate(Hs), Hf)
+
+
+def test_quantize_tensor_matches_reference_kernel_source():
+    g = _load("quant_tensor.npz")
+    for i in range(5):
+        x = g[f"x_bits{i}"].view(np.float16).astype(np.float32)
+        q, am = O.quantize_tensor(x)
+        assert np.float32(am) == g[f"absmax{i}"][0]
+        assert np.array_equal(q, g[f"q{i}"])
+        deq = O.to_f16(O.dequantize_tensor(q, am))
+        assert np.array_equal(deq, g[f"deq_bits{i}"].view(np.float16).astype(np.float32))
+
+
+def test_c_restatement_agrees_with_numpy_on_quant_and_gemms():
+    rng = np.random.default_rng(7)
+    lib = native.oracle_lib()
+    M, N, K = 9, 13, 50
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    q = np.zeros((M, K), np.int8); a = np.zeros(M, np.float32)
+    lib.oracle_quantize_rows(x, q, a, M, K, 1e-5)
+    q2, a2 = O.quantize_rows(x)
+    assert np.array_equal(q, q2) and np.array_equal(a, a2)
+    Wp = O.pack_ternary(rng.integers(-1, 2, (N, K)).astype(np.int8))
+    Wq = np.zeros((N, K), np.int8)
+    lib.oracle_unpack_ternary(Wp, Wq, N, K)
+    assert np.array_equal(Wq, O.unpack_ternary(Wp, K))
+    acc = np.zeros((M, N), np.int32)
+    lib.oracle_gemm_nt_i8(q, Wq, acc, M, N, K)
+    assert np.array_equal(acc, O.gemm_fwd_acc(q, Wp, K))
+    dYq = rng.integers(-127, 128, (M, N)).astype(np.int8)
+    accx = np.zeros((M, K), np.int32)
+    lib.oracle_gemm_tn_i8(np.ascontiguousarray(dYq.T), Wq, accx, N, M, K)
+    assert np.array_equal(accx, O.gemm_dx_acc(dYq, Wp, K))
+    accw = np.zeros((N, K), np.int32)
+    lib.oracle_gemm_tn_i8(dYq, q, accw, M, N, K)
+    assert np.array_equal(accw, O.gemm_dw_acc(dYq, q))
