@@ -1,0 +1,213 @@
+// C ABI of libelleci_int2.so: argument validation and dispatch.  No entry point allocates, synchronises or
+// prints; every one returns an EL_* status.
+#include "common.cuh"
+#include "epilogue.cuh"
+
+namespace el {
+
+enum { MODE_FWD = 0, MODE_DX = 1, MODE_DW = 2 };
+
+// kernels in the other translation units
+int launch_pack(const void* src, bool from_float, float gamma, uint8_t* Wp, int N, int K, int pad_code, cudaStream_t st);
+int launch_unpack(const uint8_t* Wp, void* out, int out_dtype, int N, int K, cudaStream_t st);
+int launch_quantize_rows(const void* x, int dt, int8_t* q, float* a, int M, int K, float eps, const float* fold_absmax,
+                         float* fold_max, cudaStream_t st);
+int launch_quantize_tensor(const void* x, int dt, int8_t* q, float* absmax, long long size, cudaStream_t st);
+int launch_dequantize_tensor(const int8_t* q, const float* absmax, void* out, int dt, long long size, cudaStream_t st);
+int launch_quantize_grad(const void* dY, int dt, const float* xa, const float* ga, int8_t* Gq, int M, int N, cudaStream_t st);
+int launch_hysteresis(const float* dW, uint8_t* Wp, uint8_t* Hp, const HystParams& p, int N, int K, uint32_t idx_base,
+                      cudaStream_t st);
+int launch_gemm_simple(int mode, const int8_t* A, const void* B, int R, int C, int D, const EpiParams& epi, cudaStream_t st);
+int gemm_tc_eligible(int mode, const void* A, const void* B, int R, int C, int D);
+int launch_gemm_tc(int mode, const int8_t* A, const void* B, int R, int C, int D, const EpiParams& epi, int32_t* status,
+                   cudaStream_t st);
+int launch_dw_hysteresis_tc(const int8_t* Gq, const int8_t* Xq, const float* g_absmax, uint8_t* Wp, uint8_t* Hp,
+                            const HystParams& hp, uint32_t idx_base, int M, int N, int K, int32_t* status, cudaStream_t st);
+
+static thread_local int g_last_cuda_error = 0;
+
+int record_cuda_error(cudaError_t e) {
+    g_last_cuda_error = (int)e;
+    return EL_ERR_CUDA;
+}
+
+int check_launch() {
+    const cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? EL_OK : record_cuda_error(e);
+}
+
+static int g_sm_count[64];
+static int g_cc_major[64];
+
+static int device_info(int* sms, int* major) {
+    int dev = 0;
+    EL_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) {
+        int a = 0, b = 0;
+        EL_CUDA_TRY(cudaDeviceGetAttribute(&a, cudaDevAttrMultiProcessorCount, dev));
+        EL_CUDA_TRY(cudaDeviceGetAttribute(&b, cudaDevAttrComputeCapabilityMajor, dev));
+        if (sms) *sms = a;
+        if (major) *major = b;
+        return EL_OK;
+    }
+    if (g_sm_count[dev] == 0) {   // benign race: every thread would store the same values
+        int a = 0, b = 0;
+        EL_CUDA_TRY(cudaDeviceGetAttribute(&a, cudaDevAttrMultiProcessorCount, dev));
+        EL_CUDA_TRY(cudaDeviceGetAttribute(&b, cudaDevAttrComputeCapabilityMajor, dev));
+        g_cc_major[dev] = b;
+        g_sm_count[dev] = a;
+    }
+    if (sms) *sms = g_sm_count[dev];
+    if (major) *major = g_cc_major[dev];
+    return EL_OK;
+}
+
+int device_sm_count(int* out) { return device_info(out, nullptr); }
+
+int require_sm100() {
+    int major = 0;
+    const int rc = device_info(nullptr, &major);
+    if (rc != EL_OK) return rc;
+    return major == 10 ? EL_OK : EL_ERR_DEVICE;
+}
+
+static inline bool float_dtype(int dt) { return dt == EL_F16 || dt == EL_BF16 || dt == EL_F32; }
+static inline bool out_dtype_ok(int dt) { return dt == EL_F16 || dt == EL_BF16 || dt == EL_F32 || dt == EL_I32; }
+
+static int gemm_dispatch(int mode, const int8_t* A, const void* B, int R, int C, int D, const EpiParams& epi, int flags,
+                         int32_t* status, cudaStream_t st) {
+    if (flags != EL_PATH_AUTO && flags != EL_PATH_SIMPLE && flags != EL_PATH_TC) return EL_ERR_INVALID_ARG;
+    if (R == 0 || C == 0) return EL_OK;
+    if (flags == EL_PATH_SIMPLE) return launch_gemm_simple(mode, A, B, R, C, D, epi, st);
+    const int elig = (D > 0) ? gemm_tc_eligible(mode, A, B, R, C, D) : EL_ERR_UNSUPPORTED_SHAPE;
+    if (flags == EL_PATH_TC) return elig != EL_OK ? elig : launch_gemm_tc(mode, A, B, R, C, D, epi, status, st);
+    // auto: the tensor-core tile is 128 rows deep; very small problems go to the CUDA-core kernel
+    if (elig == EL_OK && R >= 32) return launch_gemm_tc(mode, A, B, R, C, D, epi, status, st);
+    return launch_gemm_simple(mode, A, B, R, C, D, epi, st);
+}
+
+}  // namespace el
+
+using namespace el;
+
+extern "C" {
+
+int el_version(void) { return 100; }
+
+const char* el_status_string(int s) {
+    switch (s) {
+        case EL_OK: return "ok";
+        case EL_ERR_INVALID_ARG: return "invalid argument";
+        case EL_ERR_NULL_PTR: return "null pointer";
+        case EL_ERR_ALIGNMENT: return "pointer or pitch alignment";
+        case EL_ERR_UNSUPPORTED_SHAPE: return "shape not supported by the requested path";
+        case EL_ERR_CUDA: return "CUDA runtime error";
+        case EL_ERR_DEVICE: return "device is not sm_100";
+        case EL_ERR_DRIVER: return "tensor-map descriptor rejected by the driver";
+        default: return "unknown status";
+    }
+}
+
+int el_last_cuda_error(void) { return g_last_cuda_error; }
+
+int el_pack_ternary(const int8_t* w, uint8_t* W_packed, int N, int K, int pad_code, el_stream_t stream) {
+    if (N < 0 || K < 0 || pad_code < 0 || pad_code > 3) return EL_ERR_INVALID_ARG;
+    if (N == 0 || K == 0) return EL_OK;
+    if (!w || !W_packed) return EL_ERR_NULL_PTR;
+    return launch_pack(w, false, 1.0f, W_packed, N, K, pad_code, (cudaStream_t)stream);
+}
+
+int el_ternarize_pack(const float* W, float gamma, uint8_t* W_packed, int N, int K, el_stream_t stream) {
+    if (N < 0 || K < 0 || !(gamma > 0.0f)) return EL_ERR_INVALID_ARG;
+    if (N == 0 || K == 0) return EL_OK;
+    if (!W || !W_packed) return EL_ERR_NULL_PTR;
+    return launch_pack(W, true, gamma, W_packed, N, K, 0, (cudaStream_t)stream);
+}
+
+int el_unpack_ternary(const uint8_t* W_packed, void* out, int out_dtype, int N, int K, el_stream_t stream) {
+    if (N < 0 || K < 0 || !out_dtype_ok(out_dtype)) return EL_ERR_INVALID_ARG;
+    if (N == 0 || K == 0) return EL_OK;
+    if (!W_packed || !out) return EL_ERR_NULL_PTR;
+    return launch_unpack(W_packed, out, out_dtype, N, K, (cudaStream_t)stream);
+}
+
+int el_quantize_rows(const void* x, int x_dtype, int8_t* q, float* row_absmax, int M, int K, float eps,
+                     const float* fold_absmax, float* fold_max, el_stream_t stream) {
+    if (M < 0 || K < 0 || !float_dtype(x_dtype) || !(eps > 0.0f)) return EL_ERR_INVALID_ARG;
+    if ((fold_absmax == nullptr) != (fold_max == nullptr)) return EL_ERR_INVALID_ARG;
+    if (M == 0) return EL_OK;
+    if (!row_absmax || (K > 0 && (!x || !q))) return EL_ERR_NULL_PTR;
+    return launch_quantize_rows(x, x_dtype, q, row_absmax, M, K, eps, fold_absmax, fold_max, (cudaStream_t)stream);
+}
+
+int el_quantize_tensor(const void* x, int x_dtype, int8_t* q, float* absmax, long long size, el_stream_t stream) {
+    if (size < 0 || !float_dtype(x_dtype)) return EL_ERR_INVALID_ARG;
+    if (!absmax || (size > 0 && (!x || !q))) return EL_ERR_NULL_PTR;
+    return launch_quantize_tensor(x, x_dtype, q, absmax, size, (cudaStream_t)stream);
+}
+
+int el_dequantize_tensor(const int8_t* q, const float* absmax, void* out, int out_dtype, long long size, el_stream_t stream) {
+    if (size < 0 || !float_dtype(out_dtype)) return EL_ERR_INVALID_ARG;
+    if (size == 0) return EL_OK;
+    if (!q || !absmax || !out) return EL_ERR_NULL_PTR;
+    return launch_dequantize_tensor(q, absmax, out, out_dtype, size, (cudaStream_t)stream);
+}
+
+int el_quantize_grad(const void* dY, int dy_dtype, const float* x_absmax, const float* g_absmax, int8_t* Gq, int M, int N,
+                     el_stream_t stream) {
+    if (M < 0 || N < 0 || !float_dtype(dy_dtype)) return EL_ERR_INVALID_ARG;
+    if (M == 0 || N == 0) return EL_OK;
+    if (!dY || !x_absmax || !g_absmax || !Gq) return EL_ERR_NULL_PTR;
+    return launch_quantize_grad(dY, dy_dtype, x_absmax, g_absmax, Gq, M, N, (cudaStream_t)stream);
+}
+
+int el_gemm_fwd(const int8_t* Xq, const uint8_t* W_packed, void* Y, int out_dtype, const float* absmax, int absmax_stride,
+                float gamma, int M, int N, int K, int flags, int32_t* dev_status, el_stream_t stream) {
+    if (M < 0 || N < 0 || K < 0 || !out_dtype_ok(out_dtype) || (absmax_stride != 0 && absmax_stride != 1)) return EL_ERR_INVALID_ARG;
+    if (M == 0 || N == 0) return EL_OK;
+    if (!Y || !absmax || (K > 0 && (!Xq || !W_packed))) return EL_ERR_NULL_PTR;
+    const EpiParams epi{Y, (long long)N, out_dtype, absmax, absmax_stride, gamma};
+    return gemm_dispatch(MODE_FWD, Xq, W_packed, M, N, K, epi, flags, dev_status, (cudaStream_t)stream);
+}
+
+int el_gemm_dx(const int8_t* dYq, const uint8_t* W_packed, void* dX, int out_dtype, const float* absmax, int absmax_stride,
+               float gamma, int M, int N, int K, int flags, int32_t* dev_status, el_stream_t stream) {
+    if (M < 0 || N < 0 || K < 0 || !out_dtype_ok(out_dtype) || (absmax_stride != 0 && absmax_stride != 1)) return EL_ERR_INVALID_ARG;
+    if (M == 0 || K == 0) return EL_OK;
+    if (!dX || !absmax || (N > 0 && (!dYq || !W_packed))) return EL_ERR_NULL_PTR;
+    const EpiParams epi{dX, (long long)K, out_dtype, absmax, absmax_stride, gamma};
+    return gemm_dispatch(MODE_DX, dYq, W_packed, M, K, N, epi, flags, dev_status, (cudaStream_t)stream);
+}
+
+int el_gemm_dw(const int8_t* Gq, const int8_t* Xq, void* dW, int out_dtype, const float* g_absmax, int M, int N, int K,
+               int flags, int32_t* dev_status, el_stream_t stream) {
+    if (M < 0 || N < 0 || K < 0 || (out_dtype != EL_F32 && out_dtype != EL_I32)) return EL_ERR_INVALID_ARG;
+    if (N == 0 || K == 0) return EL_OK;
+    if (!dW || !g_absmax || (M > 0 && (!Gq || !Xq))) return EL_ERR_NULL_PTR;
+    const EpiParams epi{dW, (long long)K, out_dtype, g_absmax, 0, 1.0f};
+    return gemm_dispatch(MODE_DW, Gq, Xq, N, K, M, epi, flags, dev_status, (cudaStream_t)stream);
+}
+
+int el_hysteresis_from_dw(const float* dW, uint8_t* W_packed, uint8_t* H_packed, float lr, float lr_scale, int threshold,
+                          float decay_rate, int step, int N, int K, uint32_t idx_base, int ftz, el_stream_t stream) {
+    if (N < 0 || K < 0) return EL_ERR_INVALID_ARG;
+    if ((long long)N * K > 0x7FFFFFFFLL) return EL_ERR_UNSUPPORTED_SHAPE;   // the weight index is a 32-bit counter
+    if (N == 0 || K == 0) return EL_OK;
+    if (!dW || !W_packed || !H_packed) return EL_ERR_NULL_PTR;
+    const HystParams hp = make_hyst_params(lr, lr_scale, threshold, decay_rate, (uint32_t)step, ftz != 0);
+    return launch_hysteresis(dW, W_packed, H_packed, hp, N, K, idx_base, (cudaStream_t)stream);
+}
+
+int el_dw_hysteresis(const int8_t* Gq, const int8_t* Xq, const float* g_absmax, uint8_t* W_packed, uint8_t* H_packed,
+                     float lr, float lr_scale, int threshold, float decay_rate, int step, uint32_t idx_base, int M, int N,
+                     int K, int32_t* dev_status, el_stream_t stream) {
+    if (M <= 0 || N < 0 || K < 0) return EL_ERR_INVALID_ARG;
+    if ((long long)N * K > 0x7FFFFFFFLL) return EL_ERR_UNSUPPORTED_SHAPE;
+    if (N == 0 || K == 0) return EL_OK;
+    if (!Gq || !Xq || !g_absmax || !W_packed || !H_packed) return EL_ERR_NULL_PTR;
+    const HystParams hp = make_hyst_params(lr, lr_scale, threshold, decay_rate, (uint32_t)step, 1);
+    return launch_dw_hysteresis_tc(Gq, Xq, g_absmax, W_packed, H_packed, hp, idx_base, M, N, K, dev_status,
+                                   (cudaStream_t)stream);
+}
+
+}  // extern "C"

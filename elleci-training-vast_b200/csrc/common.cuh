@@ -1,0 +1,131 @@
+// Shared device helpers of the INT2 linear library: field codes, the per-weight hysteresis update,
+// number conversions and the host-side launch bookkeeping.  sm_100a only.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/elleci_int2.h"
+
+namespace el {
+
+// ---- host-side error bookkeeping ---------------------------------------------------------------------
+int record_cuda_error(cudaError_t e);   // stores e for el_last_cuda_error(), returns EL_ERR_CUDA
+int check_launch();                      // cudaGetLastError() -> EL_OK / EL_ERR_CUDA
+int device_sm_count(int* out);           // SM count of the current device (cached per device)
+int require_sm100();                     // EL_OK when the current device is compute capability 10.x
+
+#define EL_CUDA_TRY(call)                                          \
+    do {                                                           \
+        cudaError_t e__ = (call);                                  \
+        if (e__ != cudaSuccess) return ::el::record_cuda_error(e__); \
+    } while (0)
+
+// ---- 2-bit weight code: 0 -> -1, 1 -> 0, 2 -> +1, 3 -> 0 -------------------------------------------------
+__device__ __forceinline__ int decode2(uint32_t c) {
+    c &= 3u;
+    return (c == 2u) - (c == 0u);
+}
+
+// Sixteen 2-bit codes (one 32-bit word, code j at bits 2j) -> sixteen int8 in natural order, as four words.
+// A byte-permute with the table {0xFF,0x00,0x01,0x00} decodes four codes at once when each code sits in
+// its own nibble; the even and odd codes are split into two nibble streams and interleaved again.
+__device__ __forceinline__ void decode16(uint32_t x, uint32_t out[4]) {
+    const uint32_t lut = 0x000100FFu;
+    const uint32_t te = x & 0x33333333u;          // nibble i = code 2i
+    const uint32_t to = (x >> 2) & 0x33333333u;   // nibble i = code 2i+1
+    const uint32_t e0 = __byte_perm(lut, 0, te);        // codes 0,2,4,6
+    const uint32_t e1 = __byte_perm(lut, 0, te >> 16);  // codes 8,10,12,14
+    const uint32_t o0 = __byte_perm(lut, 0, to);        // codes 1,3,5,7
+    const uint32_t o1 = __byte_perm(lut, 0, to >> 16);  // codes 9,11,13,15
+    out[0] = __byte_perm(e0, o0, 0x5140);
+    out[1] = __byte_perm(e0, o0, 0x7362);
+    out[2] = __byte_perm(e1, o1, 0x5140);
+    out[3] = __byte_perm(e1, o1, 0x7362);
+}
+
+// ---- float helpers ----------------------------------------------------------------------------------------
+__device__ __forceinline__ float ftz32(float x) { return fabsf(x) < 1.17549435e-38f ? 0.0f : x; }
+__host__ inline float ftz32_host(float x) {
+    return (x < 1.17549435e-38f && x > -1.17549435e-38f) ? 0.0f : x;
+}
+
+template <typename T> __device__ __forceinline__ float to_float(T v);
+template <> __device__ __forceinline__ float to_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_float<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+__device__ __forceinline__ float finite_or_zero(float v) { return (fabsf(v) <= 3.402823466e38f) ? v : 0.0f; }
+
+// ---- hysteresis: one weight ---------------------------------------------------------------------------------
+struct HystParams {
+    float lr_scaled;   // (lr*lr_scale)*thr, flushed like the reference's fast-math build when ftz
+    float decay;
+    int thr;           // clamp(threshold, 1, 7)
+    uint32_t s1, s2;   // step*2654435761, step*2246822519 (uint32 wrap-around)
+    int ftz;
+};
+
+__device__ __forceinline__ uint32_t mix2(uint32_t h) {
+    h = ((h >> 16) ^ h) * 0x45d9f3bu;
+    h = ((h >> 16) ^ h) * 0x45d9f3bu;
+    return h;
+}
+
+// Updates (q, h) of weight `idx` from its gradient.  q in {-1,0,1}, h a signed counter.
+__device__ __forceinline__ void hyst_update_one(float grad, int& q, int& h, uint32_t idx, const HystParams& p) {
+    const float r1 = (float)(mix2(idx ^ p.s1) & 0xFFFFFFu) * (1.0f / 16777216.0f);
+    const float r2 = (float)(mix2(idx ^ p.s2) & 0xFFFFFFu) * (1.0f / 16777216.0f);
+    if (p.ftz) grad = ftz32(grad);
+    float d_raw = __fmul_rn(-grad, p.lr_scaled);
+    if (p.ftz) d_raw = ftz32(d_raw);
+    const float a = fabsf(d_raw);
+    const float fl = floorf(a);
+    const float frac = __fsub_rn(a, fl);
+    float v = __fadd_rn(fl, (r1 < frac) ? 1.0f : 0.0f);
+    v = (d_raw >= 0.0f) ? v : -v;
+    int delta = __float2int_rz(v);   // saturating; NaN converts to 0
+    delta = max(-31, min(31, delta));
+    int hn = h + delta;
+    if (q != 0 && r2 < p.decay) hn -= q;
+    const int thr = p.thr;
+    int qn = q;
+    if (hn >= thr) {
+        if (q == 1) hn = thr; else { qn = q + 1; hn = 0; }
+    } else if (hn <= -thr) {
+        if (q == -1) hn = -thr; else { qn = q - 1; hn = 0; }
+    }
+    hn = max(-thr, min(thr, hn));
+    q = qn;
+    h = hn;
+}
+
+// Host-side preparation of HystParams from the API arguments.
+inline HystParams make_hyst_params(float lr, float lr_scale, int threshold, float decay, uint32_t step, int ftz) {
+    HystParams p;
+    p.thr = threshold < 1 ? 1 : (threshold > 7 ? 7 : threshold);
+    if (ftz) { lr = ftz32_host(lr); lr_scale = ftz32_host(lr_scale); decay = ftz32_host(decay); }
+    volatile float prod = lr * lr_scale;
+    float pr = prod;
+    if (ftz) pr = ftz32_host(pr);
+    volatile float ls = pr * (float)p.thr;
+    p.lr_scaled = ftz ? ftz32_host(ls) : (float)ls;
+    p.decay = decay;
+    p.s1 = step * 2654435761u;
+    p.s2 = step * 2246822519u;
+    p.ftz = ftz;
+    return p;
+}
+
+// ---- output conversion -------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+}  // namespace el

@@ -1,0 +1,512 @@
+// Tensor-core integer GEMMs of the INT2 linear path for sm_100a: tcgen05.mma kind::i8 with the int32
+// accumulators in tensor memory, operands staged by TMA, the 2-bit weights expanded to int8 inside shared
+// memory, and the scaling (or hysteresis) epilogue reading the accumulators back with tcgen05.ld.
+//
+// One persistent CTA per SM walks output tiles of 128 x BN.  Warp roles:
+//   warp 0      TMA producer: activations (and, for the weight-gradient GEMM, both operands) plus the packed
+//               2-bit weight tile of every 128-deep reduction block, through a ring of shared-memory stages
+//   warp 1      allocates tensor memory; one lane issues the MMAs and commits them to the ring's barriers
+//   warps 2-5   epilogue: tcgen05.ld of one of two accumulators while the MMAs fill the other
+//   warps 6-13  transform: expand the packed weight tile into the 128-byte-swizzled int8 operand tile
+//
+// The three GEMMs differ only in where the reduction index lies in memory:
+//   FWD  Y [M,N] = Xq [M,K] . Wq[N,K]^T   A K-major (TMA),  B K-major  (expanded from W_packed rows)
+//   DX   dX[M,K] = dYq[M,N] . Wq[N,K]     A K-major (TMA),  B MN-major (the same expanded rows, read transposed)
+//   DW   dW[N,K] = Gq [M,N]^T . Xq[M,K]   A MN-major (TMA), B MN-major (TMA)
+// so the expanded weight tile has one shared-memory image (row r at r*128 bytes, 16-byte chunk c at
+// (c ^ (r & 7)) * 16) and only the matrix descriptors change.
+//
+// Every wait on an mbarrier is bounded: when it gives up, the kernel records a code in *status, lets its
+// outstanding copies land, frees tensor memory and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "epilogue.cuh"
+
+namespace el {
+
+enum { MODE_FWD = 0, MODE_DX = 1, MODE_DW = 2 };
+enum { EPI_SCALE = 0, EPI_HYST = 1 };
+
+namespace tc {
+
+constexpr int BM = 128;            // rows of an output tile (UMMA M)
+constexpr int BK = 128;            // reduction depth per stage (bytes of int8)
+constexpr int UMMA_K = 32;         // reduction depth of one kind::i8 instruction
+constexpr int WARP_TMA = 0, WARP_MMA = 1, NUM_EPI_WARPS = 4, WARP_XF0 = 6, NUM_XF_WARPS = 8;   // warps 2..5: epilogue
+constexpr int NUM_THREADS = (WARP_XF0 + NUM_XF_WARPS) * 32;   // 448
+constexpr long long WAIT_LIMIT_CYCLES = 1LL << 31;   // about a second
+
+constexpr int A_BYTES = BM * BK;                       // 16 KB
+template <int BN> struct Cfg {
+    static constexpr int B_BYTES = BN * BK;            // expanded / int8 B tile
+    static constexpr int P_BYTES = BN * BK / 4;        // packed weight tile
+    __host__ __device__ static constexpr int STAGES(int mode) { return mode == MODE_DW ? (BN == 256 ? 4 : 6) : (BN == 256 ? 3 : 5); }
+    __host__ __device__ static constexpr int STAGE_BYTES(int mode) { return A_BYTES + B_BYTES + (mode == MODE_DW ? 0 : P_BYTES); }
+    __host__ __device__ static constexpr int SMEM_BYTES(int mode) { return STAGES(mode) * STAGE_BYTES(mode) + 1024 /*align*/ + 256 /*barriers*/; }
+};
+
+struct Params {
+    int R, C, D;                    // output rows, output columns, reduction depth
+    int tiles_r, tiles_c, k_blocks;
+    EpiParams epi;
+    int vec_ok;                     // output rows keep 16-byte alignment
+    int32_t* status;
+    // hysteresis epilogue (DW only)
+    uint8_t* Wp;
+    uint8_t* Hp;
+    int pK, pH;
+    HystParams hp;
+    uint32_t idx_base;
+};
+
+// ---- PTX wrappers -------------------------------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait; false means it gave up (and *status now holds `code`), or that another role already did.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int32_t* status, int code) {
+    if (mbar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+    uint32_t n = 0;
+    while (true) {
+        if (mbar_try(bar, parity)) return true;
+        if ((++n & 1023u) == 0) {
+            if (status != nullptr && *reinterpret_cast<volatile int32_t*>(status) != 0) return false;
+            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+                if (status != nullptr) atomicCAS(status, 0, code);
+                return false;
+            }
+        }
+    }
+}
+// The same for a whole warp: every lane polls, and the warp agrees on the outcome before it goes on to
+// warp-wide (.sync.aligned) instructions.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, int32_t* status, int code) {
+    const bool ok = mbar_wait(bar, parity, status, code);
+    return __all_sync(0xffffffffu, ok);
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1.
+//   K-major:  rows of 128 bytes, 8-row groups 1024 bytes apart (SBO); LBO unused.
+//   MN-major: 128-element blocks along M/N `lbo` bytes apart, groups of 8 reduction rows 1024 bytes apart (SBO).
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t)((1024u >> 4) & 0x3FFFu) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// Instruction descriptor of kind::i8: int32 accumulate, signed 8-bit A and B, the two major-ness bits, N and M.
+__host__ __device__ constexpr uint32_t make_idesc(int a_mn_major, int b_mn_major, int n) {
+    return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)a_mn_major << 15) | ((uint32_t)b_mn_major << 16) |
+           ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+// ---- the kernel ----------------------------------------------------------------------------------------------
+
+template <int MODE, int BN, int EPI>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Params p) {
+    using C = Cfg<BN>;
+    constexpr int STAGES = C::STAGES(MODE);
+    constexpr int STAGE_BYTES = C::STAGE_BYTES(MODE);
+    constexpr bool XFORM = (MODE != MODE_DW);
+    constexpr uint32_t TMEM_COLS = 2 * BN;     // two accumulators of BN int32 columns (256 or 512: powers of two)
+    constexpr uint32_t TX_BYTES = A_BYTES + (XFORM ? C::P_BYTES : C::B_BYTES);
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    // stage s: [A 16K][B BN*128][P BN*32]
+    const uint32_t bars = smem_base + STAGES * STAGE_BYTES;
+    uint8_t* bars_gen = smem_gen + STAGES * STAGE_BYTES;
+    auto bar_full = [&](int s) { return bars + 8u * s; };
+    auto bar_ready = [&](int s) { return bars + 8u * (STAGES + s); };
+    auto bar_empty = [&](int s) { return bars + 8u * (2 * STAGES + s); };
+    auto bar_tfull = [&](int a) { return bars + 8u * (3 * STAGES + a); };
+    auto bar_tempty = [&](int a) { return bars + 8u * (3 * STAGES + 2 + a); };
+    volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(bars_gen + 8 * (3 * STAGES + 4));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_tiles = p.tiles_r * p.tiles_c;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(bar_full(s), 1);
+            mbar_init(bar_ready(s), NUM_XF_WARPS);
+            mbar_init(bar_empty(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(bar_tfull(a), 1);
+            mbar_init(bar_tempty(a), NUM_EPI_WARPS);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_async_smem();
+    }
+    if (warp == WARP_MMA) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_holder)),
+                     "r"(TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_holder;
+    bool failed = false;
+
+    if (warp == WARP_TMA) {
+        // ================= producer =================
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            for (int t = blockIdx.x; t < num_tiles && !failed; t += gridDim.x) {
+                const int r0 = (t % p.tiles_r) * BM, c0 = (t / p.tiles_r) * BN;
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!mbar_wait(bar_empty(s), ph ^ 1u, p.status, 1)) { failed = true; break; }
+                    const uint32_t sa = smem_base + s * STAGE_BYTES, sb = sa + A_BYTES, sp = sb + C::B_BYTES;
+                    const int d0 = kb * BK;
+                    mbar_expect_tx(bar_full(s), TX_BYTES);
+                    if (MODE == MODE_FWD) {
+                        tma_load_2d(sa, &tmA, bar_full(s), d0, r0);            // Xq  [128 rows x 128 B]
+                        tma_load_2d(sp, &tmB, bar_full(s), d0 >> 2, c0);       // W   [BN rows x 32 B]
+                    } else if (MODE == MODE_DX) {
+                        tma_load_2d(sa, &tmA, bar_full(s), d0, r0);            // dYq [128 rows x 128 B]
+                        tma_load_2d(sp, &tmB, bar_full(s), c0 >> 2, d0);       // W   [128 rows x BN/4 B]
+                    } else {
+                        tma_load_2d(sa, &tmA, bar_full(s), r0, d0);            // Gq  [128 m-rows x 128 n]
+#pragma unroll
+                        for (int b = 0; b < BN / 128; ++b)
+                            tma_load_2d(sb + b * 16384, &tmB, bar_full(s), c0 + b * 128, d0);   // Xq [128 m-rows x 128 k]
+                    }
+                    if (++s == STAGES) { s = 0; ph ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == WARP_MMA) {
+        // ================= MMA issuer =================
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(MODE == MODE_DW, MODE != MODE_FWD, BN);
+            int s = 0;
+            uint32_t ph = 0;
+            int it = 0;
+            for (int t = blockIdx.x; t < num_tiles && !failed; t += gridDim.x, ++it) {
+                const int acc = it & 1;
+                const uint32_t acc_ph = (uint32_t)(it >> 1) & 1u;
+                if (!mbar_wait(bar_tempty(acc), acc_ph ^ 1u, p.status, 2)) { failed = true; break; }
+                tcgen05_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!mbar_wait(bar_full(s), ph, p.status, 3)) { failed = true; break; }
+                    if (XFORM && !mbar_wait(bar_ready(s), ph, p.status, 4)) { failed = true; break; }
+                    tcgen05_fence_after();
+                    const uint32_t sa = smem_base + s * STAGE_BYTES, sb = sa + A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        // K-major: step 32 bytes along the row; MN-major: step 32 reduction rows of 128 bytes
+                        const uint64_t da = (MODE == MODE_DW) ? make_desc(sa + k * 4096, 16384) : make_desc(sa + k * 32, 16);
+                        const uint64_t db = (MODE == MODE_FWD) ? make_desc(sb + k * 32, 16) : make_desc(sb + k * 4096, 16384);
+                        umma_i8(d_tmem, da, db, idesc, (kb | k) != 0);
+                    }
+                    umma_commit(bar_empty(s));
+                    if (++s == STAGES) { s = 0; ph ^= 1u; }
+                }
+                if (!failed) umma_commit(bar_tfull(acc));
+            }
+        }
+    } else if (warp < WARP_XF0) {
+        // ================= epilogue =================
+        const int quarter = warp & 3;                 // the tensor-memory lanes this warp may read
+        const int row_in_tile = quarter * 32 + lane;
+        int it = 0;
+        for (int t = blockIdx.x; t < num_tiles && !failed; t += gridDim.x, ++it) {
+            const int r0 = (t % p.tiles_r) * BM, c0 = (t / p.tiles_r) * BN;
+            const int acc = it & 1;
+            const uint32_t acc_ph = (uint32_t)(it >> 1) & 1u;
+            if (!mbar_wait_warp(bar_tfull(acc), acc_ph, p.status, 5)) { failed = true; break; }
+            tcgen05_fence_after();
+            const int row = r0 + row_in_tile;
+            const bool row_ok = row < p.R;
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
+            if (EPI == EPI_SCALE) {
+                const float sc = row_ok ? epi_row_scale(p.epi, row) : 0.0f;
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_ld32(taddr + c * 32, v);
+                    tmem_ld_wait();
+                    const int col0 = c0 + c * 32;
+                    if (row_ok && col0 < p.C) epi_store_chunk32(p.epi, row, col0, p.C, v, sc, p.vec_ok != 0);
+                }
+            } else {
+                // weight-gradient tile -> hysteresis update of 32 weights of row `row` per chunk
+                const float sc = epi_row_scale(p.epi, 0);   // g_absmax/127 (one scale for the tensor)
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_ld32(taddr + c * 32, v);
+                    tmem_ld_wait();
+                    const int col0 = c0 + c * 32;
+                    if (row_ok && col0 < p.C) {     // K % 32 == 0: a chunk is inside or outside as a whole
+                        uint2* wptr = reinterpret_cast<uint2*>(p.Wp + (size_t)row * p.pK + (col0 >> 2));
+                        uint4* hptr = reinterpret_cast<uint4*>(p.Hp + (size_t)row * p.pH + (col0 >> 1));
+                        const uint2 w2 = *wptr;
+                        const uint4 h4 = *hptr;
+                        uint32_t w[2] = {w2.x, w2.y};
+                        uint32_t h[4] = {h4.x, h4.y, h4.z, h4.w};
+                        const uint32_t idx0 = p.idx_base + (uint32_t)row * (uint32_t)p.C + (uint32_t)col0;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const int wi = j >> 4, ws = (j & 15) * 2, hi = j >> 3, hs = (j & 7) * 4;
+                            int q = decode2(w[wi] >> ws);
+                            int hv = (int)((h[hi] >> hs) & 0xFu);
+                            hv = (hv & 8) ? hv - 16 : hv;
+                            hyst_update_one(__fmul_rn((float)(int)v[j], sc), q, hv, idx0 + j, p.hp);
+                            w[wi] = (w[wi] & ~(3u << ws)) | ((uint32_t)(q + 1) << ws);
+                            h[hi] = (h[hi] & ~(0xFu << hs)) | (((uint32_t)hv & 0xFu) << hs);
+                        }
+                        *wptr = make_uint2(w[0], w[1]);
+                        *hptr = make_uint4(h[0], h[1], h[2], h[3]);
+                    }
+                }
+            }
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_tempty(acc));
+        }
+    } else if (XFORM) {
+        // ================= transform: packed 2-bit rows -> swizzled int8 operand tile =================
+        const int xt = threadIdx.x - WARP_XF0 * 32;       // 0..255
+        constexpr int PROW = (MODE == MODE_FWD) ? 32 : BN / 4;     // packed bytes per tile row
+        constexpr int SEGS = PROW / 16;                              // 16-byte segments (64 weights) per row
+        constexpr int ROWS = (MODE == MODE_FWD) ? BN : 128;
+        constexpr int ITEMS = ROWS * SEGS;
+        int s = 0;
+        uint32_t ph = 0;
+        for (int t = blockIdx.x; t < num_tiles && !failed; t += gridDim.x) {
+            for (int kb = 0; kb < p.k_blocks; ++kb) {
+                if (!mbar_wait_warp(bar_full(s), ph, p.status, 6)) { failed = true; break; }
+                uint8_t* sb = smem_gen + s * STAGE_BYTES + A_BYTES;
+                const uint8_t* sp = sb + C::B_BYTES;
+#pragma unroll
+                for (int i = xt; i < ITEMS; i += NUM_XF_WARPS * 32) {
+                    const int row = i / SEGS, seg = i % SEGS;
+                    const uint4 pk = *reinterpret_cast<const uint4*>(sp + row * PROW + seg * 16);
+                    const uint32_t px[4] = {pk.x, pk.y, pk.z, pk.w};
+                    uint8_t* dst_row = sb + (seg >> 1) * 16384 + row * 128;
+#pragma unroll
+                    for (int w = 0; w < 4; ++w) {
+                        uint32_t o[4];
+                        decode16(px[w], o);
+                        const int chunk = (seg & 1) * 4 + w;
+                        *reinterpret_cast<uint4*>(dst_row + ((chunk ^ (row & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                    }
+                }
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_ready(s));
+                if (++s == STAGES) { s = 0; ph ^= 1u; }
+            }
+        }
+    }
+
+    // ---- teardown ------------------------------------------------------------------------------------------------
+    if (p.status != nullptr && *reinterpret_cast<volatile int32_t*>(p.status) != 0) {
+        // a wait gave up somewhere: give copies and MMAs still in flight time to land before the CTA's
+        // shared and tensor memory are released
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000) { }
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == WARP_MMA) {
+        tcgen05_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ---- host side -------------------------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+        tried = true;
+    }
+    return fn;
+}
+
+// 2-D byte tensor [rows, cols] with row pitch `pitch`; box [box_rows, box_cols]; out-of-range reads give zero.
+static int make_map(CUtensorMap* m, const void* base, uint64_t cols, uint64_t rows, uint64_t pitch, uint32_t box_cols,
+                    uint32_t box_rows, bool swizzle128) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (fn == nullptr) return EL_ERR_DRIVER;
+    if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (pitch & 15) != 0) return EL_ERR_ALIGNMENT;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {pitch};
+    cuuint32_t box[2] = {box_cols, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? EL_OK : EL_ERR_DRIVER;
+}
+
+template <int MODE, int BN, int EPI>
+static int launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB, Params& p, cudaStream_t st) {
+    constexpr int smem = Cfg<BN>::SMEM_BYTES(MODE);
+    static bool attr_set[64] = {};
+    int dev = 0;
+    EL_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+        EL_CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<MODE, BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+    }
+    int sms = 0;
+    int rc = device_sm_count(&sms);
+    if (rc != EL_OK) return rc;
+    p.tiles_r = (p.R + BM - 1) / BM;
+    p.tiles_c = (p.C + BN - 1) / BN;
+    p.k_blocks = (p.D + BK - 1) / BK;
+    const long long tiles = (long long)p.tiles_r * p.tiles_c;
+    if (tiles == 0) return EL_OK;
+    if (p.k_blocks == 0) return EL_ERR_UNSUPPORTED_SHAPE;
+    const int grid = (int)(tiles < sms ? tiles : sms);
+    gemm_tc_kernel<MODE, BN, EPI><<<grid, NUM_THREADS, smem, st>>>(tmA, tmB, p);
+    return check_launch();
+}
+
+}  // namespace tc
+
+// Whether the tensor-core kernel can take this problem (TMA needs 16-byte aligned bases and pitches).
+int gemm_tc_eligible(int mode, const void* A, const void* B, int R, int C, int D) {
+    if (R <= 0 || C <= 0 || D <= 0) return EL_ERR_UNSUPPORTED_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return EL_ERR_ALIGNMENT;
+    switch (mode) {
+        case MODE_FWD: return (D % 64 == 0) ? EL_OK : EL_ERR_UNSUPPORTED_SHAPE;                    // Xq pitch D, W pitch D/4
+        case MODE_DX: return (D % 16 == 0 && C % 64 == 0) ? EL_OK : EL_ERR_UNSUPPORTED_SHAPE;     // dYq pitch D(=N), W pitch C/4
+        case MODE_DW: return (R % 16 == 0 && C % 16 == 0) ? EL_OK : EL_ERR_UNSUPPORTED_SHAPE;     // Gq pitch R(=N), Xq pitch C
+        default: return EL_ERR_INVALID_ARG;
+    }
+}
+
+int launch_gemm_tc(int mode, const int8_t* A, const void* B, int R, int C, int D, const EpiParams& epi, int32_t* status,
+                   cudaStream_t st) {
+    int rc = gemm_tc_eligible(mode, A, B, R, C, D);
+    if (rc != EL_OK) return rc;
+    rc = require_sm100();
+    if (rc != EL_OK) return rc;
+    tc::Params p{};
+    p.R = R; p.C = C; p.D = D;
+    p.epi = epi;
+    p.status = status;
+    const int esz = (epi.out_dtype == EL_BF16 || epi.out_dtype == EL_F16) ? 2 : 4;
+    p.vec_ok = ((reinterpret_cast<uintptr_t>(epi.out) & 15) == 0) && ((epi.ldo * esz) % 16 == 0);
+    CUtensorMap tmA, tmB;
+    constexpr int BN = 256;
+    if (mode == MODE_FWD) {
+        if ((rc = tc::make_map(&tmA, A, D, R, D, 128, 128, true)) != EL_OK) return rc;
+        if ((rc = tc::make_map(&tmB, B, D / 4, C, D / 4, 32, BN, false)) != EL_OK) return rc;
+        return tc::launch_t<MODE_FWD, BN, EPI_SCALE>(tmA, tmB, p, st);
+    } else if (mode == MODE_DX) {
+        if ((rc = tc::make_map(&tmA, A, D, R, D, 128, 128, true)) != EL_OK) return rc;
+        if ((rc = tc::make_map(&tmB, B, C / 4, D, C / 4, BN / 4, 128, false)) != EL_OK) return rc;
+        return tc::launch_t<MODE_DX, BN, EPI_SCALE>(tmA, tmB, p, st);
+    } else {
+        if ((rc = tc::make_map(&tmA, A, R, D, R, 128, 128, true)) != EL_OK) return rc;
+        if ((rc = tc::make_map(&tmB, B, C, D, C, 128, 128, true)) != EL_OK) return rc;
+        return tc::launch_t<MODE_DW, BN, EPI_SCALE>(tmA, tmB, p, st);
+    }
+}
+
+int launch_dw_hysteresis_tc(const int8_t* Gq, const int8_t* Xq, const float* g_absmax, uint8_t* Wp, uint8_t* Hp,
+                            const HystParams& hp, uint32_t idx_base, int M, int N, int K, int32_t* status, cudaStream_t st) {
+    int rc = gemm_tc_eligible(MODE_DW, Gq, Xq, N, K, M);
+    if (rc != EL_OK) return rc;
+    if (K % 32 != 0) return EL_ERR_UNSUPPORTED_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(Wp) & 7) || (reinterpret_cast<uintptr_t>(Hp) & 15)) return EL_ERR_ALIGNMENT;
+    rc = require_sm100();
+    if (rc != EL_OK) return rc;
+    tc::Params p{};
+    p.R = N; p.C = K; p.D = M;
+    p.epi = EpiParams{nullptr, 0, EL_F32, g_absmax, 0, 1.0f};
+    p.status = status;
+    p.Wp = Wp; p.Hp = Hp; p.pK = K / 4; p.pH = K / 2;
+    p.hp = hp; p.idx_base = idx_base;
+    CUtensorMap tmA, tmB;
+    if ((rc = tc::make_map(&tmA, Gq, N, M, N, 128, 128, true)) != EL_OK) return rc;
+    if ((rc = tc::make_map(&tmB, Xq, K, M, K, 128, 128, true)) != EL_OK) return rc;
+    return tc::launch_t<MODE_DW, 256, EPI_HYST>(tmA, tmB, p, st);
+}
+
+}  // namespace el

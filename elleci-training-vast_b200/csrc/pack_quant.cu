@@ -1,0 +1,352 @@
+// Memory-bound kernels of the INT2 linear path: ternary packing / unpacking, per-token and per-tensor
+// absmax int8 quantisation, gradient quantisation for the integer weight gradient.
+// All of them stream their operands once with 16-byte accesses where the shape allows it.
+#include "common.cuh"
+
+namespace el {
+
+// ---------------------------------------------------------------------------------------------------------
+// pack / ternarise / unpack
+// ---------------------------------------------------------------------------------------------------------
+
+// One thread per packed byte (four weights).
+template <bool FROM_FLOAT>
+__global__ void pack_kernel(const void* __restrict__ src, float gamma, uint8_t* __restrict__ Wp, int N, int K,
+                            int pK, int pad_code) {
+    const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= (long long)N * pK) return;
+    const int n = (int)(t / pK), b = (int)(t % pK);
+    uint32_t byte = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int k = b * 4 + j;
+        uint32_t code = (uint32_t)pad_code;
+        if (k < K) {
+            int q;
+            if (FROM_FLOAT) {
+                const float w = static_cast<const float*>(src)[(size_t)n * K + k];
+                float r = rintf(__fdiv_rn(w, gamma));     // round half to even
+                r = fminf(1.0f, fmaxf(-1.0f, r));
+                q = (r != r) ? 0 : (int)r;
+            } else {
+                q = static_cast<const int8_t*>(src)[(size_t)n * K + k];
+                q = max(-1, min(1, q));
+            }
+            code = (uint32_t)(q + 1);
+        }
+        byte |= code << (2 * j);
+    }
+    Wp[t] = (uint8_t)byte;
+}
+
+template <typename OutT>
+__device__ __forceinline__ OutT from_int(int v);
+template <> __device__ __forceinline__ float from_int<float>(int v) { return (float)v; }
+template <> __device__ __forceinline__ __half from_int<__half>(int v) { return __float2half((float)v); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_int<__nv_bfloat16>(int v) { return __float2bfloat16((float)v); }
+template <> __device__ __forceinline__ int8_t from_int<int8_t>(int v) { return (int8_t)v; }
+
+template <typename OutT>
+__global__ void unpack_kernel(const uint8_t* __restrict__ Wp, OutT* __restrict__ out, int N, int K, int pK) {
+    const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= (long long)N * pK) return;
+    const int n = (int)(t / pK), b = (int)(t % pK);
+    const uint32_t byte = Wp[t];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int k = b * 4 + j;
+        if (k < K) out[(size_t)n * K + k] = from_int<OutT>(decode2(byte >> (2 * j)));
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// per-token quantisation: one CTA per row
+// ---------------------------------------------------------------------------------------------------------
+
+__device__ __forceinline__ float block_max(float v, float* red) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    if (l == 0) red[w] = v;
+    __syncthreads();
+    const int nw = (blockDim.x + 31) >> 5;
+    v = (l < nw) ? red[l] : 0.0f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    __syncthreads();
+    return v;
+}
+
+template <typename T> struct Vec8 { uint4 raw; };
+
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, float v[8]);
+template <> __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float v[8]) {
+    const uint4 r = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        v[2 * i] = __uint_as_float(w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    }
+}
+template <> __device__ __forceinline__ void load8<__half>(const __half* p, float v[8]) {
+    const uint4 r = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
+        const float2 f = __half22float2(h);
+        v[2 * i] = f.x;
+        v[2 * i + 1] = f.y;
+    }
+}
+template <> __device__ __forceinline__ void load8<float>(const float* p, float v[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    const float4 b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+
+__device__ __forceinline__ int quant_half_even(float x, float s) {
+    float r = rintf(__fmul_rn(x, s));
+    r = fminf(127.0f, fmaxf(-128.0f, r));
+    return (int)r;
+}
+
+// VEC: the row pitch and base allow 8-element vector loads and 8-byte stores.
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(256)
+quantize_rows_kernel(const T* __restrict__ x, int8_t* __restrict__ q, float* __restrict__ row_absmax, int K,
+                     float eps, const float* __restrict__ fold_absmax, float* __restrict__ fold_max) {
+    __shared__ float red[8];
+    const int m = blockIdx.x;
+    const T* xr = x + (size_t)m * K;
+    int8_t* qr = q + (size_t)m * K;
+    float amax = 0.0f;
+    if (VEC) {
+        for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
+            float v[8];
+            load8<T>(xr + k, v);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(finite_or_zero(v[i])));
+        }
+    } else {
+        for (int k = threadIdx.x; k < K; k += blockDim.x) amax = fmaxf(amax, fabsf(finite_or_zero(to_float<T>(xr[k]))));
+    }
+    amax = block_max(amax, red);
+    const float a = fmaxf(amax, eps);
+    const float s = __fdiv_rn(127.0f, a);
+    if (threadIdx.x == 0) {
+        row_absmax[m] = a;
+        if (fold_max != nullptr) {
+            const float g = __fmul_rn(amax, __fdiv_rn(fold_absmax[m], 127.0f));
+            if (g > 0.0f) atomicMax(reinterpret_cast<int*>(fold_max), __float_as_int(g));
+        }
+    }
+    if (VEC) {
+        for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
+            float v[8];
+            load8<T>(xr + k, v);     // second read of the row: served by L1/L2
+            uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                w0 |= (uint32_t)(quant_half_even(finite_or_zero(v[i]), s) & 0xFF) << (8 * i);
+                w1 |= (uint32_t)(quant_half_even(finite_or_zero(v[4 + i]), s) & 0xFF) << (8 * i);
+            }
+            *reinterpret_cast<uint2*>(qr + k) = make_uint2(w0, w1);
+        }
+    } else {
+        for (int k = threadIdx.x; k < K; k += blockDim.x)
+            qr[k] = (int8_t)quant_half_even(finite_or_zero(to_float<T>(xr[k])), s);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// per-tensor quantisation (the reference CUDA path's rule)
+// ---------------------------------------------------------------------------------------------------------
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+tensor_absmax_kernel(const T* __restrict__ x, float* __restrict__ absmax, long long size) {
+    __shared__ float red[8];
+    float amax = 0.0f;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < size; i += (long long)gridDim.x * blockDim.x)
+        amax = fmaxf(amax, fabsf(finite_or_zero(to_float<T>(x[i]))));
+    amax = block_max(amax, red);
+    if (threadIdx.x == 0 && amax > 0.0f) atomicMax(reinterpret_cast<int*>(absmax), __float_as_int(amax));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+tensor_quant_kernel(const T* __restrict__ x, int8_t* __restrict__ q, const float* __restrict__ absmax, long long size) {
+    const float a = *absmax;
+    const float inv = (a > 1e-8f) ? __fdiv_rn(127.0f, a) : 0.0f;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < size; i += (long long)gridDim.x * blockDim.x) {
+        const float v = finite_or_zero(to_float<T>(x[i]));
+        const float r = fmaxf(-127.0f, fminf(127.0f, roundf(__fmul_rn(v, inv))));   // half away from zero
+        q[i] = (int8_t)r;
+    }
+}
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half from_float<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+tensor_dequant_kernel(const int8_t* __restrict__ q, const float* __restrict__ absmax, T* __restrict__ out, long long size) {
+    const float sc = __fdiv_rn(*absmax, 127.0f);
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < size; i += (long long)gridDim.x * blockDim.x)
+        out[i] = from_float<T>(__fmul_rn((float)q[i], sc));
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// gradient quantisation: Gq = clamp(rint((dY * x_absmax[m]/127) * inv), +-127)
+// ---------------------------------------------------------------------------------------------------------
+
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(256)
+quantize_grad_kernel(const T* __restrict__ dY, const float* __restrict__ x_absmax, const float* __restrict__ g_absmax,
+                     int8_t* __restrict__ Gq, int N) {
+    const int m = blockIdx.x;
+    const float g = *g_absmax;
+    const float inv = (g >= 1e-30f) ? __fdiv_rn(127.0f, g) : 0.0f;
+    const float sx = __fdiv_rn(x_absmax[m], 127.0f);
+    const T* yr = dY + (size_t)m * N;
+    int8_t* gr = Gq + (size_t)m * N;
+    auto qz = [&](float v) -> int {
+        const float f = __fmul_rn(finite_or_zero(v), sx);
+        float r = rintf(__fmul_rn(f, inv));
+        r = fminf(127.0f, fmaxf(-127.0f, r));
+        return (int)r;
+    };
+    if (VEC) {
+        for (int k = threadIdx.x * 8; k < N; k += blockDim.x * 8) {
+            float v[8];
+            load8<T>(yr + k, v);
+            uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                w0 |= (uint32_t)(qz(v[i]) & 0xFF) << (8 * i);
+                w1 |= (uint32_t)(qz(v[4 + i]) & 0xFF) << (8 * i);
+            }
+            *reinterpret_cast<uint2*>(gr + k) = make_uint2(w0, w1);
+        }
+    } else {
+        for (int k = threadIdx.x; k < N; k += blockDim.x) gr[k] = (int8_t)qz(to_float<T>(yr[k]));
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// launchers
+// ---------------------------------------------------------------------------------------------------------
+
+static inline int grid_for(long long work, int block, int cap = 0) {
+    long long g = (work + block - 1) / block;
+    if (cap > 0 && g > cap) g = cap;
+    return (int)(g < 1 ? 1 : g);
+}
+
+int launch_pack(const void* src, bool from_float, float gamma, uint8_t* Wp, int N, int K, int pad_code, cudaStream_t st) {
+    const int pK = (K + 3) / 4;
+    const long long work = (long long)N * pK;
+    if (work == 0) return EL_OK;
+    if (from_float) pack_kernel<true><<<grid_for(work, 256), 256, 0, st>>>(src, gamma, Wp, N, K, pK, pad_code);
+    else pack_kernel<false><<<grid_for(work, 256), 256, 0, st>>>(src, gamma, Wp, N, K, pK, pad_code);
+    return check_launch();
+}
+
+int launch_unpack(const uint8_t* Wp, void* out, int out_dtype, int N, int K, cudaStream_t st) {
+    const int pK = (K + 3) / 4;
+    const long long work = (long long)N * pK;
+    if (work == 0) return EL_OK;
+    const int g = grid_for(work, 256);
+    switch (out_dtype) {
+        case EL_F16: unpack_kernel<__half><<<g, 256, 0, st>>>(Wp, (__half*)out, N, K, pK); break;
+        case EL_BF16: unpack_kernel<__nv_bfloat16><<<g, 256, 0, st>>>(Wp, (__nv_bfloat16*)out, N, K, pK); break;
+        case EL_F32: unpack_kernel<float><<<g, 256, 0, st>>>(Wp, (float*)out, N, K, pK); break;
+        case EL_I32: unpack_kernel<int8_t><<<g, 256, 0, st>>>(Wp, (int8_t*)out, N, K, pK); break;
+        default: return EL_ERR_INVALID_ARG;
+    }
+    return check_launch();
+}
+
+template <typename T>
+static int launch_quantize_rows_t(const T* x, int8_t* q, float* a, int M, int K, float eps, const float* fold_absmax,
+                                  float* fold_max, cudaStream_t st) {
+    const bool vec = (K % 8 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0) &&
+                     ((reinterpret_cast<uintptr_t>(q) & 7) == 0);
+    if (vec) quantize_rows_kernel<T, true><<<M, 256, 0, st>>>(x, q, a, K, eps, fold_absmax, fold_max);
+    else quantize_rows_kernel<T, false><<<M, 256, 0, st>>>(x, q, a, K, eps, fold_absmax, fold_max);
+    return check_launch();
+}
+
+int launch_quantize_rows(const void* x, int dt, int8_t* q, float* a, int M, int K, float eps, const float* fold_absmax,
+                         float* fold_max, cudaStream_t st) {
+    if (M == 0) return EL_OK;
+    switch (dt) {
+        case EL_F16: return launch_quantize_rows_t((const __half*)x, q, a, M, K, eps, fold_absmax, fold_max, st);
+        case EL_BF16: return launch_quantize_rows_t((const __nv_bfloat16*)x, q, a, M, K, eps, fold_absmax, fold_max, st);
+        case EL_F32: return launch_quantize_rows_t((const float*)x, q, a, M, K, eps, fold_absmax, fold_max, st);
+        default: return EL_ERR_INVALID_ARG;
+    }
+}
+
+template <typename T>
+static int launch_quantize_tensor_t(const T* x, int8_t* q, float* absmax, long long size, cudaStream_t st) {
+    int sms = 148;
+    device_sm_count(&sms);
+    const int g = grid_for(size, 256, sms * 8);
+    tensor_absmax_kernel<T><<<g, 256, 0, st>>>(x, absmax, size);
+    int rc = check_launch();
+    if (rc != EL_OK) return rc;
+    tensor_quant_kernel<T><<<g, 256, 0, st>>>(x, q, absmax, size);
+    return check_launch();
+}
+
+int launch_quantize_tensor(const void* x, int dt, int8_t* q, float* absmax, long long size, cudaStream_t st) {
+    EL_CUDA_TRY(cudaMemsetAsync(absmax, 0, sizeof(float), st));
+    if (size == 0) return EL_OK;
+    switch (dt) {
+        case EL_F16: return launch_quantize_tensor_t((const __half*)x, q, absmax, size, st);
+        case EL_BF16: return launch_quantize_tensor_t((const __nv_bfloat16*)x, q, absmax, size, st);
+        case EL_F32: return launch_quantize_tensor_t((const float*)x, q, absmax, size, st);
+        default: return EL_ERR_INVALID_ARG;
+    }
+}
+
+int launch_dequantize_tensor(const int8_t* q, const float* absmax, void* out, int dt, long long size, cudaStream_t st) {
+    if (size == 0) return EL_OK;
+    int sms = 148;
+    device_sm_count(&sms);
+    const int g = grid_for(size, 256, sms * 8);
+    switch (dt) {
+        case EL_F16: tensor_dequant_kernel<__half><<<g, 256, 0, st>>>(q, absmax, (__half*)out, size); break;
+        case EL_BF16: tensor_dequant_kernel<__nv_bfloat16><<<g, 256, 0, st>>>(q, absmax, (__nv_bfloat16*)out, size); break;
+        case EL_F32: tensor_dequant_kernel<float><<<g, 256, 0, st>>>(q, absmax, (float*)out, size); break;
+        default: return EL_ERR_INVALID_ARG;
+    }
+    return check_launch();
+}
+
+template <typename T>
+static int launch_quantize_grad_t(const T* dY, const float* xa, const float* ga, int8_t* Gq, int M, int N, cudaStream_t st) {
+    const bool vec = (N % 8 == 0) && ((reinterpret_cast<uintptr_t>(dY) & 15) == 0) &&
+                     ((reinterpret_cast<uintptr_t>(Gq) & 7) == 0);
+    if (vec) quantize_grad_kernel<T, true><<<M, 256, 0, st>>>(dY, xa, ga, Gq, N);
+    else quantize_grad_kernel<T, false><<<M, 256, 0, st>>>(dY, xa, ga, Gq, N);
+    return check_launch();
+}
+
+int launch_quantize_grad(const void* dY, int dt, const float* xa, const float* ga, int8_t* Gq, int M, int N, cudaStream_t st) {
+    if (M == 0 || N == 0) return EL_OK;
+    switch (dt) {
+        case EL_F16: return launch_quantize_grad_t((const __half*)dY, xa, ga, Gq, M, N, st);
+        case EL_BF16: return launch_quantize_grad_t((const __nv_bfloat16*)dY, xa, ga, Gq, M, N, st);
+        case EL_F32: return launch_quantize_grad_t((const float*)dY, xa, ga, Gq, M, N, st);
+        default: return EL_ERR_INVALID_ARG;
+    }
+}
+
+}  // namespace el

@@ -1,0 +1,313 @@
+"""The operator surface of the INT2 linear path, on torch tensors.
+
+The first group of functions keeps the names, argument meaning and error behaviour of the reference's
+extension module `int2_tc_ops` (kernels/int2/int2_tc_ops.cpp:502-538): CUDA tensors in, outputs
+allocated here, work queued on the current CUDA stream, `W_packed` / `H_packed` updated in place,
+`RuntimeError` on bad arguments.  The second group is the per-token (bf16) path and the fused
+weight-gradient + hysteresis step, which the reference does not have.
+
+Every function ends in one call of the C-ABI library (include/elleci_int2.h); none computes in torch.
+"""
+from __future__ import annotations
+
+import math
+import os
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import EL_BF16, EL_F16, EL_F32, EL_I32, EL_PATH_AUTO, EL_PATH_SIMPLE, EL_PATH_TC, ElleciError, call
+
+_DT = {torch.float16: EL_F16, torch.bfloat16: EL_BF16, torch.float32: EL_F32, torch.int32: EL_I32}
+GRAD_EPS = 1e-30          # floor of a gradient row's absmax (an all-zero row quantises to zeros)
+ACT_EPS = 1e-5            # floor of an activation row's absmax (model/common/bitnet_legacy.py:45,75)
+
+_status_bufs: dict = {}
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _require(cond: bool, msg: str) -> None:
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def _cuda(t: torch.Tensor, name: str) -> None:
+    _require(isinstance(t, torch.Tensor) and t.is_cuda, f"{name} must be a CUDA tensor")
+
+
+def device_status(device: torch.device) -> torch.Tensor:
+    """The int32 word the tensor-core kernels write when a bounded wait gives up (0 = healthy)."""
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    buf = _status_bufs.get(key)
+    if buf is None:
+        buf = torch.zeros(1, dtype=torch.int32, device=device)
+        _status_bufs[key] = buf
+    return buf
+
+
+def check_device_status(device: torch.device) -> None:
+    """Synchronises and raises if a tensor-core kernel reported a failed wait."""
+    code = int(device_status(device).item())
+    if code != 0:
+        device_status(device).zero_()
+        raise ElleciError("tensor-core kernel", code, f"a bounded barrier wait gave up (code {code})")
+
+
+def _maybe_check(device: torch.device) -> None:
+    if os.environ.get("ELLECI_CHECK_STATUS") == "1":
+        check_device_status(device)
+
+
+# ==============================================================================================
+# Group 1: the reference extension's surface (per-tensor scales, fp16 I/O)
+# ==============================================================================================
+
+def quantize_activation_async(input: torch.Tensor, d_global_max: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(int8 tensor, absmax[1]) of a float tensor, per-tensor rule; no host sync
+    (tc_quantize_activation_async, kernels/int2/int2_tc_ops.cpp:343-371).  `d_global_max` is accepted for
+    signature compatibility; the absmax is accumulated in the returned scale tensor, so concurrent
+    streams do not share scratch."""
+    _cuda(input, "Input")
+    _cuda(d_global_max, "d_global_max")
+    _require(input.dtype in (torch.float16, torch.bfloat16, torch.float32), "Input must be float16")
+    x = input.contiguous()
+    out = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+    scale = torch.empty(1, dtype=torch.float32, device=x.device)
+    call("el_quantize_tensor", x.data_ptr(), _DT[x.dtype], out.data_ptr(), scale.data_ptr(), x.numel(), _stream())
+    return out, scale
+
+
+def quantize_activation(input: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """tc_quantize_activation (kernels/int2/int2_tc_ops.cpp:279-305)."""
+    _cuda(input, "Input")
+    return quantize_activation_async(input, input)
+
+
+def dequantize_activation(input_int8: torch.Tensor, scale: torch.Tensor, dtype: torch.dtype = torch.float16) -> torch.Tensor:
+    """int8 * (absmax/127) -> fp16 (tc_dequantize_activation, kernels/int2/int2_tc_ops.cpp:310-337)."""
+    _cuda(input_int8, "Input")
+    _cuda(scale, "scale")
+    _require(input_int8.dtype == torch.int8, "Input must be int8")
+    _require(scale.dtype == torch.float32, "scale must be float32")
+    q = input_int8.contiguous()
+    out = torch.empty(q.shape, dtype=dtype, device=q.device)
+    call("el_dequantize_tensor", q.data_ptr(), scale.data_ptr(), out.data_ptr(), _DT[dtype], q.numel(), _stream())
+    return out
+
+
+def _gemm_fwd(Xq, W_packed, absmax, stride, gamma, out_dtype, path=EL_PATH_AUTO):
+    _cuda(Xq, "X_int8"); _cuda(W_packed, "W_packed"); _cuda(absmax, "d_scale_x")
+    _require(Xq.dtype == torch.int8, "X_int8 must be int8")
+    _require(W_packed.dtype == torch.uint8, "W_packed must be uint8")
+    _require(absmax.dtype == torch.float32, "d_scale_x must be float32")
+    _require(W_packed.dim() == 2, "W_packed must be 2-D [N, ceil(K/4)]")
+    N, pK = W_packed.shape
+    K = Xq.shape[-1]
+    _require((K + 3) // 4 == pK, f"Dimension mismatch: X has {K} features but W_packed has packed_K={pK} "
+                                 f"(expected ceil(K/4)={(K + 3) // 4})")
+    Xf = Xq.contiguous().view(-1, K)
+    M = Xf.shape[0]
+    _require(stride == 0 or absmax.numel() == M, "one absmax per token expected")
+    Wc = W_packed.contiguous()
+    Y = torch.empty(M, N, dtype=out_dtype, device=Xq.device)
+    st = device_status(Xq.device)
+    call("el_gemm_fwd", Xf.data_ptr(), Wc.data_ptr(), Y.data_ptr(), _DT[out_dtype], absmax.data_ptr(), stride,
+         float(gamma), M, N, K, path, st.data_ptr(), _stream())
+    _maybe_check(Xq.device)
+    return Y.view(*Xq.shape[:-1], N)
+
+
+def _gemm_dx(dYq, W_packed, absmax, stride, gamma, K, out_dtype, path=EL_PATH_AUTO):
+    _cuda(dYq, "dY_int8"); _cuda(W_packed, "W_packed"); _cuda(absmax, "d_scale_dy")
+    _require(dYq.dtype == torch.int8, "dY_int8 must be int8")
+    _require(W_packed.dtype == torch.uint8, "W_packed must be uint8")
+    _require(absmax.dtype == torch.float32, "d_scale_dy must be float32")
+    N, pK = W_packed.shape
+    _require(dYq.shape[-1] == N, f"dY has {dYq.shape[-1]} features but W_packed has {N} rows")
+    _require((K + 3) // 4 == pK, f"K={K} does not match W_packed's packed_K={pK}")
+    Yf = dYq.contiguous().view(-1, N)
+    M = Yf.shape[0]
+    _require(stride == 0 or absmax.numel() == M, "one absmax per token expected")
+    Wc = W_packed.contiguous()
+    dX = torch.empty(M, K, dtype=out_dtype, device=dYq.device)
+    st = device_status(dYq.device)
+    call("el_gemm_dx", Yf.data_ptr(), Wc.data_ptr(), dX.data_ptr(), _DT[out_dtype], absmax.data_ptr(), stride,
+         float(gamma), M, N, int(K), path, st.data_ptr(), _stream())
+    _maybe_check(dYq.device)
+    return dX.view(*dYq.shape[:-1], K)
+
+
+def matmul_int8(X_int8: torch.Tensor, W_packed: torch.Tensor, d_scale_x: torch.Tensor, gamma: float,
+                out_dtype: torch.dtype = torch.float16, path: int = EL_PATH_AUTO) -> torch.Tensor:
+    """Y = X_int8 @ W^T * (scale_x/127) * gamma, fp16 out (tc_matmul_int8, kernels/int2/int2_tc_ops.cpp:381-425)."""
+    return _gemm_fwd(X_int8, W_packed, d_scale_x, 0, gamma, out_dtype, path)
+
+
+def backward_input_int8(dY_int8: torch.Tensor, W_packed: torch.Tensor, d_scale_dy: torch.Tensor, gamma: float, K: int,
+                        out_dtype: torch.dtype = torch.float16, path: int = EL_PATH_AUTO) -> torch.Tensor:
+    """dX = dY_int8 @ W * (scale_dy/127) * gamma (tc_backward_input_int8, kernels/int2/int2_tc_ops.cpp:435-470)."""
+    return _gemm_dx(dY_int8, W_packed, d_scale_dy, 0, gamma, K, out_dtype, path)
+
+
+def hysteresis_step_v2(dW: torch.Tensor, W_packed: torch.Tensor, H_packed: torch.Tensor, lr: float, lr_scale: float,
+                       threshold: int, decay: float, step: int, idx_base: int = 0, ftz: bool = True) -> None:
+    """In-place hysteresis update from a float32 gradient (tc_hysteresis_step_v2,
+    kernels/int2/int2_tc_ops.cpp:214-257); same checks, same integer results."""
+    _cuda(dW, "dW")
+    _require(W_packed.is_cuda and H_packed.is_cuda, "State must be on CUDA")
+    _require(dW.dtype == torch.float32, "dW must be float32")
+    _require(dW.dim() == 2, "dW must be 2-D [N, K]")
+    dW = dW.contiguous()
+    N, K = dW.shape
+    pK, pH = (K + 3) // 4, (K + 1) // 2
+    _require(W_packed.dim() == 2 and tuple(W_packed.shape) == (N, pK), f"W_packed expected [{N}, {pK}] = [N, ceil(K/4)]")
+    _require(H_packed.dim() == 2 and tuple(H_packed.shape) == (N, pH), f"H_packed expected [{N}, {pH}] = [N, ceil(K/2)]")
+    _require(W_packed.dtype == torch.uint8 and H_packed.dtype == torch.uint8, "W_packed/H_packed must be uint8")
+    _require(W_packed.is_contiguous() and H_packed.is_contiguous(), "W_packed/H_packed must be contiguous")
+    step32 = int(step) & 0xFFFFFFFF
+    step_i = step32 - (1 << 32) if step32 >= (1 << 31) else step32
+    call("el_hysteresis_from_dw", dW.data_ptr(), W_packed.data_ptr(), H_packed.data_ptr(), float(lr), float(lr_scale),
+         int(threshold), float(decay), step_i, N, K, int(idx_base) & 0xFFFFFFFF, int(bool(ftz)), _stream())
+
+
+def unpack_int2(W_packed: torch.Tensor, W_out: torch.Tensor, K: int) -> None:
+    """W_packed -> dense {-1,0,+1} matrix in W_out's dtype (tc_unpack_int2, kernels/int2/int2_tc_ops.cpp:476-499)."""
+    _cuda(W_packed, "W_packed"); _cuda(W_out, "W_fp16")
+    _require(W_packed.dtype == torch.uint8, "W_packed must be uint8")
+    N = W_packed.shape[0]
+    _require(W_out.shape[0] == N, "W_fp16 row count must match W_packed")
+    _require(W_out.shape[1] == K, "W_fp16 col count must equal K")
+    _require(W_out.is_contiguous() and W_packed.is_contiguous(), "tensors must be contiguous")
+    dt = EL_I32 if W_out.dtype == torch.int8 else _DT[W_out.dtype]
+    call("el_unpack_ternary", W_packed.data_ptr(), W_out.data_ptr(), dt, N, int(K), _stream())
+
+
+def memory_stats() -> dict:
+    """GPU memory statistics (tc_memory_stats, kernels/int2/int2_tc_ops.cpp:264-273)."""
+    free, total = torch.cuda.mem_get_info()
+    return {"free_bytes": free, "total_bytes": total, "used_bytes": total - free}
+
+
+# ==============================================================================================
+# Group 2: per-token path, packing, integer weight gradient, fused dW + hysteresis
+# ==============================================================================================
+
+def pack_int2(w_ternary: torch.Tensor, pad_code: int = 0) -> torch.Tensor:
+    """[N,K] in {-1,0,1} (any dtype) -> packed uint8 [N, ceil(K/4)] on the device."""
+    _cuda(w_ternary, "w_ternary")
+    w = w_ternary.to(torch.int8).contiguous()
+    N, K = w.shape
+    out = torch.empty(N, (K + 3) // 4, dtype=torch.uint8, device=w.device)
+    call("el_pack_ternary", w.data_ptr(), out.data_ptr(), N, K, int(pad_code), _stream())
+    return out
+
+
+def ternarize_pack(weight: torch.Tensor, gamma: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """clamp(round(W/gamma), -1, 1) packed in one pass (the arithmetic of Int2LinearTC.init_from_float,
+    core/bitnet/int2_linear_tc.py:399-400, then _pack_int2_cpu)."""
+    _cuda(weight, "weight")
+    w = weight.float().contiguous()
+    N, K = w.shape
+    if out is None:
+        out = torch.empty(N, (K + 3) // 4, dtype=torch.uint8, device=w.device)
+    _require(out.is_contiguous() and tuple(out.shape) == (N, (K + 3) // 4), "bad W_packed buffer")
+    call("el_ternarize_pack", w.data_ptr(), float(gamma), out.data_ptr(), N, K, _stream())
+    return out
+
+
+def quantize_rows(x: torch.Tensor, eps: float = ACT_EPS, fold_absmax: Optional[torch.Tensor] = None):
+    """Per-token absmax int8 quantisation.  Returns (q int8 like x, absmax float32 [M]) and, when
+    `fold_absmax` [M] is given, also max_m(absmax[m]*fold_absmax[m]/127) as a float32 [1] tensor."""
+    _cuda(x, "x")
+    _require(x.dtype in _DT and x.dtype != torch.int32, "x must be float16, bfloat16 or float32")
+    xc = x.contiguous()
+    K = xc.shape[-1]
+    M = math.prod(xc.shape[:-1])
+    q = torch.empty(xc.shape, dtype=torch.int8, device=x.device)
+    a = torch.empty(M, dtype=torch.float32, device=x.device)
+    fold_max = None
+    if fold_absmax is not None:
+        _require(fold_absmax.dtype == torch.float32 and fold_absmax.numel() == M, "fold_absmax must be float32 [M]")
+        fold_max = torch.zeros(1, dtype=torch.float32, device=x.device)
+    call("el_quantize_rows", xc.data_ptr(), _DT[xc.dtype], q.data_ptr(), a.data_ptr(), M, K, float(eps),
+         _ptr(fold_absmax), _ptr(fold_max), _stream())
+    return (q, a) if fold_absmax is None else (q, a, fold_max)
+
+
+def matmul_rows(Xq: torch.Tensor, W_packed: torch.Tensor, row_absmax: torch.Tensor, gamma: float,
+                out_dtype: torch.dtype = torch.bfloat16, path: int = EL_PATH_AUTO) -> torch.Tensor:
+    """Y[m,:] = (Xq[m,:] @ W^T) * (row_absmax[m]/127) * gamma: the forward GEMM with per-token scales."""
+    return _gemm_fwd(Xq, W_packed, row_absmax, 1, gamma, out_dtype, path)
+
+
+def backward_input_rows(dYq: torch.Tensor, W_packed: torch.Tensor, row_absmax: torch.Tensor, gamma: float, K: int,
+                        out_dtype: torch.dtype = torch.bfloat16, path: int = EL_PATH_AUTO) -> torch.Tensor:
+    """dX[m,:] = (dYq[m,:] @ W) * (row_absmax[m]/127) * gamma: the dX GEMM with per-token scales."""
+    return _gemm_dx(dYq, W_packed, row_absmax, 1, gamma, K, out_dtype, path)
+
+
+def quantize_grad(dY: torch.Tensor, x_absmax: torch.Tensor, g_absmax: torch.Tensor) -> torch.Tensor:
+    """Gq = int8 of (dY * x_absmax[m]/127) under the per-tensor maximum g_absmax[1]."""
+    _cuda(dY, "dY")
+    yc = dY.contiguous()
+    N = yc.shape[-1]
+    M = math.prod(yc.shape[:-1])
+    _require(x_absmax.dtype == torch.float32 and x_absmax.numel() == M, "x_absmax must be float32 [M]")
+    _require(g_absmax.dtype == torch.float32 and g_absmax.numel() == 1, "g_absmax must be float32 [1]")
+    Gq = torch.empty(yc.shape, dtype=torch.int8, device=dY.device)
+    call("el_quantize_grad", yc.data_ptr(), _DT[yc.dtype], x_absmax.data_ptr(), g_absmax.data_ptr(), Gq.data_ptr(), M, N,
+         _stream())
+    return Gq
+
+
+def weight_grad(Gq: torch.Tensor, Xq: torch.Tensor, g_absmax: torch.Tensor, raw: bool = False,
+                path: int = EL_PATH_AUTO) -> torch.Tensor:
+    """dW[n,k] = (sum_m Gq[m,n]*Xq[m,k]) * (g_absmax/127) as float32 [N,K] (int32 sums when raw=True)."""
+    _cuda(Gq, "Gq"); _cuda(Xq, "Xq")
+    _require(Gq.dtype == torch.int8 and Xq.dtype == torch.int8, "Gq and Xq must be int8")
+    N, K = Gq.shape[-1], Xq.shape[-1]
+    G2, X2 = Gq.contiguous().view(-1, N), Xq.contiguous().view(-1, K)
+    M = G2.shape[0]
+    _require(X2.shape[0] == M, "Gq and Xq must have the same number of tokens")
+    dt = torch.int32 if raw else torch.float32
+    dW = torch.empty(N, K, dtype=dt, device=Gq.device)
+    st = device_status(Gq.device)
+    call("el_gemm_dw", G2.data_ptr(), X2.data_ptr(), dW.data_ptr(), _DT[dt], g_absmax.data_ptr(), M, N, K, path,
+         st.data_ptr(), _stream())
+    _maybe_check(Gq.device)
+    return dW
+
+
+def dw_hysteresis_supported(N: int, K: int) -> bool:
+    """Shapes the fused weight-gradient + hysteresis kernel takes (others use weight_grad + hysteresis_step_v2)."""
+    return N % 16 == 0 and K % 32 == 0
+
+
+def dw_hysteresis(Gq: torch.Tensor, Xq: torch.Tensor, g_absmax: torch.Tensor, W_packed: torch.Tensor,
+                  H_packed: torch.Tensor, lr: float, lr_scale: float, threshold: int, decay: float, step: int,
+                  idx_base: int = 0) -> None:
+    """Fused weight-gradient GEMM + hysteresis update, in place on W_packed / H_packed."""
+    _cuda(Gq, "Gq"); _cuda(Xq, "Xq")
+    _require(Gq.dtype == torch.int8 and Xq.dtype == torch.int8, "Gq and Xq must be int8")
+    N, K = Gq.shape[-1], Xq.shape[-1]
+    G2, X2 = Gq.contiguous().view(-1, N), Xq.contiguous().view(-1, K)
+    M = G2.shape[0]
+    _require(X2.shape[0] == M, "Gq and Xq must have the same number of tokens")
+    _require(tuple(W_packed.shape) == (N, (K + 3) // 4) and tuple(H_packed.shape) == (N, (K + 1) // 2),
+             "W_packed / H_packed shape mismatch")
+    _require(W_packed.is_contiguous() and H_packed.is_contiguous(), "W_packed/H_packed must be contiguous")
+    step32 = int(step) & 0xFFFFFFFF
+    step_i = step32 - (1 << 32) if step32 >= (1 << 31) else step32
+    st = device_status(Gq.device)
+    call("el_dw_hysteresis", G2.data_ptr(), X2.data_ptr(), g_absmax.data_ptr(), W_packed.data_ptr(), H_packed.data_ptr(),
+         float(lr), float(lr_scale), int(threshold), float(decay), step_i, int(idx_base) & 0xFFFFFFFF, M, N, K,
+         st.data_ptr(), _stream())
+    _maybe_check(Gq.device)

@@ -1,0 +1,158 @@
+/*
+ * elleci_int2.h - C ABI of the B200 (sm_100a) BitNet INT2 linear library (libelleci_int2.so).
+ *
+ * Every entry point takes raw device pointers, sizes and a CUDA stream; the caller owns all memory.
+ * Nothing here allocates, synchronises or prints.  Every function returns EL_OK (0) or a negative
+ * EL_ERR_* code; el_status_string() names it and el_last_cuda_error() gives the CUDA error code behind
+ * EL_ERR_CUDA on the calling thread.  All calls are asynchronous on `stream` and re-entrant across
+ * streams and devices (there is no hidden scratch memory).
+ *
+ * Each declaration cites the interface of the reference project (step325/Elleci-Training-Vast,
+ * paths relative to its root) that it replaces.
+ *
+ * Data formats (identical to the reference's, kernels/int2/int2_packed.cuh:9-86):
+ *   W_packed  uint8 [N, ceil(K/4)]  four ternary weights per byte, weight k at bits 2*(k%4) of byte k/4;
+ *                                   code 0 = -1, 1 = 0, 2 = +1, 3 = reserved (reads as 0)
+ *   H_packed  uint8 [N, ceil(K/2)]  two signed 4-bit hysteresis counters per byte, even k in the low nibble
+ *   Xq        int8  [M, K]          quantised activations, row-major
+ *   absmax    float [M] or [1]      max |x| of a token row (or of the whole tensor); the dequantisation
+ *                                   scale is absmax/127, applied in the GEMM epilogue
+ */
+#ifndef ELLECI_INT2_H_
+#define ELLECI_INT2_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* A CUDA stream handle (cudaStream_t), passed as an opaque pointer so that the header needs no CUDA include. */
+typedef void* el_stream_t;
+
+/* Exported symbol marker (the library is built with hidden default visibility). */
+#if defined(__GNUC__)
+#define EL_API __attribute__((visibility("default")))
+#else
+#define EL_API
+#endif
+
+/* ---- status codes ---------------------------------------------------------------------------------- */
+#define EL_OK                     0
+#define EL_ERR_INVALID_ARG       -1   /* a size, dtype or flag is out of range */
+#define EL_ERR_NULL_PTR          -2   /* a required pointer is NULL */
+#define EL_ERR_ALIGNMENT         -3   /* a pointer or pitch breaks an alignment rule of the requested path */
+#define EL_ERR_UNSUPPORTED_SHAPE -4   /* the requested path cannot run this shape (see the function's notes) */
+#define EL_ERR_CUDA              -5   /* a CUDA runtime call failed; see el_last_cuda_error() */
+#define EL_ERR_DEVICE            -6   /* the current device is not an sm_100 part */
+#define EL_ERR_DRIVER            -7   /* the driver refused a tensor-map descriptor */
+
+/* ---- element types of floating-point / output buffers ------------------------------------------------ */
+#define EL_F16  0
+#define EL_BF16 1
+#define EL_F32  2
+#define EL_I32  3   /* raw int32 accumulators (outputs only): the bit-exact check of a GEMM */
+
+/* ---- GEMM path selection (flags argument) ------------------------------------------------------------ */
+#define EL_PATH_AUTO   0   /* tensor-core (tcgen05) kernel when the shape allows it, CUDA-core kernel otherwise */
+#define EL_PATH_SIMPLE 1   /* force the CUDA-core kernel (any shape) */
+#define EL_PATH_TC     2   /* require the tcgen05 kernel; EL_ERR_UNSUPPORTED_SHAPE / EL_ERR_ALIGNMENT if it cannot run */
+
+EL_API int el_version(void);
+EL_API const char* el_status_string(int status);
+EL_API int el_last_cuda_error(void);
+
+/* Device-side error word written by the tensor-core kernels when one of their bounded waits gives up
+ * (0 = no error; otherwise a code naming the wait).  `dev_status` arguments below may be NULL. */
+
+/* ---- weight format --------------------------------------------------------------------------------- */
+
+/* Packs int8 ternary weights w[N,K] into W_packed; unused fields of a row's last byte get pad_code (0..3).
+ * Replaces Int2LinearTC._pack_int2_cpu (core/bitnet/int2_linear_tc.py:414-436) and the test packer
+ * pack_int2 (kernels/tests/kernel_build.py:69-81), which run on the host. */
+EL_API int el_pack_ternary(const int8_t* w, uint8_t* W_packed, int N, int K, int pad_code, el_stream_t stream);
+
+/* q = clamp(round_half_even(W/gamma), -1, 1) packed in one pass (padding code 0, as the module packer).
+ * Replaces Int2LinearTC.init_from_float (core/bitnet/int2_linear_tc.py:391-412). */
+EL_API int el_ternarize_pack(const float* W, float gamma, uint8_t* W_packed, int N, int K, el_stream_t stream);
+
+/* Decodes W_packed into a dense [N,K] matrix of {-1,0,+1}; out_dtype EL_F16 / EL_BF16 / EL_F32, or
+ * EL_I32 meaning int8 output.  Replaces int2_unpack_to_fp16 (kernels/int2/int2_unpack.cu:157-174,
+ * binding kernels/int2/int2_tc_ops.cpp:476-499). */
+EL_API int el_unpack_ternary(const uint8_t* W_packed, void* out, int out_dtype, int N, int K, el_stream_t stream);
+
+/* ---- activation quantisation ------------------------------------------------------------------------ */
+
+/* Per-token absmax int8 quantisation: a[m] = max(max_k |x[m,k]|, eps), q = clamp(rint(x*(127/a)), -128, 127);
+ * non-finite inputs count as 0.  x_dtype EL_F16 / EL_BF16 / EL_F32.  Replaces BitLinear.activation_quant
+ * (model/common/bitnet_legacy.py:58-87), in integer form.
+ * Optional gradient folding (both NULL to disable): with fold_absmax[M] given, fold_max[1] receives, by an
+ * atomic max, max_m(a[m] * (fold_absmax[m]/127)); the caller zeroes fold_max first. */
+EL_API int el_quantize_rows(const void* x, int x_dtype, int8_t* q, float* row_absmax, int M, int K, float eps,
+                     const float* fold_absmax, float* fold_max, el_stream_t stream);
+
+/* Per-tensor absmax int8 quantisation: absmax[0] = max finite |x| (the call zeroes it first),
+ * q = clamp(roundf(x * (absmax > 1e-8 ? 127/absmax : 0)), -127, 127).  Replaces quantize_activation_async
+ * (kernels/int2/int2_activation_quant.cu:313-343, binding kernels/int2/int2_tc_ops.cpp:343-371); the scratch
+ * word of the reference is the caller's own absmax buffer here. */
+EL_API int el_quantize_tensor(const void* x, int x_dtype, int8_t* q, float* absmax, long long size, el_stream_t stream);
+
+/* out = q * (absmax[0]/127).  Replaces dequantize_activation (int2_activation_quant.cu:290-304,
+ * binding int2_tc_ops.cpp:310-337). */
+EL_API int el_dequantize_tensor(const int8_t* q, const float* absmax, void* out, int out_dtype, long long size,
+                         el_stream_t stream);
+
+/* Gq[m,n] = clamp(rint((dY[m,n] * (x_absmax[m]/127)) * inv), -127, 127), inv = g >= 1e-30 ? 127/g : 0,
+ * g = g_absmax[0] (from el_quantize_rows' fold_max).  The per-token activation scale folded into the output
+ * gradient makes the weight gradient an exact integer GEMM.  No counterpart in the reference, which forms dW
+ * with a library fp16 GEMM (core/bitnet/int2_linear_tc.py:525-537). */
+EL_API int el_quantize_grad(const void* dY, int dy_dtype, const float* x_absmax, const float* g_absmax, int8_t* Gq,
+                     int M, int N, el_stream_t stream);
+
+/* ---- GEMMs ------------------------------------------------------------------------------------------- */
+
+/* Y[m,n] = out_dtype( float(sum_k Xq[m,k]*Wq[n,k]) * ((absmax[m*absmax_stride]/127) * gamma) ).
+ * absmax_stride 1 = per-token scales, 0 = one per-tensor scale.  Tensor-core path needs K % 64 == 0 and
+ * 16-byte aligned Xq / W_packed.  Replaces int2_matmul_int8_tc_v2 (kernels/int2/int2_matmul_int8_tc_v2.cu:
+ * 500-537, binding tc_matmul_int8 kernels/int2/int2_tc_ops.cpp:381-425). */
+EL_API int el_gemm_fwd(const int8_t* Xq, const uint8_t* W_packed, void* Y, int out_dtype, const float* absmax,
+                int absmax_stride, float gamma, int M, int N, int K, int flags, int32_t* dev_status,
+                el_stream_t stream);
+
+/* dX[m,k] = out_dtype( float(sum_n dYq[m,n]*Wq[n,k]) * ((absmax[m*absmax_stride]/127) * gamma) ).
+ * Tensor-core path needs N % 16 == 0 and K % 64 == 0.  Replaces int2_backward_dx_int8_tc_v2
+ * (kernels/int2/int2_backward_int8_tc_v2.cu:465-499, binding tc_backward_input_int8 int2_tc_ops.cpp:435-470). */
+EL_API int el_gemm_dx(const int8_t* dYq, const uint8_t* W_packed, void* dX, int out_dtype, const float* absmax,
+               int absmax_stride, float gamma, int M, int N, int K, int flags, int32_t* dev_status,
+               el_stream_t stream);
+
+/* dW[n,k] = float(sum_m Gq[m,n]*Xq[m,k]) * (g_absmax[0]/127)   (out_dtype EL_F32, or EL_I32 for the raw sums).
+ * Tensor-core path needs N % 16 == 0 and K % 16 == 0.  Replaces `torch.mm(dY_2d.t(), X_2d).float()`
+ * (core/bitnet/int2_linear_tc.py:537, core/bitnet/int2_linear_tc_offload.py:247). */
+EL_API int el_gemm_dw(const int8_t* Gq, const int8_t* Xq, void* dW, int out_dtype, const float* g_absmax, int M, int N,
+               int K, int flags, int32_t* dev_status, el_stream_t stream);
+
+/* ---- hysteresis ---------------------------------------------------------------------------------------- */
+
+/* One hysteresis update of W_packed / H_packed from a float32 gradient dW[N,K], in place; bit-exact with
+ * int2_hysteresis_v2_update (kernels/int2/int2_hysteresis_v2.cu:54-194, binding tc_hysteresis_step_v2
+ * kernels/int2/int2_tc_ops.cpp:214-257), including its fast-math flush of float32 denormals when ftz != 0.
+ * idx_base offsets the random-number counter (n*K + k) for a row shard of a larger matrix. */
+EL_API int el_hysteresis_from_dw(const float* dW, uint8_t* W_packed, uint8_t* H_packed, float lr, float lr_scale,
+                          int threshold, float decay_rate, int step, int N, int K, uint32_t idx_base, int ftz,
+                          el_stream_t stream);
+
+/* Weight-gradient GEMM fused with the hysteresis update: the int32 sums of el_gemm_dw stay on chip, are scaled
+ * by g_absmax[0]/127 and drive the same per-weight update as el_hysteresis_from_dw (ftz on); W_packed and
+ * H_packed are rewritten in place and dW never reaches memory.  Needs N % 16 == 0 and K % 32 == 0
+ * (EL_ERR_UNSUPPORTED_SHAPE otherwise: use el_gemm_dw + el_hysteresis_from_dw).  Replaces the pair
+ * torch.mm + hysteresis_step_v2 of Int2LinearTC.hysteresis_update (core/bitnet/int2_linear_tc.py:483-548). */
+EL_API int el_dw_hysteresis(const int8_t* Gq, const int8_t* Xq, const float* g_absmax, uint8_t* W_packed,
+                     uint8_t* H_packed, float lr, float lr_scale, int threshold, float decay_rate, int step,
+                     uint32_t idx_base, int M, int N, int K, int32_t* dev_status, el_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ELLECI_INT2_H_ */

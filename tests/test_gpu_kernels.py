@@ -1,0 +1,256 @@
+"""Parity of the CUDA kernels with the CPU oracle, through the package's operator surface (which ends in the
+C ABI).  Integer results are compared bit for bit; scaled outputs share the oracle's float32 arithmetic and are
+compared exactly too (the tolerances the path promises, 1e-2 for bf16 and 1e-5 for fp32, are asserted against
+the reference's own legacy layer in test_oracle_golden.py)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import int2_oracle as O
+from oracle import native
+
+from conftest import GOLDEN
+from helpers import make_layer_inputs, random_packed, t2n
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.fixture(scope="module")
+def ops(pkg):
+    assert os.path.exists(pkg.LIB_PATH), "the CUDA library must be built in-tree"
+    return pkg.int2_tc_ops
+
+
+def _cuda(a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a))
+    return (t if dtype is None else t.to(dtype)).to(DEV)
+
+
+# ---- weight format ------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("N,K", [(8, 8), (5, 7), (16, 130), (3, 1), (33, 64), (130, 126), (256, 256)])
+def test_pack_unpack_bit_exact(ops, N, K):
+    rng = np.random.default_rng(N * 1000 + K)
+    w = rng.integers(-1, 2, (N, K)).astype(np.int8)
+    for pad in (0, 1):
+        got = ops.pack_int2(_cuda(w), pad_code=pad).cpu().numpy()
+        assert np.array_equal(got, O.pack_ternary(w, pad_code=pad))
+    Wp = rng.integers(0, 256, (N, (K + 3) // 4)).astype(np.uint8)       # every code, also the reserved one
+    for dt in (torch.float16, torch.bfloat16, torch.float32, torch.int8):
+        out = torch.empty(N, K, dtype=dt, device=DEV)
+        ops.unpack_int2(_cuda(Wp), out, K)
+        assert np.array_equal(t2n(out).astype(np.int8), O.unpack_ternary(Wp, K))
+
+
+def test_ternarize_pack_matches_golden_init_from_float(ops):
+    g = np.load(os.path.join(GOLDEN, "ternarize.npz"))
+    for i in range(3):
+        got = ops.ternarize_pack(_cuda(g[f"W{i}"]), float(g[f"gamma{i}"])).cpu().numpy()
+        assert np.array_equal(got, g[f"W_packed{i}"])
+
+
+# ---- activation quantisation -----------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("M,K", [(1, 255), (7, 64), (16, 1536), (33, 100), (4, 11008), (5, 8)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_quantize_rows_bit_exact(ops, M, K, dtype):
+    g = torch.Generator().manual_seed(M * 7 + K)
+    x = (torch.randn(M, K, generator=g) * 3.0).to(dtype)
+    x[0, : min(K, 3)] = 0.0
+    if M > 2:
+        x[1] = 0.0                      # all-zero token: absmax clamps to eps
+        x[2, 0] = float("inf")          # non-finite values count as zero
+        x[2, K - 1] = float("nan")
+    q, a = ops.quantize_rows(x.to(DEV))
+    qo, ao = O.quantize_rows(t2n(x))
+    assert np.array_equal(a.cpu().numpy(), ao)
+    assert np.array_equal(q.cpu().numpy(), qo)
+
+
+def test_quantize_rows_empty_inputs(ops):
+    q, a = ops.quantize_rows(torch.empty(0, 64, dtype=torch.bfloat16, device=DEV))
+    assert q.shape == (0, 64) and a.numel() == 0
+    q, a = ops.quantize_rows(torch.empty(3, 0, dtype=torch.bfloat16, device=DEV))
+    assert q.shape == (3, 0) and np.allclose(a.cpu().numpy(), 1e-5)
+
+
+@pytest.mark.parametrize("i", range(5))
+def test_quantize_tensor_matches_reference_kernel_golden(ops, i):
+    g = np.load(os.path.join(GOLDEN, "quant_tensor.npz"))
+    x = torch.from_numpy(g[f"x_bits{i}"].view(np.float16).copy()).to(DEV)
+    q, am = ops.quantize_activation_async(x, torch.zeros(1, device=DEV))
+    assert am.cpu().numpy()[0] == g[f"absmax{i}"][0]
+    assert np.array_equal(q.cpu().numpy(), g[f"q{i}"])
+    deq = ops.dequantize_activation(q, am)
+    assert np.array_equal(deq.cpu().numpy().view(np.uint16), g[f"deq_bits{i}"])
+
+
+def test_grad_quantisation_bit_exact(ops):
+    d = make_layer_inputs(37, 96, 80, seed=3, dy_std=1e-3)
+    x, dY = d["x"], d["dY"]
+    _, ax = ops.quantize_rows(x.to(DEV))
+    dYq, ady, gmax = ops.quantize_rows(dY.to(DEV), 1e-30, fold_absmax=ax)
+    Gq = ops.quantize_grad(dY.to(DEV), ax, gmax)
+    _, axo = O.quantize_rows(t2n(x))
+    dYqo, adyo = O.quantize_rows(t2n(dY), eps=1e-30)
+    Gqo, go = O.grad_quantize(t2n(dY), axo)
+    assert np.array_equal(dYq.cpu().numpy(), dYqo) and np.array_equal(ady.cpu().numpy(), adyo)
+    assert gmax.cpu().numpy()[0] == go
+    assert np.array_equal(Gq.cpu().numpy(), Gqo)
+
+
+# ---- hysteresis ---------------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("i", range(6))
+def test_hysteresis_matches_reference_kernel_golden(ops, i):
+    g = np.load(os.path.join(GOLDEN, "hysteresis.npz"))
+    N, K, thr, lr, ls, dec, step = g[f"params{i}"]
+    N, K, thr, step = int(N), int(K), int(thr), int(step)
+    W, H = _cuda(g[f"W0_{i}"]), _cuda(g[f"H0_{i}"])
+    dW = _cuda(g[f"dW{i}"])
+    ops.hysteresis_step_v2(dW, W, H, lr, ls, thr, dec, step)
+    assert np.array_equal(W.cpu().numpy(), g[f"W1_{i}"]) and np.array_equal(H.cpu().numpy(), g[f"H1_{i}"])
+    ops.hysteresis_step_v2(dW, W, H, lr, ls, thr, dec, step + 1)
+    assert np.array_equal(W.cpu().numpy(), g[f"W2_{i}"]) and np.array_equal(H.cpu().numpy(), g[f"H2_{i}"])
+
+
+@pytest.mark.parametrize("N,K,thr", [(64, 64, 2), (37, 50, 3), (5, 7, 7), (16, 130, 1), (8, 20, 2), (1536, 1536, 2)])
+def test_hysteresis_bit_exact_with_special_values(ops, N, K, thr):
+    rng = np.random.default_rng(N + K)
+    Wp = rng.integers(0, 256, (N, (K + 3) // 4)).astype(np.uint8)
+    Hp = O.pack_counters(rng.integers(-7, 8, (N, K)).astype(np.int8))
+    dW = (rng.standard_normal((N, K)) * 0.05).astype(np.float32)
+    flat = dW.reshape(-1)
+    flat[0], flat[1 % flat.size], flat[2 % flat.size] = np.nan, np.inf, -np.inf
+    flat[3 % flat.size], flat[4 % flat.size] = 1e-42, -0.0
+    for step, ftz in ((1, True), (77, False), (4000000000, True)):
+        W, H = _cuda(Wp), _cuda(Hp)
+        ops.hysteresis_step_v2(_cuda(dW), W, H, 3e-3, 5.0, thr, 0.2, step, ftz=ftz)
+        Wo, Ho = native.c_hysteresis_step(dW, Wp, Hp, 3e-3, 5.0, thr, 0.2, step, K, ftz=ftz)
+        assert np.array_equal(W.cpu().numpy(), Wo) and np.array_equal(H.cpu().numpy(), Ho)
+
+
+def test_hysteresis_row_shards_equal_whole(ops):
+    rng = np.random.default_rng(11)
+    N, K = 48, 64
+    Wp, _ = random_packed(N, K, 1)
+    Hp = O.pack_counters(rng.integers(-3, 4, (N, K)).astype(np.int8))
+    dW = (rng.standard_normal((N, K)) * 0.05).astype(np.float32)
+    Wf, Hf = native.c_hysteresis_step(dW, Wp, Hp, 1e-2, 5.0, 3, 0.1, 5, K)
+    for g in (2, 4):
+        rows = N // g
+        for r in range(g):
+            sl = slice(r * rows, (r + 1) * rows)
+            W, H = _cuda(Wp[sl]), _cuda(Hp[sl])
+            ops.hysteresis_step_v2(_cuda(dW[sl]), W, H, 1e-2, 5.0, 3, 0.1, 5, idx_base=r * rows * K)
+            assert np.array_equal(W.cpu().numpy(), Wf[sl]) and np.array_equal(H.cpu().numpy(), Hf[sl])
+
+
+def test_hysteresis_rejects_bad_arguments(ops):
+    W = torch.zeros(4, 2, dtype=torch.uint8, device=DEV)
+    H = torch.zeros(4, 4, dtype=torch.uint8, device=DEV)
+    with pytest.raises(RuntimeError):
+        ops.hysteresis_step_v2(torch.zeros(4, 8, device=DEV).half(), W, H, 1e-3, 5.0, 2, 0.0, 1)       # dtype
+    with pytest.raises(RuntimeError):
+        ops.hysteresis_step_v2(torch.zeros(4, 9, device=DEV), W, H, 1e-3, 5.0, 2, 0.0, 1)              # packed shape
+    with pytest.raises(RuntimeError):
+        ops.hysteresis_step_v2(torch.zeros(32, device=DEV), W, H, 1e-3, 5.0, 2, 0.0, 1)                # not 2-D
+
+
+# ---- GEMMs --------------------------------------------------------------------------------------------------------
+
+# the reference's own edge grid (kernels/tests/test_correctness.py:17-42) plus shapes the layer really has
+SIMPLE_SHAPES = [(8, 8, 8), (256, 256, 256), (256, 260, 256), (128, 128, 130), (64, 48, 200), (33, 16, 16), (130, 126, 126),
+                 (1, 64, 64)]
+# tensor-core constraints: K % 64 == 0 (packed pitch), N % 16 == 0 (dYq / Gq pitch); M is free
+TC_SHAPES = [(128, 256, 128), (128, 256, 256), (256, 512, 384), (100, 304, 192), (1024, 1536, 1536), (160, 272, 1088),
+             (37, 64, 64), (300, 1376, 4096), (129, 16, 64)]
+
+
+def _gemm_inputs(M, N, K, seed):
+    rng = np.random.default_rng(seed)
+    Xq = rng.integers(-128, 128, (M, K)).astype(np.int8)
+    dYq = rng.integers(-128, 128, (M, N)).astype(np.int8)
+    Wp, w = random_packed(N, K, seed)
+    ax = (rng.random(M).astype(np.float32) * 4 + 0.5)
+    ay = (rng.random(M).astype(np.float32) * 1e-2 + 1e-4)
+    return Xq, dYq, Wp, ax, ay
+
+
+def _check_gemms(ops, M, N, K, path, seed=0):
+    Xq, dYq, Wp, ax, ay = _gemm_inputs(M, N, K, seed)
+    gamma = 0.0173
+    dXq, ddY, dWp, dax, day = _cuda(Xq), _cuda(dYq), _cuda(Wp), _cuda(ax), _cuda(ay)
+    acc_f = O.gemm_fwd_acc(Xq, Wp, K)
+    acc_x = O.gemm_dx_acc(dYq, Wp, K)
+    acc_w = O.gemm_dw_acc(dYq, Xq)
+    # raw int32 accumulators: bit-exact
+    assert np.array_equal(ops.matmul_rows(dXq, dWp, dax, gamma, torch.int32, path).cpu().numpy(), acc_f)
+    assert np.array_equal(ops.backward_input_rows(ddY, dWp, day, gamma, K, torch.int32, path).cpu().numpy(), acc_x)
+    g1 = torch.tensor([0.37], device=DEV)
+    assert np.array_equal(ops.weight_grad(ddY, dXq, g1, raw=True, path=path).cpu().numpy(), acc_w)
+    # scaled outputs: the oracle's float32 arithmetic, then the output rounding
+    for dt, rnd in ((torch.float32, lambda v: v), (torch.bfloat16, O.to_bf16), (torch.float16, O.to_f16)):
+        y = ops.matmul_rows(dXq, dWp, dax, gamma, dt, path)
+        assert np.array_equal(t2n(y), rnd(O.scale_rows(acc_f, ax, gamma)))
+        dx = ops.backward_input_rows(ddY, dWp, day, gamma, K, dt, path)
+        assert np.array_equal(t2n(dx), rnd(O.scale_rows(acc_x, ay, gamma)))
+    # per-tensor scale (the reference extension's calling convention)
+    s1 = torch.tensor([2.5], device=DEV)
+    y = ops.matmul_int8(dXq, dWp, s1, gamma, path=path)
+    assert np.array_equal(t2n(y), O.to_f16(O.scale_rows(acc_f, np.float32(2.5), gamma)))
+    dw = ops.weight_grad(ddY, dXq, g1, path=path)
+    assert np.array_equal(dw.cpu().numpy(), O.dw_from_acc(acc_w, np.float32(0.37)))
+
+
+@pytest.mark.parametrize("M,N,K", SIMPLE_SHAPES)
+def test_gemms_cuda_core_path_bit_exact(ops, pkg, M, N, K):
+    _check_gemms(ops, M, N, K, pkg._lib.EL_PATH_SIMPLE, seed=M + N + K)
+
+
+@pytest.mark.parametrize("M,N,K", TC_SHAPES)
+def test_gemms_tensor_core_path_bit_exact(ops, pkg, M, N, K):
+    _check_gemms(ops, M, N, K, pkg._lib.EL_PATH_TC, seed=M + N + K)
+    ops.check_device_status(torch.device(DEV))
+
+
+def test_tensor_core_forward_with_ragged_n(ops, pkg):
+    """The forward GEMM alone has no constraint on N (only dX and dW read a pitch of N bytes)."""
+    M, N, K = 200, 300, 320
+    Xq, _, Wp, ax, _ = _gemm_inputs(M, N, K, 5)
+    y = ops.matmul_rows(_cuda(Xq), _cuda(Wp), _cuda(ax), 0.02, torch.bfloat16, pkg._lib.EL_PATH_TC)
+    assert np.array_equal(t2n(y), O.to_bf16(O.scale_rows(O.gemm_fwd_acc(Xq, Wp, K), ax, 0.02)))
+    ops.check_device_status(torch.device(DEV))
+
+
+def test_tensor_core_path_refuses_unaligned_shapes(ops, pkg):
+    Xq = torch.zeros(128, 100, dtype=torch.int8, device=DEV)      # K % 64 != 0
+    Wp = torch.zeros(64, 25, dtype=torch.uint8, device=DEV)
+    a = torch.ones(128, device=DEV)
+    with pytest.raises(pkg.ElleciError) as e:
+        ops.matmul_rows(Xq, Wp, a, 1.0, torch.bfloat16, pkg._lib.EL_PATH_TC)
+    assert e.value.status == pkg._lib.EL_ERR_UNSUPPORTED_SHAPE
+    # the automatic path takes the same problem through the CUDA-core kernel
+    assert ops.matmul_rows(Xq, Wp, a, 1.0, torch.bfloat16).shape == (128, 64)
+    with pytest.raises(RuntimeError):
+        ops.matmul_rows(Xq, torch.zeros(64, 26, dtype=torch.uint8, device=DEV), a, 1.0)     # packed_K mismatch
+
+
+@pytest.mark.parametrize("M,N,K,thr", [(128, 128, 256, 2), (200, 272, 96, 3), (1024, 1536, 1536, 2)])
+def test_fused_dw_hysteresis_bit_exact(ops, M, N, K, thr):
+    rng = np.random.default_rng(M + N)
+    Gq = rng.integers(-127, 128, (M, N)).astype(np.int8)
+    Xq = rng.integers(-128, 128, (M, K)).astype(np.int8)
+    Wp, _ = random_packed(N, K, 5)
+    Hp = O.pack_counters(rng.integers(-3, 4, (N, K)).astype(np.int8))
+    g = np.float32(3e-3 if M < 1000 else 4e-4)
+    W, H = _cuda(Wp), _cuda(Hp)
+    ops.dw_hysteresis(_cuda(Gq), _cuda(Xq), torch.tensor([g], device=DEV), W, H, 1e-2, 5.0, thr, 0.01, 3, idx_base=1000)
+    ops.check_device_status(torch.device(DEV))
+    dW = O.dw_from_acc(O.gemm_dw_acc(Gq, Xq), g)
+    Wo, Ho = native.c_hysteresis_step(dW, Wp, Hp, 1e-2, 5.0, thr, 0.01, 3, K, idx_base=1000)
+    assert np.array_equal(W.cpu().numpy(), Wo) and np.array_equal(H.cpu().numpy(), Ho)
+    assert (O.unpack_ternary(Wo, K) != O.unpack_ternary(Wp, K)).mean() > 0.01      # the case does flip weights

@@ -1,0 +1,148 @@
+"""The layer-level API (Int2LinearTC / BitLinearInt2 / converters) against the oracle's composite step."""
+import io
+
+import numpy as np
+import pytest
+import torch
+import torch.nn as nn
+
+from oracle import int2_oracle as O
+from oracle import native
+
+from helpers import make_layer_inputs, t2n
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _make_layer(pkg, d, K, N, thr=2, order="reference", mode="per_token", hook=True):
+    cls = pkg.Int2LinearTCWithGradHook if hook else pkg.Int2LinearTC
+    layer = cls(K, N, threshold=thr, lr_scale=5.0, decay_rate=0.001, quant_mode=mode, hysteresis_order=order).to(DEV)
+    layer.init_from_float(d["W"].to(DEV), scale=d["gamma"])
+    layer.H_packed.copy_(torch.from_numpy(d["Hp"]))
+    layer.train()
+    return layer
+
+
+@pytest.mark.parametrize("order", ["reference", "after_dx"])
+@pytest.mark.parametrize("M,K,N,dtype", [(1024, 1536, 1536, torch.bfloat16), (96, 128, 80, torch.float32),
+                                         (64, 100, 36, torch.bfloat16)])
+def test_layer_step_matches_oracle(pkg, order, M, K, N, dtype):
+    """Forward, dX and the weight update of one layer step (benchmark configuration 0 is the first case)."""
+    d = make_layer_inputs(M, K, N, seed=0, dtype=dtype, dy_std=1e-2)
+    lr = 1e-2 if M >= 1024 else 0.5      # large enough for the small cases to flip weights too
+    layer = _make_layer(pkg, d, K, N, thr=2, order=order)
+    layer.set_lr(lr)
+    assert np.array_equal(layer.W_packed.cpu().numpy(), d["Wp"])
+    x = d["x"].to(DEV).requires_grad_(True)
+    y = layer(x)
+    y.backward(d["dY"].to(DEV))
+    torch.cuda.synchronize()
+    pkg.int2_tc_ops.check_device_status(torch.device(DEV))
+
+    out = {torch.bfloat16: "bf16", torch.float32: "f32"}[dtype]
+    yo, Xq, ax = O.bitlinear_forward(t2n(d["x"]), d["Wp"], d["gamma"], K, out=out)
+    assert np.array_equal(t2n(y), yo)
+    dWo, acc, g = O.bitlinear_dw(t2n(d["dY"]), Xq, ax)
+    Wn, Hn = native.c_hysteresis_step(dWo, d["Wp"], d["Hp"], lr, 5.0, 2, 0.001, 1, K)
+    assert np.array_equal(layer.W_packed.cpu().numpy(), Wn)
+    assert np.array_equal(layer.H_packed.cpu().numpy(), Hn)
+    assert (O.unpack_ternary(Wn, K) != O.unpack_ternary(d["Wp"], K)).any()
+    w_for_dx = Wn if order == "reference" else d["Wp"]      # the reference's hook updates the weights before dX
+    dxo = O.bitlinear_backward_dx(t2n(d["dY"]), w_for_dx, d["gamma"], K, out=out)
+    assert np.array_equal(t2n(x.grad), dxo)
+    assert layer._step_py == 1 and layer._saved_input is None
+
+
+def test_per_tensor_mode_follows_the_reference_cuda_rule(pkg):
+    M, K, N = 128, 256, 192
+    d = make_layer_inputs(M, K, N, seed=4, dtype=torch.float16)
+    layer = _make_layer(pkg, d, K, N, mode="per_tensor", hook=False)
+    x = d["x"].to(DEV).requires_grad_(True)
+    y = layer(x)
+    assert y.dtype == torch.float16
+    xq, a = O.quantize_tensor(t2n(d["x"]))
+    yo = O.to_f16(O.scale_rows(O.gemm_fwd_acc(xq, d["Wp"], K), a, d["gamma"]))
+    assert np.array_equal(t2n(y), yo)
+    y.backward(d["dY"].to(DEV))
+    dyq, ay = O.quantize_tensor(t2n(d["dY"]))
+    dxo = O.to_f16(O.scale_rows(O.gemm_dx_acc(dyq, d["Wp"], K), ay, d["gamma"]))
+    assert np.array_equal(t2n(x.grad), dxo)
+    layer.hysteresis_update(d["dY"].to(DEV), 1e-2)
+    assert layer._step_py == 1
+
+
+def test_accumulation_gate_and_missing_input(pkg):
+    d = make_layer_inputs(32, 64, 48, seed=2)
+    layer = _make_layer(pkg, d, 64, 48)
+    with pytest.raises(RuntimeError):
+        layer.hysteresis_update(d["dY"].to(DEV), 1e-2)            # no forward yet
+    pkg.disable_hysteresis()
+    try:
+        y = layer(d["x"].to(DEV).requires_grad_(True))
+        y.backward(d["dY"].to(DEV))
+        assert np.array_equal(layer.W_packed.cpu().numpy(), d["Wp"]) and layer._step_py == 0
+        assert layer._saved_input is None
+    finally:
+        pkg.enable_hysteresis()
+    y = layer(d["x"].to(DEV).requires_grad_(True))
+    y.backward(d["dY"].to(DEV))
+    assert layer._step_py == 1
+    layer.eval()
+    with torch.no_grad():
+        layer(d["x"].to(DEV))
+    assert layer._saved_input is None                              # inference keeps no activation
+
+
+def test_checkpoint_roundtrip_keeps_reference_state_names(pkg):
+    d = make_layer_inputs(16, 64, 32, seed=5)
+    layer = _make_layer(pkg, d, 64, 32)
+    layer._step_py = 7
+    layer.sync_step_buffer()
+    sd = layer.state_dict()
+    assert set(sd) == {"gamma", "W_packed", "H_packed", "_step"}
+    buf = io.BytesIO()
+    torch.save(sd, buf)
+    buf.seek(0)
+    other = pkg.Int2LinearTCWithGradHook(64, 32).to(DEV)
+    other.load_state_dict(torch.load(buf))
+    assert other._step_py == 7 and other._initialized
+    assert torch.equal(other.W_packed, layer.W_packed)
+    with torch.no_grad():
+        assert torch.equal(other.eval()(d["x"].to(DEV)), layer.eval()(d["x"].to(DEV)))
+
+
+def test_convert_all_linear_to_int2(pkg):
+    class Block(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.w1 = nn.Linear(256, 512, bias=False)
+            self.w2 = nn.Linear(512, 256, bias=True)
+            self.tiny = nn.Linear(16, 8)                # below the size floor
+            self.lm_head = nn.Linear(256, 300)          # excluded by name
+            self.norm = nn.LayerNorm(256)
+
+        def forward(self, x):
+            return self.lm_head(self.norm(self.w2(torch.nn.functional.silu(self.w1(x)))))
+
+    torch.manual_seed(0)
+    model = Block()
+    conv = pkg.convert_all_linear_to_int2(model, threshold=3, min_size=64, verbose=False)
+    layers = pkg.get_int2_layers(conv)
+    assert len(layers) == 2 and isinstance(conv.w1, pkg.BitLinearInt2) and isinstance(conv.tiny, nn.Linear)
+    assert isinstance(conv.lm_head, nn.Linear) and isinstance(model.w1, nn.Linear)      # not in place
+    assert not conv._int2_conversion_stats["errors"]
+    gamma = float(max(model.w1.weight.abs().mean().item(), 1e-5))
+    assert np.array_equal(conv.w1.weight_packed.cpu().numpy(),
+                          O.pack_ternary(O.ternarize(model.w1.weight.detach().numpy(), gamma), pad_code=0))
+    pkg.set_all_int2_lr(conv, 0.02)
+    assert conv.w1.int2_layer._lr == 0.02
+    n_other = len(pkg.get_non_int2_params(conv))
+    assert n_other == len(list(conv.parameters())) - sum(len(list(l.parameters())) for l in layers)
+    conv = conv.to(DEV).train()
+    x = torch.randn(4, 10, 256, device=DEV, dtype=torch.bfloat16)
+    conv.lm_head.to(torch.bfloat16); conv.norm.to(torch.bfloat16)
+    out = conv(x)
+    out.float().pow(2).mean().backward()
+    assert out.shape == (4, 10, 300) and torch.isfinite(out.float()).all()
+    assert conv.w1.int2_layer._step_py == 1 and conv.w2.int2_layer._step_py == 1
