@@ -1,0 +1,431 @@
+"""Benchmark of the INT2 linear layer step on B200: forward + dX + dW/hysteresis tokens per second.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload config2|config4]
+
+One "step" is one pass of the hot path over one batch of synthetic tokens: for every layer of the workload,
+per-token int8 quantisation of the activations, the forward GEMM, per-token quantisation of the output gradient,
+the dX GEMM, and the weight-gradient GEMM fused with the hysteresis update of the packed weights and counters.
+
+  config2 (default)  M = 4096 tokens through the two 7B MLP projections 4096->11008 and 11008->4096,
+                     counters seeded uniformly in [-3, 3], threshold 3, dY ~ N(0, 1e-3)
+  config4            M = 65536 tokens through one 4096->16384 projection
+
+With N > 1 (launched by torch.distributed.run, one rank per GPU) the weights are sharded along N; the output is
+all-gathered and the dX partial sums are all-reduced with NCCL (strong scaling: the problem is fixed).
+
+Rank 0 prints one JSON line.  `value` is timed with CUDA events, inputs resident in HBM, L2 flushed between
+steps; `e2e` goes through the module API with pinned host buffers copied in every step; `--impl reference`
+times the CPU port of the reference layer (oracle/cpu_baseline.py) instead.
+"""
+from __future__ import annotations
+
+import argparse
+import importlib.util
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    "config2": dict(M=4096, layers=[(4096, 11008), (11008, 4096)], threshold=3, counters=3, dy_std=1e-3,
+                    desc="config2: M=4096 tokens, layers 4096->11008 + 11008->4096, fwd + dX + dW/hysteresis"),
+    "config4": dict(M=65536, layers=[(4096, 16384)], threshold=3, counters=3, dy_std=1e-3,
+                    desc="config4: M=65536 tokens, layer 4096->16384, fwd + dX + dW/hysteresis"),
+}
+LR, LR_SCALE, DECAY = 1e-2, 5.0, 0.001
+METRIC = "BitLinear fwd+bwd+hysteresis tokens/s at 7B shapes"
+
+
+def load_package():
+    name = "elleci_training_vast_b200"
+    if name in sys.modules:
+        return sys.modules[name]
+    pkg_dir = os.path.join(ROOT, "elleci-training-vast_b200")
+    spec = importlib.util.spec_from_file_location(name, os.path.join(pkg_dir, "__init__.py"),
+                                                  submodule_search_locations=[pkg_dir])
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# clock sampling (read-only NVML queries from a thread during the timed region)
+# ------------------------------------------------------------------------------------------------------------------
+
+class ClockSampler:
+    def __init__(self, device_index: int):
+        self.samples, self.reasons, self.sm_max = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = int(visible.split(",")[device_index]) if visible and visible.split(",")[device_index].isdigit() else device_index
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.sm_max = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:  # noqa: BLE001 - no NVML: the clocks key says so
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {
+            nv.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
+            nv.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
+            nv.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
+            nv.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:  # noqa: BLE001
+                pass
+            time.sleep(0.004)
+
+    def start(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        if self._thread is not None:
+            self._stop.set()
+            self._thread.join()
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.sm_max, "reasons": ["unavailable"]}
+        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.sm_max, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# reference arm: the CPU port of the reference layer on the host cores
+# ------------------------------------------------------------------------------------------------------------------
+
+def cpu_baseline_sample(wl, steps: int, warmup: int, sample_tokens: int):
+    import torch
+    from oracle import cpu_baseline as cb
+    from oracle import native
+    native.build_oracle_lib()
+    layers = [cb.CpuLayer(K, N, torch.bfloat16, seed=i, counters=wl["counters"]) for i, (K, N) in enumerate(wl["layers"])]
+    times, spent = [], 0.0
+    for i in range(warmup + steps):
+        full, cpu_s = cb.time_step(layers, wl["M"], sample_tokens, torch.bfloat16, lr=LR, threshold=wl["threshold"], seed=i)
+        spent += cpu_s
+        if i >= warmup:
+            times.append(full)
+    sec = sum(times) / len(times)
+    return {
+        "value": wl["M"] / sec, "unit": "tokens/s", "cores": cb.cores_used(), "kind": "port",
+        "sample": (f"{steps} steps after {warmup} warm-up; forward+dX+dW (torch, bf16) on {sample_tokens} of "
+                   f"{wl['M']} tokens per step scaled to {wl['M']}, plus the hysteresis update of every weight"),
+        "ms_per_step": sec * 1e3, "cpu_seconds_spent": spent,
+    }
+
+
+def run_reference(args, wl):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps, warmup = max(1, min(args.steps, 5)), max(1, min(args.warmup, 2))
+    base = cpu_baseline_sample(wl, steps, warmup, sample_tokens=min(512, wl["M"]))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": base["value"], "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": steps, "warmup": warmup, "ms_per_step": base["ms_per_step"], "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16 (CPU torch) + int (hysteresis)", "data": "synthetic",
+        "config": {"workload": wl["desc"], "M": wl["M"], "layers": wl["layers"]},
+        "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": base["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------------------------------
+
+class Timer:
+    """CUDA-event pairs on the current stream, grouped by name; read after a synchronize."""
+
+    def __init__(self, torch):
+        self.torch, self.pairs, self.enabled = torch, {}, False
+
+    def run(self, name, fn, *a, **k):
+        if not self.enabled:
+            return fn(*a, **k)
+        e0, e1 = self.torch.cuda.Event(enable_timing=True), self.torch.cuda.Event(enable_timing=True)
+        e0.record()
+        out = fn(*a, **k)
+        e1.record()
+        self.pairs.setdefault(name, []).append((e0, e1))
+        return out
+
+    def totals(self):
+        return {n: (sum(a.elapsed_time(b) for a, b in ps), len(ps)) for n, ps in self.pairs.items()}
+
+
+def run_ours(args, wl):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    pkg = load_package()
+    ops = pkg.int2_tc_ops
+    if not os.path.exists(pkg.LIB_PATH):
+        raise SystemExit("libelleci_int2.so is not built; there is no fallback path")
+
+    M, thr = wl["M"], wl["threshold"]
+    gen = torch.Generator().manual_seed(1234)
+
+    # ---- state: one (sharded) layer per projection ------------------------------------------------------------
+    class L:
+        pass
+
+    layers = []
+    for li, (K, N) in enumerate(wl["layers"]):
+        lay = L()
+        lay.K, lay.N = K, N
+        lay.n0, lay.n1 = pkg.sharded.shard_rows(N, world, rank)
+        lay.Nl = lay.n1 - lay.n0
+        Wl = torch.randn(lay.Nl, K, generator=torch.Generator().manual_seed(100 + li * 16 + rank)) * 0.02
+        lay.gamma = 0.0160
+        lay.Wp = ops.ternarize_pack(Wl.to(dev), lay.gamma)
+        h = torch.randint(-wl["counters"], wl["counters"] + 1, (lay.Nl, K), generator=gen, dtype=torch.int8)
+        hb = (h & 0xF).to(torch.uint8).view(lay.Nl, K // 2, 2)
+        lay.Hp = (hb[:, :, 0] | (hb[:, :, 1] << 4)).to(dev).contiguous()
+        lay.W0, lay.H0 = lay.Wp.clone(), lay.Hp.clone()
+        lay.x = torch.randn(M, K, generator=gen).to(torch.bfloat16).to(dev)
+        lay.dY = (torch.randn(M, N, generator=gen) * wl["dy_std"]).to(torch.bfloat16).to(dev)
+        lay.step = 0
+        layers.append(lay)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)      # larger than the 126 MB L2
+    timer = Timer(torch)
+
+    def layer_step(lay):
+        """One layer: forward, then (reference order) the weight update, then dX."""
+        K, Nl = lay.K, lay.Nl
+        Xq, ax = timer.run("quantize_rows", ops.quantize_rows, lay.x)
+        y = timer.run("gemm_fwd", ops.matmul_rows, Xq, lay.Wp, ax, lay.gamma, torch.bfloat16)
+        if world > 1:
+            gathered = torch.empty(world * M, Nl, dtype=torch.bfloat16, device=dev)
+            timer.run("all_gather_y", dist.all_gather_into_tensor, gathered, y)
+            y = timer.run("permute_y", lambda t: t.view(world, M, Nl).permute(1, 0, 2).reshape(M, world * Nl), gathered)
+        window = lay.dY[:, lay.n0:lay.n1] if world > 1 else lay.dY
+        if world > 1:
+            raw = timer.run("absmax_rows", ops.absmax_rows, window)
+            timer.run("all_reduce_absmax", dist.all_reduce, raw, op=dist.ReduceOp.MAX)
+            dYq, ady, gmax = timer.run("quantize_rows_dy", ops.quantize_rows, window, ops.GRAD_EPS, ax, raw)
+        else:
+            dYq, ady, gmax = timer.run("quantize_rows_dy", ops.quantize_rows, window, ops.GRAD_EPS, ax)
+        Gq = timer.run("quantize_grad", ops.quantize_grad, window, ax, gmax)
+        lay.step += 1
+        timer.run("gemm_dw_hysteresis", ops.dw_hysteresis, Gq, Xq, gmax, lay.Wp, lay.Hp, LR, LR_SCALE, thr, DECAY, lay.step,
+                  lay.n0 * K)
+        if world > 1:
+            acc = timer.run("gemm_dx", ops.backward_input_rows, dYq, lay.Wp, ady, lay.gamma, K, torch.int32)
+            timer.run("all_reduce_dx", dist.all_reduce, acc)
+            dX = timer.run("scale_rows", ops.scale_rows, acc, ady, lay.gamma, torch.bfloat16)
+        else:
+            dX = timer.run("gemm_dx", ops.backward_input_rows, dYq, lay.Wp, ady, lay.gamma, K, torch.bfloat16)
+        return y, dX
+
+    def device_step():
+        for lay in layers:
+            layer_step(lay)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- warm-up ---------------------------------------------------------------------------------------------------
+    for _ in range(max(args.warmup, 3)):
+        device_step()
+    barrier()
+    ops.check_device_status(dev)
+
+    # ---- timed region: K steps, one event pair per step, L2 flushed (untimed) between steps -------------------------
+    sampler = ClockSampler(local_rank)
+    timer.enabled = True
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    barrier()
+    sampler.start()
+    for i in range(args.steps):
+        flush.zero_()
+        ev[i][0].record()
+        device_step()
+        ev[i][1].record()
+    barrier()
+    clocks = sampler.stop()
+    timer.enabled = False
+    total_ms = sum(a.elapsed_time(b) for a, b in ev)
+    if world > 1:
+        t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    ops.check_device_status(dev)
+    ms_per_step = total_ms / args.steps
+    value = M / (ms_per_step * 1e-3)
+    kernel_totals = timer.totals()
+
+    # flips actually realised by the first timed update (workload sanity, reported in config)
+    lay0 = layers[0]
+    w_now = torch.empty(lay0.Nl, lay0.K, dtype=torch.int8, device=dev)
+    w_was = torch.empty_like(w_now)
+    ops.unpack_int2(lay0.Wp, w_now, lay0.K)
+    ops.unpack_int2(lay0.W0, w_was, lay0.K)
+    changed_frac = float((w_now != w_was).float().mean().item())
+
+    # ---- end to end through the module API, inputs in pinned host memory ------------------------------------------
+    e2e = None
+    if world == 1 and not args.no_e2e:
+        mods = []
+        for lay in layers:
+            m = pkg.Int2LinearTCWithGradHook(lay.K, lay.N, threshold=thr, lr_scale=LR_SCALE, decay_rate=DECAY).to(dev)
+            m.W_packed.copy_(lay.W0)
+            m.H_packed.copy_(lay.H0)
+            m.gamma.data.fill_(lay.gamma)
+            m._gamma_cached = lay.gamma
+            m._initialized = True
+            m.set_lr(LR)
+            m.train()
+            mods.append((m, lay.x.cpu().pin_memory(), lay.dY.cpu().pin_memory()))
+        out_host = torch.empty(layers[-1].K, dtype=torch.bfloat16).pin_memory()
+        h2d = sum(x.numel() * 2 + dy.numel() * 2 for _, x, dy in mods)
+        d2h = out_host.numel() * 2
+
+        def e2e_step():
+            dx = None
+            for m, xh, dyh in mods:
+                x = xh.to(dev, non_blocking=True).requires_grad_(True)
+                dy = dyh.to(dev, non_blocking=True)
+                y = m(x)
+                y.backward(dy)
+                dx = x.grad
+            out_host.copy_(dx[0], non_blocking=True)
+
+        e_steps = max(3, min(args.steps, 20))
+        for _ in range(3):
+            e2e_step()
+        torch.cuda.synchronize()
+        ee = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(e_steps)]
+        for i in range(e_steps):
+            flush.zero_()
+            ee[i][0].record()
+            e2e_step()
+            ee[i][1].record()
+        torch.cuda.synchronize()
+        e_ms = sum(a.elapsed_time(b) for a, b in ee) / e_steps
+        e2e = {"value": M / (e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+               "ms_per_step": e_ms, "steps": e_steps}
+        ops.check_device_status(dev)
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    # ---- roofline of the dominant kernel (the tcgen05 GEMM in its three modes) ---------------------------------------
+    peaks, peak_kind = measured_peaks()
+    gemm_ops = sum(2.0 * M * (lay.Nl) * lay.K for lay in layers)           # per GEMM mode per step, this rank
+    gemm_ms = sum(kernel_totals[n][0] for n in ("gemm_fwd", "gemm_dx", "gemm_dw_hysteresis"))
+    gemm_launches = sum(kernel_totals[n][1] for n in ("gemm_fwd", "gemm_dx", "gemm_dw_hysteresis"))
+    achieved = 3.0 * gemm_ops * args.steps / (gemm_ms * 1e-3) / 1e12
+    int8_peak = 2.0 * peaks["bf16_tflops_sustained"]
+    traffic_path = os.path.join(ROOT, "profiles", "traffic.json")
+    traffic = None
+    if os.path.exists(traffic_path):
+        with open(traffic_path) as f:
+            traffic = json.load(f).get(args.workload)
+    roofline = {
+        "bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TFLOP/s", "frac": achieved / int8_peak,
+        "traffic": traffic, "kernel": "gemm_tc_kernel (tcgen05 kind::i8; forward, dX and dW+hysteresis launches)",
+        "launches": gemm_launches, "avg_launch_ms": gemm_ms / max(gemm_launches, 1),
+        "peak_source": f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({peak_kind}); nominal dense INT8 is 4500",
+        "frac_of_nominal_int8": achieved / 4500.0,
+    }
+    per_mode = {}
+    for n in ("gemm_fwd", "gemm_dx", "gemm_dw_hysteresis"):
+        ms, cnt = kernel_totals[n]
+        per_mode[n] = {"ms_per_launch": ms / cnt, "tops": gemm_ops * args.steps / (ms * 1e-3) / 1e12}
+    hbm = {}
+    bytes_per_step = {
+        "quantize_rows": sum(M * lay.K * 3 + 4 * M for lay in layers),
+        "quantize_rows_dy": sum(M * lay.Nl * 3 + 8 * M for lay in layers),
+        "quantize_grad": sum(M * lay.Nl * 3 + 4 * M for lay in layers),
+    }
+    for n, b in bytes_per_step.items():
+        if n in kernel_totals:
+            ms, cnt = kernel_totals[n]
+            gbs = b * args.steps / (ms * 1e-3) / 1e9
+            hbm[n] = {"ms_per_launch": ms / cnt, "GBps": gbs, "frac_of_hbm": gbs / peaks["hbm_gbs"]}
+    comm = {n: {"ms_per_step": kernel_totals[n][0] / args.steps} for n in kernel_totals
+            if n.startswith("all_") or n in ("permute_y", "scale_rows", "absmax_rows")}
+
+    cpu = cpu_baseline_sample(wl, steps=2, warmup=1, sample_tokens=min(512, M)) if world == 1 and not args.no_cpu else None
+
+    own_launches = sum(cnt for n, (ms, cnt) in kernel_totals.items() if not n.startswith("all_") and n != "permute_y")
+    line = {
+        "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "int8 x int2 -> int32 (bf16 in/out)", "data": "synthetic",
+        "config": {"workload": wl["desc"], "M": M, "layers": wl["layers"], "threshold": thr,
+                   "parallelism": f"N-sharded x{world}" if world > 1 else "single GPU",
+                   "l2": "256 MiB written between timed steps (untimed)", "weights_changed_after_run": changed_frac},
+        "clocks": clocks, "e2e": e2e, "gpu_launches": own_launches,
+        "roofline": roofline, "gemm_modes": per_mode, "hbm_kernels": hbm,
+    }
+    if comm:
+        line["collectives"] = comm
+    if cpu is not None:
+        line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="config2", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg of the default run")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
+    args = ap.parse_args()
+    wl = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, wl)
+    else:
+        run_ours(args, wl)
+
+
+if __name__ == "__main__":
+    main()

@@ -16,6 +16,7 @@ EL_ERR_INVALID_ARG, EL_ERR_NULL_PTR, EL_ERR_ALIGNMENT, EL_ERR_UNSUPPORTED_SHAPE 
 EL_ERR_CUDA, EL_ERR_DEVICE, EL_ERR_DRIVER = -5, -6, -7
 EL_F16, EL_BF16, EL_F32, EL_I32 = 0, 1, 2, 3
 EL_PATH_AUTO, EL_PATH_SIMPLE, EL_PATH_TC = 0, 1, 2
+EL_QUANT_FULL, EL_QUANT_ABSMAX_ONLY, EL_QUANT_WITH_ABSMAX = 0, 1, 2
 
 _vp, _i, _f, _ll, _u32 = C.c_void_p, C.c_int, C.c_float, C.c_longlong, C.c_uint32
 
@@ -27,10 +28,11 @@ SIGNATURES = {
     "el_pack_ternary": [_vp, _vp, _i, _i, _i, _vp],
     "el_ternarize_pack": [_vp, _f, _vp, _i, _i, _vp],
     "el_unpack_ternary": [_vp, _vp, _i, _i, _i, _vp],
-    "el_quantize_rows": [_vp, _i, _vp, _vp, _i, _i, _f, _vp, _vp, _vp],
+    "el_quantize_rows": [_vp, _i, _ll, _vp, _vp, _i, _i, _f, _i, _vp, _vp, _vp],
     "el_quantize_tensor": [_vp, _i, _vp, _vp, _ll, _vp],
     "el_dequantize_tensor": [_vp, _vp, _vp, _i, _ll, _vp],
-    "el_quantize_grad": [_vp, _i, _vp, _vp, _vp, _i, _i, _vp],
+    "el_quantize_grad": [_vp, _i, _ll, _vp, _vp, _vp, _i, _i, _vp],
+    "el_scale_rows": [_vp, _vp, _i, _vp, _i, _f, _i, _i, _vp],
     "el_gemm_fwd": [_vp, _vp, _vp, _i, _vp, _i, _f, _i, _i, _i, _i, _vp, _vp],
     "el_gemm_dx": [_vp, _vp, _vp, _i, _vp, _i, _f, _i, _i, _i, _i, _vp, _vp],
     "el_gemm_dw": [_vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp, _vp],

@@ -10,11 +10,13 @@ enum { MODE_FWD = 0, MODE_DX = 1, MODE_DW = 2 };
 // kernels in the other translation units
 int launch_pack(const void* src, bool from_float, float gamma, uint8_t* Wp, int N, int K, int pad_code, cudaStream_t st);
 int launch_unpack(const uint8_t* Wp, void* out, int out_dtype, int N, int K, cudaStream_t st);
-int launch_quantize_rows(const void* x, int dt, int8_t* q, float* a, int M, int K, float eps, const float* fold_absmax,
-                         float* fold_max, cudaStream_t st);
+int launch_quantize_rows(const void* x, int dt, long long ldx, int8_t* q, float* a, int M, int K, float eps, int mode,
+                         const float* fold_absmax, float* fold_max, cudaStream_t st);
+int launch_scale_rows(const int* acc, const EpiParams& epi, int M, int C, cudaStream_t st);
 int launch_quantize_tensor(const void* x, int dt, int8_t* q, float* absmax, long long size, cudaStream_t st);
 int launch_dequantize_tensor(const int8_t* q, const float* absmax, void* out, int dt, long long size, cudaStream_t st);
-int launch_quantize_grad(const void* dY, int dt, const float* xa, const float* ga, int8_t* Gq, int M, int N, cudaStream_t st);
+int launch_quantize_grad(const void* dY, int dt, long long ld, const float* xa, const float* ga, int8_t* Gq, int M, int N,
+                         cudaStream_t st);
 int launch_hysteresis(const float* dW, uint8_t* Wp, uint8_t* Hp, const HystParams& p, int N, int K, uint32_t idx_base,
                       cudaStream_t st);
 int launch_gemm_simple(int mode, const int8_t* A, const void* B, int R, int C, int D, const EpiParams& epi, cudaStream_t st);
@@ -131,13 +133,14 @@ int el_unpack_ternary(const uint8_t* W_packed, void* out, int out_dtype, int N, 
     return launch_unpack(W_packed, out, out_dtype, N, K, (cudaStream_t)stream);
 }
 
-int el_quantize_rows(const void* x, int x_dtype, int8_t* q, float* row_absmax, int M, int K, float eps,
-                     const float* fold_absmax, float* fold_max, el_stream_t stream) {
-    if (M < 0 || K < 0 || !float_dtype(x_dtype) || !(eps > 0.0f)) return EL_ERR_INVALID_ARG;
+int el_quantize_rows(const void* x, int x_dtype, long long ldx, int8_t* q, float* row_absmax, int M, int K, float eps,
+                     int mode, const float* fold_absmax, float* fold_max, el_stream_t stream) {
+    if (M < 0 || K < 0 || ldx < K || !float_dtype(x_dtype) || !(eps > 0.0f) || mode < 0 || mode > 2) return EL_ERR_INVALID_ARG;
     if ((fold_absmax == nullptr) != (fold_max == nullptr)) return EL_ERR_INVALID_ARG;
+    if (mode == EL_QUANT_ABSMAX_ONLY && fold_max != nullptr) return EL_ERR_INVALID_ARG;
     if (M == 0) return EL_OK;
-    if (!row_absmax || (K > 0 && (!x || !q))) return EL_ERR_NULL_PTR;
-    return launch_quantize_rows(x, x_dtype, q, row_absmax, M, K, eps, fold_absmax, fold_max, (cudaStream_t)stream);
+    if (!row_absmax || (K > 0 && (!x || (!q && mode != EL_QUANT_ABSMAX_ONLY)))) return EL_ERR_NULL_PTR;
+    return launch_quantize_rows(x, x_dtype, ldx, q, row_absmax, M, K, eps, mode, fold_absmax, fold_max, (cudaStream_t)stream);
 }
 
 int el_quantize_tensor(const void* x, int x_dtype, int8_t* q, float* absmax, long long size, el_stream_t stream) {
@@ -153,12 +156,21 @@ int el_dequantize_tensor(const int8_t* q, const float* absmax, void* out, int ou
     return launch_dequantize_tensor(q, absmax, out, out_dtype, size, (cudaStream_t)stream);
 }
 
-int el_quantize_grad(const void* dY, int dy_dtype, const float* x_absmax, const float* g_absmax, int8_t* Gq, int M, int N,
-                     el_stream_t stream) {
-    if (M < 0 || N < 0 || !float_dtype(dy_dtype)) return EL_ERR_INVALID_ARG;
+int el_quantize_grad(const void* dY, int dy_dtype, long long ld_dy, const float* x_absmax, const float* g_absmax, int8_t* Gq,
+                     int M, int N, el_stream_t stream) {
+    if (M < 0 || N < 0 || ld_dy < N || !float_dtype(dy_dtype)) return EL_ERR_INVALID_ARG;
     if (M == 0 || N == 0) return EL_OK;
     if (!dY || !x_absmax || !g_absmax || !Gq) return EL_ERR_NULL_PTR;
-    return launch_quantize_grad(dY, dy_dtype, x_absmax, g_absmax, Gq, M, N, (cudaStream_t)stream);
+    return launch_quantize_grad(dY, dy_dtype, ld_dy, x_absmax, g_absmax, Gq, M, N, (cudaStream_t)stream);
+}
+
+int el_scale_rows(const int32_t* acc, void* out, int out_dtype, const float* absmax, int absmax_stride, float gamma, int M,
+                  int C, el_stream_t stream) {
+    if (M < 0 || C < 0 || !out_dtype_ok(out_dtype) || (absmax_stride != 0 && absmax_stride != 1)) return EL_ERR_INVALID_ARG;
+    if (M == 0 || C == 0) return EL_OK;
+    if (!acc || !out || !absmax) return EL_ERR_NULL_PTR;
+    const EpiParams epi{out, (long long)C, out_dtype, absmax, absmax_stride, gamma};
+    return launch_scale_rows(acc, epi, M, C, (cudaStream_t)stream);
 }
 
 int el_gemm_fwd(const int8_t* Xq, const uint8_t* W_packed, void* Y, int out_dtype, const float* absmax, int absmax_stride,

@@ -2,6 +2,7 @@
 // absmax int8 quantisation, gradient quantisation for the integer weight gradient.
 // All of them stream their operands once with 16-byte accesses where the shape allows it.
 #include "common.cuh"
+#include "epilogue.cuh"
 
 namespace el {
 
@@ -114,26 +115,36 @@ __device__ __forceinline__ int quant_half_even(float x, float s) {
 }
 
 // VEC: the row pitch and base allow 8-element vector loads and 8-byte stores.
-template <typename T, bool VEC>
+// MODE 0: absmax + quantise; 1: raw absmax only; 2: quantise with the raw absmax found in row_absmax.
+template <typename T, bool VEC, int MODE>
 __global__ void __launch_bounds__(256)
-quantize_rows_kernel(const T* __restrict__ x, int8_t* __restrict__ q, float* __restrict__ row_absmax, int K,
+quantize_rows_kernel(const T* __restrict__ x, long long ldx, int8_t* __restrict__ q, float* __restrict__ row_absmax, int K,
                      float eps, const float* __restrict__ fold_absmax, float* __restrict__ fold_max) {
     __shared__ float red[8];
     const int m = blockIdx.x;
-    const T* xr = x + (size_t)m * K;
+    const T* xr = x + (size_t)m * ldx;
     int8_t* qr = q + (size_t)m * K;
     float amax = 0.0f;
-    if (VEC) {
-        for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
-            float v[8];
-            load8<T>(xr + k, v);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(finite_or_zero(v[i])));
-        }
+    if (MODE == 2) {
+        amax = row_absmax[m];
+        __syncthreads();            // every thread has read the raw value before thread 0 floors it in place
     } else {
-        for (int k = threadIdx.x; k < K; k += blockDim.x) amax = fmaxf(amax, fabsf(finite_or_zero(to_float<T>(xr[k]))));
+        if (VEC) {
+            for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
+                float v[8];
+                load8<T>(xr + k, v);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(finite_or_zero(v[i])));
+            }
+        } else {
+            for (int k = threadIdx.x; k < K; k += blockDim.x) amax = fmaxf(amax, fabsf(finite_or_zero(to_float<T>(xr[k]))));
+        }
+        amax = block_max(amax, red);
     }
-    amax = block_max(amax, red);
+    if (MODE == 1) {
+        if (threadIdx.x == 0) row_absmax[m] = amax;
+        return;
+    }
     const float a = fmaxf(amax, eps);
     const float s = __fdiv_rn(127.0f, a);
     if (threadIdx.x == 0) {
@@ -207,13 +218,13 @@ tensor_dequant_kernel(const int8_t* __restrict__ q, const float* __restrict__ ab
 
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(256)
-quantize_grad_kernel(const T* __restrict__ dY, const float* __restrict__ x_absmax, const float* __restrict__ g_absmax,
-                     int8_t* __restrict__ Gq, int N) {
+quantize_grad_kernel(const T* __restrict__ dY, long long ld, const float* __restrict__ x_absmax,
+                     const float* __restrict__ g_absmax, int8_t* __restrict__ Gq, int N) {
     const int m = blockIdx.x;
     const float g = *g_absmax;
     const float inv = (g >= 1e-30f) ? __fdiv_rn(127.0f, g) : 0.0f;
     const float sx = __fdiv_rn(x_absmax[m], 127.0f);
-    const T* yr = dY + (size_t)m * N;
+    const T* yr = dY + (size_t)m * ld;
     int8_t* gr = Gq + (size_t)m * N;
     auto qz = [&](float v) -> int {
         const float f = __fmul_rn(finite_or_zero(v), sx);
@@ -273,22 +284,25 @@ int launch_unpack(const uint8_t* Wp, void* out, int out_dtype, int N, int K, cud
 }
 
 template <typename T>
-static int launch_quantize_rows_t(const T* x, int8_t* q, float* a, int M, int K, float eps, const float* fold_absmax,
-                                  float* fold_max, cudaStream_t st) {
-    const bool vec = (K % 8 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0) &&
+static int launch_quantize_rows_t(const T* x, long long ldx, int8_t* q, float* a, int M, int K, float eps, int mode,
+                                  const float* fold_absmax, float* fold_max, cudaStream_t st) {
+    const bool vec = (K % 8 == 0) && (ldx % 8 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0) &&
                      ((reinterpret_cast<uintptr_t>(q) & 7) == 0);
-    if (vec) quantize_rows_kernel<T, true><<<M, 256, 0, st>>>(x, q, a, K, eps, fold_absmax, fold_max);
-    else quantize_rows_kernel<T, false><<<M, 256, 0, st>>>(x, q, a, K, eps, fold_absmax, fold_max);
+#define EL_QR(V, MD) quantize_rows_kernel<T, V, MD><<<M, 256, 0, st>>>(x, ldx, q, a, K, eps, fold_absmax, fold_max)
+    if (mode == 0) { if (vec) EL_QR(true, 0); else EL_QR(false, 0); }
+    else if (mode == 1) { if (vec) EL_QR(true, 1); else EL_QR(false, 1); }
+    else { if (vec) EL_QR(true, 2); else EL_QR(false, 2); }
+#undef EL_QR
     return check_launch();
 }
 
-int launch_quantize_rows(const void* x, int dt, int8_t* q, float* a, int M, int K, float eps, const float* fold_absmax,
-                         float* fold_max, cudaStream_t st) {
+int launch_quantize_rows(const void* x, int dt, long long ldx, int8_t* q, float* a, int M, int K, float eps, int mode,
+                         const float* fold_absmax, float* fold_max, cudaStream_t st) {
     if (M == 0) return EL_OK;
     switch (dt) {
-        case EL_F16: return launch_quantize_rows_t((const __half*)x, q, a, M, K, eps, fold_absmax, fold_max, st);
-        case EL_BF16: return launch_quantize_rows_t((const __nv_bfloat16*)x, q, a, M, K, eps, fold_absmax, fold_max, st);
-        case EL_F32: return launch_quantize_rows_t((const float*)x, q, a, M, K, eps, fold_absmax, fold_max, st);
+        case EL_F16: return launch_quantize_rows_t((const __half*)x, ldx, q, a, M, K, eps, mode, fold_absmax, fold_max, st);
+        case EL_BF16: return launch_quantize_rows_t((const __nv_bfloat16*)x, ldx, q, a, M, K, eps, mode, fold_absmax, fold_max, st);
+        case EL_F32: return launch_quantize_rows_t((const float*)x, ldx, q, a, M, K, eps, mode, fold_absmax, fold_max, st);
         default: return EL_ERR_INVALID_ARG;
     }
 }
@@ -331,22 +345,44 @@ int launch_dequantize_tensor(const int8_t* q, const float* absmax, void* out, in
 }
 
 template <typename T>
-static int launch_quantize_grad_t(const T* dY, const float* xa, const float* ga, int8_t* Gq, int M, int N, cudaStream_t st) {
-    const bool vec = (N % 8 == 0) && ((reinterpret_cast<uintptr_t>(dY) & 15) == 0) &&
+static int launch_quantize_grad_t(const T* dY, long long ld, const float* xa, const float* ga, int8_t* Gq, int M, int N,
+                                  cudaStream_t st) {
+    const bool vec = (N % 8 == 0) && (ld % 8 == 0) && ((reinterpret_cast<uintptr_t>(dY) & 15) == 0) &&
                      ((reinterpret_cast<uintptr_t>(Gq) & 7) == 0);
-    if (vec) quantize_grad_kernel<T, true><<<M, 256, 0, st>>>(dY, xa, ga, Gq, N);
-    else quantize_grad_kernel<T, false><<<M, 256, 0, st>>>(dY, xa, ga, Gq, N);
+    if (vec) quantize_grad_kernel<T, true><<<M, 256, 0, st>>>(dY, ld, xa, ga, Gq, N);
+    else quantize_grad_kernel<T, false><<<M, 256, 0, st>>>(dY, ld, xa, ga, Gq, N);
     return check_launch();
 }
 
-int launch_quantize_grad(const void* dY, int dt, const float* xa, const float* ga, int8_t* Gq, int M, int N, cudaStream_t st) {
+int launch_quantize_grad(const void* dY, int dt, long long ld, const float* xa, const float* ga, int8_t* Gq, int M, int N,
+                         cudaStream_t st) {
     if (M == 0 || N == 0) return EL_OK;
     switch (dt) {
-        case EL_F16: return launch_quantize_grad_t((const __half*)dY, xa, ga, Gq, M, N, st);
-        case EL_BF16: return launch_quantize_grad_t((const __nv_bfloat16*)dY, xa, ga, Gq, M, N, st);
-        case EL_F32: return launch_quantize_grad_t((const float*)dY, xa, ga, Gq, M, N, st);
+        case EL_F16: return launch_quantize_grad_t((const __half*)dY, ld, xa, ga, Gq, M, N, st);
+        case EL_BF16: return launch_quantize_grad_t((const __nv_bfloat16*)dY, ld, xa, ga, Gq, M, N, st);
+        case EL_F32: return launch_quantize_grad_t((const float*)dY, ld, xa, ga, Gq, M, N, st);
         default: return EL_ERR_INVALID_ARG;
     }
+}
+
+// int32 sums -> scaled output, four columns per thread
+__global__ void __launch_bounds__(256)
+scale_rows_kernel(const int* __restrict__ acc, EpiParams epi, int M, int C) {
+    const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const int cg = (C + 3) / 4;
+    if (t >= (long long)M * cg) return;
+    const int m = (int)(t / cg), c0 = (int)(t % cg) * 4;
+    const float sc = epi_row_scale(epi, m);
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        if (c0 + j < C) epi_store_one(epi, m, c0 + j, acc[(size_t)m * C + c0 + j], sc);
+}
+
+int launch_scale_rows(const int* acc, const EpiParams& epi, int M, int C, cudaStream_t st) {
+    const long long work = (long long)M * ((C + 3) / 4);
+    if (work == 0) return EL_OK;
+    scale_rows_kernel<<<(int)((work + 255) / 256), 256, 0, st>>>(acc, epi, M, C);
+    return check_launch();
 }
 
 }  // namespace el

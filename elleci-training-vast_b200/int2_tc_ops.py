@@ -223,23 +223,66 @@ def ternarize_pack(weight: torch.Tensor, gamma: float, out: Optional[torch.Tenso
     return out
 
 
-def quantize_rows(x: torch.Tensor, eps: float = ACT_EPS, fold_absmax: Optional[torch.Tensor] = None):
-    """Per-token absmax int8 quantisation.  Returns (q int8 like x, absmax float32 [M]) and, when
-    `fold_absmax` [M] is given, also max_m(absmax[m]*fold_absmax[m]/127) as a float32 [1] tensor."""
+def _rows_view(t: torch.Tensor):
+    """(tensor, M, cols, row pitch) of a 2-D view whose rows are contiguous (a column window of a wider
+    matrix qualifies), or of any tensor after flattening its leading dimensions."""
+    if t.dim() == 2 and t.stride(1) == 1 and t.stride(0) >= t.shape[1]:
+        return t, t.shape[0], t.shape[1], t.stride(0)
+    tc = t.contiguous()
+    cols = tc.shape[-1]
+    return tc, math.prod(tc.shape[:-1]), cols, cols
+
+
+def quantize_rows(x: torch.Tensor, eps: float = ACT_EPS, fold_absmax: Optional[torch.Tensor] = None,
+                  raw_absmax: Optional[torch.Tensor] = None):
+    """Per-token absmax int8 quantisation.  Returns (q int8, absmax float32 [M]) and, when `fold_absmax` [M] is
+    given, also max_m(rawmax[m]*fold_absmax[m]/127) as a float32 [1] tensor.  `raw_absmax` [M] supplies row
+    maxima found elsewhere (reduced over the ranks of a column-sharded tensor); it is floored at eps in place
+    and returned as the absmax.  A 2-D column window `x[:, a:b]` is read in place."""
     _cuda(x, "x")
     _require(x.dtype in _DT and x.dtype != torch.int32, "x must be float16, bfloat16 or float32")
-    xc = x.contiguous()
-    K = xc.shape[-1]
-    M = math.prod(xc.shape[:-1])
-    q = torch.empty(xc.shape, dtype=torch.int8, device=x.device)
-    a = torch.empty(M, dtype=torch.float32, device=x.device)
+    xv, M, K, ld = _rows_view(x)
+    q = torch.empty(*x.shape[:-1], K, dtype=torch.int8, device=x.device)
+    if raw_absmax is None:
+        a = torch.empty(M, dtype=torch.float32, device=x.device)
+        mode = _lib.EL_QUANT_FULL
+    else:
+        _require(raw_absmax.dtype == torch.float32 and raw_absmax.numel() == M and raw_absmax.is_contiguous(),
+                 "raw_absmax must be a contiguous float32 [M]")
+        a = raw_absmax
+        mode = _lib.EL_QUANT_WITH_ABSMAX
     fold_max = None
     if fold_absmax is not None:
         _require(fold_absmax.dtype == torch.float32 and fold_absmax.numel() == M, "fold_absmax must be float32 [M]")
         fold_max = torch.zeros(1, dtype=torch.float32, device=x.device)
-    call("el_quantize_rows", xc.data_ptr(), _DT[xc.dtype], q.data_ptr(), a.data_ptr(), M, K, float(eps),
+    call("el_quantize_rows", xv.data_ptr(), _DT[xv.dtype], ld, q.data_ptr(), a.data_ptr(), M, K, float(eps), mode,
          _ptr(fold_absmax), _ptr(fold_max), _stream())
     return (q, a) if fold_absmax is None else (q, a, fold_max)
+
+
+def absmax_rows(x: torch.Tensor) -> torch.Tensor:
+    """Raw max |x[m,:]| per row (float32 [M]), without the eps floor: the first half of quantize_rows for a
+    column shard, to be max-reduced over ranks and passed back as `raw_absmax`."""
+    _cuda(x, "x")
+    _require(x.dtype in _DT and x.dtype != torch.int32, "x must be float16, bfloat16 or float32")
+    xv, M, K, ld = _rows_view(x)
+    a = torch.empty(M, dtype=torch.float32, device=x.device)
+    call("el_quantize_rows", xv.data_ptr(), _DT[xv.dtype], ld, None, a.data_ptr(), M, K, 1.0, _lib.EL_QUANT_ABSMAX_ONLY,
+         None, None, _stream())
+    return a
+
+
+def scale_rows(acc: torch.Tensor, row_absmax: torch.Tensor, gamma: float, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """out = acc * (row_absmax[m]/127) * gamma for int32 sums [M,C] (the GEMM epilogue as its own pass)."""
+    _cuda(acc, "acc")
+    _require(acc.dtype == torch.int32 and acc.dim() == 2 and acc.is_contiguous(), "acc must be a contiguous int32 [M,C]")
+    M, C = acc.shape
+    stride = 0 if row_absmax.numel() == 1 else 1
+    _require(stride == 0 or row_absmax.numel() == M, "one absmax per row expected")
+    out = torch.empty(M, C, dtype=out_dtype, device=acc.device)
+    call("el_scale_rows", acc.data_ptr(), out.data_ptr(), _DT[out_dtype], row_absmax.data_ptr(), stride, float(gamma), M, C,
+         _stream())
+    return out
 
 
 def matmul_rows(Xq: torch.Tensor, W_packed: torch.Tensor, row_absmax: torch.Tensor, gamma: float,
@@ -255,15 +298,14 @@ def backward_input_rows(dYq: torch.Tensor, W_packed: torch.Tensor, row_absmax: t
 
 
 def quantize_grad(dY: torch.Tensor, x_absmax: torch.Tensor, g_absmax: torch.Tensor) -> torch.Tensor:
-    """Gq = int8 of (dY * x_absmax[m]/127) under the per-tensor maximum g_absmax[1]."""
+    """Gq = int8 of (dY * x_absmax[m]/127) under the per-tensor maximum g_absmax[1]; a 2-D column window of a
+    wider dY is read in place."""
     _cuda(dY, "dY")
-    yc = dY.contiguous()
-    N = yc.shape[-1]
-    M = math.prod(yc.shape[:-1])
+    yv, M, N, ld = _rows_view(dY)
     _require(x_absmax.dtype == torch.float32 and x_absmax.numel() == M, "x_absmax must be float32 [M]")
     _require(g_absmax.dtype == torch.float32 and g_absmax.numel() == 1, "g_absmax must be float32 [1]")
-    Gq = torch.empty(yc.shape, dtype=torch.int8, device=dY.device)
-    call("el_quantize_grad", yc.data_ptr(), _DT[yc.dtype], x_absmax.data_ptr(), g_absmax.data_ptr(), Gq.data_ptr(), M, N,
+    Gq = torch.empty(*dY.shape[:-1], N, dtype=torch.int8, device=dY.device)
+    call("el_quantize_grad", yv.data_ptr(), _DT[yv.dtype], ld, x_absmax.data_ptr(), g_absmax.data_ptr(), Gq.data_ptr(), M, N,
          _stream())
     return Gq
 

@@ -1,0 +1,164 @@
+"""INT2 linear layer sharded along N (output features) over the GPUs of one node.
+
+Rank r of g owns rows [r*N/g, (r+1)*N/g) of `W_packed` / `H_packed`; activations are replicated (every rank
+sees all M tokens).  The reference has no multi-GPU code; this is the sharding its layer admits:
+
+  forward   local Y_r[M, N/g] = Q(X) . W_r^T, then one all-gather -> Y[M, N]
+  dX        local int32 partial sums dYq[:, shard] . W_r, summed over ranks (exact: integer addition is
+            associative, so the result is bit-identical to one GPU), then scaled once
+  dW        local to the shard: no communication; the per-weight random-number counter uses the global
+            row index, so the flips equal those of the unsharded layer
+  scales    a token's absmax of dY spans all N columns: each rank reduces its column window and a max
+            all-reduce of M floats completes it
+
+Collectives go through torch.distributed (NCCL over NVLink on GPUs; gloo in the CPU tests, where a stand-in
+for the operator module is injected).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+from torch.autograd import Function
+
+from .int2_tc_ops import ACT_EPS, GRAD_EPS
+
+_FLOAT_IO = (torch.float16, torch.bfloat16, torch.float32)
+
+
+def shard_rows(n_total: int, world: int, rank: int):
+    """[start, stop) of the rows rank `rank` owns; N must divide evenly (and by 16 per shard for the
+    tensor-core kernels to take the shard)."""
+    if n_total % world != 0:
+        raise ValueError(f"out_features={n_total} is not divisible by the group size {world}")
+    per = n_total // world
+    return rank * per, (rank + 1) * per
+
+
+class _ShardedLinearFn(Function):
+    @staticmethod
+    def forward(ctx, x: torch.Tensor, gamma: torch.Tensor, layer: "ShardedInt2Linear") -> torch.Tensor:
+        ops, grp = layer.ops, layer.group
+        K, Nl, g = layer.in_features, layer.local_out_features, layer.world
+        io = x.dtype if x.dtype in _FLOAT_IO else torch.bfloat16
+        x2 = x.reshape(-1, K)
+        Xq, ax = ops.quantize_rows(x2 if x2.dtype in _FLOAT_IO else x2.to(io), ACT_EPS)
+        y_local = ops.matmul_rows(Xq, layer.W_packed, ax, layer.gamma_value(), io)
+        M = x2.shape[0]
+        if g > 1:
+            gathered = torch.empty(g * M, Nl, dtype=io, device=x.device)     # rank-major concatenation
+            dist.all_gather_into_tensor(gathered, y_local.contiguous(), group=grp)
+            y = gathered.view(g, M, Nl).permute(1, 0, 2).reshape(M, g * Nl)
+        else:
+            y = y_local
+        ctx.layer, ctx.io, ctx.x_shape = layer, io, x.shape
+        ctx.saved = (Xq, ax) if layer.training else None
+        return y.view(*x.shape[:-1], g * Nl)
+
+    @staticmethod
+    def backward(ctx, dY: torch.Tensor):
+        layer = ctx.layer
+        ops, grp = layer.ops, layer.group
+        K, Nl, g, r = layer.in_features, layer.local_out_features, layer.world, layer.rank
+        dY2 = dY.reshape(-1, g * Nl)
+        if dY2.dtype not in _FLOAT_IO:
+            dY2 = dY2.to(ctx.io)
+        window = dY2[:, r * Nl:(r + 1) * Nl]                # this rank's columns, read in place
+        raw = ops.absmax_rows(window)
+        if g > 1:
+            dist.all_reduce(raw, op=dist.ReduceOp.MAX, group=grp)
+        do_update = layer.training and layer.hysteresis_enabled and ctx.saved is not None
+        if do_update:
+            Xq, ax = ctx.saved
+            dYq, ady, gmax = ops.quantize_rows(window, GRAD_EPS, fold_absmax=ax, raw_absmax=raw)
+        else:
+            dYq, ady = ops.quantize_rows(window, GRAD_EPS, raw_absmax=raw)
+
+        def update():
+            layer._step_py += 1
+            Gq = ops.quantize_grad(window, ax, gmax)
+            idx_base = layer.row_start * K
+            if ops.dw_hysteresis_supported(Nl, K):
+                ops.dw_hysteresis(Gq, Xq, gmax, layer.W_packed, layer.H_packed, layer._lr, layer.lr_scale, layer.threshold,
+                                  layer.decay_rate, layer._step_py, idx_base)
+            else:
+                dW = ops.weight_grad(Gq, Xq, gmax)
+                ops.hysteresis_step_v2(dW, layer.W_packed, layer.H_packed, layer._lr, layer.lr_scale, layer.threshold,
+                                       layer.decay_rate, layer._step_py, idx_base)
+
+        if do_update and layer.hysteresis_order == "reference":
+            update()                                        # as the reference's hook: before dX
+        dX = None
+        if ctx.needs_input_grad[0]:
+            gam = layer.gamma_value()
+            if g > 1:
+                acc = ops.backward_input_rows(dYq, layer.W_packed, ady, gam, K, torch.int32)
+                dist.all_reduce(acc, op=dist.ReduceOp.SUM, group=grp)
+                dX = ops.scale_rows(acc, ady, gam, ctx.io)
+            else:
+                dX = ops.backward_input_rows(dYq, layer.W_packed, ady, gam, K, ctx.io)
+            dX = dX.view(ctx.x_shape)
+        if do_update and layer.hysteresis_order != "reference":
+            update()
+        return dX, None, None
+
+
+class ShardedInt2Linear(nn.Module):
+    """One N-shard of an INT2 linear layer.  State names follow Int2LinearTC (`W_packed`, `H_packed`, `gamma`,
+    `_step`) with the shard's row count; `ops` is the operator module (the CUDA one by default)."""
+
+    def __init__(self, in_features: int, out_features: int, group: Optional[dist.ProcessGroup] = None, threshold: int = 7,
+                 lr_scale: float = 5.0, decay_rate: float = 0.001, hysteresis_order: str = "reference", ops=None):
+        super().__init__()
+        if ops is None:
+            from . import int2_tc_ops as ops_mod
+            ops = ops_mod
+        self.ops = ops
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.in_features = in_features
+        self.out_features = out_features
+        self.row_start, self.row_stop = shard_rows(out_features, self.world, self.rank)
+        self.local_out_features = self.row_stop - self.row_start
+        self.threshold, self.lr_scale, self.decay_rate = threshold, lr_scale, decay_rate
+        self.hysteresis_order = hysteresis_order
+        self.hysteresis_enabled = True
+        self._lr = 0.001
+        self._step_py = 0
+        self._gamma_cached: Optional[float] = None
+        self.register_buffer("W_packed", torch.zeros(self.local_out_features, (in_features + 3) // 4, dtype=torch.uint8))
+        self.register_buffer("H_packed", torch.zeros(self.local_out_features, (in_features + 1) // 2, dtype=torch.uint8))
+        self.gamma = nn.Parameter(torch.ones(1))
+        self.register_buffer("_step", torch.tensor(0, dtype=torch.int64))
+
+    def set_lr(self, lr: float):
+        self._lr = lr
+
+    def gamma_value(self) -> float:
+        if self._gamma_cached is None:
+            self._gamma_cached = self.gamma.detach().item()
+        return self._gamma_cached
+
+    def init_from_float(self, weight_full: torch.Tensor, scale: Optional[float] = None):
+        """Ternarises this rank's rows of the full [N,K] weight with the scale of the WHOLE matrix."""
+        assert weight_full.shape == (self.out_features, self.in_features)
+        if scale is None:
+            scale = max(weight_full.abs().mean().item(), 1e-5)
+        rows = weight_full[self.row_start:self.row_stop].to(self.W_packed.device)
+        self.W_packed.copy_(self.ops.ternarize_pack(rows, scale))
+        self.gamma.data.fill_(scale)
+        self._gamma_cached = scale
+        self.H_packed.zero_()
+
+    def load_shard(self, W_packed_full: torch.Tensor, H_packed_full: torch.Tensor, gamma: float):
+        """Takes this rank's rows out of an unsharded layer's state."""
+        self.W_packed.copy_(W_packed_full[self.row_start:self.row_stop])
+        self.H_packed.copy_(H_packed_full[self.row_start:self.row_stop])
+        self.gamma.data.fill_(gamma)
+        self._gamma_cached = float(gamma)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return _ShardedLinearFn.apply(x, self.gamma, self)

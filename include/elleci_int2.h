@@ -85,12 +85,21 @@ EL_API int el_unpack_ternary(const uint8_t* W_packed, void* out, int out_dtype, 
 /* ---- activation quantisation ------------------------------------------------------------------------ */
 
 /* Per-token absmax int8 quantisation: a[m] = max(max_k |x[m,k]|, eps), q = clamp(rint(x*(127/a)), -128, 127);
- * non-finite inputs count as 0.  x_dtype EL_F16 / EL_BF16 / EL_F32.  Replaces BitLinear.activation_quant
- * (model/common/bitnet_legacy.py:58-87), in integer form.
- * Optional gradient folding (both NULL to disable): with fold_absmax[M] given, fold_max[1] receives, by an
- * atomic max, max_m(a[m] * (fold_absmax[m]/127)); the caller zeroes fold_max first. */
-EL_API int el_quantize_rows(const void* x, int x_dtype, int8_t* q, float* row_absmax, int M, int K, float eps,
-                     const float* fold_absmax, float* fold_max, el_stream_t stream);
+ * non-finite inputs count as 0.  x_dtype EL_F16 / EL_BF16 / EL_F32; ldx is the row pitch of x in elements
+ * (>= K: a column window of a wider matrix needs no copy); q is dense [M,K].  Replaces
+ * BitLinear.activation_quant (model/common/bitnet_legacy.py:58-87), in integer form.
+ * mode EL_QUANT_FULL        one pass: row_absmax[m] receives a[m], q the int8 row.
+ *      EL_QUANT_ABSMAX_ONLY row_absmax[m] receives the raw max |x[m,:]| (no floor); q is not touched.  A rank that
+ *                           holds a column shard reduces these over ranks (max) before quantising.
+ *      EL_QUANT_WITH_ABSMAX row_absmax[m] holds the raw maximum on entry (as written by ABSMAX_ONLY, possibly
+ *                           reduced over ranks); it is floored at eps in place and the row is quantised with it.
+ * Optional gradient folding (both NULL to disable; not with ABSMAX_ONLY): with fold_absmax[M] given, fold_max[1]
+ * receives, by an atomic max, max_m(rawmax[m] * (fold_absmax[m]/127)); the caller zeroes fold_max first. */
+#define EL_QUANT_FULL        0
+#define EL_QUANT_ABSMAX_ONLY 1
+#define EL_QUANT_WITH_ABSMAX 2
+EL_API int el_quantize_rows(const void* x, int x_dtype, long long ldx, int8_t* q, float* row_absmax, int M, int K,
+                            float eps, int mode, const float* fold_absmax, float* fold_max, el_stream_t stream);
 
 /* Per-tensor absmax int8 quantisation: absmax[0] = max finite |x| (the call zeroes it first),
  * q = clamp(roundf(x * (absmax > 1e-8 ? 127/absmax : 0)), -127, 127).  Replaces quantize_activation_async
@@ -105,10 +114,17 @@ EL_API int el_dequantize_tensor(const int8_t* q, const float* absmax, void* out,
 
 /* Gq[m,n] = clamp(rint((dY[m,n] * (x_absmax[m]/127)) * inv), -127, 127), inv = g >= 1e-30 ? 127/g : 0,
  * g = g_absmax[0] (from el_quantize_rows' fold_max).  The per-token activation scale folded into the output
- * gradient makes the weight gradient an exact integer GEMM.  No counterpart in the reference, which forms dW
- * with a library fp16 GEMM (core/bitnet/int2_linear_tc.py:525-537). */
-EL_API int el_quantize_grad(const void* dY, int dy_dtype, const float* x_absmax, const float* g_absmax, int8_t* Gq,
-                     int M, int N, el_stream_t stream);
+ * gradient makes the weight gradient an exact integer GEMM.  ld_dy is the row pitch of dY in elements; Gq is
+ * dense [M,N].  No counterpart in the reference, which forms dW with a library fp16 GEMM
+ * (core/bitnet/int2_linear_tc.py:525-537). */
+EL_API int el_quantize_grad(const void* dY, int dy_dtype, long long ld_dy, const float* x_absmax, const float* g_absmax,
+                            int8_t* Gq, int M, int N, el_stream_t stream);
+
+/* out[m,c] = out_dtype( float(acc[m,c]) * ((absmax[m*absmax_stride]/127) * gamma) ): the GEMM epilogue as a
+ * stand-alone pass, for int32 sums that were reduced over ranks first (dX of an N-sharded layer).  The reference
+ * has no multi-GPU path; the arithmetic is that of its GEMM epilogue (int2_backward_int8_tc_v2.cu:88-92,233). */
+EL_API int el_scale_rows(const int32_t* acc, void* out, int out_dtype, const float* absmax, int absmax_stride,
+                         float gamma, int M, int C, el_stream_t stream);
 
 /* ---- GEMMs ------------------------------------------------------------------------------------------- */
 
