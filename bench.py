@@ -410,16 +410,76 @@ def run_ours(args, wl):
         dist.destroy_process_group()
 
 
+def run_decode(args):
+    """config3: the small-M layer call at decode shapes, measured against the HBM roofline.  Sixteen distinct weight
+    buffers (180 MB, more than L2) are rotated inside one CUDA graph so that every call streams its weights from
+    HBM; time per call = graph time / 16, CUDA events around the replays."""
+    import torch
+    pkg = load_package()
+    ops = pkg.int2_tc_ops
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    peaks, peak_kind = measured_peaks()
+    cases = []
+    nbuf = 16
+    for (K, N) in [(4096, 11008), (11008, 4096)]:
+        gen = torch.Generator().manual_seed(K)
+        Ws = [torch.randint(0, 256, (N, K // 4), generator=gen, dtype=torch.uint8).to(dev) for _ in range(nbuf)]
+        for M in (1, 8, 32, 64):
+            x = torch.randn(M, K, generator=gen).to(torch.bfloat16).to(dev)
+            for W in Ws[:3]:
+                ops.linear_decode(x, W, 0.016)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                for W in Ws:
+                    y = ops.linear_decode(x, W, 0.016)
+            for _ in range(3):
+                graph.replay()
+            torch.cuda.synchronize()
+            reps = max(args.steps, 10)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / (reps * nbuf)
+            nbytes = N * K // 4 + 2 * M * K + 2 * M * N
+            gbs = nbytes / (us * 1e-6) / 1e9
+            cases.append({"M": M, "K": K, "N": N, "us_per_call": us, "GBps": gbs, "frac_of_hbm": gbs / peaks["hbm_gbs"],
+                          "algorithmic_bytes": nbytes})
+        ops.check_device_status(dev)
+        del Ws
+    head = next(c for c in cases if c["M"] == 8 and c["K"] == 4096)
+    line = {
+        "metric": "decode linear call (quantise + packed-weight GEMV), GB/s of algorithmic bytes", "value": head["GBps"],
+        "unit": "GB/s", "n_gpus": 1, "steps": max(args.steps, 10), "warmup": 3, "ms_per_step": head["us_per_call"] * 1e-3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8 x int2 -> int32 (bf16 in/out)",
+        "data": "synthetic",
+        "config": {"workload": "config3: decode shapes, M in {1,8,32,64}, 4096->11008 and 11008->4096; 16 rotating weight "
+                               "buffers (> L2) in one CUDA graph; each call = quantiser launch + GEMV launch"},
+        "roofline": {"bound": "hbm", "achieved": head["GBps"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": head["GBps"] / peaks["hbm_gbs"], "traffic": None, "peak_source": f"hbm_gbs ({peak_kind})"},
+        "cases": cases, "gpu_launches": 2 * nbuf * max(args.steps, 10),
+    }
+    print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="config2", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="config2", choices=sorted(WORKLOADS) + ["config3"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg of the default run")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
     args = ap.parse_args()
+    if args.workload == "config3":
+        if args.impl == "ours" and int(os.environ.get("RANK", "0")) == 0:
+            run_decode(args)
+        return
     wl = WORKLOADS[args.workload]
     if args.impl == "reference":
         run_reference(args, wl)

@@ -36,6 +36,8 @@ SIGNATURES = {
     "el_gemm_fwd": [_vp, _vp, _vp, _i, _vp, _i, _f, _i, _i, _i, _i, _vp, _vp],
     "el_gemm_dx": [_vp, _vp, _vp, _i, _vp, _i, _f, _i, _i, _i, _i, _vp, _vp],
     "el_gemm_dw": [_vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp, _vp],
+    "el_decode_workspace_bytes": [_i],
+    "el_linear_decode": [_vp, _i, _vp, _vp, _i, _f, _vp, _vp, _vp, C.c_size_t, _i, _i, _i, _vp, _vp],
     "el_hysteresis_from_dw": [_vp, _vp, _vp, _f, _f, _i, _f, _i, _i, _i, _u32, _i, _vp],
     "el_dw_hysteresis": [_vp, _vp, _vp, _vp, _vp, _f, _f, _i, _f, _i, _u32, _i, _i, _i, _vp, _vp],
 }
@@ -64,7 +66,8 @@ def lib() -> C.CDLL:
         for name, argtypes in SIGNATURES.items():
             fn = getattr(handle, name)
             fn.argtypes = argtypes
-            fn.restype = C.c_char_p if name == "el_status_string" else C.c_int
+            fn.restype = (C.c_char_p if name == "el_status_string" else
+                          C.c_size_t if name == "el_decode_workspace_bytes" else C.c_int)
         _lib = handle
     return _lib
 

@@ -26,6 +26,12 @@ int launch_gemm_tc(int mode, const int8_t* A, const void* B, int R, int C, int D
 int launch_dw_hysteresis_tc(const int8_t* Gq, const int8_t* Xq, const float* g_absmax, uint8_t* Wp, uint8_t* Hp,
                             const HystParams& hp, uint32_t idx_base, int M, int N, int K, int32_t* status, cudaStream_t st);
 
+int launch_quantize_rows_perm(const void* x, int dt, long long ldx, int8_t* q, float* a, int M, int K, float eps,
+                              cudaStream_t st);
+size_t decode_workspace_bytes(int N);
+int launch_decode_tc(const int8_t* Xq, const uint8_t* Wp, const EpiParams& epi, void* workspace, int M, int N, int K,
+                     int32_t* status, cudaStream_t st);
+
 static thread_local int g_last_cuda_error = 0;
 
 int record_cuda_error(cudaError_t e) {
@@ -220,6 +226,22 @@ int el_dw_hysteresis(const int8_t* Gq, const int8_t* Xq, const float* g_absmax, 
     const HystParams hp = make_hyst_params(lr, lr_scale, threshold, decay_rate, (uint32_t)step, 1);
     return launch_dw_hysteresis_tc(Gq, Xq, g_absmax, W_packed, H_packed, hp, idx_base, M, N, K, dev_status,
                                    (cudaStream_t)stream);
+}
+
+size_t el_decode_workspace_bytes(int N) { return N > 0 ? decode_workspace_bytes(N) : 0; }
+
+int el_linear_decode(const void* x, int x_dtype, const uint8_t* W_packed, void* Y, int out_dtype, float gamma,
+                     int8_t* xq_scratch, float* absmax, void* workspace, size_t workspace_bytes, int M, int N, int K,
+                     int32_t* dev_status, el_stream_t stream) {
+    if (M < 0 || N < 0 || K < 0 || !float_dtype(x_dtype) || !float_dtype(out_dtype)) return EL_ERR_INVALID_ARG;
+    if (M == 0 || N == 0) return EL_OK;
+    if (M > 64 || K == 0 || K % 64 != 0) return EL_ERR_UNSUPPORTED_SHAPE;
+    if (!x || !W_packed || !Y || !xq_scratch || !absmax || !workspace) return EL_ERR_NULL_PTR;
+    if (workspace_bytes < decode_workspace_bytes(N)) return EL_ERR_INVALID_ARG;
+    int rc = launch_quantize_rows_perm(x, x_dtype, K, xq_scratch, absmax, M, K, 1e-5f, (cudaStream_t)stream);
+    if (rc != EL_OK) return rc;
+    const EpiParams epi{Y, (long long)N, out_dtype, absmax, 1, gamma};
+    return launch_decode_tc(xq_scratch, W_packed, epi, workspace, M, N, K, dev_status, (cudaStream_t)stream);
 }
 
 }  // extern "C"

@@ -172,6 +172,42 @@ quantize_rows_kernel(const T* __restrict__ x, long long ldx, int8_t* __restrict_
     }
 }
 
+// Per-token quantisation whose int8 output is permuted inside every group of 16 reduction indices (even indices
+// first, then odd): the operand layout that matches decode16_deint.  One CTA per row; K % 16 == 0.
+template <typename T>
+__global__ void __launch_bounds__(256)
+quantize_rows_perm_kernel(const T* __restrict__ x, long long ldx, int8_t* __restrict__ q, float* __restrict__ row_absmax,
+                          int K, float eps) {
+    __shared__ float red[8];
+    const int m = blockIdx.x;
+    const T* xr = x + (size_t)m * ldx;
+    int8_t* qr = q + (size_t)m * K;
+    float amax = 0.0f;
+    for (int k = threadIdx.x * 16; k < K; k += blockDim.x * 16) {
+        float v[16];
+        load8<T>(xr + k, v);
+        load8<T>(xr + k + 8, v + 8);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(finite_or_zero(v[i])));
+    }
+    amax = block_max(amax, red);
+    const float a = fmaxf(amax, eps);
+    const float s = __fdiv_rn(127.0f, a);
+    if (threadIdx.x == 0) row_absmax[m] = a;
+    for (int k = threadIdx.x * 16; k < K; k += blockDim.x * 16) {
+        float v[16];
+        load8<T>(xr + k, v);
+        load8<T>(xr + k + 8, v + 8);
+        uint32_t w[4] = {0, 0, 0, 0};
+#pragma unroll
+        for (int p = 0; p < 16; ++p) {
+            const int src = (p < 8) ? 2 * p : 2 * (p - 8) + 1;
+            w[p >> 2] |= (uint32_t)(quant_half_even(finite_or_zero(v[src]), s) & 0xFF) << (8 * (p & 3));
+        }
+        *reinterpret_cast<uint4*>(qr + k) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+
 // ---------------------------------------------------------------------------------------------------------
 // per-tensor quantisation (the reference CUDA path's rule)
 // ---------------------------------------------------------------------------------------------------------
@@ -305,6 +341,20 @@ int launch_quantize_rows(const void* x, int dt, long long ldx, int8_t* q, float*
         case EL_F32: return launch_quantize_rows_t((const float*)x, ldx, q, a, M, K, eps, mode, fold_absmax, fold_max, st);
         default: return EL_ERR_INVALID_ARG;
     }
+}
+
+int launch_quantize_rows_perm(const void* x, int dt, long long ldx, int8_t* q, float* a, int M, int K, float eps,
+                              cudaStream_t st) {
+    if (M == 0) return EL_OK;
+    if (K % 16 != 0 || ldx % 8 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(q) & 15))
+        return EL_ERR_ALIGNMENT;
+    switch (dt) {
+        case EL_F16: quantize_rows_perm_kernel<__half><<<M, 256, 0, st>>>((const __half*)x, ldx, q, a, K, eps); break;
+        case EL_BF16: quantize_rows_perm_kernel<__nv_bfloat16><<<M, 256, 0, st>>>((const __nv_bfloat16*)x, ldx, q, a, K, eps); break;
+        case EL_F32: quantize_rows_perm_kernel<float><<<M, 256, 0, st>>>((const float*)x, ldx, q, a, K, eps); break;
+        default: return EL_ERR_INVALID_ARG;
+    }
+    return check_launch();
 }
 
 template <typename T>

@@ -353,3 +353,40 @@ def dw_hysteresis(Gq: torch.Tensor, Xq: torch.Tensor, g_absmax: torch.Tensor, W_
          float(lr), float(lr_scale), int(threshold), float(decay), step_i, int(idx_base) & 0xFFFFFFFF, M, N, K,
          st.data_ptr(), _stream())
     _maybe_check(Gq.device)
+
+
+_decode_ws: dict = {}
+
+
+def linear_decode(x: torch.Tensor, W_packed: torch.Tensor, gamma: float, out_dtype: Optional[torch.dtype] = None,
+                  workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Small-M layer call (1 <= M <= 64 tokens): per-token quantisation + the weight-streaming tensor-core kernel.
+    Same integers and rounding as quantize_rows + matmul_rows.  `workspace` (uint8, zero before first use, left
+    zero) defaults to a cached per-device, per-N buffer; calls sharing it must be stream-ordered."""
+    _cuda(x, "x"); _cuda(W_packed, "W_packed")
+    _require(x.dtype in (torch.float16, torch.bfloat16, torch.float32), "x must be float16, bfloat16 or float32")
+    _require(W_packed.dtype == torch.uint8 and W_packed.dim() == 2, "W_packed must be uint8 [N, ceil(K/4)]")
+    N, pK = W_packed.shape
+    K = x.shape[-1]
+    _require((K + 3) // 4 == pK, f"x has {K} features but W_packed has packed_K={pK}")
+    xc = x.contiguous().view(-1, K)
+    M = xc.shape[0]
+    _require(1 <= M <= 64, "linear_decode takes 1..64 tokens; use quantize_rows + matmul_rows beyond that")
+    out_dtype = out_dtype or x.dtype
+    need = _lib.lib().el_decode_workspace_bytes(N)
+    if workspace is None:
+        key = (x.device.index, N)
+        workspace = _decode_ws.get(key)
+        if workspace is None:
+            workspace = torch.zeros(need, dtype=torch.uint8, device=x.device)
+            _decode_ws[key] = workspace
+    _require(workspace.is_cuda and workspace.numel() * workspace.element_size() >= need, "workspace too small")
+    xq = torch.empty(M, K, dtype=torch.int8, device=x.device)
+    a = torch.empty(M, dtype=torch.float32, device=x.device)
+    Y = torch.empty(M, N, dtype=out_dtype, device=x.device)
+    st = device_status(x.device)
+    call("el_linear_decode", xc.data_ptr(), _DT[xc.dtype], W_packed.contiguous().data_ptr(), Y.data_ptr(), _DT[out_dtype],
+         float(gamma), xq.data_ptr(), a.data_ptr(), workspace.data_ptr(), workspace.numel() * workspace.element_size(),
+         M, N, K, st.data_ptr(), _stream())
+    _maybe_check(x.device)
+    return Y.view(*x.shape[:-1], N)

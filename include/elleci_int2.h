@@ -168,6 +168,22 @@ EL_API int el_dw_hysteresis(const int8_t* Gq, const int8_t* Xq, const float* g_a
                      uint8_t* H_packed, float lr, float lr_scale, int threshold, float decay_rate, int step,
                      uint32_t idx_base, int M, int N, int K, int32_t* dev_status, el_stream_t stream);
 
+/* ---- small-M ("decode") layer -------------------------------------------------------------------------------- */
+
+/* Y[m,n] = out_dtype( float(sum_k Q(x)[m,k]*Wq[n,k]) * ((absmax[m]/127) * gamma) ) for 1 <= M <= 64 tokens: per-token
+ * quantisation of x followed by a weight-streaming tensor-core kernel (operands swapped, stream-K over all SMs), the
+ * same integers and the same rounding as el_quantize_rows + el_gemm_fwd.  Needs K % 64 == 0 and 16-byte aligned x,
+ * W_packed, xq_scratch and workspace.  Caller-owned scratch: xq_scratch int8 [M,K] and absmax float [M] (overwritten),
+ * and `workspace` of el_decode_workspace_bytes(N) bytes, which must be all zero before its first use and is left
+ * all zero by every call (partial sums of weight tiles that span several SMs meet there); calls that share a
+ * workspace must not overlap on the GPU.  Replaces the scalar kernel the reference falls back to when M < 64
+ * (int2_matmul_int8_tc_v2_simple_kernel, kernels/int2/int2_matmul_int8_tc_v2.cu:452-473, dispatch :511-536), the
+ * path of Elleci.generate (model/model.py:505-623). */
+EL_API size_t el_decode_workspace_bytes(int N);
+EL_API int el_linear_decode(const void* x, int x_dtype, const uint8_t* W_packed, void* Y, int out_dtype, float gamma,
+                            int8_t* xq_scratch, float* absmax, void* workspace, size_t workspace_bytes, int M, int N,
+                            int K, int32_t* dev_status, el_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -254,3 +254,34 @@ def test_fused_dw_hysteresis_bit_exact(ops, M, N, K, thr):
     Wo, Ho = native.c_hysteresis_step(dW, Wp, Hp, 1e-2, 5.0, thr, 0.01, 3, K, idx_base=1000)
     assert np.array_equal(W.cpu().numpy(), Wo) and np.array_equal(H.cpu().numpy(), Ho)
     assert (O.unpack_ternary(Wo, K) != O.unpack_ternary(Wp, K)).mean() > 0.01      # the case does flip weights
+
+
+# ---- small-M decode path -------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("M", [1, 3, 8, 17, 32, 64])
+@pytest.mark.parametrize("K,N", [(4096, 11008), (11008, 4096), (256, 384), (192, 100)])
+def test_linear_decode_bit_exact(ops, M, K, N):
+    """The weight-streaming small-M kernel gives the integers and the rounding of quantize_rows + the forward GEMM;
+    run twice on one workspace to show that a call leaves the workspace clean."""
+    g = torch.Generator().manual_seed(M + K + N)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    Wp, _ = random_packed(N, K, seed=K + N)
+    gamma = 0.0161
+    Xq, ax = O.quantize_rows(t2n(x))
+    want = O.to_bf16(O.scale_rows(O.gemm_fwd_acc(Xq, Wp, K), ax, gamma))
+    ws = torch.zeros(ops._lib.lib().el_decode_workspace_bytes(N), dtype=torch.uint8, device=DEV)
+    Wd = _cuda(Wp)
+    for _ in range(2):
+        y = ops.linear_decode(x.to(DEV), Wd, gamma, workspace=ws)
+        assert np.array_equal(t2n(y), want)
+    assert int(ws.view(torch.int32).abs().sum().item()) == 0
+    ops.check_device_status(torch.device(DEV))
+
+
+def test_linear_decode_rejects_what_it_cannot_run(ops, pkg):
+    Wp = torch.zeros(64, 25, dtype=torch.uint8, device=DEV)
+    with pytest.raises(RuntimeError):
+        ops.linear_decode(torch.zeros(65, 100, dtype=torch.bfloat16, device=DEV), Wp, 1.0)       # more than 64 tokens
+    with pytest.raises(pkg.ElleciError) as e:
+        ops.linear_decode(torch.zeros(4, 100, dtype=torch.bfloat16, device=DEV), Wp, 1.0)        # K % 64 != 0
+    assert e.value.status == pkg._lib.EL_ERR_UNSUPPORTED_SHAPE
