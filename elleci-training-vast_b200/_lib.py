@@ -13,7 +13,7 @@ LIB_PATH = os.path.join(_HERE, "lib", "libelleci_int2.so")
 
 EL_OK = 0
 EL_ERR_INVALID_ARG, EL_ERR_NULL_PTR, EL_ERR_ALIGNMENT, EL_ERR_UNSUPPORTED_SHAPE = -1, -2, -3, -4
-EL_ERR_CUDA, EL_ERR_DEVICE, EL_ERR_DRIVER = -5, -6, -7
+EL_ERR_CUDA, EL_ERR_DEVICE, EL_ERR_DRIVER, EL_ERR_TOO_LARGE = -5, -6, -7, -8
 EL_F16, EL_BF16, EL_F32, EL_I32 = 0, 1, 2, 3
 EL_PATH_AUTO, EL_PATH_SIMPLE, EL_PATH_TC = 0, 1, 2
 EL_QUANT_FULL, EL_QUANT_ABSMAX_ONLY, EL_QUANT_WITH_ABSMAX = 0, 1, 2
@@ -38,6 +38,7 @@ SIGNATURES = {
     "el_gemm_dw": [_vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp, _vp],
     "el_decode_workspace_bytes": [_i],
     "el_linear_decode": [_vp, _i, _vp, _vp, _i, _f, _vp, _vp, _vp, C.c_size_t, _i, _i, _i, _vp, _vp],
+    "el_linear_decode_static": [_vp, _i, _vp, _vp, _i, _f, _i, _i, _i, _vp, _vp],
     "el_hysteresis_from_dw": [_vp, _vp, _vp, _f, _f, _i, _f, _i, _i, _i, _u32, _i, _vp],
     "el_dw_hysteresis": [_vp, _vp, _vp, _vp, _vp, _f, _f, _i, _f, _i, _u32, _i, _i, _i, _vp, _vp],
 }

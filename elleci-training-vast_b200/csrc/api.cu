@@ -112,6 +112,7 @@ const char* el_status_string(int s) {
         case EL_ERR_CUDA: return "CUDA runtime error";
         case EL_ERR_DEVICE: return "device is not sm_100";
         case EL_ERR_DRIVER: return "tensor-map descriptor rejected by the driver";
+        case EL_ERR_TOO_LARGE: return "size exceeds the fixed capacity of this entry point (static scratch: M<=64, N<=16384, K<=16384)";
         default: return "unknown status";
     }
 }

@@ -309,4 +309,71 @@ int launch_decode_tc(const int8_t* Xq, const uint8_t* Wp, const EpiParams& epi, 
     }
 }
 
+// ---- decode call that allocates nothing ------------------------------------------------------------------------------
+//
+// Some hosts of this library cannot hand it device memory: an inference server whose plug-ins are forbidden to call
+// cudaMalloc once serving has started, a runtime that owns the whole memory pool, a process already at its memory
+// budget.  el_linear_decode needs three scratch buffers from its caller; this variant keeps them in one array that
+// is part of the loaded library image, so the caller passes only the input, the weights and the output.
+
+constexpr int STATIC_MAX_TOKENS = 64;
+constexpr int STATIC_MAX_N = 16384;       // largest out_features
+constexpr int STATIC_MAX_K = 16384;       // largest in_features
+constexpr size_t STATIC_WS_BYTES = ((size_t)64 * STATIC_MAX_N + 4 * (size_t)(STATIC_MAX_N / dec::TILE_N)) * sizeof(int);
+constexpr size_t STATIC_XQ_OFFSET = (STATIC_WS_BYTES + 255) & ~(size_t)255;
+constexpr size_t STATIC_XQ_BYTES = (size_t)STATIC_MAX_TOKENS * STATIC_MAX_K;
+constexpr size_t STATIC_ABSMAX_OFFSET = STATIC_XQ_OFFSET + STATIC_XQ_BYTES;
+constexpr size_t STATIC_TOTAL_BYTES = STATIC_ABSMAX_OFFSET + 256;          // about 5.3 MB per device
+
+// Lives in every GPU that loads the library, until the process exits.  In host code this name is only a handle for
+// cudaGetSymbolAddress; it is not a device address and must never be passed to a kernel as one.
+static __device__ __align__(256) unsigned char g_decode_scratch[STATIC_TOTAL_BYTES];
+
+static void* g_decode_scratch_ptr[64];    // device address of the array, per device ordinal (filled at set-up)
+
+// Set-up for the current device: resolves the array's device address once.  Not an allocation.
+static int decode_static_setup(unsigned char** out) {
+    int dev = 0;
+    EL_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return EL_ERR_DEVICE;
+    if (g_decode_scratch_ptr[dev] == nullptr) {
+        void* ptr = nullptr;
+        EL_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_decode_scratch));
+        if (ptr == nullptr) return EL_ERR_DEVICE;
+        g_decode_scratch_ptr[dev] = ptr;
+    }
+    *out = static_cast<unsigned char*>(g_decode_scratch_ptr[dev]);
+    return EL_OK;
+}
+
+int launch_quantize_rows_perm(const void* x, int dt, long long ldx, int8_t* q, float* a, int M, int K, float eps,
+                              cudaStream_t st);
+
 }  // namespace el
+
+extern "C" EL_API int el_linear_decode_static(const void* x, int x_dtype, const uint8_t* W_packed, void* Y, int out_dtype,
+                                              float gamma, int M, int N, int K, int32_t* dev_status, el_stream_t stream) {
+    using namespace el;
+    auto is_float = [](int dt) { return dt == EL_F16 || dt == EL_BF16 || dt == EL_F32; };
+    if (M < 0 || N < 0 || K < 0 || !is_float(x_dtype) || !is_float(out_dtype)) return EL_ERR_INVALID_ARG;
+    if (M > STATIC_MAX_TOKENS || N > STATIC_MAX_N || K > STATIC_MAX_K) return EL_ERR_TOO_LARGE;
+    if (M == 0 || N == 0) return EL_OK;
+    if (K == 0 || K % 64 != 0) return EL_ERR_UNSUPPORTED_SHAPE;
+    if (!x || !W_packed || !Y) return EL_ERR_NULL_PTR;
+    unsigned char* base = nullptr;
+    int rc = decode_static_setup(&base);
+    if (rc != EL_OK) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    int8_t* xq = reinterpret_cast<int8_t*>(base + STATIC_XQ_OFFSET);
+    float* absmax = reinterpret_cast<float*>(base + STATIC_ABSMAX_OFFSET);
+    // The array keeps whatever the previous call left.  The partial-sum rows and the tile counters this call will use
+    // must start at zero, so they are cleared here on the caller's stream (the rest of the array is overwritten
+    // before it is read).
+    const size_t tiles = (size_t)(N + dec::TILE_N - 1) / dec::TILE_N;
+    EL_CUDA_TRY(cudaMemsetAsync(base, 0, (size_t)M * N * sizeof(int), st));
+    EL_CUDA_TRY(cudaMemsetAsync(base + (size_t)64 * N * sizeof(int), 0, 4 * tiles * sizeof(int), st));
+    rc = launch_quantize_rows_perm(x, x_dtype, K, xq, absmax, M, K, 1e-5f, st);
+    if (rc != EL_OK) return rc;
+    const EpiParams epi{Y, (long long)N, out_dtype, absmax, 1, gamma};
+    return launch_decode_tc(xq, W_packed, epi, base, M, N, K, dev_status, st);
+}

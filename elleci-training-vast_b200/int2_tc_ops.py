@@ -390,3 +390,23 @@ def linear_decode(x: torch.Tensor, W_packed: torch.Tensor, gamma: float, out_dty
          M, N, K, st.data_ptr(), _stream())
     _maybe_check(x.device)
     return Y.view(*x.shape[:-1], N)
+
+
+def linear_decode_static(x: torch.Tensor, W_packed: torch.Tensor, gamma: float, out: torch.Tensor) -> torch.Tensor:
+    """linear_decode for hosts that cannot allocate device memory: the library call behind it keeps its scratch in
+    a static device array (M <= 64, N <= 16384, K <= 16384) and writes into the caller's `out` [M, N].  Calls on one
+    device share that array: keep them stream-ordered.  Make the first call on a device outside stream capture."""
+    _cuda(x, "x"); _cuda(W_packed, "W_packed"); _cuda(out, "out")
+    _require(x.dtype in (torch.float16, torch.bfloat16, torch.float32) and x.is_contiguous(), "x must be a contiguous float tensor")
+    _require(W_packed.dtype == torch.uint8 and W_packed.dim() == 2 and W_packed.is_contiguous(), "W_packed must be contiguous uint8 [N, ceil(K/4)]")
+    N, pK = W_packed.shape
+    K = x.shape[-1]
+    M = math.prod(x.shape[:-1])
+    _require((K + 3) // 4 == pK, f"x has {K} features but W_packed has packed_K={pK}")
+    _require(out.is_contiguous() and out.numel() == M * N and out.dtype in (torch.float16, torch.bfloat16, torch.float32),
+             "out must be a contiguous float tensor of M*N elements")
+    st = device_status(x.device)
+    call("el_linear_decode_static", x.data_ptr(), _DT[x.dtype], W_packed.data_ptr(), out.data_ptr(), _DT[out.dtype],
+         float(gamma), M, N, K, st.data_ptr(), _stream())
+    _maybe_check(x.device)
+    return out

@@ -47,6 +47,7 @@ typedef void* el_stream_t;
 #define EL_ERR_CUDA              -5   /* a CUDA runtime call failed; see el_last_cuda_error() */
 #define EL_ERR_DEVICE            -6   /* the current device is not an sm_100 part */
 #define EL_ERR_DRIVER            -7   /* the driver refused a tensor-map descriptor */
+#define EL_ERR_TOO_LARGE         -8   /* a size exceeds the fixed capacity of the entry point (el_linear_decode_static) */
 
 /* ---- element types of floating-point / output buffers ------------------------------------------------ */
 #define EL_F16  0
@@ -183,6 +184,20 @@ EL_API size_t el_decode_workspace_bytes(int N);
 EL_API int el_linear_decode(const void* x, int x_dtype, const uint8_t* W_packed, void* Y, int out_dtype, float gamma,
                             int8_t* xq_scratch, float* absmax, void* workspace, size_t workspace_bytes, int M, int N,
                             int K, int32_t* dev_status, el_stream_t stream);
+
+/* el_linear_decode for callers that cannot give the library any device memory (no counterpart in the reference).
+ * Serving processes that forbid cudaMalloc after start-up, runtimes that own the whole memory pool and hosts at
+ * their memory budget cannot supply the scratch buffers of el_linear_decode; here the quantised tokens, their
+ * scales and the partial-sum workspace live in one static device array inside the library (about 5.3 MB, held by
+ * every GPU that loads the library until the process exits).  The caller passes only x [M,K], W_packed and Y [M,N].
+ * Limits: M <= 64, N <= 16384, K <= 16384, K % 64 == 0; larger sizes return EL_ERR_TOO_LARGE.  Same results as
+ * el_linear_decode.  The call makes no cudaMalloc / cudaFree and uses no allocating library routine.
+ * The first call on a device resolves the array's address (cudaGetSymbolAddress): make that first call with the
+ * device current and before any stream capture.  All calls on a device share the one array, which keeps the
+ * contents of the previous call; the parts that must start at zero are cleared on `stream` at the start of each
+ * call.  Two calls whose GPU work overlaps (different streams, or threads) race on it: order them. */
+EL_API int el_linear_decode_static(const void* x, int x_dtype, const uint8_t* W_packed, void* Y, int out_dtype, float gamma,
+                                   int M, int N, int K, int32_t* dev_status, el_stream_t stream);
 
 #ifdef __cplusplus
 }
