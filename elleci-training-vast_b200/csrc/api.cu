@@ -23,6 +23,8 @@ int launch_gemm_simple(int mode, const int8_t* A, const void* B, int R, int C, i
 int gemm_tc_eligible(int mode, const void* A, const void* B, int R, int C, int D);
 int launch_gemm_tc(int mode, const int8_t* A, const void* B, int R, int C, int D, const EpiParams& epi, int32_t* status,
                    cudaStream_t st);
+int launch_gemm_tc2(int mode, const int8_t* A, const void* B, int R, int C, int D, const EpiParams& epi, int32_t* status,
+                    cudaStream_t st);
 int launch_dw_hysteresis_tc(const int8_t* Gq, const int8_t* Xq, const float* g_absmax, uint8_t* Wp, uint8_t* Hp,
                             const HystParams& hp, uint32_t idx_base, int M, int N, int K, int32_t* status, cudaStream_t st);
 
@@ -82,15 +84,23 @@ int require_sm100() {
 static inline bool float_dtype(int dt) { return dt == EL_F16 || dt == EL_BF16 || dt == EL_F32; }
 static inline bool out_dtype_ok(int dt) { return dt == EL_F16 || dt == EL_BF16 || dt == EL_F32 || dt == EL_I32; }
 
+// Tensor-core launch: forward and dX run on CTA pairs unless the single-CTA kernel is asked for; dW has one kernel.
+static int launch_tc(int mode, bool single_cta, const int8_t* A, const void* B, int R, int C, int D, const EpiParams& epi,
+                     int32_t* status, cudaStream_t st) {
+    if (mode != MODE_DW && !single_cta) return launch_gemm_tc2(mode, A, B, R, C, D, epi, status, st);
+    return launch_gemm_tc(mode, A, B, R, C, D, epi, status, st);
+}
+
 static int gemm_dispatch(int mode, const int8_t* A, const void* B, int R, int C, int D, const EpiParams& epi, int flags,
                          int32_t* status, cudaStream_t st) {
-    if (flags != EL_PATH_AUTO && flags != EL_PATH_SIMPLE && flags != EL_PATH_TC) return EL_ERR_INVALID_ARG;
+    if (flags < EL_PATH_AUTO || flags > EL_PATH_TC_SINGLE) return EL_ERR_INVALID_ARG;
     if (R == 0 || C == 0) return EL_OK;
     if (flags == EL_PATH_SIMPLE) return launch_gemm_simple(mode, A, B, R, C, D, epi, st);
     const int elig = (D > 0) ? gemm_tc_eligible(mode, A, B, R, C, D) : EL_ERR_UNSUPPORTED_SHAPE;
-    if (flags == EL_PATH_TC) return elig != EL_OK ? elig : launch_gemm_tc(mode, A, B, R, C, D, epi, status, st);
-    // auto: the tensor-core tile is 128 rows deep; very small problems go to the CUDA-core kernel
-    if (elig == EL_OK && R >= 32) return launch_gemm_tc(mode, A, B, R, C, D, epi, status, st);
+    if (flags == EL_PATH_TC || flags == EL_PATH_TC_SINGLE)
+        return elig != EL_OK ? elig : launch_tc(mode, flags == EL_PATH_TC_SINGLE, A, B, R, C, D, epi, status, st);
+    // auto: the tensor-core tiles are 128 rows deep; very small problems go to the CUDA-core kernel
+    if (elig == EL_OK && R >= 32) return launch_tc(mode, R <= 128, A, B, R, C, D, epi, status, st);
     return launch_gemm_simple(mode, A, B, R, C, D, epi, st);
 }
 

@@ -1,0 +1,344 @@
+// Forward and dX GEMMs on CTA pairs (tcgen05 cta_group::2) for sm_100a.
+//
+// Expanding the 2-bit weights to int8 costs ALU-pipe time per expanded byte, and the single-CTA kernel
+// (gemm_tc.cu) pays it for a 256-row weight tile per 128 x 256 output tile.  Here two CTAs of a cluster share one
+// 256 x 256 output tile: each loads its own 128 activation rows, expands only HALF of the weight tile (128 rows of
+// 128 bytes per reduction block) and one thread of the leader CTA issues 256-row MMAs that read both halves, so the
+// expansion work per MMA cycle is halved.  Per CTA and 128-deep reduction block:
+//   A   16 KB  activations, TMA, 128-byte swizzle, K-major           (counted on the leader's "a_full" barrier)
+//   P    4 KB  packed weights, TMA, in a ring of its own, 12 deep      (local "p_full" / "p_empty" barriers)
+//   B   16 KB  expanded weights                                         (one arrival per CTA on the leader's "ready")
+// A and B share a 5-deep ring.  Each reduction block is expanded by ONE transform warp per CTA (eight blocks are in
+// flight on eight warps), so a block's barrier, fence and signalling latency overlaps with the other blocks' work.
+// FWD reads B K-major (rows = output features n); DX reads the same image MN-major (rows = reduction index n,
+// 128 output columns k per CTA).  DX expands without the final byte interleave (decode16_deint), which permutes the
+// output columns inside groups of 16; the epilogue undoes that while the sums are in registers.
+// The leader commits each stage to the "empty" barriers of both CTAs, and each tile to both "tmem_full" barriers; no
+// cluster-multicast load or commit is used.  Every mbarrier wait is bounded (tc_ptx.cuh).
+#include "common.cuh"
+#include "epilogue.cuh"
+#include "tc_ptx.cuh"
+
+namespace el {
+
+enum { MODE_FWD = 0, MODE_DX = 1 };
+
+namespace tc2 {
+
+using namespace tc;
+
+constexpr int BM = 128;            // rows per CTA (the pair covers 256)
+constexpr int BN = 256;            // output columns per pair tile (128 expanded per CTA)
+constexpr int BK = 128;
+constexpr int DB = 5;              // depth of the A+B ring
+constexpr int DP = 12;             // depth of the packed-tile ring
+constexpr int A_BYTES = BM * BK, B_BYTES = 128 * BK, P_BYTES = 128 * BK / 4;
+constexpr int AB_BYTES = A_BYTES + B_BYTES;                    // 32 KB
+constexpr int SMEM_BYTES = DB * AB_BYTES + DP * P_BYTES + 1024 + 512;
+constexpr int WARP_TMA = 0, WARP_MMA = 1, NUM_EPI_WARPS = 4, WARP_PTMA = 6, WARP_XF0 = 7, NUM_XF_WARPS = 8;   // warps 2-5: epilogue
+constexpr int NUM_THREADS = (WARP_XF0 + NUM_XF_WARPS) * 32;     // 480
+constexpr uint32_t TMEM_COLS = 2 * BN;
+
+struct Params {
+    int R, C, D;
+    int tiles_r, tiles_c, k_blocks;     // tiles_r counts 256-row pair tiles
+    EpiParams epi;
+    int vec_ok;
+    int32_t* status;
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t ring_p = smem_base + DB * AB_BYTES;
+    const uint32_t bars = ring_p + DP * P_BYTES;
+    uint8_t* bars_gen = smem_gen + DB * AB_BYTES + DP * P_BYTES;
+    auto bar_afull = [&](int s) { return bars + 8u * s; };                        // leader: both CTAs' A tiles landed
+    auto bar_ready = [&](int s) { return bars + 8u * (DB + s); };                 // leader: both halves expanded
+    auto bar_empty = [&](int s) { return bars + 8u * (2 * DB + s); };             // local: MMAs done with the A+B slot
+    auto bar_pfull = [&](int s) { return bars + 8u * (3 * DB + s); };             // local: packed tile landed
+    auto bar_pempty = [&](int s) { return bars + 8u * (3 * DB + DP + s); };       // local: packed tile read
+    auto bar_tfull = [&](int a) { return bars + 8u * (3 * DB + 2 * DP + a); };    // local: accumulator complete
+    auto bar_tempty = [&](int a) { return bars + 8u * (3 * DB + 2 * DP + 2 + a); };   // leader: both epilogues done
+    volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(bars_gen + 8 * (3 * DB + 2 * DP + 4));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();            // 0 = leader
+    const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+    const int num_tiles = p.tiles_r * p.tiles_c;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < DB; ++s) {
+            mbar_init(bar_afull(s), 1);
+            mbar_init(bar_ready(s), 2);
+            mbar_init(bar_empty(s), 1);
+        }
+        for (int s = 0; s < DP; ++s) {
+            mbar_init(bar_pfull(s), 1);
+            mbar_init(bar_pempty(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(bar_tfull(a), 1);
+            mbar_init(bar_tempty(a), 2 * NUM_EPI_WARPS);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_async_smem();
+    }
+    if (warp == WARP_MMA) {     // both CTAs of the pair take part in the allocation
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_holder)),
+                     "r"(TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    cluster_sync_all();          // the peer's barriers are initialised before anything signals them
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_holder;
+    bool failed = false;
+
+    if (warp == WARP_TMA) {
+        // ================= activation producer: this CTA's 128 rows of every reduction block =================
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            for (int t = pair; t < num_tiles && !failed; t += num_pairs) {
+                const int r0 = (t % p.tiles_r) * (2 * BM) + (int)rank * BM;
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!mbar_wait_cluster(bar_empty(s), ph ^ 1u, p.status, 21)) { failed = true; break; }
+                    if (rank == 0) mbar_expect_tx(bar_afull(s), 2 * A_BYTES);
+                    tma_load_2d_pair(smem_base + s * AB_BYTES, &tmA, mapa_u32(bar_afull(s), 0), kb * BK, r0);
+                    if (++s == DB) { s = 0; ph ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == WARP_PTMA) {
+        // ================= packed-weight producer: this CTA's half of the weight tile, running far ahead =================
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            for (int t = pair; t < num_tiles && !failed; t += num_pairs) {
+                const int c0 = (t / p.tiles_r) * BN + (int)rank * 128;     // this CTA's 128 output columns
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!mbar_wait(bar_pempty(s), ph ^ 1u, p.status, 27)) { failed = true; break; }
+                    const uint32_t sp = ring_p + s * P_BYTES;
+                    const int d0 = kb * BK;
+                    mbar_expect_tx(bar_pfull(s), P_BYTES);
+                    if (MODE == MODE_FWD) tma_load_2d(sp, &tmB, bar_pfull(s), d0 >> 2, c0);     // rows n, 32 B of k
+                    else tma_load_2d(sp, &tmB, bar_pfull(s), c0 >> 2, d0);                      // rows n (reduction), 32 B of k
+                    if (++s == DP) { s = 0; ph ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == WARP_MMA) {
+        // ================= MMA issuer (leader CTA only) =================
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = make_idesc(0, MODE == MODE_DX, BN, 2 * BM);
+            int s = 0, it = 0;
+            uint32_t ph = 0;
+            for (int t = pair; t < num_tiles && !failed; t += num_pairs, ++it) {
+                const int acc = it & 1;
+                const uint32_t acc_ph = (uint32_t)(it >> 1) & 1u;
+                if (!mbar_wait_cluster(bar_tempty(acc), acc_ph ^ 1u, p.status, 22)) { failed = true; break; }
+                tcgen05_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!mbar_wait_cluster(bar_afull(s), ph, p.status, 23)) { failed = true; break; }
+                    if (!mbar_wait_cluster(bar_ready(s), ph, p.status, 24)) { failed = true; break; }
+                    tcgen05_fence_after();
+                    const uint32_t sa = smem_base + s * AB_BYTES, sb = sa + A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / 32; ++k) {
+                        const uint64_t da = make_desc(sa + k * 32, 16);
+                        const uint64_t db = (MODE == MODE_FWD) ? make_desc(sb + k * 32, 16) : make_desc(sb + k * 4096, 16384);
+                        umma_i8_pair(d_tmem, da, db, idesc, (kb | k) != 0);
+                    }
+                    umma_commit_pair(mapa_u32(bar_empty(s), 0));
+                    umma_commit_pair(mapa_u32(bar_empty(s), 1));
+                    if (++s == DB) { s = 0; ph ^= 1u; }
+                }
+                if (!failed) {
+                    umma_commit_pair(mapa_u32(bar_tfull(acc), 0));
+                    umma_commit_pair(mapa_u32(bar_tfull(acc), 1));
+                }
+            }
+        }
+    } else if (warp < WARP_XF0) {
+        // ================= epilogue (each CTA stores its own 128 rows x 256 columns) =================
+        const int quarter = warp & 3;
+        const int row_in_tile = quarter * 32 + lane;
+        int it = 0;
+        for (int t = pair; t < num_tiles && !failed; t += num_pairs, ++it) {
+            const int r0 = (t % p.tiles_r) * (2 * BM) + (int)rank * BM, c0 = (t / p.tiles_r) * BN;
+            const int acc = it & 1;
+            const uint32_t acc_ph = (uint32_t)(it >> 1) & 1u;
+            if (!mbar_wait_warp(bar_tfull(acc), acc_ph, p.status, 25)) { failed = true; break; }
+            tcgen05_fence_after();
+            const int row = r0 + row_in_tile;
+            const bool row_ok = row < p.R;
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
+            const float sc = row_ok ? epi_row_scale(p.epi, row) : 0.0f;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld32(taddr + c * 32, v);
+                tmem_ld_wait();
+                const int col0 = c0 + c * 32;
+                if (row_ok && col0 < p.C) {
+                    if (MODE == MODE_DX) {
+                        // column 16g+p of the tile holds output column 16g + KPERM16[p] (de-interleaved expansion)
+                        uint32_t w[32];
+#pragma unroll
+                        for (int g = 0; g < 2; ++g)
+#pragma unroll
+                            for (int q = 0; q < 16; ++q) w[16 * g + ((q < 8) ? 2 * q : 2 * (q - 8) + 1)] = v[16 * g + q];
+                        epi_store_chunk32(p.epi, row, col0, p.C, w, sc, p.vec_ok != 0);
+                    } else {
+                        epi_store_chunk32(p.epi, row, col0, p.C, v, sc, p.vec_ok != 0);
+                    }
+                }
+            }
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(mapa_u32(bar_tempty(acc), 0));
+        }
+    } else {
+        // ================= transform: 128 packed rows of 32 bytes -> 128 rows of 128 int8, swizzled =================
+        // Warp w expands the reduction blocks g = w, w+8, ... of this CTA's sequence on its own; lane l takes the
+        // 16-byte segments l, l+32, ... (row = segment/2) of the packed tile.
+        const int xw = warp - WARP_XF0;
+        int g = 0;
+        for (int t = pair; t < num_tiles && !failed; t += num_pairs) {
+            for (int kb = 0; kb < p.k_blocks; ++kb, ++g) {
+                if ((g & (NUM_XF_WARPS - 1)) != xw) continue;
+                const int sp = g % DP, sb_i = g % DB;
+                const uint32_t php = (uint32_t)(g / DP) & 1u, phb = (uint32_t)(g / DB) & 1u;
+                // A barrier only tells the parity of its phase, so a waiter must never be two phases ahead of it.
+                // Waiting first until the MMAs have consumed this warp's previous block (g-8) keeps every wait
+                // below within one phase: the MMAs run in order, so all blocks up to g-8 are then behind us.
+                if (g >= NUM_XF_WARPS) {
+                    const int gp = g - NUM_XF_WARPS;
+                    if (!mbar_wait_warp(bar_empty(gp % DB), (uint32_t)(gp / DB) & 1u, p.status, 29)) { failed = true; break; }
+                }
+                if (!mbar_wait_warp(bar_pfull(sp), php, p.status, 26)) { failed = true; break; }
+                const uint8_t* src = smem_gen + DB * AB_BYTES + sp * P_BYTES;
+                uint4 pk[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) pk[j] = *reinterpret_cast<const uint4*>(src + (lane + 32 * j) * 16);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_pempty(sp));
+                if (!mbar_wait_warp(bar_empty(sb_i), phb ^ 1u, p.status, 28)) { failed = true; break; }
+                uint8_t* sb = smem_gen + sb_i * AB_BYTES + A_BYTES;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int item = lane + 32 * j, row = item >> 1, seg = item & 1;
+                    const uint32_t px[4] = {pk[j].x, pk[j].y, pk[j].z, pk[j].w};
+                    uint8_t* dst_row = sb + row * 128;
+#pragma unroll
+                    for (int w = 0; w < 4; ++w) {
+                        uint32_t o[4];
+                        if (MODE == MODE_DX) decode16_deint(px[w], o);
+                        else decode16(px[w], o);
+                        const int chunk = seg * 4 + w;
+                        *reinterpret_cast<uint4*>(dst_row + ((chunk ^ (row & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                    }
+                }
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(mapa_u32(bar_ready(sb_i), 0));
+            }
+        }
+    }
+
+    // ---- teardown: both CTAs are done with each other's shared and tensor memory before either frees anything ------
+    if (p.status != nullptr && *reinterpret_cast<volatile int32_t*>(p.status) != 0) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000) { }
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == WARP_MMA) {
+        tcgen05_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+template <int MODE>
+static int launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB, Params& p, cudaStream_t st) {
+    static bool attr_set[64] = {};
+    static int max_pairs[64] = {};
+    int dev = 0;
+    EL_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return EL_ERR_DEVICE;
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.stream = st;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (!attr_set[dev]) {
+        EL_CUDA_TRY(cudaFuncSetAttribute(gemm_tc2_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        int sms = 0;
+        const int rc = device_sm_count(&sms);
+        if (rc != EL_OK) return rc;
+        cfg.gridDim = dim3((unsigned)(sms & ~1), 1, 1);
+        int clusters = 0;
+        EL_CUDA_TRY(cudaOccupancyMaxActiveClusters(&clusters, gemm_tc2_kernel<MODE>, &cfg));
+        if (clusters < 1) return EL_ERR_DEVICE;
+        max_pairs[dev] = clusters < sms / 2 ? clusters : sms / 2;
+        attr_set[dev] = true;
+    }
+    p.tiles_r = (p.R + 2 * BM - 1) / (2 * BM);
+    p.tiles_c = (p.C + BN - 1) / BN;
+    p.k_blocks = (p.D + BK - 1) / BK;
+    const long long tiles = (long long)p.tiles_r * p.tiles_c;
+    if (tiles == 0) return EL_OK;
+    if (p.k_blocks == 0) return EL_ERR_UNSUPPORTED_SHAPE;
+    const int pairs = (int)(tiles < max_pairs[dev] ? tiles : max_pairs[dev]);
+    cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
+    EL_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<MODE>, tmA, tmB, p));
+    return check_launch();
+}
+
+}  // namespace tc2
+
+namespace tc {
+int make_map(CUtensorMap* m, const void* base, uint64_t cols, uint64_t rows, uint64_t pitch, uint32_t box_cols,
+             uint32_t box_rows, bool swizzle128);
+}
+int gemm_tc_eligible(int mode, const void* A, const void* B, int R, int C, int D);
+
+// Forward (mode 0) and dX (mode 1) on CTA pairs; same eligibility as the single-CTA kernel.
+int launch_gemm_tc2(int mode, const int8_t* A, const void* B, int R, int C, int D, const EpiParams& epi, int32_t* status,
+                    cudaStream_t st) {
+    if (mode != MODE_FWD && mode != MODE_DX) return EL_ERR_INVALID_ARG;
+    int rc = gemm_tc_eligible(mode, A, B, R, C, D);
+    if (rc != EL_OK) return rc;
+    rc = require_sm100();
+    if (rc != EL_OK) return rc;
+    tc2::Params p{};
+    p.R = R; p.C = C; p.D = D;
+    p.epi = epi;
+    p.status = status;
+    const int esz = (epi.out_dtype == EL_BF16 || epi.out_dtype == EL_F16) ? 2 : 4;
+    p.vec_ok = ((reinterpret_cast<uintptr_t>(epi.out) & 15) == 0) && ((epi.ldo * esz) % 16 == 0);
+    CUtensorMap tmA, tmB;
+    if ((rc = tc::make_map(&tmA, A, D, R, D, 128, 128, true)) != EL_OK) return rc;
+    if (mode == MODE_FWD) {
+        if ((rc = tc::make_map(&tmB, B, D / 4, C, D / 4, 32, 128, false)) != EL_OK) return rc;
+        return tc2::launch_t<MODE_FWD>(tmA, tmB, p, st);
+    }
+    if ((rc = tc::make_map(&tmB, B, C / 4, D, C / 4, 32, 128, false)) != EL_OK) return rc;
+    return tc2::launch_t<MODE_DX>(tmA, tmB, p, st);
+}
+
+}  // namespace el

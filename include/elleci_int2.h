@@ -59,6 +59,7 @@ typedef void* el_stream_t;
 #define EL_PATH_AUTO   0   /* tensor-core (tcgen05) kernel when the shape allows it, CUDA-core kernel otherwise */
 #define EL_PATH_SIMPLE 1   /* force the CUDA-core kernel (any shape) */
 #define EL_PATH_TC     2   /* require the tcgen05 kernel; EL_ERR_UNSUPPORTED_SHAPE / EL_ERR_ALIGNMENT if it cannot run */
+#define EL_PATH_TC_SINGLE 3 /* as EL_PATH_TC, but forward / dX on the single-CTA kernel instead of CTA pairs */
 
 EL_API int el_version(void);
 EL_API const char* el_status_string(int status);

@@ -167,7 +167,7 @@ SIMPLE_SHAPES = [(8, 8, 8), (256, 256, 256), (256, 260, 256), (128, 128, 130), (
                  (1, 64, 64)]
 # tensor-core constraints: K % 64 == 0 (packed pitch), N % 16 == 0 (dYq / Gq pitch); M is free
 TC_SHAPES = [(128, 256, 128), (128, 256, 256), (256, 512, 384), (100, 304, 192), (1024, 1536, 1536), (160, 272, 1088),
-             (37, 64, 64), (300, 1376, 4096), (129, 16, 64)]
+             (37, 64, 64), (300, 1376, 4096), (129, 16, 64), (700, 528, 320)]
 
 
 def _gemm_inputs(M, N, K, seed):
@@ -211,9 +211,11 @@ def test_gemms_cuda_core_path_bit_exact(ops, pkg, M, N, K):
     _check_gemms(ops, M, N, K, pkg._lib.EL_PATH_SIMPLE, seed=M + N + K)
 
 
+@pytest.mark.parametrize("single_cta", [False, True])
 @pytest.mark.parametrize("M,N,K", TC_SHAPES)
-def test_gemms_tensor_core_path_bit_exact(ops, pkg, M, N, K):
-    _check_gemms(ops, M, N, K, pkg._lib.EL_PATH_TC, seed=M + N + K)
+def test_gemms_tensor_core_path_bit_exact(ops, pkg, M, N, K, single_cta):
+    """Forward and dX run on CTA pairs (cta_group::2) or, on request, on the single-CTA kernel; dW has one kernel."""
+    _check_gemms(ops, M, N, K, pkg._lib.EL_PATH_TC_SINGLE if single_cta else pkg._lib.EL_PATH_TC, seed=M + N + K)
     ops.check_device_status(torch.device(DEV))
 
 

@@ -1,0 +1,79 @@
+"""The N-sharded layer on real GPUs (NCCL, one process per GPU): a sharded step must reproduce the single-GPU layer
+step bit for bit.  Skipped on a box with one GPU (the CPU-rank test covers the host logic there)."""
+import os
+import socket
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from conftest import load_package
+from helpers import make_layer_inputs
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+M, K, N = 512, 1024, 2048
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _worker(rank, world, port, order, out_dir):
+    sys.path.insert(0, HERE)
+    sys.path.insert(0, os.path.dirname(HERE))
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        pkg = load_package()
+        d = make_layer_inputs(M, K, N, seed=3, dtype=torch.bfloat16, dy_std=1e-2, counters=1)
+        layer = pkg.sharded.ShardedInt2Linear(K, N, threshold=2, hysteresis_order=order).to(dev)
+        layer.load_shard(torch.from_numpy(d["Wp"]), torch.from_numpy(d["Hp"]), d["gamma"])
+        layer.set_lr(0.5)
+        x = d["x"].to(dev).requires_grad_(True)
+        y = layer.train()(x)
+        y.backward(d["dY"].to(dev))
+        torch.cuda.synchronize()
+        pkg.int2_tc_ops.check_device_status(dev)
+        torch.save({"y": y.detach().cpu(), "dx": x.grad.cpu(), "W": layer.W_packed.cpu(), "H": layer.H_packed.cpu(),
+                    "rows": (layer.row_start, layer.row_stop)}, os.path.join(out_dir, f"rank{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("order", ["reference", "after_dx"])
+def test_sharded_step_on_gpus_equals_single_gpu(tmp_path, order):
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    pkg = load_package()
+    d = make_layer_inputs(M, K, N, seed=3, dtype=torch.bfloat16, dy_std=1e-2, counters=1)
+    ref = pkg.Int2LinearTCWithGradHook(K, N, threshold=2, hysteresis_order=order).to("cuda:0")
+    ref.W_packed.copy_(torch.from_numpy(d["Wp"]))
+    ref.H_packed.copy_(torch.from_numpy(d["Hp"]))
+    ref.gamma.data.fill_(d["gamma"])
+    ref._gamma_cached = d["gamma"]
+    ref._initialized = True
+    ref.set_lr(0.5)
+    x = d["x"].to("cuda:0").requires_grad_(True)
+    y = ref.train()(x)
+    y.backward(d["dY"].to("cuda:0"))
+    torch.cuda.synchronize()
+    assert not torch.equal(ref.W_packed.cpu(), torch.from_numpy(d["Wp"]))
+    mp.spawn(_worker, args=(world, _free_port(), order, str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        res = torch.load(os.path.join(tmp_path, f"rank{r}.pt"))
+        a, b = res["rows"]
+        assert torch.equal(res["y"], y.detach().cpu())
+        assert torch.equal(res["dx"], x.grad.cpu())
+        assert torch.equal(res["W"], ref.W_packed.cpu()[a:b]) and torch.equal(res["H"], ref.H_packed.cpu()[a:b])
