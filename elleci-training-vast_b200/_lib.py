@@ -9,7 +9,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libelleci_int2.so")
+# ELLECI_INT2_LIB points at another build of the same library (a debug or experimental build)
+LIB_PATH = os.environ.get("ELLECI_INT2_LIB") or os.path.join(_HERE, "lib", "libelleci_int2.so")
 
 EL_OK = 0
 EL_ERR_INVALID_ARG, EL_ERR_NULL_PTR, EL_ERR_ALIGNMENT, EL_ERR_UNSUPPORTED_SHAPE = -1, -2, -3, -4

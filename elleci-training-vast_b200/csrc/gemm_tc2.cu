@@ -6,10 +6,11 @@
 // 128 bytes per reduction block) and one thread of the leader CTA issues 256-row MMAs that read both halves, so the
 // expansion work per MMA cycle is halved.  Per CTA and 128-deep reduction block:
 //   A   16 KB  activations, TMA, 128-byte swizzle, K-major           (counted on the leader's "a_full" barrier)
-//   P    4 KB  packed weights, TMA, in a ring of its own, 12 deep      (local "p_full" / "p_empty" barriers)
+//   P    4 KB  packed weights, TMA                                     (local "p_full" / "p_empty" barriers)
 //   B   16 KB  expanded weights                                         (one arrival per CTA on the leader's "ready")
-// A and B share a 5-deep ring.  Each reduction block is expanded by ONE transform warp per CTA (eight blocks are in
-// flight on eight warps), so a block's barrier, fence and signalling latency overlaps with the other blocks' work.
+// Three rings: A 5 deep, B and P 6 deep.  Each reduction block is expanded by ONE transform warp per CTA into
+// that warp's own B slot (six blocks are in flight on six warps), so a block's barrier, fence and signalling
+// latency overlaps with the other blocks' work.
 // FWD reads B K-major (rows = output features n); DX reads the same image MN-major (rows = reduction index n,
 // 128 output columns k per CTA).  DX expands without the final byte interleave (decode16_deint), which permutes the
 // output columns inside groups of 16; the epilogue undoes that while the sums are in registers.
@@ -30,13 +31,14 @@ using namespace tc;
 constexpr int BM = 128;            // rows per CTA (the pair covers 256)
 constexpr int BN = 256;            // output columns per pair tile (128 expanded per CTA)
 constexpr int BK = 128;
-constexpr int DB = 5;              // depth of the A+B ring
-constexpr int DP = 12;             // depth of the packed-tile ring
+constexpr int DA = 5;              // depth of the activation ring
+constexpr int DB = 6;              // depth of the expanded-weight ring: one slot per transform warp
+constexpr int DP = 6;              // depth of the packed-tile ring: one slot per transform warp
 constexpr int A_BYTES = BM * BK, B_BYTES = 128 * BK, P_BYTES = 128 * BK / 4;
-constexpr int AB_BYTES = A_BYTES + B_BYTES;                    // 32 KB
-constexpr int SMEM_BYTES = DB * AB_BYTES + DP * P_BYTES + 1024 + 512;
-constexpr int WARP_TMA = 0, WARP_MMA = 1, NUM_EPI_WARPS = 4, WARP_PTMA = 6, WARP_XF0 = 7, NUM_XF_WARPS = 8;   // warps 2-5: epilogue
-constexpr int NUM_THREADS = (WARP_XF0 + NUM_XF_WARPS) * 32;     // 480
+constexpr int E_BYTES = 4 * 4096;   // epilogue staging for TMA stores: 4 KB per epilogue warp
+constexpr int SMEM_BYTES = DA * A_BYTES + DB * B_BYTES + DP * P_BYTES + E_BYTES + 1024 + 512;
+constexpr int WARP_TMA = 0, WARP_MMA = 1, NUM_EPI_WARPS = 4, WARP_PTMA = 6, WARP_XF0 = 7, NUM_XF_WARPS = 6;   // warps 2-5: epilogue
+constexpr int NUM_THREADS = (WARP_XF0 + NUM_XF_WARPS) * 32;     // 416
 constexpr uint32_t TMEM_COLS = 2 * BN;
 
 struct Params {
@@ -44,26 +46,31 @@ struct Params {
     int tiles_r, tiles_c, k_blocks;     // tiles_r counts 256-row pair tiles
     EpiParams epi;
     int vec_ok;
+    int tma_store;                      // the output takes TMA stores (16-byte aligned base and pitch)
     int32_t* status;
 };
 
 template <int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Params p) {
+gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                const __grid_constant__ CUtensorMap tmOut, const Params p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    const uint32_t ring_p = smem_base + DB * AB_BYTES;
-    const uint32_t bars = ring_p + DP * P_BYTES;
-    uint8_t* bars_gen = smem_gen + DB * AB_BYTES + DP * P_BYTES;
-    auto bar_afull = [&](int s) { return bars + 8u * s; };                        // leader: both CTAs' A tiles landed
-    auto bar_ready = [&](int s) { return bars + 8u * (DB + s); };                 // leader: both halves expanded
-    auto bar_empty = [&](int s) { return bars + 8u * (2 * DB + s); };             // local: MMAs done with the A+B slot
-    auto bar_pfull = [&](int s) { return bars + 8u * (3 * DB + s); };             // local: packed tile landed
-    auto bar_pempty = [&](int s) { return bars + 8u * (3 * DB + DP + s); };       // local: packed tile read
-    auto bar_tfull = [&](int a) { return bars + 8u * (3 * DB + 2 * DP + a); };    // local: accumulator complete
-    auto bar_tempty = [&](int a) { return bars + 8u * (3 * DB + 2 * DP + 2 + a); };   // leader: both epilogues done
-    volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(bars_gen + 8 * (3 * DB + 2 * DP + 4));
+    const uint32_t ring_b = smem_base + DA * A_BYTES;
+    const uint32_t ring_p = ring_b + DB * B_BYTES;
+    const uint32_t ring_e = ring_p + DP * P_BYTES;
+    const uint32_t bars = ring_e + E_BYTES;
+    uint8_t* bars_gen = smem_gen + DA * A_BYTES + DB * B_BYTES + DP * P_BYTES + E_BYTES;
+    auto bar_afull = [&](int s) { return bars + 8u * s; };                         // leader: both CTAs' A tiles landed
+    auto bar_aempty = [&](int s) { return bars + 8u * (DA + s); };                 // local: MMAs done with the A slot
+    auto bar_ready = [&](int s) { return bars + 8u * (2 * DA + s); };              // leader: both halves expanded
+    auto bar_bempty = [&](int s) { return bars + 8u * (2 * DA + DB + s); };        // local: MMAs done with the B slot
+    auto bar_pfull = [&](int s) { return bars + 8u * (2 * DA + 2 * DB + s); };     // local: packed tile landed
+    auto bar_pempty = [&](int s) { return bars + 8u * (2 * DA + 2 * DB + DP + s); };   // local: packed tile read
+    auto bar_tfull = [&](int a) { return bars + 8u * (2 * DA + 2 * DB + 2 * DP + a); };        // local: accumulator complete
+    auto bar_tempty = [&](int a) { return bars + 8u * (2 * DA + 2 * DB + 2 * DP + 2 + a); };   // leader: both epilogues done
+    volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(bars_gen + 8 * (2 * DA + 2 * DB + 2 * DP + 4));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();            // 0 = leader
@@ -71,10 +78,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const int num_tiles = p.tiles_r * p.tiles_c;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < DB; ++s) {
+        for (int s = 0; s < DA; ++s) {
             mbar_init(bar_afull(s), 1);
+            mbar_init(bar_aempty(s), 1);
+        }
+        for (int s = 0; s < DB; ++s) {
             mbar_init(bar_ready(s), 2);
-            mbar_init(bar_empty(s), 1);
+            mbar_init(bar_bempty(s), 1);
         }
         for (int s = 0; s < DP; ++s) {
             mbar_init(bar_pfull(s), 1);
@@ -108,10 +118,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             for (int t = pair; t < num_tiles && !failed; t += num_pairs) {
                 const int r0 = (t % p.tiles_r) * (2 * BM) + (int)rank * BM;
                 for (int kb = 0; kb < p.k_blocks; ++kb) {
-                    if (!mbar_wait_cluster(bar_empty(s), ph ^ 1u, p.status, 21)) { failed = true; break; }
+                    if (!mbar_wait_cluster(bar_aempty(s), ph ^ 1u, p.status, 21)) { failed = true; break; }
                     if (rank == 0) mbar_expect_tx(bar_afull(s), 2 * A_BYTES);
-                    tma_load_2d_pair(smem_base + s * AB_BYTES, &tmA, mapa_u32(bar_afull(s), 0), kb * BK, r0);
-                    if (++s == DB) { s = 0; ph ^= 1u; }
+                    tma_load_2d_pair(smem_base + s * A_BYTES, &tmA, mapa_u32(bar_afull(s), 0), kb * BK, r0);
+                    if (++s == DA) { s = 0; ph ^= 1u; }
                 }
             }
         }
@@ -137,8 +147,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         // ================= MMA issuer (leader CTA only) =================
         if (lane == 0 && rank == 0) {
             constexpr uint32_t idesc = make_idesc(0, MODE == MODE_DX, BN, 2 * BM);
-            int s = 0, it = 0;
-            uint32_t ph = 0;
+            int sa = 0, sb = 0, it = 0;
+            uint32_t pha = 0, phb = 0;
             for (int t = pair; t < num_tiles && !failed; t += num_pairs, ++it) {
                 const int acc = it & 1;
                 const uint32_t acc_ph = (uint32_t)(it >> 1) & 1u;
@@ -146,19 +156,22 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 tcgen05_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
                 for (int kb = 0; kb < p.k_blocks; ++kb) {
-                    if (!mbar_wait_cluster(bar_afull(s), ph, p.status, 23)) { failed = true; break; }
-                    if (!mbar_wait_cluster(bar_ready(s), ph, p.status, 24)) { failed = true; break; }
+                    if (!mbar_wait_cluster(bar_afull(sa), pha, p.status, 23)) { failed = true; break; }
+                    if (!mbar_wait_cluster(bar_ready(sb), phb, p.status, 24)) { failed = true; break; }
                     tcgen05_fence_after();
-                    const uint32_t sa = smem_base + s * AB_BYTES, sb = sa + A_BYTES;
+                    const uint32_t a_addr = smem_base + sa * A_BYTES, b_addr = ring_b + sb * B_BYTES;
 #pragma unroll
                     for (int k = 0; k < BK / 32; ++k) {
-                        const uint64_t da = make_desc(sa + k * 32, 16);
-                        const uint64_t db = (MODE == MODE_FWD) ? make_desc(sb + k * 32, 16) : make_desc(sb + k * 4096, 16384);
+                        const uint64_t da = make_desc(a_addr + k * 32, 16);
+                        const uint64_t db = (MODE == MODE_FWD) ? make_desc(b_addr + k * 32, 16) : make_desc(b_addr + k * 4096, 16384);
                         umma_i8_pair(d_tmem, da, db, idesc, (kb | k) != 0);
                     }
-                    umma_commit_pair(mapa_u32(bar_empty(s), 0));
-                    umma_commit_pair(mapa_u32(bar_empty(s), 1));
-                    if (++s == DB) { s = 0; ph ^= 1u; }
+                    umma_commit_pair(mapa_u32(bar_aempty(sa), 0));
+                    umma_commit_pair(mapa_u32(bar_aempty(sa), 1));
+                    umma_commit_pair(mapa_u32(bar_bempty(sb), 0));
+                    umma_commit_pair(mapa_u32(bar_bempty(sb), 1));
+                    if (++sa == DA) { sa = 0; pha ^= 1u; }
+                    if (++sb == DB) { sb = 0; phb ^= 1u; }
                 }
                 if (!failed) {
                     umma_commit_pair(mapa_u32(bar_tfull(acc), 0));
@@ -181,57 +194,104 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             const bool row_ok = row < p.R;
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
             const float sc = row_ok ? epi_row_scale(p.epi, row) : 0.0f;
+            const bool two_byte = (p.epi.out_dtype == EL_BF16 || p.epi.out_dtype == EL_F16);
+            const uint32_t stage = ring_e + quarter * 4096;        // this warp's staging area
+            uint8_t* stage_gen = smem_gen + DA * A_BYTES + DB * B_BYTES + DP * P_BYTES + quarter * 4096;
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
                 uint32_t v[32];
                 tmem_ld32(taddr + c * 32, v);
                 tmem_ld_wait();
                 const int col0 = c0 + c * 32;
-                if (row_ok && col0 < p.C) {
-                    if (MODE == MODE_DX) {
-                        // column 16g+p of the tile holds output column 16g + KPERM16[p] (de-interleaved expansion)
-                        uint32_t w[32];
+                if (MODE == MODE_DX) {
+                    // column 16g+p of the tile holds output column 16g + KPERM16[p] (de-interleaved expansion)
+                    uint32_t w[32];
 #pragma unroll
-                        for (int g = 0; g < 2; ++g)
+                    for (int g = 0; g < 2; ++g)
 #pragma unroll
-                            for (int q = 0; q < 16; ++q) w[16 * g + ((q < 8) ? 2 * q : 2 * (q - 8) + 1)] = v[16 * g + q];
-                        epi_store_chunk32(p.epi, row, col0, p.C, w, sc, p.vec_ok != 0);
+                        for (int q = 0; q < 16; ++q) w[16 * g + ((q < 8) ? 2 * q : 2 * (q - 8) + 1)] = v[16 * g + q];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = w[i];
+                }
+                if (p.tma_store) {
+                    if (col0 >= p.C) continue;
+                    // The warp's 32 rows x 32 columns go to shared memory in the tensor map's swizzle, then out with
+                    // one TMA store (clipped at the matrix edges).  Two-byte outputs alternate between two 2 KB
+                    // buffers; before a buffer is rewritten the store that last read it must have finished reading.
+                    if (two_byte) {
+                        if (lane == 0) bulk_wait_read<1>();
+                        __syncwarp();
+                        uint8_t* buf = stage_gen + (c & 1) * 2048 + lane * 64;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            uint32_t o[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const float lo = __fmul_rn((float)(int)v[8 * j + 2 * i], sc), hi = __fmul_rn((float)(int)v[8 * j + 2 * i + 1], sc);
+                                o[i] = (p.epi.out_dtype == EL_BF16) ? pack_bf16x2(lo, hi) : pack_f16x2(lo, hi);
+                            }
+                            *reinterpret_cast<uint4*>(buf + ((j ^ ((lane >> 1) & 3)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                        }
+                        fence_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            tma_store_2d(&tmOut, stage + (c & 1) * 2048, col0, r0 + quarter * 32);
+                            bulk_commit();
+                        }
                     } else {
-                        epi_store_chunk32(p.epi, row, col0, p.C, v, sc, p.vec_ok != 0);
+                        if (lane == 0) bulk_wait_read<0>();
+                        __syncwarp();
+                        uint8_t* buf = stage_gen + lane * 128;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            uint32_t o[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const int a = (int)v[4 * j + i];
+                                o[i] = (p.epi.out_dtype == EL_F32) ? __float_as_uint(__fmul_rn((float)a, sc)) : (uint32_t)a;
+                            }
+                            *reinterpret_cast<uint4*>(buf + ((j ^ (lane & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                        }
+                        fence_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            tma_store_2d(&tmOut, stage, col0, r0 + quarter * 32);
+                            bulk_commit();
+                        }
                     }
+                } else if (row_ok && col0 < p.C) {
+                    epi_store_chunk32(p.epi, row, col0, p.C, v, sc, false);
                 }
             }
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(mapa_u32(bar_tempty(acc), 0));
         }
+        if (lane == 0) bulk_wait_all();      // this warp's TMA stores have left shared memory and reached global memory
     } else {
         // ================= transform: 128 packed rows of 32 bytes -> 128 rows of 128 int8, swizzled =================
-        // Warp w expands the reduction blocks g = w, w+8, ... of this CTA's sequence on its own; lane l takes the
+        // Warp w expands the reduction blocks g = w, w+6, ... of this CTA's sequence on its own; lane l takes the
         // 16-byte segments l, l+32, ... (row = segment/2) of the packed tile.
         const int xw = warp - WARP_XF0;
         int g = 0;
         for (int t = pair; t < num_tiles && !failed; t += num_pairs) {
             for (int kb = 0; kb < p.k_blocks; ++kb, ++g) {
-                if ((g & (NUM_XF_WARPS - 1)) != xw) continue;
-                const int sp = g % DP, sb_i = g % DB;
+                if (g % NUM_XF_WARPS != xw) continue;
+                // Block g uses this warp's own packed slot and B slot (g % 6 == xw).  A barrier only tells the parity of
+                // its phase, so a waiter must never be two phases away from it: with one slot per warp the previous
+                // use of either slot was this warp's previous block (g-6).
+                static_assert(DP == NUM_XF_WARPS && DB == NUM_XF_WARPS, "one packed slot and one B slot per transform warp");
+                const int sp = xw, sb_i = xw;
                 const uint32_t php = (uint32_t)(g / DP) & 1u, phb = (uint32_t)(g / DB) & 1u;
-                // A barrier only tells the parity of its phase, so a waiter must never be two phases ahead of it.
-                // Waiting first until the MMAs have consumed this warp's previous block (g-8) keeps every wait
-                // below within one phase: the MMAs run in order, so all blocks up to g-8 are then behind us.
-                if (g >= NUM_XF_WARPS) {
-                    const int gp = g - NUM_XF_WARPS;
-                    if (!mbar_wait_warp(bar_empty(gp % DB), (uint32_t)(gp / DB) & 1u, p.status, 29)) { failed = true; break; }
-                }
                 if (!mbar_wait_warp(bar_pfull(sp), php, p.status, 26)) { failed = true; break; }
-                const uint8_t* src = smem_gen + DB * AB_BYTES + sp * P_BYTES;
+                const uint8_t* src = smem_gen + DA * A_BYTES + DB * B_BYTES + sp * P_BYTES;
                 uint4 pk[8];
 #pragma unroll
                 for (int j = 0; j < 8; ++j) pk[j] = *reinterpret_cast<const uint4*>(src + (lane + 32 * j) * 16);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_pempty(sp));
-                if (!mbar_wait_warp(bar_empty(sb_i), phb ^ 1u, p.status, 28)) { failed = true; break; }
-                uint8_t* sb = smem_gen + sb_i * AB_BYTES + A_BYTES;
+                if (!mbar_wait_warp(bar_bempty(sb_i), phb ^ 1u, p.status, 28)) { failed = true; break; }
+                uint8_t* sb = smem_gen + DA * A_BYTES + sb_i * B_BYTES;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     const int item = lane + 32 * j, row = item >> 1, seg = item & 1;
@@ -268,7 +328,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 }
 
 template <int MODE>
-static int launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB, Params& p, cudaStream_t st) {
+static int launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmOut, Params& p, cudaStream_t st) {
     static bool attr_set[64] = {};
     static int max_pairs[64] = {};
     int dev = 0;
@@ -305,7 +365,7 @@ static int launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB, Params& p, c
     if (p.k_blocks == 0) return EL_ERR_UNSUPPORTED_SHAPE;
     const int pairs = (int)(tiles < max_pairs[dev] ? tiles : max_pairs[dev]);
     cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
-    EL_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<MODE>, tmA, tmB, p));
+    EL_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<MODE>, tmA, tmB, tmOut, p));
     return check_launch();
 }
 
@@ -314,6 +374,7 @@ static int launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB, Params& p, c
 namespace tc {
 int make_map(CUtensorMap* m, const void* base, uint64_t cols, uint64_t rows, uint64_t pitch, uint32_t box_cols,
              uint32_t box_rows, bool swizzle128);
+int make_map_out(CUtensorMap* m, const void* base, uint64_t cols, uint64_t rows, uint64_t pitch_bytes, int esz);
 }
 int gemm_tc_eligible(int mode, const void* A, const void* B, int R, int C, int D);
 
@@ -331,14 +392,20 @@ int launch_gemm_tc2(int mode, const int8_t* A, const void* B, int R, int C, int 
     p.status = status;
     const int esz = (epi.out_dtype == EL_BF16 || epi.out_dtype == EL_F16) ? 2 : 4;
     p.vec_ok = ((reinterpret_cast<uintptr_t>(epi.out) & 15) == 0) && ((epi.ldo * esz) % 16 == 0);
-    CUtensorMap tmA, tmB;
+    CUtensorMap tmA, tmB, tmOut;
+    p.tma_store = p.vec_ok;
+    if (p.tma_store) {
+        if ((rc = tc::make_map_out(&tmOut, epi.out, C, R, (uint64_t)epi.ldo * esz, esz)) != EL_OK) return rc;
+    } else {
+        tmOut = CUtensorMap{};
+    }
     if ((rc = tc::make_map(&tmA, A, D, R, D, 128, 128, true)) != EL_OK) return rc;
     if (mode == MODE_FWD) {
         if ((rc = tc::make_map(&tmB, B, D / 4, C, D / 4, 32, 128, false)) != EL_OK) return rc;
-        return tc2::launch_t<MODE_FWD>(tmA, tmB, p, st);
+        return tc2::launch_t<MODE_FWD>(tmA, tmB, tmOut, p, st);
     }
     if ((rc = tc::make_map(&tmB, B, C / 4, D, C / 4, 32, 128, false)) != EL_OK) return rc;
-    return tc2::launch_t<MODE_DX>(tmA, tmB, p, st);
+    return tc2::launch_t<MODE_DX>(tmA, tmB, tmOut, p, st);
 }
 
 }  // namespace el
