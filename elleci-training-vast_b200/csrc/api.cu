@@ -34,6 +34,9 @@ size_t decode_workspace_bytes(int N);
 int launch_decode_tc(const int8_t* Xq, const uint8_t* Wp, const EpiParams& epi, void* workspace, int M, int N, int K,
                      int32_t* status, cudaStream_t st);
 
+int launch_gemv_small(const void* x, int x_dtype, const uint8_t* Wp, const EpiParams& epi, int M, int N, int K, cudaStream_t st);
+int decode_gemv_max_tokens();
+
 static thread_local int g_last_cuda_error = 0;
 
 int record_cuda_error(cudaError_t e) {
@@ -73,6 +76,10 @@ static int device_info(int* sms, int* major) {
 }
 
 int device_sm_count(int* out) { return device_info(out, nullptr); }
+
+// Token count up to which the decode call uses the CUDA-core GEMV (el_set_decode_gemv_max_tokens).
+static int g_gemv_max_tokens = 4;
+int decode_gemv_max_tokens() { return g_gemv_max_tokens; }
 
 int require_sm100() {
     int major = 0;
@@ -239,6 +246,12 @@ int el_dw_hysteresis(const int8_t* Gq, const int8_t* Xq, const float* g_absmax, 
                                    (cudaStream_t)stream);
 }
 
+int el_set_decode_gemv_max_tokens(int max_tokens) {
+    if (max_tokens < 0 || max_tokens > 8) return EL_ERR_INVALID_ARG;
+    g_gemv_max_tokens = max_tokens;
+    return EL_OK;
+}
+
 size_t el_decode_workspace_bytes(int N) { return N > 0 ? decode_workspace_bytes(N) : 0; }
 
 int el_linear_decode(const void* x, int x_dtype, const uint8_t* W_packed, void* Y, int out_dtype, float gamma,
@@ -249,6 +262,10 @@ int el_linear_decode(const void* x, int x_dtype, const uint8_t* W_packed, void* 
     if (M > 64 || K == 0 || K % 64 != 0) return EL_ERR_UNSUPPORTED_SHAPE;
     if (!x || !W_packed || !Y || !xq_scratch || !absmax || !workspace) return EL_ERR_NULL_PTR;
     if (workspace_bytes < decode_workspace_bytes(N)) return EL_ERR_INVALID_ARG;
+    if (M <= decode_gemv_max_tokens()) {      // a handful of tokens: one CUDA-core launch, no scratch touched
+        const EpiParams gepi{Y, (long long)N, out_dtype, nullptr, 0, gamma};
+        return launch_gemv_small(x, x_dtype, W_packed, gepi, M, N, K, (cudaStream_t)stream);
+    }
     int rc = launch_quantize_rows_perm(x, x_dtype, K, xq_scratch, absmax, M, K, 1e-5f, (cudaStream_t)stream);
     if (rc != EL_OK) return rc;
     const EpiParams epi{Y, (long long)N, out_dtype, absmax, 1, gamma};

@@ -5,7 +5,8 @@
 //     are the narrow N operand (B, 16/32/64 rows, zero-filled by TMA beyond M), so no tensor-core rows are wasted;
 //   * one CTA per SM, and the (128-row weight tile, 128-deep reduction block) units are dealt out as one contiguous
 //     range per CTA (stream-K), so every SM pulls the same number of bytes whatever N/128 is;
-//   * a 12-deep TMA ring for the packed tiles (48 KB in flight per SM) feeds a 4-deep ring of expanded tiles;
+//   * eight packed-tile slots and eight expanded-tile slots, one of each per transform warp: warp w expands the units
+//     w, w+8, ... of its CTA on its own, so eight units are in flight and a unit's latencies overlap with the others';
 //   * the expansion uses the de-interleaved decode; the tokens were quantised with the matching permutation of the
 //     reduction index (launch_quantize_rows_perm), which leaves the integer sums unchanged;
 //   * partial sums of a tile that spans several CTAs are added into an int32 workspace with red.global.add (exact,
@@ -23,8 +24,8 @@ using namespace tc;
 
 constexpr int TILE_N = 128;      // weight rows per tile (UMMA M)
 constexpr int BK = 128;          // reduction depth per unit
-constexpr int DP = 12;           // packed-tile ring depth
-constexpr int DA = 4;            // expanded-tile ring depth
+constexpr int DP = 8;            // packed-tile slots: one per transform warp
+constexpr int DA = 8;            // expanded-tile slots: one per transform warp
 constexpr int A_BYTES = TILE_N * BK;        // 16 KB
 constexpr int P_BYTES = TILE_N * BK / 4;    // 4 KB
 constexpr int WARP_TMA = 0, WARP_MMA = 1, NUM_EPI_WARPS = 4, WARP_XF0 = 6, NUM_XF_WARPS = 8;
@@ -74,10 +75,10 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     if (threadIdx.x == 0) {
         for (int s = 0; s < DP; ++s) {
             mbar_init(bar_pfull(s), 1);
-            mbar_init(bar_pempty(s), NUM_XF_WARPS + 1);
+            mbar_init(bar_pempty(s), 2);          // the transform warp that read P, and the MMAs that read B
         }
         for (int s = 0; s < DA; ++s) {
-            mbar_init(bar_ready(s), NUM_XF_WARPS);
+            mbar_init(bar_ready(s), 1);
             mbar_init(bar_aempty(s), 1);
         }
         for (int a = 0; a < 2; ++a) {
@@ -195,11 +196,18 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
                 if (before + cnt == p.k_blocks) {
                     __threadfence();
                     if (n_ok) {
-                        for (int m = 0; m < p.M; ++m) {
-                            int* slot = p.acc_ws + (size_t)m * p.N + n;
-                            const int sum = __ldcg(slot);
-                            epi_store_one(p.epi, m, n, sum, epi_row_scale(p.epi, m));
-                            __stcg(slot, 0);
+                        for (int m0 = 0; m0 < p.M; m0 += 8) {       // eight independent loads in flight per lane
+                            int sum[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                sum[j] = (m0 + j < p.M) ? __ldcg(p.acc_ws + (size_t)(m0 + j) * p.N + n) : 0;
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                if (m0 + j < p.M) {
+                                    epi_store_one(p.epi, m0 + j, n, sum[j], epi_row_scale(p.epi, m0 + j));
+                                    __stcg(p.acc_ws + (size_t)(m0 + j) * p.N + n, 0);
+                                }
+                            }
                         }
                     }
                     if (lane == 0) *counter = 0;
@@ -209,32 +217,37 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         }
     } else {
         // ================= transform: packed rows -> swizzled int8 A tile (de-interleaved decode) =================
-        const int xt = threadIdx.x - WARP_XF0 * 32;     // 0..255: row = xt/2, 16-byte segment = xt%2
-        const int row = xt >> 1, seg = xt & 1;
-        int sp = 0, sa = 0;
-        uint32_t php = 0, pha = 0;
-        for (long long u = u_lo; u < u_hi; ++u) {
-            if (!mbar_wait_warp(bar_pfull(sp), php, p.status, 16)) { failed = true; break; }
-            if (!mbar_wait_warp(bar_aempty(sa), pha ^ 1u, p.status, 17)) { failed = true; break; }
-            const uint8_t* sp_gen = smem_gen + DA * A_BYTES + sp * C::SLOT + C::B_BYTES;
-            uint8_t* dst_row = smem_gen + sa * A_BYTES + row * 128;
-            const uint4 pk = *reinterpret_cast<const uint4*>(sp_gen + row * 32 + seg * 16);
-            const uint32_t px[4] = {pk.x, pk.y, pk.z, pk.w};
+        // Warp w owns packed slot w and expanded slot w and takes the units j = w, w+8, ... of this CTA; lane l takes
+        // the 16-byte segments l, l+32, ... (row = segment/2) of the 128 x 32-byte packed tile.
+        static_assert(DP == NUM_XF_WARPS && DA == NUM_XF_WARPS, "one slot of each ring per transform warp");
+        const int xw = warp - WARP_XF0;
+        const long long n_units = u_hi - u_lo;
+        for (long long j = xw; j < n_units; j += NUM_XF_WARPS) {
+            const uint32_t phs = (uint32_t)(j / NUM_XF_WARPS) & 1u;
+            if (!mbar_wait_warp(bar_pfull(xw), phs, p.status, 16)) { failed = true; break; }
+            const uint8_t* sp_gen = smem_gen + DA * A_BYTES + xw * C::SLOT + C::B_BYTES;
+            uint4 pk[8];
 #pragma unroll
-            for (int w = 0; w < 4; ++w) {
-                uint32_t o[4];
-                decode16_deint(px[w], o);
-                const int chunk = seg * 4 + w;
-                *reinterpret_cast<uint4*>(dst_row + ((chunk ^ (row & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+            for (int q = 0; q < 8; ++q) pk[q] = *reinterpret_cast<const uint4*>(sp_gen + (lane + 32 * q) * 16);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_pempty(xw));
+            if (!mbar_wait_warp(bar_aempty(xw), phs ^ 1u, p.status, 17)) { failed = true; break; }
+            uint8_t* dst = smem_gen + xw * A_BYTES;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const int item = lane + 32 * q, row = item >> 1, seg = item & 1;
+                const uint32_t px[4] = {pk[q].x, pk[q].y, pk[q].z, pk[q].w};
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    uint32_t o[4];
+                    decode16_deint(px[w], o);
+                    const int chunk = seg * 4 + w;
+                    *reinterpret_cast<uint4*>(dst + row * 128 + ((chunk ^ (row & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                }
             }
             fence_async_smem();
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(bar_ready(sa));
-                mbar_arrive(bar_pempty(sp));
-            }
-            if (++sp == DP) { sp = 0; php ^= 1u; }
-            if (++sa == DA) { sa = 0; pha ^= 1u; }
+            if (lane == 0) mbar_arrive(bar_ready(xw));
         }
     }
 
@@ -348,6 +361,8 @@ static int decode_static_setup(unsigned char** out) {
 
 int launch_quantize_rows_perm(const void* x, int dt, long long ldx, int8_t* q, float* a, int M, int K, float eps,
                               cudaStream_t st);
+int launch_gemv_small(const void* x, int x_dtype, const uint8_t* Wp, const EpiParams& epi, int M, int N, int K, cudaStream_t st);
+int decode_gemv_max_tokens();
 
 }  // namespace el
 
@@ -360,10 +375,14 @@ extern "C" EL_API int el_linear_decode_static(const void* x, int x_dtype, const 
     if (M == 0 || N == 0) return EL_OK;
     if (K == 0 || K % 64 != 0) return EL_ERR_UNSUPPORTED_SHAPE;
     if (!x || !W_packed || !Y) return EL_ERR_NULL_PTR;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (M <= decode_gemv_max_tokens()) {      // the few-token kernel needs no scratch at all
+        const EpiParams gepi{Y, (long long)N, out_dtype, nullptr, 0, gamma};
+        return launch_gemv_small(x, x_dtype, W_packed, gepi, M, N, K, st);
+    }
     unsigned char* base = nullptr;
     int rc = decode_static_setup(&base);
     if (rc != EL_OK) return rc;
-    cudaStream_t st = (cudaStream_t)stream;
     int8_t* xq = reinterpret_cast<int8_t*>(base + STATIC_XQ_OFFSET);
     float* absmax = reinterpret_cast<float*>(base + STATIC_ABSMAX_OFFSET);
     // The array keeps whatever the previous call left.  The partial-sum rows and the tile counters this call will use

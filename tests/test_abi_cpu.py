@@ -15,7 +15,7 @@ def test_library_exports_every_declared_symbol():
     pkg = load_package()
     handle = pkg._lib.lib()
     names = _declared_symbols()
-    assert len(names) >= 19
+    assert len(names) >= 20
     for name in names:
         assert hasattr(handle, name), name
         assert name in pkg._lib.SIGNATURES, f"{name} has no ctypes signature"

@@ -260,9 +260,19 @@ def test_fused_dw_hysteresis_bit_exact(ops, M, N, K, thr):
 
 # ---- small-M decode path -------------------------------------------------------------------------------------------
 
+@pytest.fixture
+def gemv_threshold(ops):
+    """Lets a test choose between the few-token CUDA-core GEMV and the tensor-core decode kernel."""
+    def set_(v):
+        assert ops._lib.lib().el_set_decode_gemv_max_tokens(v) == 0
+    yield set_
+    set_(4)
+
+
+@pytest.mark.parametrize("gemv_max", [0, 8])
 @pytest.mark.parametrize("M", [1, 3, 8, 17, 32, 64])
 @pytest.mark.parametrize("K,N", [(4096, 11008), (11008, 4096), (256, 384), (192, 100)])
-def test_linear_decode_bit_exact(ops, M, K, N):
+def test_linear_decode_bit_exact(ops, gemv_threshold, M, K, N, gemv_max):
     """The weight-streaming small-M kernel gives the integers and the rounding of quantize_rows + the forward GEMM;
     run twice on one workspace to show that a call leaves the workspace clean."""
     g = torch.Generator().manual_seed(M + K + N)
@@ -271,6 +281,7 @@ def test_linear_decode_bit_exact(ops, M, K, N):
     gamma = 0.0161
     Xq, ax = O.quantize_rows(t2n(x))
     want = O.to_bf16(O.scale_rows(O.gemm_fwd_acc(Xq, Wp, K), ax, gamma))
+    gemv_threshold(gemv_max)          # 0: tensor-core kernel for every M; 8: CUDA-core GEMV up to 8 tokens
     ws = torch.zeros(ops._lib.lib().el_decode_workspace_bytes(N), dtype=torch.uint8, device=DEV)
     Wd = _cuda(Wp)
     for _ in range(2):
