@@ -73,10 +73,10 @@ __device__ __forceinline__ float finite_or_zero(float v) { return (fabsf(v) <= 3
 
 // ---- hysteresis: one weight ---------------------------------------------------------------------------------
 struct HystParams {
-    float lr_scaled;   // (lr*lr_scale)*thr, flushed like the reference's fast-math build when ftz
-    float decay;
-    int thr;           // clamp(threshold, 1, 7)
-    uint32_t s1, s2;   // step*2654435761, step*2246822519 (uint32 wrap-around)
+    float lr_scaled;     // (lr*lr_scale)*thr, flushed like the reference's fast-math build when ftz
+    uint32_t decay_u24;  // number of 24-bit random values u with u/2^24 < decay_rate (the decay test, as an integer)
+    int thr;             // clamp(threshold, 1, 7)
+    uint32_t s1, s2;     // step*2654435761, step*2246822519 (uint32 wrap-around)
     int ftz;
 };
 
@@ -87,31 +87,30 @@ __device__ __forceinline__ uint32_t mix2(uint32_t h) {
 }
 
 // Updates (q, h) of weight `idx` from its gradient.  q in {-1,0,1}, h a signed counter.
+// FTZ reproduces the reference build's flush of float32 denormals (inputs and result of the one multiply that can
+// meet them) with the hardware's own .ftz multiply.
+template <bool FTZ>
 __device__ __forceinline__ void hyst_update_one(float grad, int& q, int& h, uint32_t idx, const HystParams& p) {
-    const float r1 = (float)(mix2(idx ^ p.s1) & 0xFFFFFFu) * (1.0f / 16777216.0f);
-    const float r2 = (float)(mix2(idx ^ p.s2) & 0xFFFFFFu) * (1.0f / 16777216.0f);
-    if (p.ftz) grad = ftz32(grad);
-    float d_raw = __fmul_rn(-grad, p.lr_scaled);
-    if (p.ftz) d_raw = ftz32(d_raw);
+    const uint32_t u1 = mix2(idx ^ p.s1) & 0xFFFFFFu;
+    const uint32_t u2 = mix2(idx ^ p.s2) & 0xFFFFFFu;
+    float d_raw;
+    if (FTZ) asm("mul.ftz.f32 %0, %1, %2;" : "=f"(d_raw) : "f"(-grad), "f"(p.lr_scaled));
+    else d_raw = __fmul_rn(-grad, p.lr_scaled);
     const float a = fabsf(d_raw);
     const float fl = floorf(a);
     const float frac = __fsub_rn(a, fl);
+    const float r1 = (float)u1 * (1.0f / 16777216.0f);
     float v = __fadd_rn(fl, (r1 < frac) ? 1.0f : 0.0f);
     v = (d_raw >= 0.0f) ? v : -v;
     int delta = __float2int_rz(v);   // saturating; NaN converts to 0
     delta = max(-31, min(31, delta));
     int hn = h + delta;
-    if (q != 0 && r2 < p.decay) hn -= q;
+    if (q != 0 && u2 < p.decay_u24) hn -= q;
     const int thr = p.thr;
-    int qn = q;
-    if (hn >= thr) {
-        if (q == 1) hn = thr; else { qn = q + 1; hn = 0; }
-    } else if (hn <= -thr) {
-        if (q == -1) hn = -thr; else { qn = q - 1; hn = 0; }
-    }
-    hn = max(-thr, min(thr, hn));
-    q = qn;
-    h = hn;
+    // crossing +thr moves -1 -> 0 -> +1 and resets the counter; at +1 the counter saturates (clamp); same downwards
+    const int mv = (hn >= thr && q < 1) ? 1 : ((hn <= -thr && q > -1) ? -1 : 0);
+    q += mv;
+    h = mv ? 0 : max(-thr, min(thr, hn));
 }
 
 // Host-side preparation of HystParams from the API arguments.
@@ -124,7 +123,15 @@ inline HystParams make_hyst_params(float lr, float lr_scale, int threshold, floa
     if (ftz) pr = ftz32_host(pr);
     volatile float ls = pr * (float)p.thr;
     p.lr_scaled = ftz ? ftz32_host(ls) : (float)ls;
-    p.decay = decay;
+    // r2 = u/2^24 < decay  <=>  u < decay*2^24 (exact in double)  <=>  u < ceil(decay*2^24) for integer u
+    const double t = (double)decay * 16777216.0;
+    if (!(t > 0.0)) p.decay_u24 = 0;                    // also NaN: the comparison is then always false
+    else if (t >= 16777216.0) p.decay_u24 = 16777216u;
+    else {
+        uint32_t c = (uint32_t)t;
+        if ((double)c < t) ++c;
+        p.decay_u24 = c;
+    }
     p.s1 = step * 2654435761u;
     p.s2 = step * 2246822519u;
     p.ftz = ftz;

@@ -223,7 +223,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                             int q = decode2(w[wi] >> ws);
                             int hv = (int)((h[hi] >> hs) & 0xFu);
                             hv = (hv & 8) ? hv - 16 : hv;
-                            hyst_update_one(__fmul_rn((float)(int)v[j], sc), q, hv, idx0 + j, p.hp);
+                            hyst_update_one<true>(__fmul_rn((float)(int)v[j], sc), q, hv, idx0 + j, p.hp);
                             w[wi] = (w[wi] & ~(3u << ws)) | ((uint32_t)(q + 1) << ws);
                             h[hi] = (h[hi] & ~(0xFu << hs)) | (((uint32_t)hv & 0xFu) << hs);
                         }

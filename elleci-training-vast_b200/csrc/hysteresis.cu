@@ -6,7 +6,7 @@
 
 namespace el {
 
-template <bool VEC>
+template <bool VEC, bool FTZ>
 __global__ void __launch_bounds__(256)
 hysteresis_kernel(const float* __restrict__ dW, uint8_t* __restrict__ Wp, uint8_t* __restrict__ Hp, HystParams p,
                   int N, int K, int pK, int pH, uint32_t idx_base) {
@@ -36,7 +36,7 @@ hysteresis_kernel(const float* __restrict__ dW, uint8_t* __restrict__ Wp, uint8_
             int q = decode2(wbits >> (2 * j));
             int h = (int)((hbits >> (4 * j)) & 0xFu);
             h = (h & 8) ? h - 16 : h;
-            hyst_update_one(grad[j], q, h, idx0 + j, p);
+            hyst_update_one<FTZ>(grad[j], q, h, idx0 + j, p);
             wbits = (wbits & ~(3u << (2 * j))) | ((uint32_t)(q + 1) << (2 * j));
             hbits = (hbits & ~(0xFu << (4 * j))) | (((uint32_t)h & 0xFu) << (4 * j));
         }
@@ -58,8 +58,10 @@ int launch_hysteresis(const float* dW, uint8_t* Wp, uint8_t* Hp, const HystParam
     const int grid = (int)((work + 255) / 256);
     const bool vec = (K % 4 == 0) && ((reinterpret_cast<uintptr_t>(dW) & 15) == 0) &&
                      ((reinterpret_cast<uintptr_t>(Hp) & 1) == 0);
-    if (vec) hysteresis_kernel<true><<<grid, 256, 0, st>>>(dW, Wp, Hp, p, N, K, pK, pH, idx_base);
-    else hysteresis_kernel<false><<<grid, 256, 0, st>>>(dW, Wp, Hp, p, N, K, pK, pH, idx_base);
+    if (vec && p.ftz) hysteresis_kernel<true, true><<<grid, 256, 0, st>>>(dW, Wp, Hp, p, N, K, pK, pH, idx_base);
+    else if (vec) hysteresis_kernel<true, false><<<grid, 256, 0, st>>>(dW, Wp, Hp, p, N, K, pK, pH, idx_base);
+    else if (p.ftz) hysteresis_kernel<false, true><<<grid, 256, 0, st>>>(dW, Wp, Hp, p, N, K, pK, pH, idx_base);
+    else hysteresis_kernel<false, false><<<grid, 256, 0, st>>>(dW, Wp, Hp, p, N, K, pK, pH, idx_base);
     return check_launch();
 }
 
