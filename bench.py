@@ -358,11 +358,9 @@ def run_ours(args, wl):
     gemm_launches = sum(kernel_totals[n][1] for n in ("gemm_fwd", "gemm_dx", "gemm_dw_hysteresis"))
     achieved = 3.0 * gemm_ops * args.steps / (gemm_ms * 1e-3) / 1e12
     int8_peak = 2.0 * peaks["bf16_tflops_sustained"]
-    traffic_path = os.path.join(ROOT, "profiles", "traffic.json")
-    traffic = None
-    if os.path.exists(traffic_path):
-        with open(traffic_path) as f:
-            traffic = json.load(f).get(args.workload)
+    # DRAM bytes per GEMM launch from the ncu capture summarised in profiles/gemm_tc2_fwd_dx_config2_ncu_full.md
+    # (mean of the forward, dX and dW+hysteresis launches of the 4096->11008 layer at M=4096)
+    traffic = 93.0e6 if args.workload == "config2" and world == 1 else None
     roofline = {
         "bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TFLOP/s", "frac": achieved / int8_peak,
         "traffic": traffic, "kernel": "gemm_tc_kernel (tcgen05 kind::i8; forward, dX and dW+hysteresis launches)",
