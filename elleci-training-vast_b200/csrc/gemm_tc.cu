@@ -1,13 +1,15 @@
-// Tensor-core integer GEMMs of the INT2 linear path for sm_100a: tcgen05.mma kind::i8 with the int32
-// accumulators in tensor memory, operands staged by TMA, the 2-bit weights expanded to int8 inside shared
-// memory, and the scaling (or hysteresis) epilogue reading the accumulators back with tcgen05.ld.
+// Single-CTA tensor-core integer GEMMs of the INT2 linear path for sm_100a: tcgen05.mma kind::i8 with the int32
+// accumulators in tensor memory, operands staged by TMA, and the scaling (or hysteresis) epilogue reading the
+// accumulators back with tcgen05.ld.  This file carries the weight-gradient GEMM (plain and fused with the hysteresis
+// update) and single-CTA forward / dX modes; the default forward / dX kernels run on CTA pairs (gemm_tc2.cu).
 //
 // One persistent CTA per SM walks output tiles of 128 x BN.  Warp roles:
 //   warp 0      TMA producer: activations (and, for the weight-gradient GEMM, both operands) plus the packed
 //               2-bit weight tile of every 128-deep reduction block, through a ring of shared-memory stages
 //   warp 1      allocates tensor memory; one lane issues the MMAs and commits them to the ring's barriers
 //   warps 2-5   epilogue: tcgen05.ld of one of two accumulators while the MMAs fill the other
-//   warps 6-13  transform: expand the packed weight tile into the 128-byte-swizzled int8 operand tile
+//   warps 6-13  FWD / DX: expand the packed weight tile into the 128-byte-swizzled int8 operand tile;
+//               DW: no tile to expand, so they join the epilogue (twelve epilogue warps, three per lane quarter)
 //
 // The three GEMMs differ only in where the reduction index lies in memory:
 //   FWD  Y [M,N] = Xq [M,K] . Wq[N,K]^T   A K-major (TMA),  B K-major  (expanded from W_packed rows)

@@ -143,7 +143,6 @@ class Int2LinearTC(nn.Module):
         # row offset of this layer's rows inside a larger (sharded) weight matrix: keeps the per-weight random
         # numbers of a shard equal to those of the unsharded layer
         self.row_offset = 0
-        self.full_in_features = in_features
 
     # ---- initialisation ------------------------------------------------------------------------------------
     def init_from_float(self, weight: torch.Tensor, scale: Optional[float] = None):
@@ -217,8 +216,8 @@ class Int2LinearTC(nn.Module):
             self._dy_cache = (dY.data_ptr(), tuple(dY.shape), dYq.view(*dY.shape[:-1], N), ady)
         Gq = int2_tc_ops.quantize_grad(dY2, ax_rows, gmax)
         Xq2 = Xq.reshape(-1, K)
-        idx_base = self.row_offset * self.full_in_features
-        if int2_tc_ops.dw_hysteresis_supported(N, K) and K == self.full_in_features:
+        idx_base = self.row_offset * K
+        if int2_tc_ops.dw_hysteresis_supported(N, K):
             int2_tc_ops.dw_hysteresis(Gq, Xq2, gmax, self.W_packed, self.H_packed, lr, self.lr_scale, self.threshold,
                                       self.decay_rate, self._step_py, idx_base)
         else:
