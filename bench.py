@@ -223,6 +223,18 @@ def run_ours(args, wl):
         lay.x = torch.randn(M, K, generator=gen).to(torch.bfloat16).to(dev)
         lay.dY = (torch.randn(M, N, generator=gen) * wl["dy_std"]).to(torch.bfloat16).to(dev)
         lay.step = 0
+        lay.symm = None
+        if world > 1 and not args.no_fused_gather:
+            import torch.distributed._symmetric_memory as symm_mem
+            # two sets of buffers alternate between steps, which removes the barriers that would otherwise guard reuse
+            lay.symm, lay.symm_dx = [], []
+            for _ in range(2):
+                ybuf = symm_mem.empty((M, N), dtype=torch.bfloat16, device=dev)
+                lay.symm.append((ybuf, symm_mem.rendezvous(ybuf, dist.group.WORLD)))
+                parts = symm_mem.empty((world, M // world, K), dtype=torch.int32, device=dev)
+                dxbuf = symm_mem.empty((M, K), dtype=torch.bfloat16, device=dev)
+                lay.symm_dx.append((parts, symm_mem.rendezvous(parts, dist.group.WORLD), dxbuf,
+                                    symm_mem.rendezvous(dxbuf, dist.group.WORLD)))
         layers.append(lay)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)      # larger than the 126 MB L2
     timer = Timer(torch)
@@ -231,13 +243,23 @@ def run_ours(args, wl):
         """One layer: forward, then (reference order) the weight update, then dX."""
         K, Nl = lay.K, lay.Nl
         Xq, ax = timer.run("quantize_rows", ops.quantize_rows, lay.x)
-        y = timer.run("gemm_fwd", ops.matmul_rows, Xq, lay.Wp, ax, lay.gamma, torch.bfloat16)
-        if world > 1:
+        if lay.symm is not None:
+            # forward GEMM fused with the all-gather: the epilogue stores into every rank's Y over NVLink
+            ybuf, hdl = lay.symm[lay.step & 1]
+            timer.run("gemm_fwd", ops.matmul_rows_gather, Xq, lay.Wp, ax, lay.gamma, hdl.buffer_ptrs, lay.N, lay.n0, torch.bfloat16)
+            timer.run("barrier_post", hdl.barrier, channel=1)
+            y = ybuf
+        else:
+            y = timer.run("gemm_fwd", ops.matmul_rows, Xq, lay.Wp, ax, lay.gamma, torch.bfloat16)
+        if world > 1 and lay.symm is None:
             gathered = torch.empty(world * M, Nl, dtype=torch.bfloat16, device=dev)
             timer.run("all_gather_y", dist.all_gather_into_tensor, gathered, y)
             y = timer.run("permute_y", lambda t: t.view(world, M, Nl).permute(1, 0, 2).reshape(M, world * Nl), gathered)
         window = lay.dY[:, lay.n0:lay.n1] if world > 1 else lay.dY
-        if world > 1:
+        if world > 1 and lay.dY.numel() * 2 <= (256 << 20):
+            raw = timer.run("absmax_rows", ops.absmax_rows, lay.dY)      # replicated dY: scan all of it, no collective
+            dYq, ady, gmax = timer.run("quantize_rows_dy", ops.quantize_rows, window, ops.GRAD_EPS, ax, raw)
+        elif world > 1:
             raw = timer.run("absmax_rows", ops.absmax_rows, window)
             timer.run("all_reduce_absmax", dist.all_reduce, raw, op=dist.ReduceOp.MAX)
             dYq, ady, gmax = timer.run("quantize_rows_dy", ops.quantize_rows, window, ops.GRAD_EPS, ax, raw)
@@ -247,7 +269,16 @@ def run_ours(args, wl):
         lay.step += 1
         timer.run("gemm_dw_hysteresis", ops.dw_hysteresis, Gq, Xq, gmax, lay.Wp, lay.Hp, LR, LR_SCALE, thr, DECAY, lay.step,
                   lay.n0 * K)
-        if world > 1:
+        if lay.symm is not None:
+            # dX GEMM fused with the reduce-scatter of its int32 partial sums (epilogue TMA stores into the owners'
+            # staging buffers), then each rank sums + scales its rows and writes them into every rank's dX
+            parts, hp, dxbuf, hd = lay.symm_dx[lay.step & 1]
+            timer.run("gemm_dx", ops.backward_input_scatter, dYq, lay.Wp, K, hp.buffer_ptrs, rank)
+            timer.run("barrier_dx1", hp.barrier, channel=3)
+            timer.run("reduce_scale_gather", ops.reduce_scale_gather, parts, hd.buffer_ptrs, rank, ady, lay.gamma, M, K, torch.bfloat16)
+            timer.run("barrier_dx2", hd.barrier, channel=4)
+            dX = dxbuf
+        elif world > 1:
             acc = timer.run("gemm_dx", ops.backward_input_rows, dYq, lay.Wp, ady, lay.gamma, K, torch.int32)
             timer.run("all_reduce_dx", dist.all_reduce, acc)
             dX = timer.run("scale_rows", ops.scale_rows, acc, ady, lay.gamma, torch.bfloat16)
@@ -400,17 +431,21 @@ def run_ours(args, wl):
             gbs = b * args.steps / (ms * 1e-3) / 1e9
             hbm[n] = {"ms_per_launch": ms / cnt, "GBps": gbs, "frac_of_hbm": gbs / peaks["hbm_gbs"]}
     comm = {n: {"ms_per_step": kernel_totals[n][0] / args.steps} for n in kernel_totals
-            if n.startswith("all_") or n in ("permute_y", "scale_rows", "absmax_rows")}
+            if n.startswith("all_") or n.startswith("barrier_") or n in ("permute_y", "scale_rows", "absmax_rows", "reduce_scale_gather")}
 
     cpu = cpu_baseline_sample(wl, steps=2, warmup=1, sample_tokens=min(512, M)) if world == 1 and not args.no_cpu else None
 
-    own_launches = sum(cnt for n, (ms, cnt) in kernel_totals.items() if not n.startswith("all_") and n != "permute_y")
+    own_launches = sum(cnt for n, (ms, cnt) in kernel_totals.items()
+                       if not n.startswith("all_") and not n.startswith("barrier_") and n != "permute_y")
     line = {
         "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "int8 x int2 -> int32 (bf16 in/out)", "data": "synthetic",
         "config": {"workload": wl["desc"], "M": M, "layers": wl["layers"], "threshold": thr,
-                   "parallelism": f"N-sharded x{world}" if world > 1 else "single GPU",
+                   "parallelism": (f"N-sharded x{world}, " + ("Y all-gathered and dX all-reduced by NCCL" if args.no_fused_gather else
+                                                              "Y gathered and dX partial sums reduce-scattered by TMA stores from "
+                                                              "the GEMM epilogues, dX rows summed and re-gathered by peer stores")
+                                   ) if world > 1 else "single GPU",
                    "l2": "256 MiB written between timed steps (untimed)", "weights_changed_after_run": changed_frac},
         "clocks": clocks, "e2e": e2e, "gpu_launches": own_launches,
         "roofline": roofline, "gemm_modes": per_mode, "hbm_kernels": hbm,
@@ -491,6 +526,8 @@ def main():
     ap.add_argument("--workload", default="config2", choices=sorted(WORKLOADS) + ["config3"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg of the default run")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
+    ap.add_argument("--no-fused-gather", action="store_true",
+                    help="N > 1: all-gather the output with NCCL instead of TMA stores from the GEMM epilogue")
     args = ap.parse_args()
     if args.workload == "config3":
         if args.impl == "ours" and int(os.environ.get("RANK", "0")) == 0:

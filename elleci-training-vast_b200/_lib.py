@@ -35,6 +35,9 @@ SIGNATURES = {
     "el_quantize_grad": [_vp, _i, _ll, _vp, _vp, _vp, _i, _i, _vp],
     "el_scale_rows": [_vp, _vp, _i, _vp, _i, _f, _i, _i, _vp],
     "el_gemm_fwd": [_vp, _vp, _vp, _i, _vp, _i, _f, _i, _i, _i, _i, _vp, _vp],
+    "el_gemm_fwd_gather": [_vp, _vp, _vp, _i, _ll, _ll, _i, _vp, _i, _f, _i, _i, _i, _vp, _vp],
+    "el_gemm_dx_scatter": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp],
+    "el_reduce_scale_gather": [_vp, _vp, _i, _i, _i, _vp, _f, _i, _i, _vp],
     "el_gemm_dx": [_vp, _vp, _vp, _i, _vp, _i, _f, _i, _i, _i, _i, _vp, _vp],
     "el_gemm_dw": [_vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp, _vp],
     "el_decode_workspace_bytes": [_i],

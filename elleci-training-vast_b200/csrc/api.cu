@@ -24,7 +24,9 @@ int gemm_tc_eligible(int mode, const void* A, const void* B, int R, int C, int D
 int launch_gemm_tc(int mode, const int8_t* A, const void* B, int R, int C, int D, const EpiParams& epi, int32_t* status,
                    cudaStream_t st);
 int launch_gemm_tc2(int mode, const int8_t* A, const void* B, int R, int C, int D, const EpiParams& epi, int32_t* status,
-                    cudaStream_t st);
+                    cudaStream_t st, void* const* dst, int n_dst, long long ld_total, long long col_offset, int rows_per_dst);
+int launch_reduce_scale_gather(const int* parts, int n_parts, void* const* out_all, int n_ranks, long long row_offset,
+                               long long rows_total, const EpiParams& epi, int Mr, int C, cudaStream_t st);
 int launch_dw_hysteresis_tc(const int8_t* Gq, const int8_t* Xq, const float* g_absmax, uint8_t* Wp, uint8_t* Hp,
                             const HystParams& hp, uint32_t idx_base, int M, int N, int K, int32_t* status, cudaStream_t st);
 
@@ -94,7 +96,7 @@ static inline bool out_dtype_ok(int dt) { return dt == EL_F16 || dt == EL_BF16 |
 // Tensor-core launch: forward and dX run on CTA pairs unless the single-CTA kernel is asked for; dW has one kernel.
 static int launch_tc(int mode, bool single_cta, const int8_t* A, const void* B, int R, int C, int D, const EpiParams& epi,
                      int32_t* status, cudaStream_t st) {
-    if (mode != MODE_DW && !single_cta) return launch_gemm_tc2(mode, A, B, R, C, D, epi, status, st);
+    if (mode != MODE_DW && !single_cta) return launch_gemm_tc2(mode, A, B, R, C, D, epi, status, st, nullptr, 0, 0, 0, 0);
     return launch_gemm_tc(mode, A, B, R, C, D, epi, status, st);
 }
 
@@ -204,6 +206,46 @@ int el_gemm_fwd(const int8_t* Xq, const uint8_t* W_packed, void* Y, int out_dtyp
     if (!Y || !absmax || (K > 0 && (!Xq || !W_packed))) return EL_ERR_NULL_PTR;
     const EpiParams epi{Y, (long long)N, out_dtype, absmax, absmax_stride, gamma};
     return gemm_dispatch(MODE_FWD, Xq, W_packed, M, N, K, epi, flags, dev_status, (cudaStream_t)stream);
+}
+
+int el_gemm_fwd_gather(const int8_t* Xq, const uint8_t* W_packed, void* const* Y_all, int n_ranks, long long ld_total,
+                       long long col_offset, int out_dtype, const float* absmax, int absmax_stride, float gamma, int M, int N,
+                       int K, int32_t* dev_status, el_stream_t stream) {
+    if (M < 0 || N < 0 || K < 0 || !float_dtype(out_dtype) || (absmax_stride != 0 && absmax_stride != 1)) return EL_ERR_INVALID_ARG;
+    if (M == 0 || N == 0) return EL_OK;
+    if (!Y_all || !absmax || !Xq || !W_packed) return EL_ERR_NULL_PTR;
+    const EpiParams epi{nullptr, ld_total, out_dtype, absmax, absmax_stride, gamma};
+    return launch_gemm_tc2(MODE_FWD, Xq, W_packed, M, N, K, epi, dev_status, (cudaStream_t)stream, Y_all, n_ranks, ld_total,
+                           col_offset, 0);
+}
+
+int el_gemm_dx_scatter(const int8_t* dYq, const uint8_t* W_packed, void* const* parts_all, int n_ranks, int rank, int M, int N,
+                       int K, int32_t* dev_status, el_stream_t stream) {
+    if (M < 0 || N < 0 || K < 0 || n_ranks < 1 || n_ranks > 8 || rank < 0 || rank >= n_ranks) return EL_ERR_INVALID_ARG;
+    if (M == 0 || K == 0) return EL_OK;
+    if (M % (32 * n_ranks) != 0) return EL_ERR_UNSUPPORTED_SHAPE;
+    if (!dYq || !W_packed || !parts_all) return EL_ERR_NULL_PTR;
+    const int Mr = M / n_ranks;
+    void* dst[8];
+    for (int d = 0; d < n_ranks; ++d) {
+        if (!parts_all[d]) return EL_ERR_NULL_PTR;
+        dst[d] = static_cast<char*>(parts_all[d]) + (size_t)rank * Mr * K * sizeof(int);     // slot `rank` of owner d
+    }
+    const float one = 1.0f;
+    (void)one;
+    const EpiParams epi{nullptr, (long long)K, EL_I32, nullptr, 0, 1.0f};
+    return launch_gemm_tc2(MODE_DX, dYq, W_packed, M, K, N, epi, dev_status, (cudaStream_t)stream, dst, n_ranks, 0, 0, Mr);
+}
+
+int el_reduce_scale_gather(const int32_t* parts, void* const* dX_all, int n_ranks, int rank, int out_dtype, const float* absmax,
+                           float gamma, int M, int K, el_stream_t stream) {
+    if (M < 0 || K < 0 || n_ranks < 1 || n_ranks > 8 || rank < 0 || rank >= n_ranks || !float_dtype(out_dtype)) return EL_ERR_INVALID_ARG;
+    if (M == 0 || K == 0) return EL_OK;
+    if (M % n_ranks != 0 || K % 4 != 0) return EL_ERR_UNSUPPORTED_SHAPE;
+    if (!parts || !dX_all || !absmax) return EL_ERR_NULL_PTR;
+    const int Mr = M / n_ranks;
+    const EpiParams epi{nullptr, (long long)K, out_dtype, absmax + (size_t)rank * Mr, 1, gamma};
+    return launch_reduce_scale_gather(parts, n_ranks, dX_all, n_ranks, (long long)rank * Mr, M, epi, Mr, K, (cudaStream_t)stream);
 }
 
 int el_gemm_dx(const int8_t* dYq, const uint8_t* W_packed, void* dX, int out_dtype, const float* absmax, int absmax_stride,

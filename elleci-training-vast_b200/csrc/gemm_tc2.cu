@@ -41,19 +41,26 @@ constexpr int WARP_TMA = 0, WARP_MMA = 1, NUM_EPI_WARPS = 4, WARP_PTMA = 6, WARP
 constexpr int NUM_THREADS = (WARP_XF0 + NUM_XF_WARPS) * 32;     // 416
 constexpr uint32_t TMEM_COLS = 2 * BN;
 
+constexpr int MAX_DST = 8;         // output destinations of one launch (the ranks of an N-sharded layer)
+struct OutMaps {
+    CUtensorMap m[MAX_DST];
+};
+
 struct Params {
     int R, C, D;
     int tiles_r, tiles_c, k_blocks;     // tiles_r counts 256-row pair tiles
     EpiParams epi;
     int vec_ok;
     int tma_store;                      // the output takes TMA stores (16-byte aligned base and pitch)
+    int n_dst;                          // destinations that receive every output block (1 unless gathered over ranks)
+    int rows_per_dst;                   // > 0: scatter instead - rows [d*rows_per_dst, (d+1)*rows_per_dst) go to destination d only
     int32_t* status;
 };
 
 template <int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                const __grid_constant__ CUtensorMap tmOut, const Params p) {
+                const __grid_constant__ OutMaps outs, const Params p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -235,7 +242,14 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         fence_async_smem();
                         __syncwarp();
                         if (lane == 0) {
-                            tma_store_2d(&tmOut, stage + (c & 1) * 2048, col0, r0 + quarter * 32);
+                            const int rb = r0 + quarter * 32;
+                            if (p.rows_per_dst > 0) {              // scatter: this 32-row block belongs to one owner
+                                const int d = rb / p.rows_per_dst;
+                                if (d < p.n_dst) tma_store_2d(&outs.m[d], stage + (c & 1) * 2048, col0, rb - d * p.rows_per_dst);
+                            } else {
+                                for (int d = 0; d < p.n_dst; ++d)  // own buffer and, when gathering, every peer's
+                                    tma_store_2d(&outs.m[d], stage + (c & 1) * 2048, col0, rb);
+                            }
                             bulk_commit();
                         }
                     } else {
@@ -255,7 +269,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         fence_async_smem();
                         __syncwarp();
                         if (lane == 0) {
-                            tma_store_2d(&tmOut, stage, col0, r0 + quarter * 32);
+                            const int rb = r0 + quarter * 32;
+                            if (p.rows_per_dst > 0) {
+                                const int d = rb / p.rows_per_dst;
+                                if (d < p.n_dst) tma_store_2d(&outs.m[d], stage, col0, rb - d * p.rows_per_dst);
+                            } else {
+                                for (int d = 0; d < p.n_dst; ++d) tma_store_2d(&outs.m[d], stage, col0, rb);
+                            }
                             bulk_commit();
                         }
                     }
@@ -328,7 +348,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 }
 
 template <int MODE>
-static int launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmOut, Params& p, cudaStream_t st) {
+static int launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB, const OutMaps& outs, Params& p, cudaStream_t st) {
     static bool attr_set[64] = {};
     static int max_pairs[64] = {};
     int dev = 0;
@@ -365,7 +385,7 @@ static int launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtens
     if (p.k_blocks == 0) return EL_ERR_UNSUPPORTED_SHAPE;
     const int pairs = (int)(tiles < max_pairs[dev] ? tiles : max_pairs[dev]);
     cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
-    EL_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<MODE>, tmA, tmB, tmOut, p));
+    EL_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<MODE>, tmA, tmB, outs, p));
     return check_launch();
 }
 
@@ -379,8 +399,14 @@ int make_map_out(CUtensorMap* m, const void* base, uint64_t cols, uint64_t rows,
 int gemm_tc_eligible(int mode, const void* A, const void* B, int R, int C, int D);
 
 // Forward (mode 0) and dX (mode 1) on CTA pairs; same eligibility as the single-CTA kernel.
+// `dst` (optional): n_dst base pointers of [R, ld_total] output matrices that all receive this launch's [R, C] result
+// at column `col_offset` (the own buffer and the peers' buffers of an N-sharded layer: the all-gather of the output
+// happens as TMA stores from the epilogue).  With dst == nullptr the result goes to epi.out alone.
+// `rows_per_dst` > 0 selects the scatter form instead: dst[d] is a dense [rows_per_dst, C] matrix that receives the
+// rows [d*rows_per_dst, (d+1)*rows_per_dst) of the result (the reduce-scatter half of a cross-rank reduction of dX).
 int launch_gemm_tc2(int mode, const int8_t* A, const void* B, int R, int C, int D, const EpiParams& epi, int32_t* status,
-                    cudaStream_t st) {
+                    cudaStream_t st, void* const* dst, int n_dst, long long ld_total, long long col_offset,
+                    int rows_per_dst) {
     if (mode != MODE_FWD && mode != MODE_DX) return EL_ERR_INVALID_ARG;
     int rc = gemm_tc_eligible(mode, A, B, R, C, D);
     if (rc != EL_OK) return rc;
@@ -391,21 +417,42 @@ int launch_gemm_tc2(int mode, const int8_t* A, const void* B, int R, int C, int 
     p.epi = epi;
     p.status = status;
     const int esz = (epi.out_dtype == EL_BF16 || epi.out_dtype == EL_F16) ? 2 : 4;
-    p.vec_ok = ((reinterpret_cast<uintptr_t>(epi.out) & 15) == 0) && ((epi.ldo * esz) % 16 == 0);
-    CUtensorMap tmA, tmB, tmOut;
-    p.tma_store = p.vec_ok;
-    if (p.tma_store) {
-        if ((rc = tc::make_map_out(&tmOut, epi.out, C, R, (uint64_t)epi.ldo * esz, esz)) != EL_OK) return rc;
+    tc2::OutMaps outs{};
+    CUtensorMap tmA, tmB;
+    if (dst != nullptr && rows_per_dst > 0) {
+        if (n_dst < 1 || n_dst > tc2::MAX_DST || rows_per_dst % 32 != 0 || (long long)rows_per_dst * n_dst < R) return EL_ERR_INVALID_ARG;
+        for (int d = 0; d < n_dst; ++d) {
+            if (dst[d] == nullptr) return EL_ERR_NULL_PTR;
+            if ((rc = tc::make_map_out(&outs.m[d], dst[d], C, rows_per_dst, (uint64_t)C * esz, esz)) != EL_OK) return rc;
+        }
+        p.n_dst = n_dst;
+        p.rows_per_dst = rows_per_dst;
+        p.tma_store = 1;
+        p.vec_ok = 1;
+    } else if (dst != nullptr) {
+        if (n_dst < 1 || n_dst > tc2::MAX_DST || ld_total < col_offset + C || col_offset < 0) return EL_ERR_INVALID_ARG;
+        if (C % 32 != 0) return EL_ERR_UNSUPPORTED_SHAPE;      // 32-column store boxes must not reach into a neighbour's window
+        for (int d = 0; d < n_dst; ++d) {
+            if (dst[d] == nullptr) return EL_ERR_NULL_PTR;
+            const char* base = static_cast<const char*>(dst[d]) + col_offset * esz;
+            if ((rc = tc::make_map_out(&outs.m[d], base, C, R, (uint64_t)ld_total * esz, esz)) != EL_OK) return rc;
+        }
+        p.n_dst = n_dst;
+        p.tma_store = 1;
+        p.vec_ok = 1;
     } else {
-        tmOut = CUtensorMap{};
+        p.vec_ok = ((reinterpret_cast<uintptr_t>(epi.out) & 15) == 0) && ((epi.ldo * esz) % 16 == 0);
+        p.tma_store = p.vec_ok;
+        p.n_dst = 1;
+        if (p.tma_store && (rc = tc::make_map_out(&outs.m[0], epi.out, C, R, (uint64_t)epi.ldo * esz, esz)) != EL_OK) return rc;
     }
     if ((rc = tc::make_map(&tmA, A, D, R, D, 128, 128, true)) != EL_OK) return rc;
     if (mode == MODE_FWD) {
         if ((rc = tc::make_map(&tmB, B, D / 4, C, D / 4, 32, 128, false)) != EL_OK) return rc;
-        return tc2::launch_t<MODE_FWD>(tmA, tmB, tmOut, p, st);
+        return tc2::launch_t<MODE_FWD>(tmA, tmB, outs, p, st);
     }
     if ((rc = tc::make_map(&tmB, B, C / 4, D, C / 4, 32, 128, false)) != EL_OK) return rc;
-    return tc2::launch_t<MODE_DX>(tmA, tmB, tmOut, p, st);
+    return tc2::launch_t<MODE_DX>(tmA, tmB, outs, p, st);
 }
 
 }  // namespace el

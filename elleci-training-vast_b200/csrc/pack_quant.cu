@@ -435,4 +435,54 @@ int launch_scale_rows(const int* acc, const EpiParams& epi, int M, int C, cudaSt
     return check_launch();
 }
 
+// Cross-rank reduction, owner side: out rows = scale(sum over n_parts of parts[p][Mr, C]) written into the row window
+// [row_offset, row_offset + Mr) of every rank's output matrix (own buffer and peer mappings: plain stores over NVLink).
+struct GatherDst {
+    void* p[8];
+};
+
+__global__ void __launch_bounds__(256)
+reduce_scale_gather_kernel(const int* __restrict__ parts, int n_parts, GatherDst dst, int n_ranks, long long row_offset,
+                           EpiParams epi, int Mr, int C) {
+    const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const int cg = C >> 2;
+    if (t >= (long long)Mr * cg) return;
+    const int m = (int)(t / cg), c0 = (int)(t % cg) * 4;
+    const size_t part_stride = (size_t)Mr * C;
+    int4 sum = *reinterpret_cast<const int4*>(parts + (size_t)m * C + c0);
+    for (int p = 1; p < n_parts; ++p) {
+        const int4 v = *reinterpret_cast<const int4*>(parts + p * part_stride + (size_t)m * C + c0);
+        sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+    }
+    const float sc = epi_row_scale(epi, m);
+    const float f0 = __fmul_rn((float)sum.x, sc), f1 = __fmul_rn((float)sum.y, sc);
+    const float f2 = __fmul_rn((float)sum.z, sc), f3 = __fmul_rn((float)sum.w, sc);
+    const size_t o = (size_t)(row_offset + m) * C + c0;
+    for (int d = 0; d < n_ranks; ++d) {
+        if (epi.out_dtype == EL_F32) {
+            *reinterpret_cast<float4*>(static_cast<float*>(dst.p[d]) + o) = make_float4(f0, f1, f2, f3);
+        } else {
+            const uint32_t lo = (epi.out_dtype == EL_BF16) ? pack_bf16x2(f0, f1) : pack_f16x2(f0, f1);
+            const uint32_t hi = (epi.out_dtype == EL_BF16) ? pack_bf16x2(f2, f3) : pack_f16x2(f2, f3);
+            *reinterpret_cast<uint2*>(static_cast<uint16_t*>(dst.p[d]) + o) = make_uint2(lo, hi);
+        }
+    }
+}
+
+int launch_reduce_scale_gather(const int* parts, int n_parts, void* const* out_all, int n_ranks, long long row_offset,
+                               long long rows_total, const EpiParams& epi, int Mr, int C, cudaStream_t st) {
+    (void)rows_total;
+    GatherDst dst{};
+    for (int d = 0; d < n_ranks; ++d) {
+        if (out_all[d] == nullptr) return EL_ERR_NULL_PTR;
+        if (reinterpret_cast<uintptr_t>(out_all[d]) & 15) return EL_ERR_ALIGNMENT;
+        dst.p[d] = out_all[d];
+    }
+    if (reinterpret_cast<uintptr_t>(parts) & 15) return EL_ERR_ALIGNMENT;
+    const long long work = (long long)Mr * (C >> 2);
+    if (work == 0) return EL_OK;
+    reduce_scale_gather_kernel<<<(int)((work + 255) / 256), 256, 0, st>>>(parts, n_parts, dst, n_ranks, row_offset, epi, Mr, C);
+    return check_launch();
+}
+
 }  // namespace el

@@ -291,6 +291,58 @@ def matmul_rows(Xq: torch.Tensor, W_packed: torch.Tensor, row_absmax: torch.Tens
     return _gemm_fwd(Xq, W_packed, row_absmax, 1, gamma, out_dtype, path)
 
 
+def matmul_rows_gather(Xq: torch.Tensor, W_packed: torch.Tensor, row_absmax: torch.Tensor, gamma: float,
+                       out_ptrs, ld_total: int, col_offset: int, out_dtype: torch.dtype = torch.bfloat16) -> None:
+    """Forward GEMM of an N-shard whose epilogue writes the result into column window `col_offset` of every rank's
+    [M, ld_total] output buffer (`out_ptrs`: device addresses, own buffer and peer mappings): a fused all-gather."""
+    _cuda(Xq, "X_int8"); _cuda(W_packed, "W_packed"); _cuda(row_absmax, "row_absmax")
+    _require(Xq.dtype == torch.int8 and W_packed.dtype == torch.uint8, "Xq must be int8 and W_packed uint8")
+    N, pK = W_packed.shape
+    K = Xq.shape[-1]
+    _require((K + 3) // 4 == pK, f"X has {K} features but W_packed has packed_K={pK}")
+    Xf = Xq.contiguous().view(-1, K)
+    M = Xf.shape[0]
+    _require(row_absmax.numel() == M, "one absmax per token expected")
+    keep, arr = _ptr_array(out_ptrs)
+    st = device_status(Xq.device)
+    call("el_gemm_fwd_gather", Xf.data_ptr(), W_packed.contiguous().data_ptr(), arr, len(out_ptrs),
+         int(ld_total), int(col_offset), _DT[out_dtype], row_absmax.data_ptr(), 1, float(gamma), M, N, K, st.data_ptr(), _stream())
+    _maybe_check(Xq.device)
+
+
+def _ptr_array(ptrs):
+    import ctypes
+    arr = (ctypes.c_void_p * len(ptrs))(*[int(p) for p in ptrs])
+    return arr, ctypes.cast(arr, ctypes.c_void_p)
+
+
+def backward_input_scatter(dYq: torch.Tensor, W_packed: torch.Tensor, K: int, parts_ptrs, rank: int) -> None:
+    """dX GEMM of an N-shard whose epilogue scatters the int32 partial sums: token rows owned by rank d go to slot
+    `rank` of rank d's staging buffer [n_ranks, M/n_ranks, K] (`parts_ptrs`: device addresses, own and peer mappings)."""
+    _cuda(dYq, "dY_int8"); _cuda(W_packed, "W_packed")
+    _require(dYq.dtype == torch.int8 and W_packed.dtype == torch.uint8, "dYq must be int8 and W_packed uint8")
+    N = W_packed.shape[0]
+    Yf = dYq.contiguous().view(-1, N)
+    M = Yf.shape[0]
+    keep, arr = _ptr_array(parts_ptrs)
+    st = device_status(dYq.device)
+    call("el_gemm_dx_scatter", Yf.data_ptr(), W_packed.contiguous().data_ptr(), arr, len(parts_ptrs), int(rank), M, N, int(K),
+         st.data_ptr(), _stream())
+    _maybe_check(dYq.device)
+
+
+def reduce_scale_gather(parts: torch.Tensor, out_ptrs, rank: int, row_absmax: torch.Tensor, gamma: float, M: int, K: int,
+                        out_dtype: torch.dtype = torch.bfloat16) -> None:
+    """Owner side of the dX reduction: sums this rank's [n_ranks, M/n_ranks, K] int32 partials, scales them and writes
+    the rows into every rank's dX [M, K] (`out_ptrs`).  `row_absmax` holds the absmax of all M tokens."""
+    _cuda(parts, "parts")
+    _require(parts.dtype == torch.int32 and parts.is_contiguous(), "parts must be a contiguous int32 tensor")
+    _require(row_absmax.dtype == torch.float32 and row_absmax.numel() == M, "row_absmax must be float32 [M]")
+    keep, arr = _ptr_array(out_ptrs)
+    call("el_reduce_scale_gather", parts.data_ptr(), arr, len(out_ptrs), int(rank), _DT[out_dtype], row_absmax.data_ptr(),
+         float(gamma), int(M), int(K), _stream())
+
+
 def backward_input_rows(dYq: torch.Tensor, W_packed: torch.Tensor, row_absmax: torch.Tensor, gamma: float, K: int,
                         out_dtype: torch.dtype = torch.bfloat16, path: int = EL_PATH_AUTO) -> torch.Tensor:
     """dX[m,:] = (dYq[m,:] @ W) * (row_absmax[m]/127) * gamma: the dX GEMM with per-token scales."""

@@ -12,7 +12,12 @@ sees all M tokens).  The reference has no multi-GPU code; this is the sharding i
             all-reduce of M floats completes it
 
 Collectives go through torch.distributed (NCCL over NVLink on GPUs; gloo in the CPU tests, where a stand-in
-for the operator module is injected).
+for the operator module is injected).  With `fused_gather=True` (CUDA only) the forward all-gather is not a collective
+at all: the output of every rank lives in symmetric memory and each rank's GEMM epilogue writes its columns straight
+into all ranks' buffers with TMA stores over NVLink (`el_gemm_fwd_gather`), followed by one device-side barrier.  The
+dX reduction is fused the same way: the dX epilogue scatters its int32 partial rows to the rank that owns them
+(`el_gemm_dx_scatter`), the owner sums, scales and writes its rows of dX into every rank (`el_reduce_scale_gather`).
+Every symmetric buffer exists twice and calls alternate between the two, so no barrier guards the reuse of a buffer.
 """
 from __future__ import annotations
 
@@ -41,12 +46,23 @@ class _ShardedLinearFn(Function):
     @staticmethod
     def forward(ctx, x: torch.Tensor, gamma: torch.Tensor, layer: "ShardedInt2Linear") -> torch.Tensor:
         ops, grp = layer.ops, layer.group
-        K, Nl, g = layer.in_features, layer.local_out_features, layer.world
+        K, Nl, g, r_ = layer.in_features, layer.local_out_features, layer.world, layer.rank
         io = x.dtype if x.dtype in _FLOAT_IO else torch.bfloat16
         x2 = x.reshape(-1, K)
         Xq, ax = ops.quantize_rows(x2 if x2.dtype in _FLOAT_IO else x2.to(io), ACT_EPS)
-        y_local = ops.matmul_rows(Xq, layer.W_packed, ax, layer.gamma_value(), io)
         M = x2.shape[0]
+        if g > 1 and layer.fused_gather:
+            # Two output buffers alternate between calls.  A rank can only start call i+1 after the barrier of call i,
+            # by which time every rank has issued (in stream order) its reads of the buffer of call i-1: no barrier is
+            # needed before overwriting that buffer.
+            buf, hdl = layer._symmetric_output(M, io)
+            ops.matmul_rows_gather(Xq, layer.W_packed, ax, layer.gamma_value(), hdl.buffer_ptrs, g * Nl, r_ * Nl, io)
+            hdl.barrier(channel=1)          # every rank's stores into this rank's buffer have landed
+            y = buf.clone() if layer.copy_output else buf
+            ctx.layer, ctx.io, ctx.x_shape = layer, io, x.shape
+            ctx.saved = (Xq, ax) if layer.training else None
+            return y.view(*x.shape[:-1], g * Nl)
+        y_local = ops.matmul_rows(Xq, layer.W_packed, ax, layer.gamma_value(), io)
         if g > 1:
             gathered = torch.empty(g * M, Nl, dtype=io, device=x.device)     # rank-major concatenation
             dist.all_gather_into_tensor(gathered, y_local.contiguous(), group=grp)
@@ -66,9 +82,12 @@ class _ShardedLinearFn(Function):
         if dY2.dtype not in _FLOAT_IO:
             dY2 = dY2.to(ctx.io)
         window = dY2[:, r * Nl:(r + 1) * Nl]                # this rank's columns, read in place
-        raw = ops.absmax_rows(window)
-        if g > 1:
-            dist.all_reduce(raw, op=dist.ReduceOp.MAX, group=grp)
+        if g > 1 and dY2.numel() * dY2.element_size() <= layer.local_absmax_bytes:
+            raw = ops.absmax_rows(dY2)      # dY is replicated: for small gradients reading all of it beats a collective
+        else:
+            raw = ops.absmax_rows(window)
+            if g > 1:
+                dist.all_reduce(raw, op=dist.ReduceOp.MAX, group=grp)
         do_update = layer.training and layer.hysteresis_enabled and ctx.saved is not None
         if do_update:
             Xq, ax = ctx.saved
@@ -93,7 +112,17 @@ class _ShardedLinearFn(Function):
         dX = None
         if ctx.needs_input_grad[0]:
             gam = layer.gamma_value()
-            if g > 1:
+            M_tok = dY2.shape[0]
+            if g > 1 and layer.fused_gather and M_tok % (32 * g) == 0:
+                # reduce-scatter of the int32 partial sums as TMA stores from the dX epilogue, then each rank sums
+                # and scales the rows it owns and writes them into every rank's dX: no collective kernel
+                parts, hp, dxbuf, hd = layer._symmetric_dx(M_tok, ctx.io)     # alternating buffers, as in the forward
+                ops.backward_input_scatter(dYq, layer.W_packed, K, hp.buffer_ptrs, r)
+                hp.barrier(channel=3)       # all partial sums of my rows have landed
+                ops.reduce_scale_gather(parts, hd.buffer_ptrs, r, ady, gam, M_tok, K, ctx.io)
+                hd.barrier(channel=4)       # all rows of my dX have landed
+                dX = dxbuf.clone() if layer.copy_output else dxbuf
+            elif g > 1:
                 acc = ops.backward_input_rows(dYq, layer.W_packed, ady, gam, K, torch.int32)
                 dist.all_reduce(acc, op=dist.ReduceOp.SUM, group=grp)
                 dX = ops.scale_rows(acc, ady, gam, ctx.io)
@@ -110,7 +139,8 @@ class ShardedInt2Linear(nn.Module):
     `_step`) with the shard's row count; `ops` is the operator module (the CUDA one by default)."""
 
     def __init__(self, in_features: int, out_features: int, group: Optional[dist.ProcessGroup] = None, threshold: int = 7,
-                 lr_scale: float = 5.0, decay_rate: float = 0.001, hysteresis_order: str = "reference", ops=None):
+                 lr_scale: float = 5.0, decay_rate: float = 0.001, hysteresis_order: str = "reference", ops=None,
+                 fused_gather: bool = False, copy_output: bool = True):
         super().__init__()
         if ops is None:
             from . import int2_tc_ops as ops_mod
@@ -126,6 +156,12 @@ class ShardedInt2Linear(nn.Module):
         self.threshold, self.lr_scale, self.decay_rate = threshold, lr_scale, decay_rate
         self.hysteresis_order = hysteresis_order
         self.hysteresis_enabled = True
+        # fused_gather: forward all-gather as TMA stores from the GEMM epilogue into symmetric memory (CUDA only).
+        # copy_output=False hands out the symmetric buffer itself: valid until this layer's forward (backward) after next.
+        self.fused_gather = fused_gather
+        self.copy_output = copy_output
+        self._symm = {}
+        self.local_absmax_bytes = 256 << 20     # below this size every rank scans the whole replicated dY itself
         self._lr = 0.001
         self._step_py = 0
         self._gamma_cached: Optional[float] = None
@@ -136,6 +172,38 @@ class ShardedInt2Linear(nn.Module):
 
     def set_lr(self, lr: float):
         self._lr = lr
+
+    def _symmetric_output(self, M: int, dtype: torch.dtype):
+        """The [M, N] output buffer in symmetric memory and its rendezvous handle (allocated once per shape)."""
+        key = (M, dtype)
+        if key not in self._symm:
+            import torch.distributed._symmetric_memory as symm_mem
+            pair = []
+            for _ in range(2):
+                buf = symm_mem.empty((M, self.out_features), dtype=dtype, device=self.W_packed.device)
+                pair.append((buf, symm_mem.rendezvous(buf, self.group if self.group is not None else dist.group.WORLD)))
+            self._symm[key] = [pair, 0]
+        entry = self._symm[key]
+        entry[1] ^= 1
+        return entry[0][entry[1]]
+
+    def _symmetric_dx(self, M: int, dtype: torch.dtype):
+        """Staging buffer [g, M/g, K] int32 for incoming partial sums, the dX buffer [M, K], and their handles."""
+        key = ("dx", M, dtype)
+        if key not in self._symm:
+            import torch.distributed._symmetric_memory as symm_mem
+            grp = self.group if self.group is not None else dist.group.WORLD
+            pair = []
+            for _ in range(2):
+                parts = symm_mem.empty((self.world, M // self.world, self.in_features), dtype=torch.int32, device=self.W_packed.device)
+                hp = symm_mem.rendezvous(parts, grp)
+                dx = symm_mem.empty((M, self.in_features), dtype=dtype, device=self.W_packed.device)
+                hd = symm_mem.rendezvous(dx, grp)
+                pair.append((parts, hp, dx, hd))
+            self._symm[key] = [pair, 0]
+        entry = self._symm[key]
+        entry[1] ^= 1
+        return entry[0][entry[1]]
 
     def gamma_value(self) -> float:
         if self._gamma_cached is None:

@@ -138,12 +138,35 @@ EL_API int el_gemm_fwd(const int8_t* Xq, const uint8_t* W_packed, void* Y, int o
                 int absmax_stride, float gamma, int M, int N, int K, int flags, int32_t* dev_status,
                 el_stream_t stream);
 
+/* Forward GEMM of one N-shard fused with the all-gather of the output: the [M,N] result of el_gemm_fwd (N = this
+ * rank's rows of W_packed) is written at column col_offset of EVERY matrix Y_all[r] (r < n_ranks <= 8, each [M, ld_total]
+ * of out_dtype): the rank's own buffer and the peer-mapped buffers of the other ranks (symmetric memory / IPC
+ * mappings).  The epilogue sends each output block with TMA stores over NVLink while later tiles compute; there is no
+ * separate collective.  The caller orders the ranks (a barrier after the kernel before any rank reads Y, and before
+ * the next call overwrites it).  Needs the tensor-core path (K % 64 == 0), N % 32 == 0 and 16-byte aligned bases,
+ * pitch and col_offset.  No counterpart in the reference, which is single-GPU (README.md:58). */
+EL_API int el_gemm_fwd_gather(const int8_t* Xq, const uint8_t* W_packed, void* const* Y_all, int n_ranks, long long ld_total,
+                              long long col_offset, int out_dtype, const float* absmax, int absmax_stride, float gamma,
+                              int M, int N, int K, int32_t* dev_status, el_stream_t stream);
+
 /* dX[m,k] = out_dtype( float(sum_n dYq[m,n]*Wq[n,k]) * ((absmax[m*absmax_stride]/127) * gamma) ).
  * Tensor-core path needs N % 16 == 0 and K % 64 == 0.  Replaces int2_backward_dx_int8_tc_v2
  * (kernels/int2/int2_backward_int8_tc_v2.cu:465-499, binding tc_backward_input_int8 int2_tc_ops.cpp:435-470). */
 EL_API int el_gemm_dx(const int8_t* dYq, const uint8_t* W_packed, void* dX, int out_dtype, const float* absmax,
                int absmax_stride, float gamma, int M, int N, int K, int flags, int32_t* dev_status,
                el_stream_t stream);
+
+/* dX GEMM of one N-shard fused with the reduce-scatter of its partial sums: rank `rank` of n_ranks (<= 8) computes the
+ * int32 sums of el_gemm_dx over its rows of W_packed and the epilogue stores the token rows [d*M/n_ranks, (d+1)*M/n_ranks)
+ * into slot `rank` of parts_all[d], rank d's staging buffer of shape [n_ranks, M/n_ranks, K] int32 (own buffer or a
+ * peer mapping; TMA stores over NVLink).  After a barrier, rank d owns all partial sums of its rows:
+ * el_reduce_scale_gather adds them (exact), scales by (absmax[m]/127)*gamma and writes the rows into every rank's
+ * dX [M,K] (dX_all[r]), which completes the all-reduce.  Needs M % (32*n_ranks) == 0, N % 16 == 0, K % 64 == 0.
+ * No counterpart in the reference (single-GPU). */
+EL_API int el_gemm_dx_scatter(const int8_t* dYq, const uint8_t* W_packed, void* const* parts_all, int n_ranks, int rank,
+                              int M, int N, int K, int32_t* dev_status, el_stream_t stream);
+EL_API int el_reduce_scale_gather(const int32_t* parts, void* const* dX_all, int n_ranks, int rank, int out_dtype,
+                                  const float* absmax, float gamma, int M, int K, el_stream_t stream);
 
 /* dW[n,k] = float(sum_m Gq[m,n]*Xq[m,k]) * (g_absmax[0]/127)   (out_dtype EL_F32, or EL_I32 for the raw sums).
  * Tensor-core path needs N % 16 == 0 and K % 16 == 0.  Replaces `torch.mm(dY_2d.t(), X_2d).float()`

@@ -25,7 +25,7 @@ def _free_port():
     return port
 
 
-def _worker(rank, world, port, order, out_dir):
+def _worker(rank, world, port, order, out_dir, fused):
     sys.path.insert(0, HERE)
     sys.path.insert(0, os.path.dirname(HERE))
     os.environ["MASTER_ADDR"] = "127.0.0.1"
@@ -37,7 +37,7 @@ def _worker(rank, world, port, order, out_dir):
     try:
         pkg = load_package()
         d = make_layer_inputs(M, K, N, seed=3, dtype=torch.bfloat16, dy_std=1e-2, counters=1)
-        layer = pkg.sharded.ShardedInt2Linear(K, N, threshold=2, hysteresis_order=order).to(dev)
+        layer = pkg.sharded.ShardedInt2Linear(K, N, threshold=2, hysteresis_order=order, fused_gather=fused).to(dev)
         layer.load_shard(torch.from_numpy(d["Wp"]), torch.from_numpy(d["Hp"]), d["gamma"])
         layer.set_lr(0.5)
         x = d["x"].to(dev).requires_grad_(True)
@@ -51,8 +51,10 @@ def _worker(rank, world, port, order, out_dir):
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("fused", [False, True])
 @pytest.mark.parametrize("order", ["reference", "after_dx"])
-def test_sharded_step_on_gpus_equals_single_gpu(tmp_path, order):
+def test_sharded_step_on_gpus_equals_single_gpu(tmp_path, order, fused):
+    """fused=True: the forward all-gather happens as TMA stores from the GEMM epilogue into symmetric memory."""
     world = min(torch.cuda.device_count(), 4)
     if world < 2:
         pytest.skip("needs at least two GPUs")
@@ -70,7 +72,7 @@ def test_sharded_step_on_gpus_equals_single_gpu(tmp_path, order):
     y.backward(d["dY"].to("cuda:0"))
     torch.cuda.synchronize()
     assert not torch.equal(ref.W_packed.cpu(), torch.from_numpy(d["Wp"]))
-    mp.spawn(_worker, args=(world, _free_port(), order, str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), order, str(tmp_path), fused), nprocs=world, join=True)
     for r in range(world):
         res = torch.load(os.path.join(tmp_path, f"rank{r}.pt"))
         a, b = res["rows"]
