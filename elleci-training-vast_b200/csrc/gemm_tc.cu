@@ -330,19 +330,20 @@ int make_map(CUtensorMap* m, const void* base, uint64_t cols, uint64_t rows, uin
     return r == CUDA_SUCCESS ? EL_OK : EL_ERR_DRIVER;
 }
 
-// Output tensor [rows, cols] of 2- or 4-byte elements for the epilogue's TMA stores: boxes of 32 columns x 32 rows
-// (64-byte swizzle for 2-byte elements, 128-byte swizzle for 4-byte ones); the store clips at the edges.
-int make_map_out(CUtensorMap* m, const void* base, uint64_t cols, uint64_t rows, uint64_t pitch_bytes, int esz) {
+// Output tensor [rows, cols] of 2- or 4-byte elements for the epilogue's TMA stores: boxes of `box_cols` columns x 32
+// rows whose rows are 64 or 128 bytes (swizzled by that width); the store clips at the edges.
+int make_map_out(CUtensorMap* m, const void* base, uint64_t cols, uint64_t rows, uint64_t pitch_bytes, int esz, int box_cols) {
     EncodeTiledFn fn = get_encode_fn();
     if (fn == nullptr) return EL_ERR_DRIVER;
     if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (pitch_bytes & 15) != 0) return EL_ERR_ALIGNMENT;
     cuuint64_t dims[2] = {cols, rows};
     cuuint64_t strides[1] = {pitch_bytes};
-    cuuint32_t box[2] = {32, 32};
+    if (box_cols * esz != 64 && box_cols * esz != 128) return EL_ERR_INVALID_ARG;
+    cuuint32_t box[2] = {(cuuint32_t)box_cols, 32};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = fn(m, esz == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base),
                     dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    esz == 2 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                    box_cols * esz == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? EL_OK : EL_ERR_DRIVER;
 }

@@ -222,13 +222,17 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 }
                 if (p.tma_store) {
                     if (col0 >= p.C) continue;
-                    // The warp's 32 rows x 32 columns go to shared memory in the tensor map's swizzle, then out with
-                    // one TMA store (clipped at the matrix edges).  Two-byte outputs alternate between two 2 KB
-                    // buffers; before a buffer is rewritten the store that last read it must have finished reading.
+                    // The warp's 32 rows go to shared memory in the tensor map's 128-byte swizzle (32 columns of four-byte
+                    // or 64 columns of two-byte elements), then out with one TMA store, clipped at the matrix edges.
+                    // Before the buffer is rewritten the store that last read it must have finished reading.
                     if (two_byte) {
-                        if (lane == 0) bulk_wait_read<1>();
-                        __syncwarp();
-                        uint8_t* buf = stage_gen + (c & 1) * 2048 + lane * 64;
+                        // two 32-column chunks share one 4 KB buffer (32 rows x 128 bytes) and leave as one store
+                        const int h = c & 1;
+                        if (h == 0) {
+                            if (lane == 0) bulk_wait_read<0>();
+                            __syncwarp();
+                        }
+                        uint8_t* buf = stage_gen + lane * 128;
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
                             uint32_t o[4];
@@ -237,18 +241,19 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                                 const float lo = __fmul_rn((float)(int)v[8 * j + 2 * i], sc), hi = __fmul_rn((float)(int)v[8 * j + 2 * i + 1], sc);
                                 o[i] = (p.epi.out_dtype == EL_BF16) ? pack_bf16x2(lo, hi) : pack_f16x2(lo, hi);
                             }
-                            *reinterpret_cast<uint4*>(buf + ((j ^ ((lane >> 1) & 3)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                            *reinterpret_cast<uint4*>(buf + (((4 * h + j) ^ (lane & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
                         }
+                        if (h == 0 && col0 + 32 < p.C) continue;      // the second half of the box follows
                         fence_async_smem();
                         __syncwarp();
                         if (lane == 0) {
-                            const int rb = r0 + quarter * 32;
+                            const int rb = r0 + quarter * 32, cb = col0 - 32 * h;
                             if (p.rows_per_dst > 0) {              // scatter: this 32-row block belongs to one owner
                                 const int d = rb / p.rows_per_dst;
-                                if (d < p.n_dst) tma_store_2d(&outs.m[d], stage + (c & 1) * 2048, col0, rb - d * p.rows_per_dst);
+                                if (d < p.n_dst) tma_store_2d(&outs.m[d], stage, cb, rb - d * p.rows_per_dst);
                             } else {
                                 for (int d = 0; d < p.n_dst; ++d)  // own buffer and, when gathering, every peer's
-                                    tma_store_2d(&outs.m[d], stage + (c & 1) * 2048, col0, rb);
+                                    tma_store_2d(&outs.m[d], stage, cb, rb);
                             }
                             bulk_commit();
                         }
@@ -394,7 +399,7 @@ static int launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB, const OutMap
 namespace tc {
 int make_map(CUtensorMap* m, const void* base, uint64_t cols, uint64_t rows, uint64_t pitch, uint32_t box_cols,
              uint32_t box_rows, bool swizzle128);
-int make_map_out(CUtensorMap* m, const void* base, uint64_t cols, uint64_t rows, uint64_t pitch_bytes, int esz);
+int make_map_out(CUtensorMap* m, const void* base, uint64_t cols, uint64_t rows, uint64_t pitch_bytes, int esz, int box_cols);
 }
 int gemm_tc_eligible(int mode, const void* A, const void* B, int R, int C, int D);
 
@@ -423,7 +428,7 @@ int launch_gemm_tc2(int mode, const int8_t* A, const void* B, int R, int C, int 
         if (n_dst < 1 || n_dst > tc2::MAX_DST || rows_per_dst % 32 != 0 || (long long)rows_per_dst * n_dst < R) return EL_ERR_INVALID_ARG;
         for (int d = 0; d < n_dst; ++d) {
             if (dst[d] == nullptr) return EL_ERR_NULL_PTR;
-            if ((rc = tc::make_map_out(&outs.m[d], dst[d], C, rows_per_dst, (uint64_t)C * esz, esz)) != EL_OK) return rc;
+            if ((rc = tc::make_map_out(&outs.m[d], dst[d], C, rows_per_dst, (uint64_t)C * esz, esz, 128 / esz)) != EL_OK) return rc;
         }
         p.n_dst = n_dst;
         p.rows_per_dst = rows_per_dst;
@@ -435,7 +440,7 @@ int launch_gemm_tc2(int mode, const int8_t* A, const void* B, int R, int C, int 
         for (int d = 0; d < n_dst; ++d) {
             if (dst[d] == nullptr) return EL_ERR_NULL_PTR;
             const char* base = static_cast<const char*>(dst[d]) + col_offset * esz;
-            if ((rc = tc::make_map_out(&outs.m[d], base, C, R, (uint64_t)ld_total * esz, esz)) != EL_OK) return rc;
+            if ((rc = tc::make_map_out(&outs.m[d], base, C, R, (uint64_t)ld_total * esz, esz, 128 / esz)) != EL_OK) return rc;
         }
         p.n_dst = n_dst;
         p.tma_store = 1;
@@ -444,7 +449,7 @@ int launch_gemm_tc2(int mode, const int8_t* A, const void* B, int R, int C, int 
         p.vec_ok = ((reinterpret_cast<uintptr_t>(epi.out) & 15) == 0) && ((epi.ldo * esz) % 16 == 0);
         p.tma_store = p.vec_ok;
         p.n_dst = 1;
-        if (p.tma_store && (rc = tc::make_map_out(&outs.m[0], epi.out, C, R, (uint64_t)epi.ldo * esz, esz)) != EL_OK) return rc;
+        if (p.tma_store && (rc = tc::make_map_out(&outs.m[0], epi.out, C, R, (uint64_t)epi.ldo * esz, esz, 128 / esz)) != EL_OK) return rc;
     }
     if ((rc = tc::make_map(&tmA, A, D, R, D, 128, 128, true)) != EL_OK) return rc;
     if (mode == MODE_FWD) {
