@@ -42,6 +42,7 @@ SIGNATURES = {
     "el_gemm_dw": [_vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp, _vp],
     "el_decode_workspace_bytes": [_i],
     "el_set_decode_gemv_max_tokens": [_i],
+    "el_set_decode_overlap": [_i],
     "el_linear_decode": [_vp, _i, _vp, _vp, _i, _f, _vp, _vp, _vp, C.c_size_t, _i, _i, _i, _vp, _vp],
     "el_linear_decode_static": [_vp, _i, _vp, _vp, _i, _f, _i, _i, _i, _vp, _vp],
     "el_hysteresis_from_dw": [_vp, _vp, _vp, _f, _f, _i, _f, _i, _i, _i, _u32, _i, _vp],

@@ -36,7 +36,7 @@ size_t decode_workspace_bytes(int N);
 int launch_decode_tc(const int8_t* Xq, const uint8_t* Wp, const EpiParams& epi, void* workspace, int M, int N, int K,
                      int32_t* status, cudaStream_t st);
 
-int launch_gemv_small(const void* x, int x_dtype, const uint8_t* Wp, const EpiParams& epi, int M, int N, int K, cudaStream_t st);
+int launch_gemv_small(const void* x, int x_dtype, const uint8_t* Wp, const EpiParams& epi, int M, int N, int K, cudaStream_t st, bool overlap);
 int decode_gemv_max_tokens();
 
 static thread_local int g_last_cuda_error = 0;
@@ -82,6 +82,8 @@ int device_sm_count(int* out) { return device_info(out, nullptr); }
 // Token count up to which the decode call uses the CUDA-core GEMV (el_set_decode_gemv_max_tokens).
 static int g_gemv_max_tokens = 4;
 int decode_gemv_max_tokens() { return g_gemv_max_tokens; }
+static int g_decode_overlap = 0;
+bool decode_overlap() { return g_decode_overlap != 0; }
 
 int require_sm100() {
     int major = 0;
@@ -294,6 +296,11 @@ int el_set_decode_gemv_max_tokens(int max_tokens) {
     return EL_OK;
 }
 
+int el_set_decode_overlap(int enable) {
+    g_decode_overlap = enable ? 1 : 0;
+    return EL_OK;
+}
+
 size_t el_decode_workspace_bytes(int N) { return N > 0 ? decode_workspace_bytes(N) : 0; }
 
 int el_linear_decode(const void* x, int x_dtype, const uint8_t* W_packed, void* Y, int out_dtype, float gamma,
@@ -306,7 +313,7 @@ int el_linear_decode(const void* x, int x_dtype, const uint8_t* W_packed, void* 
     if (workspace_bytes < decode_workspace_bytes(N)) return EL_ERR_INVALID_ARG;
     if (M <= decode_gemv_max_tokens()) {      // a handful of tokens: one CUDA-core launch, no scratch touched
         const EpiParams gepi{Y, (long long)N, out_dtype, nullptr, 0, gamma};
-        return launch_gemv_small(x, x_dtype, W_packed, gepi, M, N, K, (cudaStream_t)stream);
+        return launch_gemv_small(x, x_dtype, W_packed, gepi, M, N, K, (cudaStream_t)stream, decode_overlap());
     }
     int rc = launch_quantize_rows_perm(x, x_dtype, K, xq_scratch, absmax, M, K, 1e-5f, (cudaStream_t)stream);
     if (rc != EL_OK) return rc;

@@ -361,7 +361,8 @@ static int decode_static_setup(unsigned char** out) {
 
 int launch_quantize_rows_perm(const void* x, int dt, long long ldx, int8_t* q, float* a, int M, int K, float eps,
                               cudaStream_t st);
-int launch_gemv_small(const void* x, int x_dtype, const uint8_t* Wp, const EpiParams& epi, int M, int N, int K, cudaStream_t st);
+int launch_gemv_small(const void* x, int x_dtype, const uint8_t* Wp, const EpiParams& epi, int M, int N, int K, cudaStream_t st, bool overlap);
+bool decode_overlap();
 int decode_gemv_max_tokens();
 
 }  // namespace el
@@ -378,7 +379,7 @@ extern "C" EL_API int el_linear_decode_static(const void* x, int x_dtype, const 
     cudaStream_t st = (cudaStream_t)stream;
     if (M <= decode_gemv_max_tokens()) {      // the few-token kernel needs no scratch at all
         const EpiParams gepi{Y, (long long)N, out_dtype, nullptr, 0, gamma};
-        return launch_gemv_small(x, x_dtype, W_packed, gepi, M, N, K, st);
+        return launch_gemv_small(x, x_dtype, W_packed, gepi, M, N, K, st, decode_overlap());
     }
     unsigned char* base = nullptr;
     int rc = decode_static_setup(&base);

@@ -46,12 +46,41 @@ template <> __device__ __forceinline__ void gv_load16<float>(const float* p, flo
     }
 }
 
-constexpr int GV_THREADS = 256;
+// round-to-nearest-even and clamp to [-128, 127] in one conversion; NaN gives 0
+__device__ __forceinline__ int gv_quant(float v) {
+    int q;
+    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q) : "f"(v));
+    return q;
+}
+
+// Quantises 16 consecutive values of one token and stores them in the lane order of phase 2.  CHECKED: non-finite
+// values count as zero (the slow path, taken only when a token holds an infinity).
+template <typename T, bool CHECKED>
+__device__ __forceinline__ uint4 gv_quant16(const T* src, float s) {
+    float v[16];
+    gv_load16<T>(src, v);
+    int q[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) q[i] = gv_quant(__fmul_rn(CHECKED ? finite_or_zero(v[i]) : v[i], s));
+    uint32_t w[4];
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+        // bytes 4g..4g+3 of the output take the sources p<8 ? 2p : 2(p-8)+1
+        const int p0 = 4 * g;
+        const int s0 = (p0 < 8) ? 2 * p0 : 2 * (p0 - 8) + 1;           // sources s0, s0+2, s0+4, s0+6
+        const uint32_t lo = __byte_perm((uint32_t)q[s0], (uint32_t)q[s0 + 2], 0x0040);
+        const uint32_t hi = __byte_perm((uint32_t)q[s0 + 4], (uint32_t)q[s0 + 6], 0x0040);
+        w[g] = __byte_perm(lo, hi, 0x5410);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
 
 // Shared memory: float amax[MT]; then per token ceil(K/2048)*128 uint4 (chunk i of 64 weights -> four uint4 at
 // ((i/32)*4 + j)*32 + i%32, so that consecutive lanes read consecutive 16-byte words).
-template <typename T, int MT, int RB>
-__global__ void __launch_bounds__(GV_THREADS, (MT <= 4) ? 3 : 2)
+// One CTA of THREADS threads per SM: the token quantisation of phase 1 is repeated by every CTA, so few large CTAs
+// keep its share of the instruction count small.
+template <typename T, int MT, int RB, int THREADS>
+__global__ void __launch_bounds__(THREADS, 1)
 gemv_small_kernel(const T* __restrict__ x, const uint8_t* __restrict__ Wp, EpiParams epi, int M, int N, int K, float eps) {
     extern __shared__ uint4 gv_smem[];
     float* s_amax = reinterpret_cast<float*>(gv_smem);
@@ -59,16 +88,18 @@ gemv_small_kernel(const T* __restrict__ x, const uint8_t* __restrict__ Wp, EpiPa
     const int chunks = K >> 6;                    // 64 weights per chunk
     const int xs_per_m = ((chunks + 31) >> 5) * 128;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    constexpr int WARPS = THREADS / 32;
 
     // ---- phase 0: the first batch of packed weights is requested before anything else ------------------------------------
     // A warp works on RB rows at once and on two 64-weight chunks per lane and row, so that 2*RB 16-byte loads per
     // lane are in flight: a row of 1024 packed bytes alone would leave the warp waiting on one memory latency per row.
-    // The host picks RB so that the grid is a single wave in which every warp has exactly one batch of RB rows.  The
-    // loads do not depend on the tokens, so their DRAM latency runs under the quantisation of phase 1; when the launch
-    // is a programmatic dependent launch they also run under the tail of the previous kernel of the stream.
+    // Warp w of CTA b is warp number w*gridDim.x + b of the grid and takes the rows congruent to that number: rows that
+    // do not divide evenly among the warps are spread over all CTAs.  The host picks RB so that a warp's rows are one
+    // batch.  The loads do not depend on the tokens, so their DRAM latency runs under the quantisation of phase 1;
+    // when the launch is a programmatic dependent launch they also run under the tail of the previous kernel.
     const int pK = K >> 2;
-    const int warps_total = gridDim.x * (GV_THREADS / 32);
-    const int nb_first = blockIdx.x * (GV_THREADS / 32) + warp;
+    const int warps_total = gridDim.x * WARPS;
+    const int nb_first = warp * gridDim.x + blockIdx.x;
     uint4 pk[2][RB];
     auto load_batch = [&](int nb, int i0) {
 #pragma unroll
@@ -89,21 +120,24 @@ gemv_small_kernel(const T* __restrict__ x, const uint8_t* __restrict__ Wp, EpiPa
     bool prefetched = true;
 
     // ---- phase 1: per-token absmax, then int8 into shared memory -----------------------------------------------------
+    // fmaxf drops NaN operands and keeps infinities: a finite maximum means that the token holds no infinity, and NaN
+    // quantises to 0 by the conversion itself, which is what counting non-finite values as zero gives.
+    __shared__ float red[MT][WARPS];
+    __shared__ int s_checked;
     float amax[MT];
 #pragma unroll
     for (int m = 0; m < MT; ++m) amax[m] = 0.0f;
-    for (int g = tid; g < (K >> 4); g += GV_THREADS) {
+    for (int g = tid; g < (K >> 4); g += THREADS) {
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
             if (m < M) {
                 float v[16];
                 gv_load16<T>(x + (size_t)m * K + g * 16, v);
 #pragma unroll
-                for (int i = 0; i < 16; ++i) amax[m] = fmaxf(amax[m], fabsf(finite_or_zero(v[i])));
+                for (int i = 0; i < 16; ++i) amax[m] = fmaxf(amax[m], fabsf(v[i]));
             }
         }
     }
-    __shared__ float red[MT][GV_THREADS / 32];
 #pragma unroll
     for (int m = 0; m < MT; ++m) {
         float v = amax[m];
@@ -112,31 +146,58 @@ gemv_small_kernel(const T* __restrict__ x, const uint8_t* __restrict__ Wp, EpiPa
         if (lane == 0) red[m][warp] = v;
     }
     __syncthreads();
-    if (tid < MT) {
-        float v = 0.0f;
-#pragma unroll
-        for (int w = 0; w < GV_THREADS / 32; ++w) v = fmaxf(v, red[tid][w]);
-        s_amax[tid] = fmaxf(v, eps);
+    if (tid == 0) {
+        bool inf_seen = false;
+        for (int m = 0; m < MT; ++m) {
+            float v = 0.0f;
+            for (int w = 0; w < WARPS; ++w) v = fmaxf(v, red[m][w]);
+            inf_seen = inf_seen || !(v <= 3.402823466e38f);
+            s_amax[m] = fmaxf(v, eps);
+        }
+        s_checked = inf_seen ? 1 : 0;
     }
     __syncthreads();
-    for (int g = tid; g < (K >> 4); g += GV_THREADS) {
+    if (s_checked) {
+        // some token holds an infinity: redo the maxima with non-finite values counted as zero
+        __syncthreads();
+#pragma unroll
+        for (int m = 0; m < MT; ++m) amax[m] = 0.0f;
+        for (int g = tid; g < (K >> 4); g += THREADS) {
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+                if (m < M) {
+                    float v[16];
+                    gv_load16<T>(x + (size_t)m * K + g * 16, v);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) amax[m] = fmaxf(amax[m], fabsf(finite_or_zero(v[i])));
+                }
+            }
+        }
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            float v = amax[m];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+            if (lane == 0) red[m][warp] = v;
+        }
+        __syncthreads();
+        if (tid < MT) {
+            float v = 0.0f;
+            for (int w = 0; w < WARPS; ++w) v = fmaxf(v, red[tid][w]);
+            s_amax[tid] = fmaxf(v, eps);
+        }
+        __syncthreads();
+    }
+    const bool checked = s_checked != 0;
+    for (int g = tid; g < (K >> 4); g += THREADS) {
         const int i = g >> 2, j = g & 3;
         const int slot = ((i >> 5) * 4 + j) * 32 + (i & 31);
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
             if (m < M) {
-                float v[16];
-                gv_load16<T>(x + (size_t)m * K + g * 16, v);
                 const float s = __fdiv_rn(127.0f, s_amax[m]);
-                uint32_t w[4] = {0, 0, 0, 0};
-#pragma unroll
-                for (int p = 0; p < 16; ++p) {
-                    const int src = (p < 8) ? 2 * p : 2 * (p - 8) + 1;
-                    float r = rintf(__fmul_rn(finite_or_zero(v[src]), s));
-                    r = fminf(127.0f, fmaxf(-128.0f, r));
-                    w[p >> 2] |= (uint32_t)((int)r & 0xFF) << (8 * (p & 3));
-                }
-                xs[m * xs_per_m + slot] = make_uint4(w[0], w[1], w[2], w[3]);
+                const T* src = x + (size_t)m * K + g * 16;
+                xs[m * xs_per_m + slot] = checked ? gv_quant16<T, true>(src, s) : gv_quant16<T, false>(src, s);
             }
         }
     }
@@ -164,6 +225,7 @@ gemv_small_kernel(const T* __restrict__ x, const uint8_t* __restrict__ Wp, EpiPa
                     for (int m = 0; m < MT; ++m) xv[m] = (m < M) ? xs[m * xs_per_m + base + j * 32] : make_uint4(0, 0, 0, 0);
 #pragma unroll
                     for (int r = 0; r < RB; ++r) {
+                        if (r > 0 && nb + r * warps_total >= N) continue;      // same for the whole warp
                         const uint32_t word = (j == 0) ? pk[u][r].x : (j == 1) ? pk[u][r].y : (j == 2) ? pk[u][r].z : pk[u][r].w;
                         uint32_t wv[4];
                         decode16_deint(word, wv);
@@ -180,13 +242,14 @@ gemv_small_kernel(const T* __restrict__ x, const uint8_t* __restrict__ Wp, EpiPa
         }
 #pragma unroll
         for (int r = 0; r < RB; ++r) {
+            const int n = nb + r * warps_total;
+            if (n >= N) continue;
 #pragma unroll
             for (int m = 0; m < MT; ++m) {
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) acc[r][m] += __shfl_xor_sync(0xffffffffu, acc[r][m], o);
             }
-            const int n = nb + r * warps_total;
-            if (lane == 0 && n < N) {
+            if (lane == 0) {
 #pragma unroll
                 for (int m = 0; m < MT; ++m) {
                     if (m < M) {
@@ -199,58 +262,67 @@ gemv_small_kernel(const T* __restrict__ x, const uint8_t* __restrict__ Wp, EpiPa
     }
 }
 
-template <typename T, int MT, int RB>
+template <typename T, int MT, int RB, int THREADS>
 static int launch_gemv_rb(const T* x, const uint8_t* Wp, const EpiParams& epi, int M, int N, int K, size_t smem, int grid,
-                          cudaStream_t st) {
+                          cudaStream_t st, bool overlap) {
     static bool attr_set[64] = {};
     int dev = 0;
     EL_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-        EL_CUDA_TRY(cudaFuncSetAttribute(gemv_small_kernel<T, MT, RB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        EL_CUDA_TRY(cudaFuncSetAttribute(gemv_small_kernel<T, MT, RB, THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
-    gemv_small_kernel<T, MT, RB><<<grid, GV_THREADS, smem, st>>>(x, Wp, epi, M, N, K, 1e-5f);
+    // overlap: programmatic dependent launch.  The kernel may start while earlier work of the stream still runs; it only
+    // loads packed weights until its griddepcontrol.wait, which returns once that earlier work has completed.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = overlap ? 1 : 0;
+    EL_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_small_kernel<T, MT, RB, THREADS>, x, Wp, epi, M, N, K, 1e-5f));
     return check_launch();
 }
 
 template <typename T, int MT>
-static int launch_gemv_t(const T* x, const uint8_t* Wp, const EpiParams& epi, int M, int N, int K, cudaStream_t st) {
+static int launch_gemv_t(const T* x, const uint8_t* Wp, const EpiParams& epi, int M, int N, int K, cudaStream_t st, bool overlap) {
+    constexpr int THREADS = (MT <= 2) ? 768 : (MT <= 4) ? 512 : 384;       // by registers: one CTA per SM each time
+    constexpr int WARPS = THREADS / 32;
     const int chunks = K >> 6;
     const size_t smem = 32 + (size_t)MT * (((chunks + 31) >> 5) * 128) * sizeof(uint4);
     if (smem > 200 * 1024) return EL_ERR_UNSUPPORTED_SHAPE;
     int sms = 0;
     const int rc = device_sm_count(&sms);
     if (rc != EL_OK) return rc;
-    // resident CTAs per SM: three by registers for up to four tokens, two otherwise; fewer when shared memory binds
-    int per_sm = (MT <= 4) ? 3 : 2;
-    while (per_sm > 1 && smem * per_sm > 200 * 1024) --per_sm;
-    const int slots = sms * per_sm;
-    const int rows_per_cta1 = GV_THREADS / 32;
-    // smallest batch (1, 2 or 4 rows per warp) whose grid fits in one wave; 4 if even that needs more than one
-    int rb = 1;
-    while (rb < 4 && (N + rows_per_cta1 * rb - 1) / (rows_per_cta1 * rb) > slots) rb *= 2;
-    const int grid = (N + rows_per_cta1 * rb - 1) / (rows_per_cta1 * rb);
-    if (rb == 1) return launch_gemv_rb<T, MT, 1>(x, Wp, epi, M, N, K, smem, grid, st);
-    if (rb == 2) return launch_gemv_rb<T, MT, 2>(x, Wp, epi, M, N, K, smem, grid < slots ? grid : slots, st);
-    return launch_gemv_rb<T, MT, 4>(x, Wp, epi, M, N, K, smem, grid < slots ? grid : slots, st);
+    int grid = (N + WARPS - 1) / WARPS;
+    if (grid > sms) grid = sms;
+    // smallest batch (1, 2 or 4 rows per warp) that covers a warp's rows in one pass; 4 if even that needs several
+    const int per_warp = (N + grid * WARPS - 1) / (grid * WARPS);
+    if (per_warp <= 1) return launch_gemv_rb<T, MT, 1, THREADS>(x, Wp, epi, M, N, K, smem, grid, st, overlap);
+    if (per_warp <= 2) return launch_gemv_rb<T, MT, 2, THREADS>(x, Wp, epi, M, N, K, smem, grid, st, overlap);
+    return launch_gemv_rb<T, MT, 4, THREADS>(x, Wp, epi, M, N, K, smem, grid, st, overlap);
 }
 
 template <typename T>
-static int launch_gemv_m(const T* x, const uint8_t* Wp, const EpiParams& epi, int M, int N, int K, cudaStream_t st) {
-    if (M <= 1) return launch_gemv_t<T, 1>(x, Wp, epi, M, N, K, st);
-    if (M <= 2) return launch_gemv_t<T, 2>(x, Wp, epi, M, N, K, st);
-    if (M <= 4) return launch_gemv_t<T, 4>(x, Wp, epi, M, N, K, st);
-    return launch_gemv_t<T, 8>(x, Wp, epi, M, N, K, st);
+static int launch_gemv_m(const T* x, const uint8_t* Wp, const EpiParams& epi, int M, int N, int K, cudaStream_t st, bool overlap) {
+    if (M <= 1) return launch_gemv_t<T, 1>(x, Wp, epi, M, N, K, st, overlap);
+    if (M <= 2) return launch_gemv_t<T, 2>(x, Wp, epi, M, N, K, st, overlap);
+    if (M <= 4) return launch_gemv_t<T, 4>(x, Wp, epi, M, N, K, st, overlap);
+    return launch_gemv_t<T, 8>(x, Wp, epi, M, N, K, st, overlap);
 }
 
 // x [M,K] float (16-byte aligned rows), 1 <= M <= 8, K % 64 == 0.  epi.absmax is not read: the scales are computed here.
-int launch_gemv_small(const void* x, int x_dtype, const uint8_t* Wp, const EpiParams& epi, int M, int N, int K, cudaStream_t st) {
+int launch_gemv_small(const void* x, int x_dtype, const uint8_t* Wp, const EpiParams& epi, int M, int N, int K, cudaStream_t st, bool overlap) {
     if (M < 1 || M > 8 || K % 64 != 0) return EL_ERR_UNSUPPORTED_SHAPE;
     if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(Wp) & 15)) return EL_ERR_ALIGNMENT;
     switch (x_dtype) {
-        case EL_BF16: return launch_gemv_m((const __nv_bfloat16*)x, Wp, epi, M, N, K, st);
-        case EL_F16: return launch_gemv_m((const __half*)x, Wp, epi, M, N, K, st);
-        case EL_F32: return launch_gemv_m((const float*)x, Wp, epi, M, N, K, st);
+        case EL_BF16: return launch_gemv_m((const __nv_bfloat16*)x, Wp, epi, M, N, K, st, overlap);
+        case EL_F16: return launch_gemv_m((const __half*)x, Wp, epi, M, N, K, st, overlap);
+        case EL_F32: return launch_gemv_m((const float*)x, Wp, epi, M, N, K, st, overlap);
         default: return EL_ERR_INVALID_ARG;
     }
 }

@@ -444,6 +444,13 @@ def linear_decode(x: torch.Tensor, W_packed: torch.Tensor, gamma: float, out_dty
     return Y.view(*x.shape[:-1], N)
 
 
+def set_decode_overlap(enable: bool) -> None:
+    """Lets consecutive small-M decode calls (up to the GEMV token limit) overlap: the call is issued as a programmatic
+    dependent launch that loads its packed weights while earlier work of the stream finishes, and reads x / writes Y
+    only afterwards.  Only valid while nothing queued on the stream writes W_packed (inference).  Process-wide."""
+    call("el_set_decode_overlap", 1 if enable else 0)
+
+
 def linear_decode_static(x: torch.Tensor, W_packed: torch.Tensor, gamma: float, out: torch.Tensor) -> torch.Tensor:
     """linear_decode for hosts that cannot allocate device memory: the library call behind it keeps its scratch in
     a static device array (M <= 64, N <= 16384, K <= 16384) and writes into the caller's `out` [M, N].  Calls on one

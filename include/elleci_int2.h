@@ -208,6 +208,12 @@ EL_API size_t el_decode_workspace_bytes(int N);
 /* Tuning: calls with at most `max_tokens` tokens (0..8, default 4) take a single-launch CUDA-core GEMV that
  * quantises the tokens itself and touches no scratch; larger ones take the tensor-core kernel.  Process-wide. */
 EL_API int el_set_decode_gemv_max_tokens(int max_tokens);
+/* Tuning, off by default: with `enable` != 0 the single-launch GEMV of el_linear_decode is issued as a programmatic
+ * dependent launch.  It may then start while earlier work of the stream still runs; until that work has completed it
+ * only loads W_packed, and it reads x and writes Y afterwards.  Enable it only when nothing queued earlier on the
+ * stream writes W_packed (inference: the weights are constant).  Consecutive decode calls then overlap their weight
+ * loads with the tail of the previous call.  Process-wide; no counterpart in the reference. */
+EL_API int el_set_decode_overlap(int enable);
 EL_API int el_linear_decode(const void* x, int x_dtype, const uint8_t* W_packed, void* Y, int out_dtype, float gamma,
                             int8_t* xq_scratch, float* absmax, void* workspace, size_t workspace_bytes, int M, int N,
                             int K, int32_t* dev_status, el_stream_t stream);

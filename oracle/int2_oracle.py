@@ -17,11 +17,14 @@ reference project root):
 * forward / dX integer GEMMs and their epilogue .. kernels/int2/int2_matmul_int8_tc_v2.cu:118-121,261
                                                    kernels/int2/int2_backward_int8_tc_v2.cu:88-92,233
 * hysteresis update .............................. kernels/int2/int2_hysteresis_v2.cu:54-152
+* pre-linear RMSNorm ............................. core/bitnet/bitnet_int2_optimized.py:72-86,
+                                                   model/common/bitnet_legacy.py:10-25
 
 Parity status: packing, ternarisation and per-token quantisation are pinned against the
 reference's own Python code (imported from the reference tree by tests/golden/make_golden.py);
 the hysteresis update is pinned against the reference kernel source compiled for the host
-(oracle/build_ref.sh).  The weight-gradient GEMM has no reproducible definition in the reference
+(oracle/build_ref.sh).  The pre-linear RMSNorm is pinned against the reference's module within floating-point
+tolerance (its row sums follow torch's summation order, which this restatement replaces by an exact one).  The weight-gradient GEMM has no reproducible definition in the reference
 (it is a library fp16 GEMM whose values no reference test pins): the integer definition used
 here (`grad_quantize` + `gemm_dw`) is this project's own and is "parity unpinned" against the
 reference.
@@ -359,6 +362,80 @@ def _repack_fields(old: np.ndarray, fields: np.ndarray, K: int, bits: int) -> np
     for j in range(per):
         out |= (full[:, :, j] << np.uint8(j * bits)).astype(np.uint8)
     return out
+
+
+# ----------------------------------------------------------------------------------------------
+# pre-linear RMSNorm   (core/bitnet/bitnet_int2_optimized.py:72-86; model/common/bitnet_legacy.py:10-25)
+# ----------------------------------------------------------------------------------------------
+
+def _round_io(x: np.ndarray, io: str) -> np.ndarray:
+    """float32 values rounded to the layer's I/O type ("bf16", "f16" or "f32") and held as float32."""
+    if io == "bf16":
+        return to_bf16(x)
+    if io == "f16":
+        return to_f16(x)
+    return np.asarray(x, dtype=np.float32)
+
+
+def rmsnorm_rstd(x: np.ndarray, eps: float = 1e-6) -> np.ndarray:
+    """rstd[m] = 1 / sqrt(mean_k x[m,k]^2 + eps) as the reference computes it in float32
+    (`x_f32 * torch.rsqrt(x_f32.pow(2).mean(-1) + eps)`): squares rounded to float32, their sum taken
+    exactly (float64 accumulation, then rounded to float32 - torch's own float32 summation order is not
+    reproducible, this is the order-free definition), divided by K, plus eps, sqrt, reciprocal - each
+    a float32 operation."""
+    x = np.asarray(x, dtype=np.float32)
+    K = x.shape[1]
+    sq = (x * x).astype(np.float32)
+    ssum = sq.astype(np.float64).sum(axis=1).astype(np.float32)
+    ms = (ssum / np.float32(K)).astype(np.float32)
+    v = (ms + np.float32(eps)).astype(np.float32)
+    return (np.float32(1.0) / np.sqrt(v).astype(np.float32)).astype(np.float32)
+
+
+def rmsnorm_forward(x: np.ndarray, weight: np.ndarray, eps: float = 1e-6, io: str = "bf16"):
+    """The reference's pre-linear RMSNorm: `norm.type_as(x) * weight.type_as(x)`: the normalised value is
+    rounded to the I/O type, the weight is rounded to the I/O type, and so is their product.
+    Returns (y float32 holding I/O-type values [M,K], rstd float32 [M])."""
+    x = _round_io(x, io)
+    rstd = rmsnorm_rstd(x, eps)
+    norm = _round_io((x * rstd[:, None]).astype(np.float32), io)
+    w = _round_io(np.asarray(weight, dtype=np.float32), io)
+    return _round_io((norm * w[None, :]).astype(np.float32), io), rstd
+
+
+def rmsnorm_quantize_rows(x, weight, norm_eps: float = 1e-6, quant_eps: float = 1e-5, io: str = "bf16"):
+    """RMSNorm followed by the per-token quantiser: what the fused kernel returns.
+    (q int8 [M,K], absmax float32 [M], rstd float32 [M])."""
+    y, rstd = rmsnorm_forward(x, weight, norm_eps, io)
+    q, a = quantize_rows(y, quant_eps)
+    return q, a, rstd
+
+
+def rmsnorm_backward(g: np.ndarray, x: np.ndarray, weight: np.ndarray, rstd: np.ndarray, io: str = "bf16"):
+    """Gradient of rmsnorm_forward for an upstream gradient g (I/O type), the quantiser being a
+    straight-through estimator (model/common/bitnet_legacy.py:83-87).  Follows autograd through the
+    reference's expression, each step in float32:
+      gn = io(g * io(w))                       gradient of `norm.type_as(x)`
+      c[m] = sum_k gn[m,k] * x[m,k]            exact sum of float32 products, rounded to float32
+      coef[m] = ((rstd*rstd)*rstd) * c / K
+      dx = io(gn * rstd - x * coef)
+      dweight[k] = sum_m g[m,k] * io(x*rstd)[m,k]   exact sum of float32 products, rounded to float32
+    Returns (dx float32 holding I/O-type values, dweight float32 [K])."""
+    g = _round_io(g, io)
+    x = _round_io(x, io)
+    rstd = np.asarray(rstd, dtype=np.float32)
+    K = x.shape[1]
+    w = _round_io(np.asarray(weight, dtype=np.float32), io)
+    gn = _round_io((g * w[None, :]).astype(np.float32), io)
+    c = (gn * x).astype(np.float32).astype(np.float64).sum(axis=1).astype(np.float32)
+    r3 = ((rstd * rstd).astype(np.float32) * rstd).astype(np.float32)
+    coef = ((r3 * c).astype(np.float32) / np.float32(K)).astype(np.float32)
+    t1 = (gn * rstd[:, None]).astype(np.float32)
+    t2 = (x * coef[:, None]).astype(np.float32)
+    dx = _round_io((t1 - t2).astype(np.float32), io)
+    norm = _round_io((x * rstd[:, None]).astype(np.float32), io)
+    dweight = (g * norm).astype(np.float32).astype(np.float64).sum(axis=0).astype(np.float32)
+    return dx, dweight
 
 
 # ----------------------------------------------------------------------------------------------

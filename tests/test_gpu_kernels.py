@@ -291,6 +291,72 @@ def test_linear_decode_bit_exact(ops, gemv_threshold, M, K, N, gemv_max):
     ops.check_device_status(torch.device(DEV))
 
 
+@pytest.mark.parametrize("gemv_max", [0, 8])
+@pytest.mark.parametrize("M", [1, 3, 8])
+def test_linear_decode_counts_non_finite_tokens_as_zero(ops, gemv_threshold, M, gemv_max):
+    """NaN and infinities in the tokens quantise to 0 and do not enter the absmax (NaN alone keeps the GEMV's fast
+    path, an infinity sends it through the checked one)."""
+    K, N = 1024, 328
+    g = torch.Generator().manual_seed(90 + M)
+    gemv_threshold(gemv_max)
+    Wp, _ = random_packed(N, K, seed=77)
+    Wd = _cuda(Wp)
+    for kind in ("nan", "inf", "both"):
+        x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+        if kind in ("nan", "both"):
+            x[0, 5] = float("nan")
+            x[M - 1, K - 1] = float("nan")
+        if kind in ("inf", "both"):
+            x[M // 2, 17] = float("inf")
+            x[0, 900] = float("-inf")
+        Xq, ax = O.quantize_rows(t2n(x))
+        want = O.to_bf16(O.scale_rows(O.gemm_fwd_acc(Xq, Wp, K), ax, 0.02))
+        y = ops.linear_decode(x.to(DEV), Wd, 0.02)
+        assert np.array_equal(t2n(y), want), kind
+    ops.check_device_status(torch.device(DEV))
+
+
+@pytest.mark.parametrize("M", [1, 4])
+def test_linear_decode_chain_with_overlap_equals_plain_chain(ops, M):
+    """Dependent-launch overlap: a chain of calls in which every call's tokens are the previous call's output (so a
+    call that started too early would read stale tokens) gives bit-identical results with the overlap on, in plain
+    stream order and replayed from a CUDA graph."""
+    K = N = 2048
+    g = torch.Generator().manual_seed(11 + M)
+    x0 = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    Ws = [_cuda(random_packed(N, K, seed=50 + i)[0]) for i in range(6)]
+
+    def chain(x):
+        outs = []
+        for W in Ws:
+            x = ops.linear_decode(x, W, 0.05)
+            outs.append(x)
+        return outs
+
+    ops.set_decode_overlap(False)
+    want = [o.clone() for o in chain(x0)]
+    assert float(want[-1].float().abs().max()) > 0
+    try:
+        ops.set_decode_overlap(True)
+        got = chain(x0)
+        torch.cuda.synchronize()
+        for a, b in zip(got, want):
+            assert torch.equal(a, b)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            got_g = chain(x0)
+        for o in got_g:
+            o.zero_()
+        graph.replay()
+        graph.replay()
+        torch.cuda.synchronize()
+        for a, b in zip(got_g, want):
+            assert torch.equal(a, b)
+    finally:
+        ops.set_decode_overlap(False)
+    ops.check_device_status(torch.device(DEV))
+
+
 def test_linear_decode_rejects_what_it_cannot_run(ops, pkg):
     Wp = torch.zeros(64, 25, dtype=torch.uint8, device=DEV)
     with pytest.raises(RuntimeError):

@@ -15,6 +15,7 @@ from helpers import make_layer_inputs
 pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 M, K, N = 512, 1024, 2048
+STEPS = 3
 
 
 def _free_port():
@@ -41,8 +42,10 @@ def _worker(rank, world, port, order, out_dir, fused):
         layer.load_shard(torch.from_numpy(d["Wp"]), torch.from_numpy(d["Hp"]), d["gamma"])
         layer.set_lr(0.5)
         x = d["x"].to(dev).requires_grad_(True)
-        y = layer.train()(x)
-        y.backward(d["dY"].to(dev))
+        for _ in range(STEPS):                       # several steps: the symmetric buffers alternate between calls
+            x.grad = None
+            y = layer.train()(x)
+            y.backward(d["dY"].to(dev))
         torch.cuda.synchronize()
         pkg.int2_tc_ops.check_device_status(dev)
         torch.save({"y": y.detach().cpu(), "dx": x.grad.cpu(), "W": layer.W_packed.cpu(), "H": layer.H_packed.cpu(),
@@ -55,7 +58,7 @@ def _worker(rank, world, port, order, out_dir, fused):
 @pytest.mark.parametrize("order", ["reference", "after_dx"])
 def test_sharded_step_on_gpus_equals_single_gpu(tmp_path, order, fused):
     """fused=True: the forward all-gather happens as TMA stores from the GEMM epilogue into symmetric memory."""
-    world = min(torch.cuda.device_count(), 4)
+    world = min(torch.cuda.device_count(), 8)
     if world < 2:
         pytest.skip("needs at least two GPUs")
     pkg = load_package()
@@ -68,8 +71,10 @@ def test_sharded_step_on_gpus_equals_single_gpu(tmp_path, order, fused):
     ref._initialized = True
     ref.set_lr(0.5)
     x = d["x"].to("cuda:0").requires_grad_(True)
-    y = ref.train()(x)
-    y.backward(d["dY"].to("cuda:0"))
+    for _ in range(STEPS):
+        x.grad = None
+        y = ref.train()(x)
+        y.backward(d["dY"].to("cuda:0"))
     torch.cuda.synchronize()
     assert not torch.equal(ref.W_packed.cpu(), torch.from_numpy(d["Wp"]))
     mp.spawn(_worker, args=(world, _free_port(), order, str(tmp_path), fused), nprocs=world, join=True)
