@@ -41,6 +41,9 @@ SIGNATURES = {
     "el_gemm_dx": [_vp, _vp, _vp, _i, _vp, _i, _f, _i, _i, _i, _i, _vp, _vp],
     "el_gemm_dw": [_vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp, _vp],
     "el_decode_workspace_bytes": [_i],
+    "el_rmsnorm_quantize_rows": [_vp, _i, C.c_longlong, _vp, _f, _vp, _vp, _vp, _i, _i, _f, _vp],
+    "el_rmsnorm_backward_workspace_bytes": [_i],
+    "el_rmsnorm_backward": [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, C.c_size_t, _i, _i, _vp],
     "el_set_decode_gemv_max_tokens": [_i],
     "el_set_decode_overlap": [_i],
     "el_linear_decode": [_vp, _i, _vp, _vp, _i, _f, _vp, _vp, _vp, C.c_size_t, _i, _i, _i, _vp, _vp],
@@ -74,7 +77,7 @@ def lib() -> C.CDLL:
             fn = getattr(handle, name)
             fn.argtypes = argtypes
             fn.restype = (C.c_char_p if name == "el_status_string" else
-                          C.c_size_t if name == "el_decode_workspace_bytes" else C.c_int)
+                          C.c_size_t if name in ("el_decode_workspace_bytes", "el_rmsnorm_backward_workspace_bytes") else C.c_int)
         _lib = handle
     return _lib
 

@@ -8,6 +8,7 @@ from typing import List, Optional
 import torch
 import torch.nn as nn
 
+from . import int2_tc_ops
 from .int2_linear_tc import Int2LinearTC, Int2LinearTCWithGradHook
 
 USING_OPTIMIZED = True
@@ -46,6 +47,7 @@ class BitLinearInt2(nn.Module):
         if use_extra_rmsnorm:
             self.extra_rmsnorm = _ExtraRMSNorm(in_features, eps=rmsnorm_eps)
         self.use_hadamard_smooth = False
+        self.fuse_rmsnorm = True          # False: run the norm as separate tensor operations, as the reference does
         cls = Int2LinearTCWithGradHook if use_grad_hook else Int2LinearTC
         self.int2_layer = cls(in_features=in_features, out_features=out_features, bias=bias, threshold=threshold,
                               lr_scale=lr_scale, decay_rate=decay_rate, use_24_sparsity=use_24_sparsity,
@@ -68,6 +70,10 @@ class BitLinearInt2(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if self.use_extra_rmsnorm:
+            if (self.fuse_rmsnorm and self.int2_layer.quant_mode == "per_token" and self.extra_rmsnorm.weight.dtype == torch.float32
+                    and int2_tc_ops.rmsnorm_supported(x)):
+                # normalisation, quantisation (and their backward) as one kernel each instead of eight tensor passes
+                return self.int2_layer(x, pre_norm=self.extra_rmsnorm)
             x = self.extra_rmsnorm(x)
         if self.int2_layer.quant_mode == "per_tensor" and x.dtype != torch.float16:
             x = x.half()

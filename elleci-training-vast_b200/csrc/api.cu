@@ -36,6 +36,11 @@ size_t decode_workspace_bytes(int N);
 int launch_decode_tc(const int8_t* Xq, const uint8_t* Wp, const EpiParams& epi, void* workspace, int M, int N, int K,
                      int32_t* status, cudaStream_t st);
 
+int launch_rmsnorm_quantize_rows(const void* x, int dt, long long ldx, const float* weight, float norm_eps, int8_t* q,
+                                 float* row_absmax, float* rstd, int M, int K, float quant_eps, cudaStream_t st);
+size_t rmsnorm_backward_workspace_bytes(int K);
+int launch_rmsnorm_backward(const void* g, const void* x, int dt, const float* weight, const float* rstd, void* dx,
+                            float* dweight, void* workspace, size_t workspace_bytes, int M, int K, cudaStream_t st);
 int launch_gemv_small(const void* x, int x_dtype, const uint8_t* Wp, const EpiParams& epi, int M, int N, int K, cudaStream_t st, bool overlap);
 int decode_gemv_max_tokens();
 
@@ -199,6 +204,30 @@ int el_scale_rows(const int32_t* acc, void* out, int out_dtype, const float* abs
     if (!acc || !out || !absmax) return EL_ERR_NULL_PTR;
     const EpiParams epi{out, (long long)C, out_dtype, absmax, absmax_stride, gamma};
     return launch_scale_rows(acc, epi, M, C, (cudaStream_t)stream);
+}
+
+int el_rmsnorm_quantize_rows(const void* x, int x_dtype, long long ldx, const float* weight, float norm_eps, int8_t* q,
+                             float* row_absmax, float* rstd, int M, int K, float quant_eps, el_stream_t stream) {
+    if (M < 0 || K < 0 || !float_dtype(x_dtype) || ldx < K) return EL_ERR_INVALID_ARG;
+    const int rc = require_sm100();
+    if (rc != EL_OK) return rc;
+    if (M == 0) return EL_OK;
+    if (!x || !weight || !q || !row_absmax || !rstd) return EL_ERR_NULL_PTR;
+    return launch_rmsnorm_quantize_rows(x, x_dtype, ldx, weight, norm_eps, q, row_absmax, rstd, M, K, quant_eps,
+                                        (cudaStream_t)stream);
+}
+
+size_t el_rmsnorm_backward_workspace_bytes(int K) { return rmsnorm_backward_workspace_bytes(K); }
+
+int el_rmsnorm_backward(const void* g, const void* x, int dtype, const float* weight, const float* rstd, void* dx,
+                        float* dweight, void* workspace, size_t workspace_bytes, int M, int K, el_stream_t stream) {
+    if (M < 0 || K < 0 || !float_dtype(dtype)) return EL_ERR_INVALID_ARG;
+    const int rc = require_sm100();
+    if (rc != EL_OK) return rc;
+    if (K == 0) return EL_OK;
+    if (!weight || !dweight || !workspace || (M > 0 && (!g || !x || !rstd || !dx))) return EL_ERR_NULL_PTR;
+    return launch_rmsnorm_backward(g, x, dtype, weight, rstd, dx, dweight, workspace, workspace_bytes, M, K,
+                                   (cudaStream_t)stream);
 }
 
 int el_gemm_fwd(const int8_t* Xq, const uint8_t* W_packed, void* Y, int out_dtype, const float* absmax, int absmax_stride,

@@ -71,6 +71,22 @@ template <> __device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat
 
 __device__ __forceinline__ float finite_or_zero(float v) { return (fabsf(v) <= 3.402823466e38f) ? v : 0.0f; }
 
+// v for finite v, NaN for infinities and NaN (v - v is 0 only for finite v).  Followed by q8_sat, which turns NaN into
+// 0, this counts non-finite inputs as zero with two additions instead of a compare and a select.
+__device__ __forceinline__ float finite_or_nan(float v) { return __fadd_rn(v, __fsub_rn(v, v)); }
+
+// round to nearest even and clamp to [-128, 127] in one conversion; NaN gives 0
+__device__ __forceinline__ int q8_sat(float v) {
+    int q;
+    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q) : "f"(v));
+    return q;
+}
+
+// the low bytes of four integers as one word (a in the lowest byte)
+__device__ __forceinline__ uint32_t pack4_s8(int a, int b, int c, int d) {
+    return __byte_perm(__byte_perm((uint32_t)a, (uint32_t)b, 0x0040), __byte_perm((uint32_t)c, (uint32_t)d, 0x0040), 0x5410);
+}
+
 // ---- hysteresis: one weight ---------------------------------------------------------------------------------
 struct HystParams {
     float lr_scaled;     // (lr*lr_scale)*thr, flushed like the reference's fast-math build when ftz

@@ -46,13 +46,6 @@ template <> __device__ __forceinline__ void gv_load16<float>(const float* p, flo
     }
 }
 
-// round-to-nearest-even and clamp to [-128, 127] in one conversion; NaN gives 0
-__device__ __forceinline__ int gv_quant(float v) {
-    int q;
-    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q) : "f"(v));
-    return q;
-}
-
 // Quantises 16 consecutive values of one token and stores them in the lane order of phase 2.  CHECKED: non-finite
 // values count as zero (the slow path, taken only when a token holds an infinity).
 template <typename T, bool CHECKED>
@@ -61,16 +54,14 @@ __device__ __forceinline__ uint4 gv_quant16(const T* src, float s) {
     gv_load16<T>(src, v);
     int q[16];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) q[i] = gv_quant(__fmul_rn(CHECKED ? finite_or_zero(v[i]) : v[i], s));
+    for (int i = 0; i < 16; ++i) q[i] = q8_sat(__fmul_rn(CHECKED ? finite_or_zero(v[i]) : v[i], s));
     uint32_t w[4];
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
         // bytes 4g..4g+3 of the output take the sources p<8 ? 2p : 2(p-8)+1
         const int p0 = 4 * g;
         const int s0 = (p0 < 8) ? 2 * p0 : 2 * (p0 - 8) + 1;           // sources s0, s0+2, s0+4, s0+6
-        const uint32_t lo = __byte_perm((uint32_t)q[s0], (uint32_t)q[s0 + 2], 0x0040);
-        const uint32_t hi = __byte_perm((uint32_t)q[s0 + 4], (uint32_t)q[s0 + 6], 0x0040);
-        w[g] = __byte_perm(lo, hi, 0x5410);
+        w[g] = pack4_s8(q[s0], q[s0 + 2], q[s0 + 4], q[s0 + 6]);
     }
     return make_uint4(w[0], w[1], w[2], w[3]);
 }

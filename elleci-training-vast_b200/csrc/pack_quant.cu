@@ -108,6 +108,44 @@ template <> __device__ __forceinline__ void load8<float>(const float* p, float v
     v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
 }
 
+// Eight consecutive elements as loaded (16 bytes of a 2-byte type, 32 bytes of float): rows are kept in registers in this
+// form between the absmax pass and the quantisation pass.
+template <typename T> struct Raw8 { uint4 a; };
+template <> struct Raw8<float> { uint4 a, b; };
+template <typename T> __device__ __forceinline__ Raw8<T> raw_load(const T* p) {
+    Raw8<T> r;
+    r.a = *reinterpret_cast<const uint4*>(p);
+    return r;
+}
+template <> __device__ __forceinline__ Raw8<float> raw_load<float>(const float* p) {
+    Raw8<float> r;
+    r.a = *reinterpret_cast<const uint4*>(p);
+    r.b = *reinterpret_cast<const uint4*>(p + 4);
+    return r;
+}
+__device__ __forceinline__ void raw_unpack(const Raw8<__nv_bfloat16>& r, float v[8]) {
+    const uint32_t w[4] = {r.a.x, r.a.y, r.a.z, r.a.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        v[2 * i] = __uint_as_float(w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    }
+}
+__device__ __forceinline__ void raw_unpack(const Raw8<__half>& r, float v[8]) {
+    const uint32_t w[4] = {r.a.x, r.a.y, r.a.z, r.a.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+        v[2 * i] = f.x;
+        v[2 * i + 1] = f.y;
+    }
+}
+__device__ __forceinline__ void raw_unpack(const Raw8<float>& r, float v[8]) {
+    v[0] = __uint_as_float(r.a.x); v[1] = __uint_as_float(r.a.y); v[2] = __uint_as_float(r.a.z); v[3] = __uint_as_float(r.a.w);
+    v[4] = __uint_as_float(r.b.x); v[5] = __uint_as_float(r.b.y); v[6] = __uint_as_float(r.b.z); v[7] = __uint_as_float(r.b.w);
+}
+constexpr int ROW_CACHE = 6;        // vectors of 8 elements a thread keeps in registers: rows up to 12288 elements
+
 __device__ __forceinline__ int quant_half_even(float x, float s) {
     float r = rintf(__fmul_rn(x, s));
     r = fminf(127.0f, fmaxf(-128.0f, r));
@@ -125,21 +163,48 @@ quantize_rows_kernel(const T* __restrict__ x, long long ldx, int8_t* __restrict_
     const T* xr = x + (size_t)m * ldx;
     int8_t* qr = q + (size_t)m * K;
     float amax = 0.0f;
+    bool row_finite = false;        // known to hold no infinity: the unchecked conversion is exact
+    Raw8<T> cache[ROW_CACHE];
     if (MODE == 2) {
         amax = row_absmax[m];
         __syncthreads();            // every thread has read the raw value before thread 0 floors it in place
     } else {
         if (VEC) {
-            for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
+            // The row is read from memory once: up to ROW_CACHE vectors per thread stay in registers for the second pass.
+            // fmaxf drops NaN operands and keeps infinities: only a row that holds an infinity needs the checked pass
+#pragma unroll
+            for (int c = 0; c < ROW_CACHE; ++c) {
+                const int k = (threadIdx.x + c * 256) * 8;
+                if (k < K) {
+                    cache[c] = raw_load<T>(xr + k);
+                    float v[8];
+                    raw_unpack(cache[c], v);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+                }
+            }
+            for (int k = (threadIdx.x + ROW_CACHE * 256) * 8; k < K; k += 256 * 8) {
                 float v[8];
                 load8<T>(xr + k, v);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(finite_or_zero(v[i])));
+                for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+            }
+            amax = block_max(amax, red);
+            if (!(amax <= 3.402823466e38f)) {          // same value in every thread of the CTA
+                amax = 0.0f;
+                for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
+                    float v[8];
+                    load8<T>(xr + k, v);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(finite_or_zero(v[i])));
+                }
+            } else {
+                row_finite = true;
             }
         } else {
             for (int k = threadIdx.x; k < K; k += blockDim.x) amax = fmaxf(amax, fabsf(finite_or_zero(to_float<T>(xr[k]))));
         }
-        amax = block_max(amax, red);
+        if (!row_finite) amax = block_max(amax, red);
     }
     if (MODE == 1) {
         if (threadIdx.x == 0) row_absmax[m] = amax;
@@ -155,16 +220,37 @@ quantize_rows_kernel(const T* __restrict__ x, long long ldx, int8_t* __restrict_
         }
     }
     if (VEC) {
-        for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
-            float v[8];
-            load8<T>(xr + k, v);     // second read of the row: served by L1/L2
-            uint32_t w0 = 0, w1 = 0;
+        // second read of the row: served by L1/L2.  q8_sat rounds, clamps and turns NaN into 0.
+        if (row_finite) {           // MODE 0 only: the cached vectors are valid
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                w0 |= (uint32_t)(quant_half_even(finite_or_zero(v[i]), s) & 0xFF) << (8 * i);
-                w1 |= (uint32_t)(quant_half_even(finite_or_zero(v[4 + i]), s) & 0xFF) << (8 * i);
+            for (int c = 0; c < ROW_CACHE; ++c) {
+                const int k = (threadIdx.x + c * 256) * 8;
+                if (k < K) {
+                    float v[8];
+                    raw_unpack(cache[c], v);
+                    int qi[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) qi[i] = q8_sat(__fmul_rn(v[i], s));
+                    *reinterpret_cast<uint2*>(qr + k) = make_uint2(pack4_s8(qi[0], qi[1], qi[2], qi[3]), pack4_s8(qi[4], qi[5], qi[6], qi[7]));
+                }
             }
-            *reinterpret_cast<uint2*>(qr + k) = make_uint2(w0, w1);
+            for (int k = (threadIdx.x + ROW_CACHE * 256) * 8; k < K; k += 256 * 8) {
+                float v[8];
+                load8<T>(xr + k, v);
+                int qi[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) qi[i] = q8_sat(__fmul_rn(v[i], s));
+                *reinterpret_cast<uint2*>(qr + k) = make_uint2(pack4_s8(qi[0], qi[1], qi[2], qi[3]), pack4_s8(qi[4], qi[5], qi[6], qi[7]));
+            }
+        } else {
+            for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
+                float v[8];
+                load8<T>(xr + k, v);
+                int qi[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) qi[i] = q8_sat(__fmul_rn(finite_or_nan(v[i]), s));
+                *reinterpret_cast<uint2*>(qr + k) = make_uint2(pack4_s8(qi[0], qi[1], qi[2], qi[3]), pack4_s8(qi[4], qi[5], qi[6], qi[7]));
+            }
         }
     } else {
         for (int k = threadIdx.x; k < K; k += blockDim.x)
@@ -188,9 +274,21 @@ quantize_rows_perm_kernel(const T* __restrict__ x, long long ldx, int8_t* __rest
         load8<T>(xr + k, v);
         load8<T>(xr + k + 8, v + 8);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(finite_or_zero(v[i])));
+        for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));       // drops NaN, keeps infinities
     }
     amax = block_max(amax, red);
+    const bool row_finite = amax <= 3.402823466e38f;      // same value in every thread of the CTA
+    if (!row_finite) {
+        amax = 0.0f;
+        for (int k = threadIdx.x * 16; k < K; k += blockDim.x * 16) {
+            float v[16];
+            load8<T>(xr + k, v);
+            load8<T>(xr + k + 8, v + 8);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(finite_or_zero(v[i])));
+        }
+        amax = block_max(amax, red);
+    }
     const float a = fmaxf(amax, eps);
     const float s = __fdiv_rn(127.0f, a);
     if (threadIdx.x == 0) row_absmax[m] = a;
@@ -198,11 +296,14 @@ quantize_rows_perm_kernel(const T* __restrict__ x, long long ldx, int8_t* __rest
         float v[16];
         load8<T>(xr + k, v);
         load8<T>(xr + k + 8, v + 8);
-        uint32_t w[4] = {0, 0, 0, 0};
+        int qi[16];
 #pragma unroll
-        for (int p = 0; p < 16; ++p) {
-            const int src = (p < 8) ? 2 * p : 2 * (p - 8) + 1;
-            w[p >> 2] |= (uint32_t)(quant_half_even(finite_or_zero(v[src]), s) & 0xFF) << (8 * (p & 3));
+        for (int i = 0; i < 16; ++i) qi[i] = q8_sat(__fmul_rn(row_finite ? v[i] : finite_or_nan(v[i]), s));
+        uint32_t w[4];
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            const int s0 = (g < 2) ? 8 * g : 8 * (g - 2) + 1;      // output bytes 4g..4g+3 take sources s0, s0+2, s0+4, s0+6
+            w[g] = pack4_s8(qi[s0], qi[s0 + 2], qi[s0 + 4], qi[s0 + 6]);
         }
         *reinterpret_cast<uint4*>(qr + k) = make_uint4(w[0], w[1], w[2], w[3]);
     }
@@ -272,13 +373,11 @@ quantize_grad_kernel(const T* __restrict__ dY, long long ld, const float* __rest
         for (int k = threadIdx.x * 8; k < N; k += blockDim.x * 8) {
             float v[8];
             load8<T>(yr + k, v);
-            uint32_t w0 = 0, w1 = 0;
+            int qi[8];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                w0 |= (uint32_t)(qz(v[i]) & 0xFF) << (8 * i);
-                w1 |= (uint32_t)(qz(v[4 + i]) & 0xFF) << (8 * i);
-            }
-            *reinterpret_cast<uint2*>(gr + k) = make_uint2(w0, w1);
+            for (int i = 0; i < 8; ++i)      // non-finite -> NaN -> 0; the conversion rounds and clamps at 127, max() at -127
+                qi[i] = max(-127, q8_sat(__fmul_rn(__fmul_rn(finite_or_nan(v[i]), sx), inv)));
+            *reinterpret_cast<uint2*>(gr + k) = make_uint2(pack4_s8(qi[0], qi[1], qi[2], qi[3]), pack4_s8(qi[4], qi[5], qi[6], qi[7]));
         }
     } else {
         for (int k = threadIdx.x; k < N; k += blockDim.x) gr[k] = (int8_t)qz(to_float<T>(yr[k]));

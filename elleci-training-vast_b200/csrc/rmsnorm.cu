@@ -1,0 +1,379 @@
+// Pre-linear RMSNorm fused with the per-token int8 quantiser, and its backward pass.
+//
+// The reference normalises the activations right before every INT2 linear call
+// (core/bitnet/bitnet_int2_optimized.py:72-86, model/common/bitnet_legacy.py:10-25):
+//     norm = x_f32 * rsqrt(mean(x_f32^2) + eps);  y = norm.type_as(x) * weight.type_as(x)
+// and then quantises y per token.  Done as separate tensor operations this reads and writes the [M, K] activation
+// about eight times; here one kernel reads the row and writes the int8 row, its absmax and its rstd.
+//
+// Row sums (of squares, and in the backward pass) are accumulated in float64, so that their float32 value does not
+// depend on the order of the additions: the result is the one the CPU oracle defines, bit for bit.
+#include "common.cuh"
+
+namespace el {
+
+int device_sm_count(int* out);
+
+namespace {
+
+template <typename T> struct Io;
+template <> struct Io<float> {
+    struct Raw { float4 a, b; };
+    static __device__ __forceinline__ Raw load_raw(const float* p) {
+        Raw r;
+        r.a = *reinterpret_cast<const float4*>(p);
+        r.b = *reinterpret_cast<const float4*>(p + 4);
+        return r;
+    }
+    static __device__ __forceinline__ void unpack(const Raw& r, float v[8]) {
+        v[0] = r.a.x; v[1] = r.a.y; v[2] = r.a.z; v[3] = r.a.w; v[4] = r.b.x; v[5] = r.b.y; v[6] = r.b.z; v[7] = r.b.w;
+    }
+    static __device__ __forceinline__ float round(float v) { return v; }
+    static __device__ __forceinline__ void load8(const float* p, float v[8]) {
+        const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+    static __device__ __forceinline__ void store8(float* p, const float v[8]) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+};
+template <> struct Io<__nv_bfloat16> {
+    struct Raw { uint4 a; };
+    static __device__ __forceinline__ Raw load_raw(const __nv_bfloat16* p) { return Raw{*reinterpret_cast<const uint4*>(p)}; }
+    static __device__ __forceinline__ void unpack(const Raw& r, float v[8]) {
+        const uint32_t w[4] = {r.a.x, r.a.y, r.a.z, r.a.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            v[2 * i] = __uint_as_float(w[i] << 16);
+            v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+        }
+    }
+    static __device__ __forceinline__ float round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+    static __device__ __forceinline__ void load8(const __nv_bfloat16* p, float v[8]) { unpack(load_raw(p), v); }
+    static __device__ __forceinline__ void store8(__nv_bfloat16* p, const float v[8]) {
+        *reinterpret_cast<uint4*>(p) = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
+                                                  pack_bf16x2(v[6], v[7]));
+    }
+};
+template <> struct Io<__half> {
+    struct Raw { uint4 a; };
+    static __device__ __forceinline__ Raw load_raw(const __half* p) { return Raw{*reinterpret_cast<const uint4*>(p)}; }
+    static __device__ __forceinline__ void unpack(const Raw& r, float v[8]) {
+        const uint32_t w[4] = {r.a.x, r.a.y, r.a.z, r.a.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+            v[2 * i] = f.x;
+            v[2 * i + 1] = f.y;
+        }
+    }
+    static __device__ __forceinline__ float round(float v) { return __half2float(__float2half_rn(v)); }
+    static __device__ __forceinline__ void load8(const __half* p, float v[8]) { unpack(load_raw(p), v); }
+    static __device__ __forceinline__ void store8(__half* p, const float v[8]) {
+        *reinterpret_cast<uint4*>(p) = make_uint4(pack_f16x2(v[0], v[1]), pack_f16x2(v[2], v[3]), pack_f16x2(v[4], v[5]),
+                                                  pack_f16x2(v[6], v[7]));
+    }
+};
+
+__device__ __forceinline__ void load8_w(const float* p, float v[8]) { Io<float>::load8(p, v); }
+
+constexpr int RN_THREADS = 256;
+constexpr int ROW_CACHE = 6;        // vectors of 8 elements a thread keeps in registers between passes
+
+// Sum over the CTA; every thread gets the result.  `red` holds one double per warp.
+__device__ __forceinline__ double block_sum(double v, double* red) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    if (l == 0) red[w] = v;
+    __syncthreads();
+    double t = 0.0;
+#pragma unroll
+    for (int i = 0; i < RN_THREADS / 32; ++i) t += red[i];     // same order in every thread
+    __syncthreads();
+    return t;
+}
+
+__device__ __forceinline__ float block_max_f(float v, float* red) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    if (l == 0) red[w] = v;
+    __syncthreads();
+    float t = 0.0f;
+#pragma unroll
+    for (int i = 0; i < RN_THREADS / 32; ++i) t = fmaxf(t, red[i]);
+    __syncthreads();
+    return t;
+}
+
+// One CTA per token.  K % 8 == 0; x rows, weight and q rows 16-byte (q: 8-byte) aligned.
+template <typename T>
+__global__ void __launch_bounds__(RN_THREADS)
+rmsnorm_quantize_rows_kernel(const T* __restrict__ x, long long ldx, const float* __restrict__ weight, int8_t* __restrict__ q,
+                             float* __restrict__ row_absmax, float* __restrict__ rstd_out, int K, float norm_eps,
+                             float quant_eps) {
+    __shared__ double red_d[RN_THREADS / 32];
+    __shared__ float red_f[RN_THREADS / 32];
+    const int m = blockIdx.x;
+    const T* xr = x + (size_t)m * ldx;
+    int8_t* qr = q + (size_t)m * K;
+
+    // The row is read from memory once: up to ROW_CACHE vectors of 8 elements per thread stay in registers for the two
+    // later passes (rows of up to 12288 elements); longer rows re-read their tail.
+    typename Io<T>::Raw cache[ROW_CACHE];
+    const int k_tail = (threadIdx.x + ROW_CACHE * RN_THREADS) * 8;
+
+    // ---- mean of squares -> rstd -------------------------------------------------------------------------------------
+    double ss = 0.0;
+#pragma unroll
+    for (int c = 0; c < ROW_CACHE; ++c) {
+        const int k = (threadIdx.x + c * RN_THREADS) * 8;
+        if (k < K) {
+            cache[c] = Io<T>::load_raw(xr + k);
+            float v[8];
+            Io<T>::unpack(cache[c], v);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ss += (double)__fmul_rn(v[i], v[i]);
+        }
+    }
+    for (int k = k_tail; k < K; k += RN_THREADS * 8) {
+        float v[8];
+        Io<T>::load8(xr + k, v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += (double)__fmul_rn(v[i], v[i]);
+    }
+    ss = block_sum(ss, red_d);
+    const float ms = __fdiv_rn((float)ss, (float)K);
+    const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(ms, norm_eps)));
+
+    // y = io(io(x*r) * io(w))
+    auto normed = [&](const float v[8], const float w[8], float y[8]) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) y[i] = Io<T>::round(__fmul_rn(Io<T>::round(__fmul_rn(v[i], r)), Io<T>::round(w[i])));
+    };
+
+    // ---- absmax of the normalised row ----------------------------------------------------------------------------------
+    // fmaxf drops NaN and keeps infinities: the checked pass runs only for a row that needs it
+    float amax = 0.0f;
+#pragma unroll
+    for (int c = 0; c < ROW_CACHE; ++c) {
+        const int k = (threadIdx.x + c * RN_THREADS) * 8;
+        if (k < K) {
+            float v[8], w[8], y[8];
+            Io<T>::unpack(cache[c], v);
+            load8_w(weight + k, w);
+            normed(v, w, y);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(y[i]));
+        }
+    }
+    for (int k = k_tail; k < K; k += RN_THREADS * 8) {
+        float v[8], w[8], y[8];
+        Io<T>::load8(xr + k, v);
+        load8_w(weight + k, w);
+        normed(v, w, y);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(y[i]));
+    }
+    amax = block_max_f(amax, red_f);
+    const bool row_finite = amax <= 3.402823466e38f;
+    if (!row_finite) {
+        amax = 0.0f;
+        for (int k = threadIdx.x * 8; k < K; k += RN_THREADS * 8) {
+            float v[8], w[8], y[8];
+            Io<T>::load8(xr + k, v);
+            load8_w(weight + k, w);
+            normed(v, w, y);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(finite_or_zero(y[i])));
+        }
+        amax = block_max_f(amax, red_f);
+    }
+    const float a = fmaxf(amax, quant_eps);
+    const float s = __fdiv_rn(127.0f, a);
+    if (threadIdx.x == 0) {
+        row_absmax[m] = a;
+        rstd_out[m] = r;
+    }
+
+    // ---- quantise --------------------------------------------------------------------------------------------------------
+    auto quantise = [&](const float v[8], int k) {
+        float w[8], y[8];
+        load8_w(weight + k, w);
+        normed(v, w, y);
+        int qi[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) qi[i] = q8_sat(__fmul_rn(row_finite ? y[i] : finite_or_nan(y[i]), s));
+        *reinterpret_cast<uint2*>(qr + k) = make_uint2(pack4_s8(qi[0], qi[1], qi[2], qi[3]), pack4_s8(qi[4], qi[5], qi[6], qi[7]));
+    };
+#pragma unroll
+    for (int c = 0; c < ROW_CACHE; ++c) {
+        const int k = (threadIdx.x + c * RN_THREADS) * 8;
+        if (k < K) {
+            float v[8];
+            Io<T>::unpack(cache[c], v);
+            quantise(v, k);
+        }
+    }
+    for (int k = k_tail; k < K; k += RN_THREADS * 8) {
+        float v[8];
+        Io<T>::load8(xr + k, v);
+        quantise(v, k);
+    }
+}
+
+// Backward.  CTA b takes the tokens b, b + gridDim.x, ...; thread t owns the same columns in every token, so the
+// per-column sums of dweight live in shared memory (one double per column) without any exchange between threads.
+// At the end the CTA writes its [K] partial sums to `partial[b]`.
+template <typename T>
+__global__ void __launch_bounds__(RN_THREADS)
+rmsnorm_backward_kernel(const T* __restrict__ g, const T* __restrict__ x, const float* __restrict__ weight,
+                        const float* __restrict__ rstd, T* __restrict__ dx, double* __restrict__ partial, int M, int K) {
+    extern __shared__ double col_sum[];          // [K]
+    __shared__ double red_d[RN_THREADS / 32];
+    for (int k = threadIdx.x * 8; k < K; k += RN_THREADS * 8) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) col_sum[k + i] = 0.0;
+    }
+    for (int m = blockIdx.x; m < M; m += gridDim.x) {
+        const T* gr = g + (size_t)m * K;
+        const T* xr = x + (size_t)m * K;
+        T* dr = dx + (size_t)m * K;
+        const float r = rstd[m];
+        // c = sum_k io(g*io(w)) * x
+        double c = 0.0;
+        for (int k = threadIdx.x * 8; k < K; k += RN_THREADS * 8) {
+            float gv[8], xv[8], w[8];
+            Io<T>::load8(gr + k, gv);
+            Io<T>::load8(xr + k, xv);
+            load8_w(weight + k, w);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) c += (double)__fmul_rn(Io<T>::round(__fmul_rn(gv[i], Io<T>::round(w[i]))), xv[i]);
+        }
+        c = block_sum(c, red_d);
+        const float r3 = __fmul_rn(__fmul_rn(r, r), r);
+        const float coef = __fdiv_rn(__fmul_rn(r3, (float)c), (float)K);
+        for (int k = threadIdx.x * 8; k < K; k += RN_THREADS * 8) {
+            float gv[8], xv[8], w[8], o[8];
+            Io<T>::load8(gr + k, gv);
+            Io<T>::load8(xr + k, xv);
+            load8_w(weight + k, w);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float gn = Io<T>::round(__fmul_rn(gv[i], Io<T>::round(w[i])));
+                o[i] = __fsub_rn(__fmul_rn(gn, r), __fmul_rn(xv[i], coef));
+                col_sum[k + i] += (double)__fmul_rn(gv[i], Io<T>::round(__fmul_rn(xv[i], r)));
+            }
+            Io<T>::store8(dr + k, o);
+        }
+    }
+    double* out = partial + (size_t)blockIdx.x * K;
+    for (int k = threadIdx.x * 8; k < K; k += RN_THREADS * 8) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) out[k + i] = col_sum[k + i];
+    }
+}
+
+// dweight[k] = float(sum over the CTAs' partial sums, in CTA order)
+__global__ void __launch_bounds__(256)
+rmsnorm_dweight_kernel(const double* __restrict__ partial, int n_parts, float* __restrict__ dweight, int K) {
+    const int k = blockIdx.x * blockDim.x + threadIdx.x;
+    if (k >= K) return;
+    double s = 0.0;
+    for (int p = 0; p < n_parts; ++p) s += partial[(size_t)p * K + k];
+    dweight[k] = (float)s;
+}
+
+int backward_grid(int M, int K) {
+    int sms = 148;
+    device_sm_count(&sms);
+    const size_t smem = (size_t)K * sizeof(double);
+    int per_sm = (int)((200u * 1024u) / (smem ? smem : 1));
+    if (per_sm < 1) per_sm = 1;
+    if (per_sm > 4) per_sm = 4;
+    const int grid = sms * per_sm;
+    return M < grid ? (M < 1 ? 1 : M) : grid;
+}
+
+}  // namespace
+
+// Largest number of CTAs the backward kernel may use (sizes the workspace independently of M).
+size_t rmsnorm_backward_workspace_bytes(int K) {
+    if (K <= 0) return 0;
+    int sms = 148;
+    device_sm_count(&sms);
+    return (size_t)sms * 4 * (size_t)K * sizeof(double);
+}
+
+int launch_rmsnorm_quantize_rows(const void* x, int dt, long long ldx, const float* weight, float norm_eps, int8_t* q,
+                                 float* row_absmax, float* rstd, int M, int K, float quant_eps, cudaStream_t st) {
+    if (M == 0) return EL_OK;
+    if (K <= 0 || K % 8 != 0) return EL_ERR_UNSUPPORTED_SHAPE;
+    const size_t esz = (dt == EL_F32) ? 4 : 2;
+    if ((reinterpret_cast<uintptr_t>(x) & 15) || ((size_t)ldx * esz) % 16 != 0 || (reinterpret_cast<uintptr_t>(weight) & 15) ||
+        (reinterpret_cast<uintptr_t>(q) & 7))
+        return EL_ERR_ALIGNMENT;
+    switch (dt) {
+        case EL_BF16:
+            rmsnorm_quantize_rows_kernel<__nv_bfloat16><<<M, RN_THREADS, 0, st>>>((const __nv_bfloat16*)x, ldx, weight, q, row_absmax,
+                                                                                   rstd, K, norm_eps, quant_eps);
+            break;
+        case EL_F16:
+            rmsnorm_quantize_rows_kernel<__half><<<M, RN_THREADS, 0, st>>>((const __half*)x, ldx, weight, q, row_absmax, rstd, K,
+                                                                            norm_eps, quant_eps);
+            break;
+        case EL_F32:
+            rmsnorm_quantize_rows_kernel<float><<<M, RN_THREADS, 0, st>>>((const float*)x, ldx, weight, q, row_absmax, rstd, K,
+                                                                           norm_eps, quant_eps);
+            break;
+        default: return EL_ERR_INVALID_ARG;
+    }
+    return check_launch();
+}
+
+template <typename T>
+static int launch_rmsnorm_backward_t(const T* g, const T* x, const float* weight, const float* rstd, T* dx, float* dweight,
+                                     double* partial, int M, int K, cudaStream_t st) {
+    const int grid = backward_grid(M, K);
+    const size_t smem = (size_t)K * sizeof(double);
+    static bool attr_set[64] = {};
+    int dev = 0;
+    EL_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+        EL_CUDA_TRY(cudaFuncSetAttribute(rmsnorm_backward_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+    }
+    rmsnorm_backward_kernel<T><<<grid, RN_THREADS, smem, st>>>(g, x, weight, rstd, dx, partial, M, K);
+    int rc = check_launch();
+    if (rc != EL_OK) return rc;
+    rmsnorm_dweight_kernel<<<(K + 255) / 256, 256, 0, st>>>(partial, grid, dweight, K);
+    return check_launch();
+}
+
+int launch_rmsnorm_backward(const void* g, const void* x, int dt, const float* weight, const float* rstd, void* dx,
+                            float* dweight, void* workspace, size_t workspace_bytes, int M, int K, cudaStream_t st) {
+    if (K <= 0 || K % 8 != 0 || (size_t)K * sizeof(double) > 200u * 1024u) return EL_ERR_UNSUPPORTED_SHAPE;
+    if (workspace_bytes < rmsnorm_backward_workspace_bytes(K)) return EL_ERR_INVALID_ARG;
+    if ((reinterpret_cast<uintptr_t>(g) & 15) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(dx) & 15) ||
+        (reinterpret_cast<uintptr_t>(weight) & 15) || (reinterpret_cast<uintptr_t>(workspace) & 15))
+        return EL_ERR_ALIGNMENT;
+    if (M == 0) {
+        EL_CUDA_TRY(cudaMemsetAsync(dweight, 0, (size_t)K * sizeof(float), st));
+        return EL_OK;
+    }
+    double* partial = static_cast<double*>(workspace);
+    switch (dt) {
+        case EL_BF16:
+            return launch_rmsnorm_backward_t((const __nv_bfloat16*)g, (const __nv_bfloat16*)x, weight, rstd, (__nv_bfloat16*)dx,
+                                             dweight, partial, M, K, st);
+        case EL_F16:
+            return launch_rmsnorm_backward_t((const __half*)g, (const __half*)x, weight, rstd, (__half*)dx, dweight, partial, M, K, st);
+        case EL_F32:
+            return launch_rmsnorm_backward_t((const float*)g, (const float*)x, weight, rstd, (float*)dx, dweight, partial, M, K, st);
+        default: return EL_ERR_INVALID_ARG;
+    }
+}
+
+}  // namespace el

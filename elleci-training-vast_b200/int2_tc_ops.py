@@ -260,6 +260,57 @@ def quantize_rows(x: torch.Tensor, eps: float = ACT_EPS, fold_absmax: Optional[t
     return (q, a) if fold_absmax is None else (q, a, fold_max)
 
 
+NORM_EPS = 1e-6            # default eps of the reference's pre-linear RMSNorm (core/bitnet/bitnet_int2_optimized.py:78)
+_norm_ws: dict = {}
+
+
+def rmsnorm_supported(x: torch.Tensor) -> bool:
+    """Shapes the fused RMSNorm kernels take: a float CUDA tensor whose feature count is a multiple of 8 (at most
+    25600) and whose rows are 16-byte aligned."""
+    K = x.shape[-1] if x.dim() else 0
+    return (x.is_cuda and x.dtype in (torch.float16, torch.bfloat16, torch.float32) and K > 0 and K % 8 == 0
+            and K <= 25600 and x.is_contiguous() and x.data_ptr() % 16 == 0)
+
+
+def rmsnorm_quantize_rows(x: torch.Tensor, weight: torch.Tensor, norm_eps: float = NORM_EPS, quant_eps: float = ACT_EPS):
+    """The reference's pre-linear RMSNorm (`_ExtraRMSNorm`, core/bitnet/bitnet_int2_optimized.py:72-86) followed by
+    the per-token quantiser, in one pass over x.  `weight` is the float32 norm weight [K].  Returns
+    (q int8 like x, absmax float32 [M], rstd float32 [M]); q and absmax equal quantize_rows(norm(x))."""
+    _cuda(x, "x"); _cuda(weight, "weight")
+    _require(x.dtype in (torch.float16, torch.bfloat16, torch.float32), "x must be float16, bfloat16 or float32")
+    xv, M, K, ld = _rows_view(x)
+    _require(weight.dtype == torch.float32 and weight.numel() == K and weight.is_contiguous(), "weight must be a contiguous float32 [K]")
+    q = torch.empty(*x.shape[:-1], K, dtype=torch.int8, device=x.device)
+    a = torch.empty(M, dtype=torch.float32, device=x.device)
+    rstd = torch.empty(M, dtype=torch.float32, device=x.device)
+    call("el_rmsnorm_quantize_rows", xv.data_ptr(), _DT[xv.dtype], ld, weight.data_ptr(), float(norm_eps), q.data_ptr(),
+         a.data_ptr(), rstd.data_ptr(), M, K, float(quant_eps), _stream())
+    return q, a, rstd
+
+
+def rmsnorm_backward(g: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, rstd: torch.Tensor):
+    """Backward of the pre-linear RMSNorm for the gradient g with respect to its output (same shape and dtype as x).
+    Returns (dx like x, dweight float32 [K])."""
+    _cuda(g, "g"); _cuda(x, "x")
+    _require(g.dtype == x.dtype and g.shape == x.shape, "g and x must have the same shape and dtype")
+    K = x.shape[-1]
+    gc, xc = g.contiguous(), x.contiguous()
+    M = xc.numel() // K if K else 0
+    _require(weight.dtype == torch.float32 and weight.numel() == K, "weight must be float32 [K]")
+    _require(rstd.dtype == torch.float32 and rstd.numel() == M, "rstd must be float32 [M]")
+    need = _lib.lib().el_rmsnorm_backward_workspace_bytes(K)
+    key = (x.device.index, K)
+    ws = _norm_ws.get(key)
+    if ws is None:
+        ws = torch.empty(need, dtype=torch.uint8, device=x.device)
+        _norm_ws[key] = ws
+    dx = torch.empty_like(xc)
+    dw = torch.empty(K, dtype=torch.float32, device=x.device)
+    call("el_rmsnorm_backward", gc.data_ptr(), xc.data_ptr(), _DT[xc.dtype], weight.contiguous().data_ptr(), rstd.data_ptr(),
+         dx.data_ptr(), dw.data_ptr(), ws.data_ptr(), need, M, K, _stream())
+    return dx.view_as(x), dw
+
+
 def absmax_rows(x: torch.Tensor) -> torch.Tensor:
     """Raw max |x[m,:]| per row (float32 [M]), without the eps floor: the first half of quantize_rows for a
     column shard, to be max-reduced over ranks and passed back as `raw_absmax`."""

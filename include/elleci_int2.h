@@ -128,6 +128,29 @@ EL_API int el_quantize_grad(const void* dY, int dy_dtype, long long ld_dy, const
 EL_API int el_scale_rows(const int32_t* acc, void* out, int out_dtype, const float* absmax, int absmax_stride,
                          float gamma, int M, int C, el_stream_t stream);
 
+/* ---- pre-linear RMSNorm fused with the per-token quantiser ------------------------------------------ */
+
+/* The reference normalises the activations right before every INT2 linear call
+ * (_ExtraRMSNorm, core/bitnet/bitnet_int2_optimized.py:72-86,203-204; _RMSNorm, model/common/bitnet_legacy.py:10-25):
+ *   y = dtype( dtype(x * rstd) * dtype(weight) ),  rstd[m] = 1/sqrt(mean_k x[m,k]^2 + norm_eps)  (float32)
+ * and quantises y per token.  This call does both in one pass over x (dtype EL_F16/EL_BF16/EL_F32, row pitch ldx
+ * elements, weight float32 [K]): q int8 [M,K] and row_absmax [M] exactly as el_quantize_rows(y, quant_eps) gives them,
+ * plus rstd [M] for the backward pass.  The sum of squares is accumulated in float64, so the result does not depend on
+ * the order of the additions.  Needs K % 8 == 0 and 16-byte aligned rows (EL_ERR_UNSUPPORTED_SHAPE / EL_ERR_ALIGNMENT
+ * otherwise). */
+EL_API int el_rmsnorm_quantize_rows(const void* x, int x_dtype, long long ldx, const float* weight, float norm_eps,
+                                    int8_t* q, float* row_absmax, float* rstd, int M, int K, float quant_eps,
+                                    el_stream_t stream);
+/* Backward of the normalisation above for an upstream gradient g [M,K] with respect to y (the quantiser is a
+ * straight-through estimator, model/common/bitnet_legacy.py:83-87), following autograd through the reference's
+ * expression:  gn = dtype(g * dtype(weight));  c[m] = sum_k gn*x;  dx = dtype(gn*rstd - x * (rstd^3 * c / K));
+ * dweight[k] = sum_m g[m,k] * dtype(x*rstd)[m,k]  (float32 [K], overwritten).  g, x, dx contiguous [M,K] of `dtype`.
+ * `workspace`: el_rmsnorm_backward_workspace_bytes(K) bytes, 16-byte aligned, contents irrelevant.  K % 8 == 0 and
+ * K <= 25600. */
+EL_API size_t el_rmsnorm_backward_workspace_bytes(int K);
+EL_API int el_rmsnorm_backward(const void* g, const void* x, int dtype, const float* weight, const float* rstd, void* dx,
+                               float* dweight, void* workspace, size_t workspace_bytes, int M, int K, el_stream_t stream);
+
 /* ---- GEMMs ------------------------------------------------------------------------------------------- */
 
 /* Y[m,n] = out_dtype( float(sum_k Xq[m,k]*Wq[n,k]) * ((absmax[m*absmax_stride]/127) * gamma) ).

@@ -64,10 +64,88 @@ def test_quantize_rows_bit_exact(ops, M, K, dtype):
         x[1] = 0.0                      # all-zero token: absmax clamps to eps
         x[2, 0] = float("inf")          # non-finite values count as zero
         x[2, K - 1] = float("nan")
+    if M > 4:
+        x[3, K // 2] = float("nan")     # NaN alone: the row keeps the unchecked conversion
+        x[4, K // 3] = float("-inf")
     q, a = ops.quantize_rows(x.to(DEV))
     qo, ao = O.quantize_rows(t2n(x))
     assert np.array_equal(a.cpu().numpy(), ao)
     assert np.array_equal(q.cpu().numpy(), qo)
+
+
+# ---- pre-linear RMSNorm fused with the quantiser ---------------------------------------------------------------
+
+_IO = {torch.bfloat16: "bf16", torch.float16: "f16", torch.float32: "f32"}
+
+
+@pytest.mark.parametrize("M,K", [(1, 8), (7, 64), (33, 1536), (16, 4096), (5, 11008)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_rmsnorm_quantize_rows_bit_exact(ops, M, K, dtype):
+    """int8 tokens, absmax and rstd equal the oracle's (RMSNorm as the reference writes it, then the per-token
+    quantiser) bit for bit: row sums are accumulated in float64 on both sides."""
+    g = torch.Generator().manual_seed(M * 11 + K)
+    x = (torch.randn(M, K, generator=g) * 2.5).to(dtype)
+    w = (1.0 + 0.3 * torch.randn(K, generator=g)).float()
+    if M > 2:
+        x[1] = 0.0                          # all-zero token: rstd = 1/sqrt(eps), absmax clamps to the quantiser's eps
+        x[2, 0] = float("nan")              # a NaN poisons the token's sum of squares: the whole token quantises to 0
+    if M > 4:
+        x[3, K - 1] = float("inf")
+    q, a, rstd = ops.rmsnorm_quantize_rows(x.to(DEV), w.to(DEV), 1e-6, 1e-5)
+    with np.errstate(all="ignore"):
+        qo, ao, ro = O.rmsnorm_quantize_rows(t2n(x), w.numpy(), 1e-6, 1e-5, _IO[dtype])
+    assert np.array_equal(rstd.cpu().numpy(), ro, equal_nan=True)
+    assert np.array_equal(a.cpu().numpy(), ao)
+    assert np.array_equal(q.cpu().numpy(), qo)
+
+
+@pytest.mark.parametrize("i", range(4))
+def test_rmsnorm_kernels_match_reference_module_golden(ops, i):
+    """The fused kernels against the reference module's own outputs (tests/golden/rmsnorm.npz): int8 tokens within
+    one step on at most 0.5 % of the elements (torch's float32 summation order differs), input gradient within one
+    unit of the I/O type, weight gradient within the precision the reference sums it in."""
+    g = np.load(os.path.join(GOLDEN, "rmsnorm.npz"))
+    io = str(g[f"io{i}"])
+    dt = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}[io]
+    x = torch.from_numpy(g[f"x{i}"]).to(dt).to(DEV)
+    w = torch.from_numpy(g[f"w{i}"]).to(DEV)
+    gy = torch.from_numpy(g[f"gy{i}"]).to(dt).to(DEV)
+    q, a, rstd = ops.rmsnorm_quantize_rows(x, w, float(g[f"eps{i}"]), 1e-5)
+    unit = {"bf16": 2.0 ** -8, "f16": 2.0 ** -11, "f32": 1e-5}[io]
+    assert np.allclose(a.cpu().numpy(), g[f"absmax{i}"], rtol=unit * 1.01, atol=0)
+    dq = np.abs(q.cpu().numpy().astype(np.int32) - g[f"q{i}"].astype(np.int32))
+    assert dq.max() <= 1 and (dq != 0).mean() <= 5e-3
+    dx, dw = ops.rmsnorm_backward(gy, x, w, rstd)
+    ref_dx = g[f"dx{i}"]
+    tol = unit * np.maximum(np.abs(ref_dx), np.abs(ref_dx).max() * 1e-3) * 1.01
+    assert np.all(np.abs(t2n(dx) - ref_dx) <= tol)
+    dw_tol = {"bf16": 1e-2, "f16": 2e-3, "f32": 1e-5}[io]
+    assert np.abs(dw.cpu().numpy() - g[f"dw{i}"]).max() <= dw_tol * np.abs(g[f"dw{i}"]).max()
+
+
+@pytest.mark.parametrize("M,K", [(1, 8), (9, 64), (300, 1536), (1200, 4096), (64, 11008)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_rmsnorm_backward_bit_exact(ops, M, K, dtype):
+    """dx and dweight equal the oracle's bit for bit (float64 row and column sums on both sides)."""
+    g = torch.Generator().manual_seed(M * 13 + K)
+    x = (torch.randn(M, K, generator=g) * 1.5).to(dtype)
+    gy = (torch.randn(M, K, generator=g) * 1e-2).to(dtype)
+    w = (1.0 + 0.3 * torch.randn(K, generator=g)).float()
+    rstd = torch.from_numpy(O.rmsnorm_rstd(t2n(x), 1e-6))
+    dx, dw = ops.rmsnorm_backward(gy.to(DEV), x.to(DEV), w.to(DEV), rstd.to(DEV))
+    dxo, dwo = O.rmsnorm_backward(t2n(gy), t2n(x), w.numpy(), rstd.numpy(), _IO[dtype])
+    assert np.array_equal(t2n(dx), dxo)
+    assert np.array_equal(dw.cpu().numpy(), dwo)
+
+
+def test_rmsnorm_rejects_what_it_cannot_run(ops, pkg):
+    x = torch.zeros(4, 100, dtype=torch.bfloat16, device=DEV)        # K % 8 != 0
+    with pytest.raises(pkg.ElleciError) as e:
+        ops.rmsnorm_quantize_rows(x, torch.ones(100, device=DEV))
+    assert e.value.status == pkg._lib.EL_ERR_UNSUPPORTED_SHAPE
+    assert not ops.rmsnorm_supported(x)
+    q, a, r = ops.rmsnorm_quantize_rows(torch.empty(0, 64, dtype=torch.bfloat16, device=DEV), torch.ones(64, device=DEV))
+    assert q.shape == (0, 64) and a.numel() == 0 and r.numel() == 0
 
 
 def test_quantize_rows_empty_inputs(ops):
@@ -88,9 +166,13 @@ def test_quantize_tensor_matches_reference_kernel_golden(ops, i):
     assert np.array_equal(deq.cpu().numpy().view(np.uint16), g[f"deq_bits{i}"])
 
 
-def test_grad_quantisation_bit_exact(ops):
+@pytest.mark.parametrize("special", [False, True])
+def test_grad_quantisation_bit_exact(ops, special):
     d = make_layer_inputs(37, 96, 80, seed=3, dy_std=1e-3)
     x, dY = d["x"], d["dY"]
+    if special:                         # non-finite gradients count as zero
+        dY = dY.clone()
+        dY[0, 0], dY[5, 79], dY[36, 40], dY[7, 7] = float("nan"), float("inf"), float("-inf"), -0.0
     _, ax = ops.quantize_rows(x.to(DEV))
     dYq, ady, gmax = ops.quantize_rows(dY.to(DEV), 1e-30, fold_absmax=ax)
     Gq = ops.quantize_grad(dY.to(DEV), ax, gmax)

@@ -146,3 +146,57 @@ def test_convert_all_linear_to_int2(pkg):
     out.float().pow(2).mean().backward()
     assert out.shape == (4, 10, 300) and torch.isfinite(out.float()).all()
     assert conv.w1.int2_layer._step_py == 1 and conv.w2.int2_layer._step_py == 1
+
+
+@pytest.mark.parametrize("M,K,N,dtype", [(256, 1536, 512, torch.bfloat16), (64, 256, 96, torch.float32)])
+def test_bitlinear_fused_rmsnorm_matches_oracle_and_unfused_module(pkg, M, K, N, dtype):
+    """BitLinearInt2 with the pre-linear RMSNorm fused into the quantiser: the step equals the oracle's composite
+    (norm -> quantise -> GEMM; dX GEMM -> norm backward) bit for bit, and agrees with the same module running the norm
+    as separate tensor operations within rel-err 1e-2 (torch sums the squares in another order; a one-ulp difference in
+    rstd can move an activation across an int8 rounding boundary, so the bound is that of the 8-bit grid for both
+    I/O types)."""
+    d = make_layer_inputs(M, K, N, seed=5, dtype=dtype, dy_std=1e-2)
+    io = {torch.bfloat16: "bf16", torch.float32: "f32"}[dtype]
+    gen = torch.Generator().manual_seed(9)
+    nw = (1.0 + 0.2 * torch.randn(K, generator=gen)).float()
+
+    def run(fused):
+        m = pkg.BitLinearInt2(K, N, threshold=2, use_grad_hook=True, hysteresis_order="after_dx").to(DEV)
+        m.fuse_rmsnorm = fused
+        m.int2_layer.init_from_float(d["W"].to(DEV), scale=d["gamma"])
+        m.int2_layer.H_packed.copy_(torch.from_numpy(d["Hp"]))
+        with torch.no_grad():
+            m.extra_rmsnorm.weight.copy_(nw)
+        m.train()
+        m.set_lr(0.5)
+        x = (d["x"] * 3.0).to(dtype).to(DEV).requires_grad_(True)
+        y = m(x)
+        y.backward(d["dY"].to(DEV))
+        torch.cuda.synchronize()
+        return m, x, y
+
+    mf, xf, yf = run(True)
+    mu, xu, yu = run(False)
+    pkg.int2_tc_ops.check_device_status(torch.device(DEV))
+
+    x_np = t2n((d["x"] * 3.0).to(dtype))
+    Xq, ax, rstd = O.rmsnorm_quantize_rows(x_np, nw.numpy(), 1e-6, 1e-5, io)
+    yo = O.scale_rows(O.gemm_fwd_acc(Xq, d["Wp"], K), ax, d["gamma"])
+    yo = O.to_bf16(yo) if io == "bf16" else yo
+    assert np.array_equal(t2n(yf), yo)
+    dxn = O.bitlinear_backward_dx(t2n(d["dY"]), d["Wp"], d["gamma"], K, out=io)     # after_dx: the old weights
+    dxo, dwo = O.rmsnorm_backward(dxn, x_np, nw.numpy(), rstd, io)
+    assert np.array_equal(t2n(xf.grad), dxo)
+    assert np.array_equal(mf.extra_rmsnorm.weight.grad.cpu().numpy(), dwo)
+    dWo, _, _ = O.bitlinear_dw(t2n(d["dY"]), Xq, ax)
+    Wn, Hn = native.c_hysteresis_step(dWo, d["Wp"], d["Hp"], 0.5, 5.0, 2, 0.001, 1, K)
+    assert np.array_equal(mf.int2_layer.W_packed.cpu().numpy(), Wn) and np.array_equal(mf.int2_layer.H_packed.cpu().numpy(), Hn)
+
+    tol = 1e-2
+
+    def rel(a, b):
+        return float((a.float() - b.float()).abs().max() / b.float().abs().max())
+
+    assert rel(yf, yu) <= tol
+    assert rel(xf.grad, xu.grad) <= tol
+    assert rel(mf.extra_rmsnorm.weight.grad, mu.extra_rmsnorm.weight.grad) <= tol
