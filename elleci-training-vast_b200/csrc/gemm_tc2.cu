@@ -49,6 +49,7 @@ struct OutMaps {
 struct Params {
     int R, C, D;
     int tiles_r, tiles_c, k_blocks;     // tiles_r counts 256-row pair tiles
+    int group_rows;                     // row tiles per band of the tile order (see tile_coords)
     EpiParams epi;
     int vec_ok;
     int tma_store;                      // the output takes TMA stores (16-byte aligned base and pitch)
@@ -56,6 +57,19 @@ struct Params {
     int rows_per_dst;                   // > 0: scatter instead - rows [d*rows_per_dst, (d+1)*rows_per_dst) go to destination d only
     int32_t* status;
 };
+
+// Tile order: bands of `group_rows` row tiles; inside a band the column tiles follow one another and the band's row tiles
+// run fastest.  The pairs of one wave then share a few weight tiles while the band's activation rows (sized by the host
+// to stay in L2) are read from HBM once instead of once per column tile.  group_rows = tiles_r is the plain row-fastest
+// order.
+__device__ __forceinline__ void tile_coords(int t, const Params& p, int& tr, int& tc) {
+    const int per_band = p.group_rows * p.tiles_c;
+    const int band = t / per_band, in = t - band * per_band;
+    const int first = band * p.group_rows;
+    const int rows_here = min(p.group_rows, p.tiles_r - first);
+    tc = in / rows_here;
+    tr = first + (in - tc * rows_here);
+}
 
 template <int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -123,7 +137,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             int s = 0;
             uint32_t ph = 0;
             for (int t = pair; t < num_tiles && !failed; t += num_pairs) {
-                const int r0 = (t % p.tiles_r) * (2 * BM) + (int)rank * BM;
+                int trow, tcol;
+                tile_coords(t, p, trow, tcol);
+                const int r0 = trow * (2 * BM) + (int)rank * BM;
                 for (int kb = 0; kb < p.k_blocks; ++kb) {
                     if (!mbar_wait_cluster(bar_aempty(s), ph ^ 1u, p.status, 21)) { failed = true; break; }
                     if (rank == 0) mbar_expect_tx(bar_afull(s), 2 * A_BYTES);
@@ -138,7 +154,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             int s = 0;
             uint32_t ph = 0;
             for (int t = pair; t < num_tiles && !failed; t += num_pairs) {
-                const int c0 = (t / p.tiles_r) * BN + (int)rank * 128;     // this CTA's 128 output columns
+                int trow, tcol;
+                tile_coords(t, p, trow, tcol);
+                const int c0 = tcol * BN + (int)rank * 128;     // this CTA's 128 output columns
                 for (int kb = 0; kb < p.k_blocks; ++kb) {
                     if (!mbar_wait(bar_pempty(s), ph ^ 1u, p.status, 27)) { failed = true; break; }
                     const uint32_t sp = ring_p + s * P_BYTES;
@@ -192,7 +210,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const int row_in_tile = quarter * 32 + lane;
         int it = 0;
         for (int t = pair; t < num_tiles && !failed; t += num_pairs, ++it) {
-            const int r0 = (t % p.tiles_r) * (2 * BM) + (int)rank * BM, c0 = (t / p.tiles_r) * BN;
+            int trow, tcol;
+            tile_coords(t, p, trow, tcol);
+            const int r0 = trow * (2 * BM) + (int)rank * BM, c0 = tcol * BN;
             const int acc = it & 1;
             const uint32_t acc_ph = (uint32_t)(it >> 1) & 1u;
             if (!mbar_wait_warp(bar_tfull(acc), acc_ph, p.status, 25)) { failed = true; break; }
@@ -385,6 +405,11 @@ static int launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB, const OutMap
     p.tiles_r = (p.R + 2 * BM - 1) / (2 * BM);
     p.tiles_c = (p.C + BN - 1) / BN;
     p.k_blocks = (p.D + BK - 1) / BK;
+    // a band's activation rows (256 rows x D bytes per row tile) should fit in a third of the 126 MB L2
+    const long long row_tile_bytes = 2LL * BM * (long long)p.k_blocks * BK;
+    long long group = (40LL << 20) / (row_tile_bytes > 0 ? row_tile_bytes : 1);
+    p.group_rows = (int)(group < 1 ? 1 : (group > p.tiles_r ? p.tiles_r : group));
+    if (p.group_rows < 1) p.group_rows = 1;
     const long long tiles = (long long)p.tiles_r * p.tiles_c;
     if (tiles == 0) return EL_OK;
     if (p.k_blocks == 0) return EL_ERR_UNSUPPORTED_SHAPE;

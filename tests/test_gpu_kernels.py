@@ -301,6 +301,24 @@ def test_gemms_tensor_core_path_bit_exact(ops, pkg, M, N, K, single_cta):
     ops.check_device_status(torch.device(DEV))
 
 
+def test_pair_kernel_banded_tile_order_bit_exact(ops, pkg):
+    """A reduction so deep (65536) that the pair kernel orders its tiles in bands of two 256-row tiles: five row
+    tiles give the bands 2 + 2 + 1 (ragged last band), two column tiles each."""
+    rng = np.random.default_rng(21)
+    M, big, small = 1280, 65536, 512
+    Xq = rng.integers(-128, 128, (M, big)).astype(np.int8)
+    Wp, _ = random_packed(small, big, 3)                     # forward: K = 65536, N = 512
+    a = _cuda(np.ones(M, np.float32))
+    y = ops.matmul_rows(_cuda(Xq), _cuda(Wp), a, 1.0, torch.int32, pkg._lib.EL_PATH_TC)
+    assert np.array_equal(y.cpu().numpy(), O.gemm_fwd_acc(Xq, Wp, big))
+    del Xq, Wp
+    dYq = rng.integers(-128, 128, (M, big)).astype(np.int8)
+    Wp2, _ = random_packed(big, small, 4)                    # dX: reduction over N = 65536, K = 512 output columns
+    dx = ops.backward_input_rows(_cuda(dYq), _cuda(Wp2), a, 1.0, small, torch.int32, pkg._lib.EL_PATH_TC)
+    assert np.array_equal(dx.cpu().numpy(), O.gemm_dx_acc(dYq, Wp2, small))
+    ops.check_device_status(torch.device(DEV))
+
+
 def test_tensor_core_forward_with_ragged_n(ops, pkg):
     """The forward GEMM alone has no constraint on N (only dX and dW read a pitch of N bytes)."""
     M, N, K = 200, 300, 320
