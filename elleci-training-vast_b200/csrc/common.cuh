@@ -129,6 +129,53 @@ __device__ __forceinline__ void hyst_update_one(float grad, int& q, int& h, uint
     h = mv ? 0 : max(-thr, min(thr, hn));
 }
 
+// The same update for 32 consecutive weights of one row held as packed words (w: 2 words of 2-bit codes, h: 4 words of
+// int4 counters), from their int32 gradient sums acc[32] scaled by sc.  Same results as 32 calls of hyst_update_one,
+// with the per-weight work trimmed for the fused weight-gradient epilogue, which is bound by these instructions:
+//  * stochastic rounding in integers: with T = ceil(|d|*2^24) (one saturating conversion, NaN -> 0),
+//    floor(|d|) + [u1/2^24 < frac(|d|)] = ((T - 1 - u1) >> 24) + 1 exactly, for every |d| up to the clamp at 31;
+//  * codes are sanitised (3 -> 1) once per word and stay biased (q+1), counters are read biased by 8 (word ^ 0x88888888);
+//  * the new words are built from zero with one multiply-add per field instead of a masked read-modify-write;
+//  * ALIGNED (idx0 a multiple of 32): idx0 + j = idx0 ^ j, so the counter xor seed is one operation per weight.
+template <bool FTZ, bool ALIGNED>
+__device__ __forceinline__ void hyst_update_chunk32(const uint32_t acc[32], float sc, uint32_t w[2], uint32_t h[4],
+                                                    uint32_t idx0, const HystParams& p) {
+    uint32_t ws[2], hb[4], wn[2] = {0u, 0u}, hn[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+    for (int i = 0; i < 2; ++i) ws[i] = w[i] ^ ((w[i] & (w[i] >> 1) & 0x55555555u) << 1);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) hb[i] = h[i] ^ 0x88888888u;
+    const uint32_t b1 = idx0 ^ p.s1, b2 = idx0 ^ p.s2;
+    const int thr = p.thr;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        const int wi = j >> 4, wsft = (j & 15) * 2, hi = j >> 3, hsft = (j & 7) * 4;
+        const int qb = (int)((ws[wi] >> wsft) & 3u);             // q + 1
+        const int nib = (int)((hb[hi] >> hsft) & 0xFu);          // h + 8
+        const uint32_t u1 = mix2(ALIGNED ? (b1 ^ (uint32_t)j) : ((idx0 + j) ^ p.s1)) & 0xFFFFFFu;
+        const uint32_t u2 = mix2(ALIGNED ? (b2 ^ (uint32_t)j) : ((idx0 + j) ^ p.s2)) & 0xFFFFFFu;
+        const float grad = __fmul_rn((float)(int)acc[j], sc);
+        float d_raw;
+        if (FTZ) asm("mul.ftz.f32 %0, %1, %2;" : "=f"(d_raw) : "f"(-grad), "f"(p.lr_scaled));
+        else d_raw = __fmul_rn(-grad, p.lr_scaled);
+        const int T = __float2int_ru(__fmul_rn(fabsf(d_raw), 16777216.0f));      // saturates; NaN -> 0
+        const int mag = min(((T - 1 - (int)u1) >> 24) + 1, 31);
+        const int sgn = (__float_as_int(d_raw) >> 31) | 1;
+        int hv = nib - 8 + sgn * mag;
+        if (qb != 1 && u2 < p.decay_u24) hv -= qb - 1;
+        const int up = (hv >= thr && qb < 2) ? 1 : 0;
+        const int dn = (hv <= -thr && qb > 0) ? 1 : 0;
+        const int mv = up - dn;
+        const int hc = mv ? 0 : max(-thr, min(thr, hv));
+        wn[wi] += (uint32_t)(qb + mv) << wsft;
+        hn[hi] += (uint32_t)hc << hsft;                          // signed fields: the bias below turns them into nibbles
+    }
+    w[0] = wn[0];
+    w[1] = wn[1];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = (hn[i] + 0x88888888u) ^ 0x88888888u;
+}
+
 // Host-side preparation of HystParams from the API arguments.
 inline HystParams make_hyst_params(float lr, float lr_scale, int threshold, float decay, uint32_t step, int ftz) {
     HystParams p;

@@ -187,10 +187,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const int r0 = (t % p.tiles_r) * BM, c0 = (t / p.tiles_r) * BN;
             const int acc = it & 1;
             const uint32_t acc_ph = (uint32_t)(it >> 1) & 1u;
-            if (!mbar_wait_warp(bar_tfull(acc), acc_ph, p.status, 5)) { failed = true; break; }
-            tcgen05_fence_after();
             const int row = r0 + row_in_tile;
             const bool row_ok = row < p.R;
+            // Fused update: the packed weights and counters of this warp's chunks do not depend on the accumulator, so they
+            // are requested before the wait for it and arrive while the tile's MMAs still run.
+            constexpr int HYST_CHUNKS = (BN / 32 + EPI_SPLIT - 1) / EPI_SPLIT;
+            uint2 w_pre[HYST_CHUNKS];
+            uint4 h_pre[HYST_CHUNKS];
+            if (EPI == EPI_HYST) {
+#pragma unroll
+                for (int i = 0; i < HYST_CHUNKS; ++i) {
+                    const int c = (XFORM ? 0 : sub) + i * EPI_SPLIT;
+                    const int col0 = c0 + c * 32;
+                    if (c < BN / 32 && row_ok && col0 < p.C) {     // K % 32 == 0: a chunk is inside or outside as a whole
+                        w_pre[i] = *reinterpret_cast<const uint2*>(p.Wp + (size_t)row * p.pK + (col0 >> 2));
+                        h_pre[i] = *reinterpret_cast<const uint4*>(p.Hp + (size_t)row * p.pH + (col0 >> 1));
+                    }
+                }
+            }
+            if (!mbar_wait_warp(bar_tfull(acc), acc_ph, p.status, 5)) { failed = true; break; }
+            tcgen05_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
             if (EPI == EPI_SCALE) {
                 const float sc = row_ok ? epi_row_scale(p.epi, row) : 0.0f;
@@ -205,32 +221,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             } else {
                 // weight-gradient tile -> hysteresis update of 32 weights of row `row` per chunk
                 const float sc = epi_row_scale(p.epi, 0);   // g_absmax/127 (one scale for the tensor)
-#pragma unroll 1
-                for (int c = (XFORM ? 0 : sub); c < BN / 32; c += EPI_SPLIT) {
+#pragma unroll
+                for (int i = 0; i < HYST_CHUNKS; ++i) {
+                    const int c = (XFORM ? 0 : sub) + i * EPI_SPLIT;
+                    if (c >= BN / 32) break;
                     uint32_t v[32];
                     tmem_ld32(taddr + c * 32, v);
                     tmem_ld_wait();
                     const int col0 = c0 + c * 32;
-                    if (row_ok && col0 < p.C) {     // K % 32 == 0: a chunk is inside or outside as a whole
-                        uint2* wptr = reinterpret_cast<uint2*>(p.Wp + (size_t)row * p.pK + (col0 >> 2));
-                        uint4* hptr = reinterpret_cast<uint4*>(p.Hp + (size_t)row * p.pH + (col0 >> 1));
-                        const uint2 w2 = *wptr;
-                        const uint4 h4 = *hptr;
-                        uint32_t w[2] = {w2.x, w2.y};
-                        uint32_t h[4] = {h4.x, h4.y, h4.z, h4.w};
+                    if (row_ok && col0 < p.C) {
+                        uint32_t w[2] = {w_pre[i].x, w_pre[i].y};
+                        uint32_t h[4] = {h_pre[i].x, h_pre[i].y, h_pre[i].z, h_pre[i].w};
                         const uint32_t idx0 = p.idx_base + (uint32_t)row * (uint32_t)p.C + (uint32_t)col0;
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            const int wi = j >> 4, ws = (j & 15) * 2, hi = j >> 3, hs = (j & 7) * 4;
-                            int q = decode2(w[wi] >> ws);
-                            int hv = (int)((h[hi] >> hs) & 0xFu);
-                            hv = (hv & 8) ? hv - 16 : hv;
-                            hyst_update_one<true>(__fmul_rn((float)(int)v[j], sc), q, hv, idx0 + j, p.hp);
-                            w[wi] = (w[wi] & ~(3u << ws)) | ((uint32_t)(q + 1) << ws);
-                            h[hi] = (h[hi] & ~(0xFu << hs)) | (((uint32_t)hv & 0xFu) << hs);
-                        }
-                        *wptr = make_uint2(w[0], w[1]);
-                        *hptr = make_uint4(h[0], h[1], h[2], h[3]);
+                        if ((p.idx_base & 31u) == 0) hyst_update_chunk32<true, true>(v, sc, w, h, idx0, p.hp);     // C % 32 == 0
+                        else hyst_update_chunk32<true, false>(v, sc, w, h, idx0, p.hp);
+                        *reinterpret_cast<uint2*>(p.Wp + (size_t)row * p.pK + (col0 >> 2)) = make_uint2(w[0], w[1]);
+                        *reinterpret_cast<uint4*>(p.Hp + (size_t)row * p.pH + (col0 >> 1)) = make_uint4(h[0], h[1], h[2], h[3]);
                     }
                 }
             }
