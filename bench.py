@@ -537,9 +537,12 @@ def run_decode(args):
         Ws = [torch.randint(0, 256, (N, K // 4), generator=gen, dtype=torch.uint8).to(dev) for _ in range(nbuf)]
         # overlap: the GEMV issued as a programmatic dependent launch (weights constant, as at inference), so that a
         # call's weight loads start under the tail of the previous call
-        for M, gemv_max, overlap in ((1, 4, False), (1, 4, True), (4, 4, False), (4, 4, True), (8, 8, True), (8, 0, False),
-                                     (32, 4, False), (64, 4, False)):
+        # columns: tokens, limit of the CUDA-core GEMV, limit of the warp-MMA kernel (tcgen05 stream-K above it), overlap
+        for M, gemv_max, mma_max, overlap in ((1, 4, 32, False), (1, 4, 32, True), (4, 4, 32, False), (4, 4, 32, True),
+                                              (8, 8, 32, True), (8, 4, 32, False), (8, 4, 32, True), (8, 0, 0, False),
+                                              (16, 4, 32, True), (32, 4, 32, True), (32, 4, 0, False), (64, 4, 32, False)):
             pkg._lib.lib().el_set_decode_gemv_max_tokens(gemv_max)
+            pkg._lib.lib().el_set_decode_mma_max_tokens(mma_max)
             ops.set_decode_overlap(overlap)
             x = torch.randn(M, K, generator=gen).to(torch.bfloat16).to(dev)
             for W in Ws[:3]:
@@ -562,11 +565,14 @@ def run_decode(args):
             us = e0.elapsed_time(e1) * 1e3 / (reps * nbuf)
             nbytes = N * K // 4 + 2 * M * K + 2 * M * N
             gbs = nbytes / (us * 1e-6) / 1e9
-            cases.append({"M": M, "K": K, "N": N, "kernel": "gemv" if M <= gemv_max else "tcgen05", "overlap": overlap, "us_per_call": us, "GBps": gbs, "frac_of_hbm": gbs / peaks["hbm_gbs"],
+            fits_mma = M <= mma_max and M * K <= 190 * 1024 * (M / (8 if M <= 8 else 16 if M <= 16 else 32))
+            kernel = "gemv" if M <= gemv_max else ("mma" if fits_mma else "tcgen05")
+            cases.append({"M": M, "K": K, "N": N, "kernel": kernel, "overlap": overlap, "us_per_call": us, "GBps": gbs, "frac_of_hbm": gbs / peaks["hbm_gbs"],
                           "algorithmic_bytes": nbytes})
         ops.check_device_status(dev)
         del Ws
     pkg._lib.lib().el_set_decode_gemv_max_tokens(4)
+    pkg._lib.lib().el_set_decode_mma_max_tokens(32)
     ops.set_decode_overlap(False)
     head = next(c for c in cases if c["M"] == 1 and c["K"] == 4096 and c["overlap"])
     line = {
@@ -574,7 +580,7 @@ def run_decode(args):
         "unit": "GB/s", "n_gpus": 1, "steps": max(args.steps, 10), "warmup": 3, "ms_per_step": head["us_per_call"] * 1e-3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8 x int2 -> int32 (bf16 in/out)",
         "data": "synthetic",
-        "config": {"workload": "config3: decode shapes, M in {1,4,8,32,64}, 4096->11008 and 11008->4096; 16 rotating weight "
+        "config": {"workload": "config3: decode shapes, M in {1,4,8,16,32,64}, 4096->11008 and 11008->4096; 16 rotating weight "
                                "buffers (> L2) in one CUDA graph; value = M=1, 4096->11008, dependent-launch overlap on"},
         "roofline": {"bound": "hbm", "achieved": head["GBps"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": head["GBps"] / peaks["hbm_gbs"], "traffic": None, "peak_source": f"hbm_gbs ({peak_kind})"},

@@ -41,6 +41,9 @@ int launch_rmsnorm_quantize_rows(const void* x, int dt, long long ldx, const flo
 size_t rmsnorm_backward_workspace_bytes(int K);
 int launch_rmsnorm_backward(const void* g, const void* x, int dt, const float* weight, const float* rstd, void* dx,
                             float* dweight, void* workspace, size_t workspace_bytes, int M, int K, cudaStream_t st);
+int launch_gemv_mma(const void* x, int x_dtype, const uint8_t* Wp, const EpiParams& epi, int M, int N, int K, cudaStream_t st,
+                    bool overlap);
+bool gemv_mma_fits(int M, int K);
 int launch_gemv_small(const void* x, int x_dtype, const uint8_t* Wp, const EpiParams& epi, int M, int N, int K, cudaStream_t st, bool overlap);
 int decode_gemv_max_tokens();
 
@@ -87,6 +90,8 @@ int device_sm_count(int* out) { return device_info(out, nullptr); }
 // Token count up to which the decode call uses the CUDA-core GEMV (el_set_decode_gemv_max_tokens).
 static int g_gemv_max_tokens = 4;
 int decode_gemv_max_tokens() { return g_gemv_max_tokens; }
+static int g_mma_max_tokens = 32;
+int decode_mma_max_tokens() { return g_mma_max_tokens; }
 static int g_decode_overlap = 0;
 bool decode_overlap() { return g_decode_overlap != 0; }
 
@@ -325,6 +330,12 @@ int el_set_decode_gemv_max_tokens(int max_tokens) {
     return EL_OK;
 }
 
+int el_set_decode_mma_max_tokens(int max_tokens) {
+    if (max_tokens < 0 || max_tokens > 32) return EL_ERR_INVALID_ARG;
+    g_mma_max_tokens = max_tokens;
+    return EL_OK;
+}
+
 int el_set_decode_overlap(int enable) {
     g_decode_overlap = enable ? 1 : 0;
     return EL_OK;
@@ -343,6 +354,10 @@ int el_linear_decode(const void* x, int x_dtype, const uint8_t* W_packed, void* 
     if (M <= decode_gemv_max_tokens()) {      // a handful of tokens: one CUDA-core launch, no scratch touched
         const EpiParams gepi{Y, (long long)N, out_dtype, nullptr, 0, gamma};
         return launch_gemv_small(x, x_dtype, W_packed, gepi, M, N, K, (cudaStream_t)stream, decode_overlap());
+    }
+    if (M <= decode_mma_max_tokens() && gemv_mma_fits(M, K)) {      // up to 32 tokens that fit in shared memory: one warp-MMA launch
+        const EpiParams gepi{Y, (long long)N, out_dtype, nullptr, 0, gamma};
+        return launch_gemv_mma(x, x_dtype, W_packed, gepi, M, N, K, (cudaStream_t)stream, decode_overlap());
     }
     int rc = launch_quantize_rows_perm(x, x_dtype, K, xq_scratch, absmax, M, K, 1e-5f, (cudaStream_t)stream);
     if (rc != EL_OK) return rc;

@@ -362,8 +362,12 @@ static int decode_static_setup(unsigned char** out) {
 int launch_quantize_rows_perm(const void* x, int dt, long long ldx, int8_t* q, float* a, int M, int K, float eps,
                               cudaStream_t st);
 int launch_gemv_small(const void* x, int x_dtype, const uint8_t* Wp, const EpiParams& epi, int M, int N, int K, cudaStream_t st, bool overlap);
+int launch_gemv_mma(const void* x, int x_dtype, const uint8_t* Wp, const EpiParams& epi, int M, int N, int K, cudaStream_t st,
+                    bool overlap);
+bool gemv_mma_fits(int M, int K);
 bool decode_overlap();
 int decode_gemv_max_tokens();
+int decode_mma_max_tokens();
 
 }  // namespace el
 
@@ -380,6 +384,10 @@ extern "C" EL_API int el_linear_decode_static(const void* x, int x_dtype, const 
     if (M <= decode_gemv_max_tokens()) {      // the few-token kernel needs no scratch at all
         const EpiParams gepi{Y, (long long)N, out_dtype, nullptr, 0, gamma};
         return launch_gemv_small(x, x_dtype, W_packed, gepi, M, N, K, st, decode_overlap());
+    }
+    if (M <= decode_mma_max_tokens() && gemv_mma_fits(M, K)) {      // neither does the warp-MMA kernel
+        const EpiParams gepi{Y, (long long)N, out_dtype, nullptr, 0, gamma};
+        return launch_gemv_mma(x, x_dtype, W_packed, gepi, M, N, K, st, decode_overlap());
     }
     unsigned char* base = nullptr;
     int rc = decode_static_setup(&base);

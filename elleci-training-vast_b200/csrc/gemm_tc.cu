@@ -38,6 +38,12 @@ constexpr int BK = 128;            // reduction depth per stage (bytes of int8)
 constexpr int UMMA_K = 32;         // reduction depth of one kind::i8 instruction
 constexpr int WARP_TMA = 0, WARP_MMA = 1, NUM_EPI_WARPS = 4, WARP_XF0 = 6, NUM_XF_WARPS = 8;   // warps 2..5: epilogue
 constexpr int NUM_THREADS = (WARP_XF0 + NUM_XF_WARPS) * 32;   // 448
+// The fused weight-gradient kernel has no weight tile to expand and is bound by its epilogue: it runs sixteen epilogue
+// warps (four per quarter of the tensor-memory lanes, two 32-column chunks each) instead of twelve.
+constexpr int DW_EXTRA_WARPS = 4;
+__host__ __device__ constexpr int num_threads(int mode, int epi) {
+    return NUM_THREADS + ((mode == MODE_DW && epi == EPI_HYST) ? DW_EXTRA_WARPS * 32 : 0);
+}
 
 constexpr int A_BYTES = BM * BK;                       // 16 KB
 template <int BN> struct Cfg {
@@ -65,7 +71,7 @@ struct Params {
 // ---- the kernel ----------------------------------------------------------------------------------------------
 
 template <int MODE, int BN, int EPI>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(num_threads(MODE, EPI), 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Params p) {
     using C = Cfg<BN>;
     constexpr int STAGES = C::STAGES(MODE);
@@ -98,7 +104,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(bar_tfull(a), 1);
-            mbar_init(bar_tempty(a), XFORM ? NUM_EPI_WARPS : NUM_EPI_WARPS + NUM_XF_WARPS);
+            mbar_init(bar_tempty(a), num_threads(MODE, EPI) / 32 - 2 - (XFORM ? NUM_XF_WARPS : 0));
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_async_smem();
@@ -178,7 +184,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // ================= epilogue =================
         // Without a weight tile to expand (DW) the eight transform warps join in: three warps share each
         // quarter of the tensor-memory lanes and take the 32-column chunks round-robin.
-        constexpr int EPI_SPLIT = XFORM ? 1 : 3;
+        constexpr int EPI_SPLIT = XFORM ? 1 : (num_threads(MODE, EPI) / 32 - 2) / 4;      // 3, or 4 in the fused kernel
         const int quarter = warp & 3;                 // the tensor-memory lanes this warp may read
         const int sub = (warp - 2) >> 2;              // 0 for warps 2-5, 1 for 6-9, 2 for 10-13
         const int row_in_tile = quarter * 32 + lane;
@@ -374,7 +380,7 @@ static int launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB, Params& p, c
     if (tiles == 0) return EL_OK;
     if (p.k_blocks == 0) return EL_ERR_UNSUPPORTED_SHAPE;
     const int grid = (int)(tiles < sms ? tiles : sms);
-    gemm_tc_kernel<MODE, BN, EPI><<<grid, NUM_THREADS, smem, st>>>(tmA, tmB, p);
+    gemm_tc_kernel<MODE, BN, EPI><<<grid, num_threads(MODE, EPI), smem, st>>>(tmA, tmB, p);
     return check_launch();
 }
 

@@ -362,14 +362,16 @@ def test_fused_dw_hysteresis_bit_exact(ops, M, N, K, thr):
 
 @pytest.fixture
 def gemv_threshold(ops):
-    """Lets a test choose between the few-token CUDA-core GEMV and the tensor-core decode kernel."""
-    def set_(v):
+    """Lets a test choose between the few-token CUDA-core GEMV (up to `v` tokens), the warp-MMA kernel (up to `mma`
+    tokens) and the tcgen05 stream-K kernel (the rest)."""
+    def set_(v, mma=0):
         assert ops._lib.lib().el_set_decode_gemv_max_tokens(v) == 0
+        assert ops._lib.lib().el_set_decode_mma_max_tokens(mma) == 0
     yield set_
-    set_(4)
+    set_(4, 32)
 
 
-@pytest.mark.parametrize("gemv_max", [0, 8])
+@pytest.mark.parametrize("gemv_max", [0, 8, "mma"])
 @pytest.mark.parametrize("M", [1, 3, 8, 17, 32, 64])
 @pytest.mark.parametrize("K,N", [(4096, 11008), (11008, 4096), (256, 384), (192, 100)])
 def test_linear_decode_bit_exact(ops, gemv_threshold, M, K, N, gemv_max):
@@ -381,7 +383,11 @@ def test_linear_decode_bit_exact(ops, gemv_threshold, M, K, N, gemv_max):
     gamma = 0.0161
     Xq, ax = O.quantize_rows(t2n(x))
     want = O.to_bf16(O.scale_rows(O.gemm_fwd_acc(Xq, Wp, K), ax, gamma))
-    gemv_threshold(gemv_max)          # 0: tensor-core kernel for every M; 8: CUDA-core GEMV up to 8 tokens
+    # 0: tcgen05 kernel for every M; 8: CUDA-core GEMV up to 8 tokens; "mma": warp-MMA kernel wherever the tokens fit
+    if gemv_max == "mma":
+        gemv_threshold(0, 32)
+    else:
+        gemv_threshold(gemv_max)
     ws = torch.zeros(ops._lib.lib().el_decode_workspace_bytes(N), dtype=torch.uint8, device=DEV)
     Wd = _cuda(Wp)
     for _ in range(2):
@@ -391,14 +397,17 @@ def test_linear_decode_bit_exact(ops, gemv_threshold, M, K, N, gemv_max):
     ops.check_device_status(torch.device(DEV))
 
 
-@pytest.mark.parametrize("gemv_max", [0, 8])
+@pytest.mark.parametrize("gemv_max", [0, 8, "mma"])
 @pytest.mark.parametrize("M", [1, 3, 8])
 def test_linear_decode_counts_non_finite_tokens_as_zero(ops, gemv_threshold, M, gemv_max):
     """NaN and infinities in the tokens quantise to 0 and do not enter the absmax (NaN alone keeps the GEMV's fast
     path, an infinity sends it through the checked one)."""
     K, N = 1024, 328
     g = torch.Generator().manual_seed(90 + M)
-    gemv_threshold(gemv_max)
+    if gemv_max == "mma":
+        gemv_threshold(0, 32)
+    else:
+        gemv_threshold(gemv_max)
     Wp, _ = random_packed(N, K, seed=77)
     Wd = _cuda(Wp)
     for kind in ("nan", "inf", "both"):
@@ -416,7 +425,7 @@ def test_linear_decode_counts_non_finite_tokens_as_zero(ops, gemv_threshold, M, 
     ops.check_device_status(torch.device(DEV))
 
 
-@pytest.mark.parametrize("M", [1, 4])
+@pytest.mark.parametrize("M", [1, 4, 12])
 def test_linear_decode_chain_with_overlap_equals_plain_chain(ops, M):
     """Dependent-launch overlap: a chain of calls in which every call's tokens are the previous call's output (so a
     call that started too early would read stale tokens) gives bit-identical results with the overlap on, in plain
