@@ -28,6 +28,12 @@ template <> struct Io<float> {
     static __device__ __forceinline__ void unpack(const Raw& r, float v[8]) {
         v[0] = r.a.x; v[1] = r.a.y; v[2] = r.a.z; v[3] = r.a.w; v[4] = r.b.x; v[5] = r.b.y; v[6] = r.b.z; v[7] = r.b.w;
     }
+    static __device__ __forceinline__ Raw pack(const float v[8]) {
+        Raw r;
+        r.a = make_float4(v[0], v[1], v[2], v[3]);
+        r.b = make_float4(v[4], v[5], v[6], v[7]);
+        return r;
+    }
     static __device__ __forceinline__ float round(float v) { return v; }
     static __device__ __forceinline__ void load8(const float* p, float v[8]) {
         const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
@@ -49,6 +55,10 @@ template <> struct Io<__nv_bfloat16> {
             v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
         }
     }
+    // values that are already bfloat16-representable: packing is exact
+    static __device__ __forceinline__ Raw pack(const float v[8]) {
+        return Raw{make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]))};
+    }
     static __device__ __forceinline__ float round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
     static __device__ __forceinline__ void load8(const __nv_bfloat16* p, float v[8]) { unpack(load_raw(p), v); }
     static __device__ __forceinline__ void store8(__nv_bfloat16* p, const float v[8]) {
@@ -67,6 +77,9 @@ template <> struct Io<__half> {
             v[2 * i] = f.x;
             v[2 * i + 1] = f.y;
         }
+    }
+    static __device__ __forceinline__ Raw pack(const float v[8]) {
+        return Raw{make_uint4(pack_f16x2(v[0], v[1]), pack_f16x2(v[2], v[3]), pack_f16x2(v[4], v[5]), pack_f16x2(v[6], v[7]))};
     }
     static __device__ __forceinline__ float round(float v) { return __half2float(__float2half_rn(v)); }
     static __device__ __forceinline__ void load8(const __half* p, float v[8]) { unpack(load_raw(p), v); }
@@ -165,6 +178,7 @@ rmsnorm_quantize_rows_kernel(const T* __restrict__ x, long long ldx, const float
             Io<T>::unpack(cache[c], v);
             load8_w(weight + k, w);
             normed(v, w, y);
+            cache[c] = Io<T>::pack(y);          // from here on the cache holds the normalised row (exact: y is of type T)
 #pragma unroll
             for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(y[i]));
         }
@@ -199,10 +213,7 @@ rmsnorm_quantize_rows_kernel(const T* __restrict__ x, long long ldx, const float
     }
 
     // ---- quantise --------------------------------------------------------------------------------------------------------
-    auto quantise = [&](const float v[8], int k) {
-        float w[8], y[8];
-        load8_w(weight + k, w);
-        normed(v, w, y);
+    auto quantise_y = [&](const float y[8], int k) {
         int qi[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) qi[i] = q8_sat(__fmul_rn(row_finite ? y[i] : finite_or_nan(y[i]), s));
@@ -212,15 +223,17 @@ rmsnorm_quantize_rows_kernel(const T* __restrict__ x, long long ldx, const float
     for (int c = 0; c < ROW_CACHE; ++c) {
         const int k = (threadIdx.x + c * RN_THREADS) * 8;
         if (k < K) {
-            float v[8];
-            Io<T>::unpack(cache[c], v);
-            quantise(v, k);
+            float y[8];
+            Io<T>::unpack(cache[c], y);
+            quantise_y(y, k);
         }
     }
     for (int k = k_tail; k < K; k += RN_THREADS * 8) {
-        float v[8];
+        float v[8], w[8], y[8];
         Io<T>::load8(xr + k, v);
-        quantise(v, k);
+        load8_w(weight + k, w);
+        normed(v, w, y);
+        quantise_y(y, k);
     }
 }
 
@@ -276,14 +289,26 @@ rmsnorm_backward_kernel(const T* __restrict__ g, const T* __restrict__ x, const 
     }
 }
 
-// dweight[k] = float(sum over the CTAs' partial sums, in CTA order)
+// dweight[k] = float(sum of the CTAs' partial sums).  A CTA covers 32 columns (one per lane); its eight warps each add
+// every eighth partial in order, and warp 0 adds the eight results in order: a fixed order of additions for any grid.
 __global__ void __launch_bounds__(256)
 rmsnorm_dweight_kernel(const double* __restrict__ partial, int n_parts, float* __restrict__ dweight, int K) {
-    const int k = blockIdx.x * blockDim.x + threadIdx.x;
-    if (k >= K) return;
+    __shared__ double part[8][32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int k = blockIdx.x * 32 + lane;
     double s = 0.0;
-    for (int p = 0; p < n_parts; ++p) s += partial[(size_t)p * K + k];
-    dweight[k] = (float)s;
+    if (k < K) {
+#pragma unroll 4
+        for (int p = warp; p < n_parts; p += 8) s += partial[(size_t)p * K + k];
+    }
+    part[warp][lane] = s;
+    __syncthreads();
+    if (warp == 0 && k < K) {
+        double t = 0.0;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) t += part[w][lane];
+        dweight[k] = (float)t;
+    }
 }
 
 int backward_grid(int M, int K) {
@@ -348,7 +373,7 @@ static int launch_rmsnorm_backward_t(const T* g, const T* x, const float* weight
     rmsnorm_backward_kernel<T><<<grid, RN_THREADS, smem, st>>>(g, x, weight, rstd, dx, partial, M, K);
     int rc = check_launch();
     if (rc != EL_OK) return rc;
-    rmsnorm_dweight_kernel<<<(K + 255) / 256, 256, 0, st>>>(partial, grid, dweight, K);
+    rmsnorm_dweight_kernel<<<(K + 31) / 32, 256, 0, st>>>(partial, grid, dweight, K);
     return check_launch();
 }
 
