@@ -538,9 +538,10 @@ def run_decode(args):
         # overlap: the GEMV issued as a programmatic dependent launch (weights constant, as at inference), so that a
         # call's weight loads start under the tail of the previous call
         # columns: tokens, limit of the CUDA-core GEMV, limit of the warp-MMA kernel (tcgen05 stream-K above it), overlap
-        for M, gemv_max, mma_max, overlap in ((1, 4, 32, False), (1, 4, 32, True), (4, 4, 32, False), (4, 4, 32, True),
-                                              (8, 8, 32, True), (8, 4, 32, False), (8, 4, 32, True), (8, 0, 0, False),
-                                              (16, 4, 32, True), (32, 4, 32, True), (32, 4, 0, False), (64, 4, 32, False)):
+        for M, gemv_max, mma_max, overlap in ((1, 1, 32, False), (1, 1, 32, True), (1, 0, 32, True), (2, 2, 32, True),
+                                              (2, 1, 32, True), (4, 4, 32, True), (4, 1, 32, False), (4, 1, 32, True),
+                                              (8, 8, 32, True), (8, 1, 32, False), (8, 1, 32, True), (8, 0, 0, False),
+                                              (16, 1, 32, True), (32, 1, 32, True), (32, 1, 0, False), (64, 1, 32, False)):
             pkg._lib.lib().el_set_decode_gemv_max_tokens(gemv_max)
             pkg._lib.lib().el_set_decode_mma_max_tokens(mma_max)
             ops.set_decode_overlap(overlap)
@@ -571,7 +572,7 @@ def run_decode(args):
                           "algorithmic_bytes": nbytes})
         ops.check_device_status(dev)
         del Ws
-    pkg._lib.lib().el_set_decode_gemv_max_tokens(4)
+    pkg._lib.lib().el_set_decode_gemv_max_tokens(2)
     pkg._lib.lib().el_set_decode_mma_max_tokens(32)
     ops.set_decode_overlap(False)
     head = next(c for c in cases if c["M"] == 1 and c["K"] == 4096 and c["overlap"])

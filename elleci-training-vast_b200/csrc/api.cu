@@ -88,7 +88,7 @@ static int device_info(int* sms, int* major) {
 int device_sm_count(int* out) { return device_info(out, nullptr); }
 
 // Token count up to which the decode call uses the CUDA-core GEMV (el_set_decode_gemv_max_tokens).
-static int g_gemv_max_tokens = 4;
+static int g_gemv_max_tokens = 2;
 int decode_gemv_max_tokens() { return g_gemv_max_tokens; }
 static int g_mma_max_tokens = 32;
 int decode_mma_max_tokens() { return g_mma_max_tokens; }

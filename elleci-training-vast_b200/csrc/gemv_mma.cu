@@ -1,4 +1,4 @@
-// Decode GEMV for 5..32 tokens, one launch: Y[m,n] = (sum_k Q(x)[m,k]*Wq[n,k]) * (absmax[m]/127) * gamma.
+// Decode GEMV for a few to 32 tokens, one launch: Y[m,n] = (sum_k Q(x)[m,k]*Wq[n,k]) * (absmax[m]/127) * gamma.
 //
 // The call is bound by streaming W_packed once and by the 2-bit -> int8 expansion of the weights; the products themselves
 // are few.  With more than a handful of tokens the dp4a of the CUDA-core GEMV (one per token and 4 weights) outgrow the
@@ -107,12 +107,22 @@ gemv_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ Wp, EpiPara
         lo = (k_ok && n0 < N) ? __ldg(reinterpret_cast<const uint4*>(Wp + (size_t)n0 * pK + (k0 >> 2))) : zeros;
         hi = (k_ok && n0 + 8 < N) ? __ldg(reinterpret_cast<const uint4*>(Wp + (size_t)(n0 + 8) * pK + (k0 >> 2))) : zeros;
     };
-    int g_next = blockIdx.x, kb_next = warp;
-    // a warp whose first block index lies beyond the reduction has no work in any row group
-    const bool has_work = warp < kblocks;
-    uint4 nlo = zeros, nhi = zeros;
+    // A warp's work items in order: row groups outermost, its blocks warp, warp + 16, ... inside.  The fragments of the
+    // next DEPTH items are always in flight (a warp has only a handful of items, each worth a fraction of a memory latency
+    // of work), the first ones from before the token quantisation.
+    const bool has_work = warp < kblocks;          // a warp whose first block lies beyond the reduction never has work
+    const int nk = has_work ? (kblocks - warp + GM_WARPS - 1) / GM_WARPS : 1;      // blocks per row group for this warp
+    constexpr int DEPTH = 2;
+    uint4 qlo[DEPTH], qhi[DEPTH];
+    int fetch_g = blockIdx.x, fetch_j = 0;         // next item to request
+    auto fetch = [&](uint4& lo, uint4& hi) {
+        if (has_work && fetch_g < row_groups) load_frag(fetch_g, warp + fetch_j * GM_WARPS, lo, hi);
+        else { lo = zeros; hi = zeros; }
+        if (++fetch_j == nk) { fetch_j = 0; fetch_g += gridDim.x; }
+    };
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    if (has_work && g_next < row_groups) load_frag(g_next, kb_next, nlo, nhi);
+#pragma unroll
+    for (int i = 0; i < DEPTH; ++i) fetch(qlo[i], qhi[i]);
     // everything below reads the tokens or writes the output: wait for the work queued before this launch
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
@@ -172,11 +182,10 @@ gemv_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ Wp, EpiPara
         for (int t = 0; t < NT; ++t) d[t][0] = d[t][1] = d[t][2] = d[t][3] = 0;
         if (has_work) {
             for (int kb = warp; kb < kblocks; kb += GM_WARPS) {
-                const uint4 lo = nlo, hi = nhi;
-                // request the next fragment (next block of this row group, or the first block of the next row group)
-                int kb2 = kb + GM_WARPS, g2 = g;
-                if (kb2 >= kblocks) { kb2 = warp; g2 = g + gridDim.x; }
-                if (g2 < row_groups) load_frag(g2, kb2, nlo, nhi);
+                const uint4 lo = qlo[0], hi = qhi[0];
+#pragma unroll
+                for (int i = 0; i + 1 < DEPTH; ++i) { qlo[i] = qlo[i + 1]; qhi[i] = qhi[i + 1]; }
+                fetch(qlo[DEPTH - 1], qhi[DEPTH - 1]);
                 const uint32_t wl[4] = {lo.x, lo.y, lo.z, lo.w}, wh[4] = {hi.x, hi.y, hi.z, hi.w};
 #pragma unroll
                 for (int w = 0; w < 4; ++w) {

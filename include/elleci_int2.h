@@ -228,7 +228,7 @@ EL_API int el_dw_hysteresis(const int8_t* Gq, const int8_t* Xq, const float* g_a
  * (int2_matmul_int8_tc_v2_simple_kernel, kernels/int2/int2_matmul_int8_tc_v2.cu:452-473, dispatch :511-536), the
  * path of Elleci.generate (model/model.py:505-623). */
 EL_API size_t el_decode_workspace_bytes(int N);
-/* Tuning: calls with at most `max_tokens` tokens (0..8, default 4) take a single-launch CUDA-core GEMV that
+/* Tuning: calls with at most `max_tokens` tokens (0..8, default 2) take a single-launch CUDA-core GEMV that
  * quantises the tokens itself and touches no scratch; larger ones take the tensor-core kernel.  Process-wide. */
 EL_API int el_set_decode_gemv_max_tokens(int max_tokens);
 /* Tuning: calls with more tokens than the limit above and at most `max_tokens` (0..32, default 32) whose int8 tokens

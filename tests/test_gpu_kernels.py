@@ -368,7 +368,7 @@ def gemv_threshold(ops):
         assert ops._lib.lib().el_set_decode_gemv_max_tokens(v) == 0
         assert ops._lib.lib().el_set_decode_mma_max_tokens(mma) == 0
     yield set_
-    set_(4, 32)
+    set_(2, 32)
 
 
 @pytest.mark.parametrize("gemv_max", [0, 8, "mma"])
