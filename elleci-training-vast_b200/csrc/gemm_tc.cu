@@ -9,7 +9,8 @@
 //   warp 1      allocates tensor memory; one lane issues the MMAs and commits them to the ring's barriers
 //   warps 2-5   epilogue: tcgen05.ld of one of two accumulators while the MMAs fill the other
 //   warps 6-13  FWD / DX: expand the packed weight tile into the 128-byte-swizzled int8 operand tile;
-//               DW: no tile to expand, so they join the epilogue (twelve epilogue warps, three per lane quarter)
+//               DW: no tile to expand, so they join the epilogue (twelve epilogue warps, three per lane quarter;
+//               sixteen, four per quarter, in the fused dW + hysteresis kernel)
 //
 // The three GEMMs differ only in where the reduction index lies in memory:
 //   FWD  Y [M,N] = Xq [M,K] . Wq[N,K]^T   A K-major (TMA),  B K-major  (expanded from W_packed rows)
@@ -182,11 +183,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
     } else if (warp < WARP_XF0 || !XFORM) {
         // ================= epilogue =================
-        // Without a weight tile to expand (DW) the eight transform warps join in: three warps share each
-        // quarter of the tensor-memory lanes and take the 32-column chunks round-robin.
+        // Without a weight tile to expand (DW) the transform warps join in: three warps (four in the fused kernel)
+        // share each quarter of the tensor-memory lanes and take the 32-column chunks round-robin.
         constexpr int EPI_SPLIT = XFORM ? 1 : (num_threads(MODE, EPI) / 32 - 2) / 4;      // 3, or 4 in the fused kernel
         const int quarter = warp & 3;                 // the tensor-memory lanes this warp may read
-        const int sub = (warp - 2) >> 2;              // 0 for warps 2-5, 1 for 6-9, 2 for 10-13
+        const int sub = (warp - 2) >> 2;              // 0 for warps 2-5, 1 for 6-9, 2 for 10-13, 3 for 14-17
         const int row_in_tile = quarter * 32 + lane;
         int it = 0;
         for (int t = blockIdx.x; t < num_tiles && !failed; t += gridDim.x, ++it) {
