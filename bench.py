@@ -416,7 +416,7 @@ def run_ours(args, wl):
     int8_peak = 2.0 * peaks["bf16_tflops_sustained"]
     # DRAM bytes per GEMM launch from the ncu capture summarised in profiles/gemm_tc2_fwd_dx_config2_ncu_full.md
     # (mean of the forward, dX and dW+hysteresis launches of the 4096->11008 layer at M=4096)
-    traffic = 93.0e6 if args.workload == "config2" and world == 1 else None
+    traffic = 91.3e6 if args.workload == "config2" and world == 1 else None
     roofline = {
         "bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TFLOP/s", "frac": achieved / int8_peak,
         "traffic": traffic, "kernel": "gemm_tc_kernel (tcgen05 kind::i8; forward, dX and dW+hysteresis launches)",

@@ -92,7 +92,6 @@ template <> struct Io<__half> {
 __device__ __forceinline__ void load8_w(const float* p, float v[8]) { Io<float>::load8(p, v); }
 
 constexpr int RN_THREADS = 256;
-constexpr int ROW_CACHE = 6;        // vectors of 8 elements a thread keeps in registers between passes
 
 // Sum over the CTA; every thread gets the result.  `red` holds one double per warp.
 __device__ __forceinline__ double block_sum(double v, double* red) {
@@ -121,9 +120,11 @@ __device__ __forceinline__ float block_max_f(float v, float* red) {
     return t;
 }
 
-// One CTA per token.  K % 8 == 0; x rows, weight and q rows 16-byte (q: 8-byte) aligned.
-template <typename T>
-__global__ void __launch_bounds__(RN_THREADS)
+// One CTA per token.  K % 8 == 0; x rows, weight and q rows 16-byte (q: 8-byte) aligned.  ROW_CACHE: vectors of 8
+// elements a thread keeps in registers between the passes (2 for rows up to 4096 elements: fewer registers, more CTAs
+// per SM, more bytes in flight; 6 for rows up to 12288).
+template <typename T, int ROW_CACHE>
+__global__ void __launch_bounds__(RN_THREADS, ROW_CACHE == 2 ? 6 : 3)
 rmsnorm_quantize_rows_kernel(const T* __restrict__ x, long long ldx, const float* __restrict__ weight, int8_t* __restrict__ q,
                              float* __restrict__ row_absmax, float* __restrict__ rstd_out, int K, float norm_eps,
                              float quant_eps) {
@@ -134,7 +135,7 @@ rmsnorm_quantize_rows_kernel(const T* __restrict__ x, long long ldx, const float
     int8_t* qr = q + (size_t)m * K;
 
     // The row is read from memory once: up to ROW_CACHE vectors of 8 elements per thread stay in registers for the two
-    // later passes (rows of up to 12288 elements); longer rows re-read their tail.
+    // later passes; longer rows re-read their tail.
     typename Io<T>::Raw cache[ROW_CACHE];
     const int k_tail = (threadIdx.x + ROW_CACHE * RN_THREADS) * 8;
 
@@ -340,21 +341,14 @@ int launch_rmsnorm_quantize_rows(const void* x, int dt, long long ldx, const flo
     if ((reinterpret_cast<uintptr_t>(x) & 15) || ((size_t)ldx * esz) % 16 != 0 || (reinterpret_cast<uintptr_t>(weight) & 15) ||
         (reinterpret_cast<uintptr_t>(q) & 7))
         return EL_ERR_ALIGNMENT;
+#define EL_RNQ(T, NC) rmsnorm_quantize_rows_kernel<T, NC><<<M, RN_THREADS, 0, st>>>((const T*)x, ldx, weight, q, row_absmax, rstd, K, norm_eps, quant_eps)
     switch (dt) {
-        case EL_BF16:
-            rmsnorm_quantize_rows_kernel<__nv_bfloat16><<<M, RN_THREADS, 0, st>>>((const __nv_bfloat16*)x, ldx, weight, q, row_absmax,
-                                                                                   rstd, K, norm_eps, quant_eps);
-            break;
-        case EL_F16:
-            rmsnorm_quantize_rows_kernel<__half><<<M, RN_THREADS, 0, st>>>((const __half*)x, ldx, weight, q, row_absmax, rstd, K,
-                                                                            norm_eps, quant_eps);
-            break;
-        case EL_F32:
-            rmsnorm_quantize_rows_kernel<float><<<M, RN_THREADS, 0, st>>>((const float*)x, ldx, weight, q, row_absmax, rstd, K,
-                                                                           norm_eps, quant_eps);
-            break;
+        case EL_BF16: if (K <= 4096) EL_RNQ(__nv_bfloat16, 2); else EL_RNQ(__nv_bfloat16, 6); break;
+        case EL_F16: if (K <= 4096) EL_RNQ(__half, 2); else EL_RNQ(__half, 6); break;
+        case EL_F32: if (K <= 4096) EL_RNQ(float, 2); else EL_RNQ(float, 6); break;
         default: return EL_ERR_INVALID_ARG;
     }
+#undef EL_RNQ
     return check_launch();
 }
 
