@@ -43,6 +43,14 @@ def test_status_strings_and_host_side_argument_checks():
     assert handle.el_hysteresis_from_dw(None, None, None, 1e-3, 5.0, 2, 0.0, 1, 70000, 70000, 0, 1, None) == lib.EL_ERR_UNSUPPORTED_SHAPE
     assert handle.el_linear_decode_static(None, lib.EL_BF16, None, None, lib.EL_BF16, 1.0, 65, 8, 64, None, None) == lib.EL_ERR_TOO_LARGE
     assert handle.el_decode_workspace_bytes(11008) == (64 * 11008 + 4 * 86) * 4
+    assert handle.el_rmsnorm_quantize_rows(None, 9, 8, None, 1e-6, None, None, None, 1, 8, 1e-5, None) == lib.EL_ERR_INVALID_ARG
+    assert handle.el_rmsnorm_quantize_rows(None, lib.EL_BF16, 4, None, 1e-6, None, None, None, 1, 8, 1e-5, None) == lib.EL_ERR_INVALID_ARG
+    assert handle.el_rmsnorm_backward(None, None, 9, None, None, None, None, None, 0, 1, 8, None) == lib.EL_ERR_INVALID_ARG
+    # tuning knobs: range-checked, process-wide
+    assert handle.el_set_decode_gemv_max_tokens(9) == lib.EL_ERR_INVALID_ARG
+    assert handle.el_set_decode_mma_max_tokens(33) == lib.EL_ERR_INVALID_ARG
+    assert handle.el_set_decode_gemv_max_tokens(2) == lib.EL_OK and handle.el_set_decode_mma_max_tokens(32) == lib.EL_OK
+    assert handle.el_set_decode_overlap(0) == lib.EL_OK
     try:
         lib.check("el_gemm_fwd", lib.EL_ERR_ALIGNMENT)
     except pkg.ElleciError as e:

@@ -186,3 +186,31 @@ def test_rmsnorm_restatement_matches_reference_module(i):
     assert np.allclose(a, g[f"absmax{i}"], rtol=unit * 1.01, atol=0)
     dq = np.abs(q.astype(np.int32) - g[f"q{i}"].astype(np.int32))
     assert dq.max() <= 1 and (dq != 0).mean() <= 5e-3
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f32"])
+def test_package_unfused_rmsnorm_module_agrees_with_restatement(dtype):
+    """The package's own `_ExtraRMSNorm` (the tensor-operation form that `fuse_rmsnorm=False` runs, and the fallback
+    for shapes the fused kernel does not take) against the oracle on the CPU: outputs and input gradients equal up to
+    the rare one-unit difference torch's float32 summation order causes, weight gradient to its summation precision."""
+    import torch
+    from conftest import load_package
+    pkg = load_package()
+    dt = {"bf16": torch.bfloat16, "f32": torch.float32}[dtype]
+    g = torch.Generator().manual_seed(5)
+    M, K = 48, 768
+    x = (torch.randn(M, K, generator=g) * 1.7).to(dt).requires_grad_(True)
+    norm = pkg.bitnet_int2_optimized._ExtraRMSNorm(K, eps=1e-6)
+    with torch.no_grad():
+        norm.weight.copy_(1.0 + 0.25 * torch.randn(K, generator=g))
+    gy = (torch.randn(M, K, generator=g) * 1e-2).to(dt)
+    y = norm(x)
+    y.backward(gy)
+    xn = x.detach().float().numpy()
+    yo, rstd = O.rmsnorm_forward(xn, norm.weight.detach().numpy(), 1e-6, dtype)
+    dxo, dwo = O.rmsnorm_backward(gy.float().numpy(), xn, norm.weight.detach().numpy(), rstd, dtype)
+    unit = {"bf16": 2.0 ** -8, "f32": 1e-5}[dtype]
+    for a, b in ((yo, y.detach().float().numpy()), (dxo, x.grad.float().numpy())):
+        assert np.all(np.abs(a - b) <= unit * np.maximum(np.abs(b), np.abs(b).max() * 1e-3) * 1.01)
+    ref_dw = norm.weight.grad.numpy()
+    assert np.abs(dwo - ref_dw).max() <= (1e-2 if dtype == "bf16" else 1e-5) * np.abs(ref_dw).max()
