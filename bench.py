@@ -531,10 +531,33 @@ def run_decode(args):
     torch.cuda.set_device(dev)
     peaks, peak_kind = measured_peaks()
     cases = []
+    stream_us = {}
     nbuf = 16
     for (K, N) in [(4096, 11008), (11008, 4096)]:
         gen = torch.Generator().manual_seed(K)
         Ws = [torch.randint(0, 256, (N, K // 4), generator=gen, dtype=torch.uint8).to(dev) for _ in range(nbuf)]
+        # yardstick of the harness itself: a device-to-device copy of the same 16 weight buffers (one copy each, 11 MB
+        # read and 11 MB written) in the same kind of graph - what moving one weight matrix per launch costs here
+        # before any decode work
+        dst = torch.empty_like(Ws[0])
+        for W in Ws[:3]:
+            dst.copy_(W)
+        torch.cuda.synchronize()
+        sgraph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(sgraph):
+            for W in Ws:
+                dst.copy_(W)
+        for _ in range(3):
+            sgraph.replay()
+        torch.cuda.synchronize()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for _ in range(max(args.steps, 10)):
+            sgraph.replay()
+        s1.record()
+        torch.cuda.synchronize()
+        stream_us[f"{K}x{N}"] = s0.elapsed_time(s1) * 1e3 / (max(args.steps, 10) * nbuf)
+        del sgraph, dst
         # overlap: the GEMV issued as a programmatic dependent launch (weights constant, as at inference), so that a
         # call's weight loads start under the tail of the previous call
         # columns: tokens, limit of the CUDA-core GEMV, limit of the warp-MMA kernel (tcgen05 stream-K above it), overlap
@@ -585,7 +608,7 @@ def run_decode(args):
                                "buffers (> L2) in one CUDA graph; value = M=1, 4096->11008, dependent-launch overlap on"},
         "roofline": {"bound": "hbm", "achieved": head["GBps"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": head["GBps"] / peaks["hbm_gbs"], "traffic": None, "peak_source": f"hbm_gbs ({peak_kind})"},
-        "cases": cases, "gpu_launches": 2 * nbuf * max(args.steps, 10),
+        "cases": cases, "copy_us_per_call": stream_us, "gpu_launches": 2 * nbuf * max(args.steps, 10),
     }
     print(json.dumps(line))
 

@@ -26,7 +26,12 @@ def _make_layer(pkg, d, K, N, thr=2, order="reference", mode="per_token", hook=T
 
 @pytest.mark.parametrize("order", ["reference", "after_dx"])
 @pytest.mark.parametrize("M,K,N,dtype", [(1024, 1536, 1536, torch.bfloat16), (96, 128, 80, torch.float32),
-                                         (64, 100, 36, torch.bfloat16)])
+                                         (64, 100, 36, torch.bfloat16),
+                                         # the awkward projections of the reference model: K=16 (dt_proj), N=48 (x_proj),
+                                         # N=16 (diff_gate), K=256 (w_kv_up), and the 4096->512 MLA latent projection
+                                         (64, 16, 64, torch.bfloat16), (64, 128, 48, torch.bfloat16),
+                                         (64, 64, 16, torch.bfloat16), (128, 256, 1024, torch.bfloat16),
+                                         (256, 4096, 512, torch.bfloat16)])
 def test_layer_step_matches_oracle(pkg, order, M, K, N, dtype):
     """Forward, dX and the weight update of one layer step (benchmark configuration 0 is the first case)."""
     d = make_layer_inputs(M, K, N, seed=0, dtype=dtype, dy_std=1e-2)
@@ -47,7 +52,8 @@ def test_layer_step_matches_oracle(pkg, order, M, K, N, dtype):
     Wn, Hn = native.c_hysteresis_step(dWo, d["Wp"], d["Hp"], lr, 5.0, 2, 0.001, 1, K)
     assert np.array_equal(layer.W_packed.cpu().numpy(), Wn)
     assert np.array_equal(layer.H_packed.cpu().numpy(), Hn)
-    assert (O.unpack_ternary(Wn, K) != O.unpack_ternary(d["Wp"], K)).any()
+    # the case does move the state (the tiniest shapes may only move counters)
+    assert (O.unpack_ternary(Wn, K) != O.unpack_ternary(d["Wp"], K)).any() or not np.array_equal(Hn, d["Hp"])
     w_for_dx = Wn if order == "reference" else d["Wp"]      # the reference's hook updates the weights before dX
     dxo = O.bitlinear_backward_dx(t2n(d["dY"]), w_for_dx, d["gamma"], K, out=out)
     assert np.array_equal(t2n(x.grad), dxo)
