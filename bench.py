@@ -227,6 +227,11 @@ def run_ours(args, wl):
         if world > 1 and not args.no_fused_gather:
             import torch.distributed._symmetric_memory as symm_mem
             # two sets of buffers alternate between steps, which removes the barriers that would otherwise guard reuse
+            lay.flags = symm_mem.empty((8,), dtype=torch.int32, device=dev)
+            lay.flags.zero_()
+            lay.flags_hdl = symm_mem.rendezvous(lay.flags, dist.group.WORLD)
+            lay.flags_hdl.barrier(channel=0)
+            lay.epoch = 0
             lay.symm, lay.symm_dx = [], []
             for _ in range(2):
                 ybuf = symm_mem.empty((M, N), dtype=torch.bfloat16, device=dev)
@@ -239,6 +244,13 @@ def run_ours(args, wl):
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)      # larger than the 126 MB L2
     timer = Timer(torch)
 
+    def peer_barrier(lay, hdl, channel):
+        if not args.own_barrier:
+            hdl.barrier(channel=channel)
+        else:
+            lay.epoch += 1
+            ops.peer_barrier(lay.flags_hdl.buffer_ptrs, rank, lay.epoch, dev)
+
     def layer_step(lay):
         """One layer: forward, then (reference order) the weight update, then dX."""
         K, Nl = lay.K, lay.Nl
@@ -247,7 +259,7 @@ def run_ours(args, wl):
             # forward GEMM fused with the all-gather: the epilogue stores into every rank's Y over NVLink
             ybuf, hdl = lay.symm[lay.step & 1]
             timer.run("gemm_fwd", ops.matmul_rows_gather, Xq, lay.Wp, ax, lay.gamma, hdl.buffer_ptrs, lay.N, lay.n0, torch.bfloat16)
-            timer.run("barrier_post", hdl.barrier, channel=1)
+            timer.run("barrier_post", peer_barrier, lay, hdl, 1)
             y = ybuf
         else:
             y = timer.run("gemm_fwd", ops.matmul_rows, Xq, lay.Wp, ax, lay.gamma, torch.bfloat16)
@@ -274,9 +286,9 @@ def run_ours(args, wl):
             # staging buffers), then each rank sums + scales its rows and writes them into every rank's dX
             parts, hp, dxbuf, hd = lay.symm_dx[lay.step & 1]
             timer.run("gemm_dx", ops.backward_input_scatter, dYq, lay.Wp, K, hp.buffer_ptrs, rank)
-            timer.run("barrier_dx1", hp.barrier, channel=3)
+            timer.run("barrier_dx1", peer_barrier, lay, hp, 3)
             timer.run("reduce_scale_gather", ops.reduce_scale_gather, parts, hd.buffer_ptrs, rank, ady, lay.gamma, M, K, torch.bfloat16)
-            timer.run("barrier_dx2", hd.barrier, channel=4)
+            timer.run("barrier_dx2", peer_barrier, lay, hd, 4)
             dX = dxbuf
         elif world > 1:
             acc = timer.run("gemm_dx", ops.backward_input_rows, dYq, lay.Wp, ady, lay.gamma, K, torch.int32)
@@ -624,6 +636,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
     ap.add_argument("--inline-kernel-events", action="store_true",
                     help="record the per-kernel event pairs inside the headline region instead of in a second pass")
+    ap.add_argument("--own-barrier", action="store_true",
+                    help="N > 1: use el_peer_barrier instead of the symmetric-memory handle's barrier (same speed)")
     ap.add_argument("--no-fused-gather", action="store_true",
                     help="N > 1: all-gather the output with NCCL instead of TMA stores from the GEMM epilogue")
     args = ap.parse_args()

@@ -46,6 +46,7 @@ SIGNATURES = {
     "el_rmsnorm_backward": [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, C.c_size_t, _i, _i, _vp],
     "el_set_decode_gemv_max_tokens": [_i],
     "el_set_decode_overlap": [_i],
+    "el_peer_barrier": [_vp, _i, _i, _u32, _vp, _vp],
     "el_set_decode_mma_max_tokens": [_i],
     "el_linear_decode": [_vp, _i, _vp, _vp, _i, _f, _vp, _vp, _vp, C.c_size_t, _i, _i, _i, _vp, _vp],
     "el_linear_decode_static": [_vp, _i, _vp, _vp, _i, _f, _i, _i, _i, _vp, _vp],

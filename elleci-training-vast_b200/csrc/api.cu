@@ -41,6 +41,8 @@ int launch_rmsnorm_quantize_rows(const void* x, int dt, long long ldx, const flo
 size_t rmsnorm_backward_workspace_bytes(int K);
 int launch_rmsnorm_backward(const void* g, const void* x, int dt, const float* weight, const float* rstd, void* dx,
                             float* dweight, void* workspace, size_t workspace_bytes, int M, int K, cudaStream_t st);
+int launch_peer_barrier(unsigned int* const* flags_all, int n_ranks, int rank, unsigned int epoch, int32_t* status,
+                        cudaStream_t st);
 int launch_gemv_mma(const void* x, int x_dtype, const uint8_t* Wp, const EpiParams& epi, int M, int N, int K, cudaStream_t st,
                     bool overlap);
 bool gemv_mma_fits(int M, int K);
@@ -291,6 +293,14 @@ int el_gemm_dx(const int8_t* dYq, const uint8_t* W_packed, void* dX, int out_dty
     if (!dX || !absmax || (N > 0 && (!dYq || !W_packed))) return EL_ERR_NULL_PTR;
     const EpiParams epi{dX, (long long)K, out_dtype, absmax, absmax_stride, gamma};
     return gemm_dispatch(MODE_DX, dYq, W_packed, M, K, N, epi, flags, dev_status, (cudaStream_t)stream);
+}
+
+int el_peer_barrier(uint32_t* const* flags_all, int n_ranks, int rank, uint32_t epoch, int32_t* dev_status, el_stream_t stream) {
+    if (!flags_all) return EL_ERR_NULL_PTR;
+    const int rc = require_sm100();
+    if (rc != EL_OK) return rc;
+    return launch_peer_barrier(reinterpret_cast<unsigned int* const*>(flags_all), n_ranks, rank, epoch, dev_status,
+                               (cudaStream_t)stream);
 }
 
 int el_gemm_dw(const int8_t* Gq, const int8_t* Xq, void* dW, int out_dtype, const float* g_absmax, int M, int N, int K,

@@ -1,0 +1,57 @@
+// Barrier between the ranks of an N-sharded layer (one process and one GPU per rank), as one tiny launch per rank.
+//
+// Every rank owns an array of n_ranks 32-bit flags in peer-mapped memory.  In barrier number `epoch` (1, 2, ... in the
+// same order on every rank) rank r stores `epoch` into slot r of every rank's array (st.release.sys: its earlier work on
+// the stream, including stores into peer memory, is visible before the flag) and then waits until all slots of its OWN
+// array have reached `epoch`.  The wait only reads this GPU's memory, is bounded (about four seconds of cycles) and
+// reports a rank that never arrives through the caller's status word instead of hanging.
+// The epilogue-store collectives of the sharded layer (el_gemm_fwd_gather, el_gemm_dx_scatter,
+// el_reduce_scale_gather) need exactly this: "all stores into my buffers have landed".  No counterpart in the reference.
+#include "common.cuh"
+
+namespace el {
+
+namespace {
+
+constexpr int PEER_MAX = 8;
+constexpr long long PEER_WAIT_CYCLES = 1LL << 33;
+
+struct PeerFlags {
+    unsigned int* p[PEER_MAX];
+};
+
+__global__ void __launch_bounds__(32)
+peer_barrier_kernel(PeerFlags flags, int n_ranks, int rank, unsigned int epoch, int32_t* status) {
+    const int i = threadIdx.x;
+    if (i >= n_ranks) return;
+    __threadfence_system();
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags.p[i] + rank), "r"(epoch) : "memory");
+    const unsigned int* mine = flags.p[rank] + i;
+    const long long t0 = clock64();
+    for (;;) {
+        unsigned int v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+        if ((int)(v - epoch) >= 0) break;            // wrap-safe "v >= epoch"
+        if (clock64() - t0 > PEER_WAIT_CYCLES) {
+            if (status != nullptr) atomicCAS(status, 0, 40 + i);      // rank i did not arrive
+            break;
+        }
+    }
+}
+
+}  // namespace
+
+int launch_peer_barrier(unsigned int* const* flags_all, int n_ranks, int rank, unsigned int epoch, int32_t* status,
+                        cudaStream_t st) {
+    if (n_ranks < 1 || n_ranks > PEER_MAX || rank < 0 || rank >= n_ranks) return EL_ERR_INVALID_ARG;
+    PeerFlags f{};
+    for (int i = 0; i < n_ranks; ++i) {
+        if (flags_all[i] == nullptr) return EL_ERR_NULL_PTR;
+        if (reinterpret_cast<uintptr_t>(flags_all[i]) & 3) return EL_ERR_ALIGNMENT;
+        f.p[i] = flags_all[i];
+    }
+    peer_barrier_kernel<<<1, 32, 0, st>>>(f, n_ranks, rank, epoch, status);
+    return check_launch();
+}
+
+}  // namespace el

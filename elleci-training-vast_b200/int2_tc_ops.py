@@ -394,6 +394,15 @@ def reduce_scale_gather(parts: torch.Tensor, out_ptrs, rank: int, row_absmax: to
          float(gamma), int(M), int(K), _stream())
 
 
+def peer_barrier(flag_ptrs, rank: int, epoch: int, device: torch.device) -> None:
+    """Barrier number `epoch` (1, 2, ... in the same order on every rank) between the ranks whose flag arrays
+    (uint32 [n_ranks] each, peer-mapped, zeroed before the first barrier) are `flag_ptrs`: one small kernel on the
+    current stream; a rank that does not arrive within seconds shows up in check_device_status."""
+    keep, arr = _ptr_array(flag_ptrs)
+    st = device_status(device)
+    call("el_peer_barrier", arr, len(flag_ptrs), int(rank), int(epoch) & 0xFFFFFFFF, st.data_ptr(), _stream())
+
+
 def backward_input_rows(dYq: torch.Tensor, W_packed: torch.Tensor, row_absmax: torch.Tensor, gamma: float, K: int,
                         out_dtype: torch.dtype = torch.bfloat16, path: int = EL_PATH_AUTO) -> torch.Tensor:
     """dX[m,:] = (dYq[m,:] @ W) * (row_absmax[m]/127) * gamma: the dX GEMM with per-token scales."""

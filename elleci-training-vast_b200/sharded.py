@@ -57,7 +57,7 @@ class _ShardedLinearFn(Function):
             # needed before overwriting that buffer.
             buf, hdl = layer._symmetric_output(M, io)
             ops.matmul_rows_gather(Xq, layer.W_packed, ax, layer.gamma_value(), hdl.buffer_ptrs, g * Nl, r_ * Nl, io)
-            hdl.barrier(channel=1)          # every rank's stores into this rank's buffer have landed
+            layer._barrier(hdl, 1)          # every rank's stores into this rank's buffer have landed
             y = buf.clone() if layer.copy_output else buf
             ctx.layer, ctx.io, ctx.x_shape = layer, io, x.shape
             ctx.saved = (Xq, ax) if layer.training else None
@@ -118,9 +118,9 @@ class _ShardedLinearFn(Function):
                 # and scales the rows it owns and writes them into every rank's dX: no collective kernel
                 parts, hp, dxbuf, hd = layer._symmetric_dx(M_tok, ctx.io)     # alternating buffers, as in the forward
                 ops.backward_input_scatter(dYq, layer.W_packed, K, hp.buffer_ptrs, r)
-                hp.barrier(channel=3)       # all partial sums of my rows have landed
+                layer._barrier(hp, 3)       # all partial sums of my rows have landed
                 ops.reduce_scale_gather(parts, hd.buffer_ptrs, r, ady, gam, M_tok, K, ctx.io)
-                hd.barrier(channel=4)       # all rows of my dX have landed
+                layer._barrier(hd, 4)       # all rows of my dX have landed
                 dX = dxbuf.clone() if layer.copy_output else dxbuf
             elif g > 1:
                 acc = ops.backward_input_rows(dYq, layer.W_packed, ady, gam, K, torch.int32)
@@ -140,7 +140,7 @@ class ShardedInt2Linear(nn.Module):
 
     def __init__(self, in_features: int, out_features: int, group: Optional[dist.ProcessGroup] = None, threshold: int = 7,
                  lr_scale: float = 5.0, decay_rate: float = 0.001, hysteresis_order: str = "reference", ops=None,
-                 fused_gather: bool = False, copy_output: bool = True):
+                 fused_gather: bool = False, copy_output: bool = True, own_barrier: bool = False):
         super().__init__()
         if ops is None:
             from . import int2_tc_ops as ops_mod
@@ -160,6 +160,13 @@ class ShardedInt2Linear(nn.Module):
         # copy_output=False hands out the symmetric buffer itself: valid until this layer's forward (backward) after next.
         self.fused_gather = fused_gather
         self.copy_output = copy_output
+        # own_barrier: the barriers of the fused path are el_peer_barrier (one small kernel over peer-mapped flags, bounded
+        # wait of a few seconds reported through the device status word) instead of the symmetric-memory handle's own
+        # barrier.  Measured equal in time (a barrier's time is the wait for the slowest rank); off by default because its
+        # bound would turn a rank that is merely seconds late into an error.
+        self.own_barrier = own_barrier
+        self._flags = None
+        self._epoch = 0
         self._symm = {}
         self.local_absmax_bytes = 256 << 20     # below this size every rank scans the whole replicated dY itself
         self._lr = 0.001
@@ -172,6 +179,21 @@ class ShardedInt2Linear(nn.Module):
 
     def set_lr(self, lr: float):
         self._lr = lr
+
+    def _barrier(self, hdl, channel: int):
+        """All ranks have finished the work queued so far (their stores into this rank's buffers have landed)."""
+        if not self.own_barrier:
+            hdl.barrier(channel=channel)
+            return
+        if self._flags is None:
+            import torch.distributed._symmetric_memory as symm_mem
+            flags = symm_mem.empty((max(self.world, 8),), dtype=torch.int32, device=self.W_packed.device)
+            flags.zero_()
+            fh = symm_mem.rendezvous(flags, self.group if self.group is not None else dist.group.WORLD)
+            fh.barrier(channel=0)           # every rank's flags are zero before anybody signals
+            self._flags = (flags, fh)
+        self._epoch += 1
+        self.ops.peer_barrier(self._flags[1].buffer_ptrs, self.rank, self._epoch, self.W_packed.device)
 
     def _symmetric_output(self, M: int, dtype: torch.dtype):
         """The [M, N] output buffer in symmetric memory and its rendezvous handle (allocated once per shape)."""

@@ -191,6 +191,15 @@ EL_API int el_gemm_dx_scatter(const int8_t* dYq, const uint8_t* W_packed, void* 
 EL_API int el_reduce_scale_gather(const int32_t* parts, void* const* dX_all, int n_ranks, int rank, int out_dtype,
                                   const float* absmax, float gamma, int M, int K, el_stream_t stream);
 
+/* Barrier between the n_ranks (<= 8) GPUs of an N-sharded layer, one process per GPU, for the three calls above:
+ * flags_all[i] is rank i's array of n_ranks uint32 flags (own memory or a peer mapping, zero before the first
+ * barrier); `epoch` counts this group's barriers 1, 2, ... identically on every rank.  The call queues one tiny kernel
+ * that publishes `epoch` in every rank's array (after all earlier work of the stream, stores to peers included) and
+ * waits until every rank has done the same.  The wait is bounded (seconds); a rank that does not arrive is reported as
+ * code 40 + its index in *dev_status.  No counterpart in the reference. */
+EL_API int el_peer_barrier(uint32_t* const* flags_all, int n_ranks, int rank, uint32_t epoch, int32_t* dev_status,
+                           el_stream_t stream);
+
 /* dW[n,k] = float(sum_m Gq[m,n]*Xq[m,k]) * (g_absmax[0]/127)   (out_dtype EL_F32, or EL_I32 for the raw sums).
  * Tensor-core path needs N % 16 == 0 and K % 16 == 0.  Replaces `torch.mm(dY_2d.t(), X_2d).float()`
  * (core/bitnet/int2_linear_tc.py:537, core/bitnet/int2_linear_tc_offload.py:247). */

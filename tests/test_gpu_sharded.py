@@ -38,7 +38,8 @@ def _worker(rank, world, port, order, out_dir, fused):
     try:
         pkg = load_package()
         d = make_layer_inputs(M, K, N, seed=3, dtype=torch.bfloat16, dy_std=1e-2, counters=1)
-        layer = pkg.sharded.ShardedInt2Linear(K, N, threshold=2, hysteresis_order=order, fused_gather=fused).to(dev)
+        layer = pkg.sharded.ShardedInt2Linear(K, N, threshold=2, hysteresis_order=order, fused_gather=bool(fused),
+                                              own_barrier=(fused == "own_barrier")).to(dev)
         layer.load_shard(torch.from_numpy(d["Wp"]), torch.from_numpy(d["Hp"]), d["gamma"])
         layer.set_lr(0.5)
         x = d["x"].to(dev).requires_grad_(True)
@@ -54,10 +55,11 @@ def _worker(rank, world, port, order, out_dir, fused):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("fused", [False, True])
+@pytest.mark.parametrize("fused", [False, True, "own_barrier"])
 @pytest.mark.parametrize("order", ["reference", "after_dx"])
 def test_sharded_step_on_gpus_equals_single_gpu(tmp_path, order, fused):
-    """fused=True: the forward all-gather happens as TMA stores from the GEMM epilogue into symmetric memory."""
+    """fused: the output all-gather and the dX reduce-scatter happen as stores from the GEMM epilogues into symmetric
+    memory, with the symmetric-memory handle's barrier between them (True) or el_peer_barrier ("own_barrier")."""
     world = min(torch.cuda.device_count(), 8)
     if world < 2:
         pytest.skip("needs at least two GPUs")
