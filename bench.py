@@ -146,7 +146,8 @@ def run_reference(args, wl):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps, warmup = max(1, min(args.steps, 5)), max(1, min(args.warmup, 2))
+    # one CPU step takes about 1.7 s on 16 cores: K steps as asked, bounded so that the run stays within a few minutes
+    steps, warmup = max(1, min(args.steps, 60)), max(1, min(args.warmup, 3))
     base = cpu_baseline_sample(wl, steps, warmup, sample_tokens=min(512, wl["M"]))
     line = {
         "impl": "reference", "metric": METRIC, "value": base["value"], "unit": "tokens/s", "n_gpus": args.gpus,
