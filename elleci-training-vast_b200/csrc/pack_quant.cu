@@ -78,7 +78,6 @@ __device__ __forceinline__ float block_max(float v, float* red) {
     return v;
 }
 
-template <typename T> struct Vec8 { uint4 raw; };
 
 template <typename T>
 __device__ __forceinline__ void load8(const T* p, float v[8]);
