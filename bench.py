@@ -252,8 +252,12 @@ def run_ours(args, wl):
             lay.epoch += 1
             ops.peer_barrier(lay.flags_hdl.buffer_ptrs, rank, lay.epoch, dev)
 
+    overlap_dx = world > 1 and not args.no_overlap_dx
+    side = torch.cuda.Stream(device=dev) if overlap_dx else None
+
     def layer_step(lay):
-        """One layer: forward, then (reference order) the weight update, then dX."""
+        """One layer: forward, then the weight update and dX (update first, as the reference's hook does; with several
+        GPUs dX first, so that its exchange can run under the update)."""
         K, Nl = lay.K, lay.Nl
         Xq, ax = timer.run("quantize_rows", ops.quantize_rows, lay.x)
         if lay.symm is not None:
@@ -278,13 +282,31 @@ def run_ours(args, wl):
             dYq, ady, gmax = timer.run("quantize_rows_dy", ops.quantize_rows, window, ops.GRAD_EPS, ax, raw)
         else:
             dYq, ady, gmax = timer.run("quantize_rows_dy", ops.quantize_rows, window, ops.GRAD_EPS, ax)
-        Gq = timer.run("quantize_grad", ops.quantize_grad, window, ax, gmax)
         lay.step += 1
-        timer.run("gemm_dw_hysteresis", ops.dw_hysteresis, Gq, Xq, gmax, lay.Wp, lay.Hp, LR, LR_SCALE, thr, DECAY, lay.step,
-                  lay.n0 * K)
-        if lay.symm is not None:
-            # dX GEMM fused with the reduce-scatter of its int32 partial sums (epilogue TMA stores into the owners'
-            # staging buffers), then each rank sums + scales its rows and writes them into every rank's dX
+
+        def update():
+            Gq = timer.run("quantize_grad", ops.quantize_grad, window, ax, gmax)
+            timer.run("gemm_dw_hysteresis", ops.dw_hysteresis, Gq, Xq, gmax, lay.Wp, lay.Hp, LR, LR_SCALE, thr, DECAY, lay.step,
+                      lay.n0 * K)
+
+        if lay.symm is not None and overlap_dx:
+            # Order "forward, dX, weight update": the dX GEMM scatters its int32 partial sums to the owners (epilogue TMA
+            # stores); after the barrier the owner's sum + scale + gather pass and its barrier run on a side stream, under
+            # the local dW + hysteresis kernel of the main stream.
+            parts, hp, dxbuf, hd = lay.symm_dx[lay.step & 1]
+            timer.run("gemm_dx", ops.backward_input_scatter, dYq, lay.Wp, K, hp.buffer_ptrs, rank)
+            timer.run("barrier_dx1", peer_barrier, lay, hp, 3)
+            main = torch.cuda.current_stream()
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                timer.run("reduce_scale_gather", ops.reduce_scale_gather, parts, hd.buffer_ptrs, rank, ady, lay.gamma, M, K, torch.bfloat16)
+                timer.run("barrier_dx2", peer_barrier, lay, hd, 4)
+            update()
+            main.wait_stream(side)
+            dX = dxbuf
+        elif lay.symm is not None:
+            # reference order: the weight update first, then dX with the scatter / sum / gather in sequence
+            update()
             parts, hp, dxbuf, hd = lay.symm_dx[lay.step & 1]
             timer.run("gemm_dx", ops.backward_input_scatter, dYq, lay.Wp, K, hp.buffer_ptrs, rank)
             timer.run("barrier_dx1", peer_barrier, lay, hp, 3)
@@ -292,10 +314,12 @@ def run_ours(args, wl):
             timer.run("barrier_dx2", peer_barrier, lay, hd, 4)
             dX = dxbuf
         elif world > 1:
+            update()
             acc = timer.run("gemm_dx", ops.backward_input_rows, dYq, lay.Wp, ady, lay.gamma, K, torch.int32)
             timer.run("all_reduce_dx", dist.all_reduce, acc)
             dX = timer.run("scale_rows", ops.scale_rows, acc, ady, lay.gamma, torch.bfloat16)
         else:
+            update()
             dX = timer.run("gemm_dx", ops.backward_input_rows, dYq, lay.Wp, ady, lay.gamma, K, torch.bfloat16)
         return y, dX
 
@@ -469,7 +493,8 @@ def run_ours(args, wl):
         "config": {"workload": wl["desc"], "M": M, "layers": wl["layers"], "threshold": thr,
                    "parallelism": (f"N-sharded x{world}, " + ("Y all-gathered and dX all-reduced by NCCL" if args.no_fused_gather else
                                                               "Y gathered and dX partial sums reduce-scattered by TMA stores from "
-                                                              "the GEMM epilogues, dX rows summed and re-gathered by peer stores")
+                                                              "the GEMM epilogues, dX rows summed and re-gathered by peer stores"
+                                                              + ("" if args.no_overlap_dx else " on a side stream under the local dW + hysteresis"))
                                    ) if world > 1 else "single GPU",
                    "l2": "256 MiB written between timed steps (untimed)", "weights_changed_after_run": changed_frac},
         "clocks": clocks, "e2e": e2e, "gpu_launches": own_launches,
@@ -637,6 +662,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
     ap.add_argument("--inline-kernel-events", action="store_true",
                     help="record the per-kernel event pairs inside the headline region instead of in a second pass")
+    ap.add_argument("--no-overlap-dx", action="store_true",
+                    help="N > 1: keep the reference order (update, then dX) with the dX exchange in sequence")
     ap.add_argument("--own-barrier", action="store_true",
                     help="N > 1: use el_peer_barrier instead of the symmetric-memory handle's barrier (same speed)")
     ap.add_argument("--no-fused-gather", action="store_true",

@@ -119,8 +119,20 @@ class _ShardedLinearFn(Function):
                 parts, hp, dxbuf, hd = layer._symmetric_dx(M_tok, ctx.io)     # alternating buffers, as in the forward
                 ops.backward_input_scatter(dYq, layer.W_packed, K, hp.buffer_ptrs, r)
                 layer._barrier(hp, 3)       # all partial sums of my rows have landed
-                ops.reduce_scale_gather(parts, hd.buffer_ptrs, r, ady, gam, M_tok, K, ctx.io)
-                layer._barrier(hd, 4)       # all rows of my dX have landed
+                if do_update and layer.hysteresis_order != "reference" and layer.overlap_dx:
+                    # the owner's sum + scale + gather pass and its barrier run on a side stream, under the local
+                    # dW + hysteresis kernel of the main stream
+                    main, side = torch.cuda.current_stream(), layer._side_stream()
+                    side.wait_stream(main)
+                    with torch.cuda.stream(side):
+                        ops.reduce_scale_gather(parts, hd.buffer_ptrs, r, ady, gam, M_tok, K, ctx.io)
+                        layer._barrier(hd, 4)
+                    update()
+                    do_update = False
+                    main.wait_stream(side)
+                else:
+                    ops.reduce_scale_gather(parts, hd.buffer_ptrs, r, ady, gam, M_tok, K, ctx.io)
+                    layer._barrier(hd, 4)       # all rows of my dX have landed
                 dX = dxbuf.clone() if layer.copy_output else dxbuf
             elif g > 1:
                 acc = ops.backward_input_rows(dYq, layer.W_packed, ady, gam, K, torch.int32)
@@ -165,6 +177,10 @@ class ShardedInt2Linear(nn.Module):
         # barrier.  Measured equal in time (a barrier's time is the wait for the slowest rank); off by default because its
         # bound would turn a rank that is merely seconds late into an error.
         self.own_barrier = own_barrier
+        # overlap_dx (fused path, hysteresis_order="after_dx"): the second half of the dX exchange runs on a side stream
+        # while the main stream runs the local dW + hysteresis kernel
+        self.overlap_dx = True
+        self._side = None
         self._flags = None
         self._epoch = 0
         self._symm = {}
@@ -179,6 +195,11 @@ class ShardedInt2Linear(nn.Module):
 
     def set_lr(self, lr: float):
         self._lr = lr
+
+    def _side_stream(self):
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=self.W_packed.device)
+        return self._side
 
     def _barrier(self, hdl, channel: int):
         """All ranks have finished the work queued so far (their stores into this rank's buffers have landed)."""
