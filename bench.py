@@ -651,13 +651,87 @@ def run_decode(args):
     print(json.dumps(line))
 
 
+def run_hbm_kernels(args):
+    """The memory-bound kernels that the layer step does not launch in its fused form, each alone at the 4096 x 11008
+    layer's size: stand-alone hysteresis update from a float32 gradient, ternarise + pack, unpack, the per-tensor
+    quantiser pair of the reference rule, the post-reduction scale pass, the plain dW GEMM's float32 output feeding the
+    stand-alone update.  L2 is flushed before every timed launch; GB/s counts the algorithmic bytes."""
+    import torch
+    pkg = load_package()
+    ops = pkg.int2_tc_ops
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    peaks, peak_kind = measured_peaks()
+    N, K, M = 11008, 4096, 4096
+    gen = torch.Generator().manual_seed(3)
+    W = (torch.randn(N, K, generator=gen) * 0.02).to(dev)
+    gamma = float(W.abs().mean().item())
+    Wp = ops.ternarize_pack(W, gamma)
+    Hp = torch.randint(0, 256, (N, K // 2), generator=gen, dtype=torch.uint8).to(dev)
+    dW = (torch.randn(N, K, generator=gen) * 1e-3).to(dev)
+    x16 = torch.randn(M, K, generator=gen).to(torch.float16).to(dev)
+    acc = torch.randint(-100000, 100000, (M, K), generator=gen, dtype=torch.int32).to(dev)
+    ax = torch.rand(M, generator=gen).to(dev) + 0.5
+    w8 = torch.empty(N, K, dtype=torch.int8, device=dev)
+    gmax = torch.zeros(1, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    reps = max(args.steps, 2)
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        total = 0.0
+        for _ in range(reps):
+            flush.fill_(1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            total += e0.elapsed_time(e1)
+        return total / reps
+
+    step = [0]
+
+    def hyst():
+        step[0] += 1
+        ops.hysteresis_step_v2(dW, Wp, Hp, 1e-2, 5.0, 3, 0.001, step[0])
+
+    q8, sc = ops.quantize_activation_async(x16, gmax)
+    cases = {
+        "hysteresis_from_dw": (hyst, N * K * 5.5),
+        "ternarize_pack": (lambda: ops.ternarize_pack(W, gamma, out=Wp), N * K * 4.25),
+        "unpack_int2": (lambda: ops.unpack_int2(Wp, w8, K), N * K * 1.25),
+        "quantize_tensor (reference rule, absmax + quantise)": (lambda: ops.quantize_activation_async(x16, gmax), M * K * 5.0),
+        "dequantize_tensor": (lambda: ops.dequantize_activation(q8, sc), M * K * 3.0),
+        "scale_rows (int32 -> bf16)": (lambda: ops.scale_rows(acc, ax, 0.02, torch.bfloat16), M * K * 6.0),
+    }
+    out = {}
+    for name, (fn, nbytes) in cases.items():
+        ms = timed(fn)
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out[name] = {"ms": ms, "GBps": gbs, "frac_of_hbm": gbs / peaks["hbm_gbs"], "algorithmic_bytes": nbytes}
+    ops.check_device_status(dev)
+    head = out["hysteresis_from_dw"]
+    print(json.dumps({
+        "metric": "stand-alone memory-bound kernels of the INT2 linear path, GB/s of algorithmic bytes", "value": head["GBps"],
+        "unit": "GB/s", "n_gpus": 1, "steps": reps, "warmup": 3, "ms_per_step": head["ms"], "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "int2/int4 state, f32 gradient", "data": "synthetic",
+        "config": {"workload": "hbm: each kernel alone at N=11008, K=4096 (M=4096 for the activation kernels), L2 flushed before "
+                               "every launch; value = stand-alone hysteresis update"},
+        "roofline": {"bound": "hbm", "achieved": head["GBps"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": head["frac_of_hbm"], "traffic": None, "peak_source": f"hbm_gbs ({peak_kind})"},
+        "kernels": out, "gpu_launches": (reps + 3) * len(cases),
+    }))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="config2", choices=sorted(WORKLOADS) + ["config3"])
+    ap.add_argument("--workload", default="config2", choices=sorted(WORKLOADS) + ["config3", "hbm"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg of the default run")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
     ap.add_argument("--inline-kernel-events", action="store_true",
@@ -669,9 +743,9 @@ def main():
     ap.add_argument("--no-fused-gather", action="store_true",
                     help="N > 1: all-gather the output with NCCL instead of TMA stores from the GEMM epilogue")
     args = ap.parse_args()
-    if args.workload == "config3":
+    if args.workload in ("config3", "hbm"):
         if args.impl == "ours" and int(os.environ.get("RANK", "0")) == 0:
-            run_decode(args)
+            run_decode(args) if args.workload == "config3" else run_hbm_kernels(args)
         return
     wl = WORKLOADS[args.workload]
     if args.impl == "reference":

@@ -137,7 +137,8 @@ __device__ __forceinline__ void hyst_update_one(float grad, int& q, int& h, uint
 //  * codes are sanitised (3 -> 1) once per word and stay biased (q+1), counters are read biased by 8 (word ^ 0x88888888);
 //  * the new words are built from zero with one multiply-add per field instead of a masked read-modify-write;
 //  * ALIGNED (idx0 a multiple of 32): idx0 + j = idx0 ^ j, so the counter xor seed is one operation per weight.
-template <bool FTZ, bool ALIGNED>
+// FROM_ACC: acc holds int32 sums to be scaled by sc; otherwise acc holds the bits of float32 gradients (sc unused).
+template <bool FTZ, bool ALIGNED, bool FROM_ACC = true>
 __device__ __forceinline__ void hyst_update_chunk32(const uint32_t acc[32], float sc, uint32_t w[2], uint32_t h[4],
                                                     uint32_t idx0, const HystParams& p) {
     uint32_t ws[2], hb[4], wn[2] = {0u, 0u}, hn[4] = {0u, 0u, 0u, 0u};
@@ -154,7 +155,7 @@ __device__ __forceinline__ void hyst_update_chunk32(const uint32_t acc[32], floa
         const int nib = (int)((hb[hi] >> hsft) & 0xFu);          // h + 8
         const uint32_t u1 = mix2(ALIGNED ? (b1 ^ (uint32_t)j) : ((idx0 + j) ^ p.s1)) & 0xFFFFFFu;
         const uint32_t u2 = mix2(ALIGNED ? (b2 ^ (uint32_t)j) : ((idx0 + j) ^ p.s2)) & 0xFFFFFFu;
-        const float grad = __fmul_rn((float)(int)acc[j], sc);
+        const float grad = FROM_ACC ? __fmul_rn((float)(int)acc[j], sc) : __uint_as_float(acc[j]);
         float d_raw;
         if (FTZ) asm("mul.ftz.f32 %0, %1, %2;" : "=f"(d_raw) : "f"(-grad), "f"(p.lr_scaled));
         else d_raw = __fmul_rn(-grad, p.lr_scaled);

@@ -50,11 +50,50 @@ hysteresis_kernel(const float* __restrict__ dW, uint8_t* __restrict__ Wp, uint8_
     }
 }
 
+// The same update with one thread per 32 consecutive weights (K % 32 == 0, so a chunk never crosses a row): 128 bytes
+// of gradient, 8 bytes of packed weights and 16 bytes of packed counters per thread, and the trimmed 32-weight update
+// of the fused epilogue (hyst_update_chunk32) - the per-weight instruction count, not HBM, bounds this kernel.
+template <bool FTZ, bool ALIGNED>
+__global__ void __launch_bounds__(256)
+hysteresis_chunk_kernel(const float* __restrict__ dW, uint8_t* __restrict__ Wp, uint8_t* __restrict__ Hp, HystParams p,
+                        long long chunks, uint32_t idx_base) {
+    const long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= chunks) return;
+    const float4* g = reinterpret_cast<const float4*>(dW) + c * 8;
+    uint32_t acc[32];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const float4 v = g[j];
+        acc[4 * j] = __float_as_uint(v.x); acc[4 * j + 1] = __float_as_uint(v.y);
+        acc[4 * j + 2] = __float_as_uint(v.z); acc[4 * j + 3] = __float_as_uint(v.w);
+    }
+    uint2* wptr = reinterpret_cast<uint2*>(Wp) + c;
+    uint4* hptr = reinterpret_cast<uint4*>(Hp) + c;
+    const uint2 w2 = *wptr;
+    const uint4 h4 = *hptr;
+    uint32_t w[2] = {w2.x, w2.y};
+    uint32_t h[4] = {h4.x, h4.y, h4.z, h4.w};
+    hyst_update_chunk32<FTZ, ALIGNED, false>(acc, 0.0f, w, h, idx_base + (uint32_t)(c * 32), p);
+    *wptr = make_uint2(w[0], w[1]);
+    *hptr = make_uint4(h[0], h[1], h[2], h[3]);
+}
+
 int launch_hysteresis(const float* dW, uint8_t* Wp, uint8_t* Hp, const HystParams& p, int N, int K, uint32_t idx_base,
                       cudaStream_t st) {
     const int pK = (K + 3) / 4, pH = (K + 1) / 2;
     const long long work = (long long)N * pK;
     if (work == 0) return EL_OK;
+    if (K % 32 == 0 && (reinterpret_cast<uintptr_t>(dW) & 15) == 0 && (reinterpret_cast<uintptr_t>(Wp) & 7) == 0 &&
+        (reinterpret_cast<uintptr_t>(Hp) & 15) == 0) {
+        const long long chunks = (long long)N * (K / 32);
+        const int cgrid = (int)((chunks + 255) / 256);
+        const bool aligned = (idx_base & 31u) == 0;
+#define EL_HC(F, A) hysteresis_chunk_kernel<F, A><<<cgrid, 256, 0, st>>>(dW, Wp, Hp, p, chunks, idx_base)
+        if (p.ftz) { if (aligned) EL_HC(true, true); else EL_HC(true, false); }
+        else { if (aligned) EL_HC(false, true); else EL_HC(false, false); }
+#undef EL_HC
+        return check_launch();
+    }
     const int grid = (int)((work + 255) / 256);
     const bool vec = (K % 4 == 0) && ((reinterpret_cast<uintptr_t>(dW) & 15) == 0) &&
                      ((reinterpret_cast<uintptr_t>(Hp) & 1) == 0);

@@ -143,7 +143,6 @@ __device__ __forceinline__ void raw_unpack(const Raw8<float>& r, float v[8]) {
     v[0] = __uint_as_float(r.a.x); v[1] = __uint_as_float(r.a.y); v[2] = __uint_as_float(r.a.z); v[3] = __uint_as_float(r.a.w);
     v[4] = __uint_as_float(r.b.x); v[5] = __uint_as_float(r.b.y); v[6] = __uint_as_float(r.b.z); v[7] = __uint_as_float(r.b.w);
 }
-constexpr int ROW_CACHE = 6;        // vectors of 8 elements a thread keeps in registers: rows up to 12288 elements
 
 __device__ __forceinline__ int quant_half_even(float x, float s) {
     float r = rintf(__fmul_rn(x, s));
@@ -153,7 +152,9 @@ __device__ __forceinline__ int quant_half_even(float x, float s) {
 
 // VEC: the row pitch and base allow 8-element vector loads and 8-byte stores.
 // MODE 0: absmax + quantise; 1: raw absmax only; 2: quantise with the raw absmax found in row_absmax.
-template <typename T, bool VEC, int MODE>
+// ROW_CACHE: vectors of 8 elements a thread keeps in registers between the passes (2 for rows up to 4096 elements: fewer
+// registers, more resident CTAs; 6 for rows up to 12288; longer rows re-read their tail).
+template <typename T, bool VEC, int MODE, int ROW_CACHE>
 __global__ void __launch_bounds__(256)
 quantize_rows_kernel(const T* __restrict__ x, long long ldx, int8_t* __restrict__ q, float* __restrict__ row_absmax, int K,
                      float eps, const float* __restrict__ fold_absmax, float* __restrict__ fold_max) {
@@ -422,7 +423,8 @@ static int launch_quantize_rows_t(const T* x, long long ldx, int8_t* q, float* a
                                   const float* fold_absmax, float* fold_max, cudaStream_t st) {
     const bool vec = (K % 8 == 0) && (ldx % 8 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0) &&
                      ((reinterpret_cast<uintptr_t>(q) & 7) == 0);
-#define EL_QR(V, MD) quantize_rows_kernel<T, V, MD><<<M, 256, 0, st>>>(x, ldx, q, a, K, eps, fold_absmax, fold_max)
+#define EL_QR(V, MD) do { if (K <= 4096) quantize_rows_kernel<T, V, MD, 2><<<M, 256, 0, st>>>(x, ldx, q, a, K, eps, fold_absmax, fold_max); \
+                         else quantize_rows_kernel<T, V, MD, 6><<<M, 256, 0, st>>>(x, ldx, q, a, K, eps, fold_absmax, fold_max); } while (0)
     if (mode == 0) { if (vec) EL_QR(true, 0); else EL_QR(false, 0); }
     else if (mode == 1) { if (vec) EL_QR(true, 1); else EL_QR(false, 1); }
     else { if (vec) EL_QR(true, 2); else EL_QR(false, 2); }
