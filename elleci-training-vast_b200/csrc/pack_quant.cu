@@ -544,28 +544,36 @@ struct GatherDst {
 __global__ void __launch_bounds__(256)
 reduce_scale_gather_kernel(const int* __restrict__ parts, int n_parts, GatherDst dst, int n_ranks, long long row_offset,
                            EpiParams epi, int Mr, int C) {
+    // one thread per 8 columns: 32 bytes of every part in flight, one 16-byte (two-byte outputs) or two 16-byte stores
+    // per destination, so that a warp's stores to a peer are 512 contiguous bytes
     const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    const int cg = C >> 2;
+    const int cg = C >> 3;
     if (t >= (long long)Mr * cg) return;
-    const int m = (int)(t / cg), c0 = (int)(t % cg) * 4;
+    const int m = (int)(t / cg), c0 = (int)(t % cg) * 8;
     const size_t part_stride = (size_t)Mr * C;
-    int4 sum = *reinterpret_cast<const int4*>(parts + (size_t)m * C + c0);
+    const int4* src = reinterpret_cast<const int4*>(parts + (size_t)m * C + c0);
+    int4 lo = src[0], hi = src[1];
     for (int p = 1; p < n_parts; ++p) {
-        const int4 v = *reinterpret_cast<const int4*>(parts + p * part_stride + (size_t)m * C + c0);
-        sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+        const int4* q = reinterpret_cast<const int4*>(parts + p * part_stride + (size_t)m * C + c0);
+        const int4 a = q[0], b = q[1];
+        lo.x += a.x; lo.y += a.y; lo.z += a.z; lo.w += a.w;
+        hi.x += b.x; hi.y += b.y; hi.z += b.z; hi.w += b.w;
     }
     const float sc = epi_row_scale(epi, m);
-    const float f0 = __fmul_rn((float)sum.x, sc), f1 = __fmul_rn((float)sum.y, sc);
-    const float f2 = __fmul_rn((float)sum.z, sc), f3 = __fmul_rn((float)sum.w, sc);
+    const float f[8] = {__fmul_rn((float)lo.x, sc), __fmul_rn((float)lo.y, sc), __fmul_rn((float)lo.z, sc), __fmul_rn((float)lo.w, sc),
+                        __fmul_rn((float)hi.x, sc), __fmul_rn((float)hi.y, sc), __fmul_rn((float)hi.z, sc), __fmul_rn((float)hi.w, sc)};
     const size_t o = (size_t)(row_offset + m) * C + c0;
-    for (int d = 0; d < n_ranks; ++d) {
-        if (epi.out_dtype == EL_F32) {
-            *reinterpret_cast<float4*>(static_cast<float*>(dst.p[d]) + o) = make_float4(f0, f1, f2, f3);
-        } else {
-            const uint32_t lo = (epi.out_dtype == EL_BF16) ? pack_bf16x2(f0, f1) : pack_f16x2(f0, f1);
-            const uint32_t hi = (epi.out_dtype == EL_BF16) ? pack_bf16x2(f2, f3) : pack_f16x2(f2, f3);
-            *reinterpret_cast<uint2*>(static_cast<uint16_t*>(dst.p[d]) + o) = make_uint2(lo, hi);
+    if (epi.out_dtype == EL_F32) {
+        for (int d = 0; d < n_ranks; ++d) {
+            float4* out = reinterpret_cast<float4*>(static_cast<float*>(dst.p[d]) + o);
+            out[0] = make_float4(f[0], f[1], f[2], f[3]);
+            out[1] = make_float4(f[4], f[5], f[6], f[7]);
         }
+    } else {
+        uint4 v;
+        if (epi.out_dtype == EL_BF16) v = make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+        else v = make_uint4(pack_f16x2(f[0], f[1]), pack_f16x2(f[2], f[3]), pack_f16x2(f[4], f[5]), pack_f16x2(f[6], f[7]));
+        for (int d = 0; d < n_ranks; ++d) *reinterpret_cast<uint4*>(static_cast<uint16_t*>(dst.p[d]) + o) = v;
     }
 }
 
@@ -579,7 +587,8 @@ int launch_reduce_scale_gather(const int* parts, int n_parts, void* const* out_a
         dst.p[d] = out_all[d];
     }
     if (reinterpret_cast<uintptr_t>(parts) & 15) return EL_ERR_ALIGNMENT;
-    const long long work = (long long)Mr * (C >> 2);
+    if (C % 8 != 0) return EL_ERR_UNSUPPORTED_SHAPE;
+    const long long work = (long long)Mr * (C >> 3);
     if (work == 0) return EL_OK;
     reduce_scale_gather_kernel<<<(int)((work + 255) / 256), 256, 0, st>>>(parts, n_parts, dst, n_ranks, row_offset, epi, Mr, C);
     return check_launch();
