@@ -1,7 +1,7 @@
 """Generates tests/golden/*.npz from the reference itself (run in a container that has the
 reference tree; the fixtures are committed, this script documents how they were made).
 
-    python tests/golden/make_golden.py [REFERENCE_ROOT]     (default /root/reference)
+    python tests/golden/make_golden.py [REFERENCE_ROOT]     (path of the reference checkout)
 
 Sources of the expected values:
   * kernels/tests/kernel_build.py            pack_int2 / unpack_int2 (pure torch, imported)

@@ -1,6 +1,6 @@
 """Generates tests/golden/rmsnorm.npz from the reference's own pre-linear RMSNorm.
 
-Run in a container that has the reference checkout (path in REFERENCE_ROOT, default /root/reference):
+Run where the reference checkout is available (its path in the environment variable REFERENCE_ROOT):
 
     python tests/golden/make_golden_rmsnorm.py
 
