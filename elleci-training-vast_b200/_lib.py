@@ -43,6 +43,9 @@ SIGNATURES = {
     "el_decode_workspace_bytes": [_i],
     "el_rmsnorm_quantize_rows": [_vp, _i, C.c_longlong, _vp, _f, _vp, _vp, _vp, _i, _i, _f, _vp],
     "el_rmsnorm_backward_workspace_bytes": [_i],
+    "el_swiglu_quantize_rows": [_vp, _vp, _i, C.c_longlong, _vp, _f, _vp, _vp, _vp, _i, _i, _f, _vp],
+    "el_swiglu_backward_workspace_bytes": [_i],
+    "el_swiglu_backward": [_vp, _vp, _vp, _i, C.c_longlong, _vp, _vp, _vp, _vp, C.c_longlong, _vp, _vp, C.c_size_t, _i, _i, _vp],
     "el_rmsnorm_backward": [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, C.c_size_t, _i, _i, _vp],
     "el_set_decode_gemv_max_tokens": [_i],
     "el_set_decode_overlap": [_i],
@@ -79,7 +82,7 @@ def lib() -> C.CDLL:
             fn = getattr(handle, name)
             fn.argtypes = argtypes
             fn.restype = (C.c_char_p if name == "el_status_string" else
-                          C.c_size_t if name in ("el_decode_workspace_bytes", "el_rmsnorm_backward_workspace_bytes") else C.c_int)
+                          C.c_size_t if name in ("el_decode_workspace_bytes", "el_rmsnorm_backward_workspace_bytes", "el_swiglu_backward_workspace_bytes") else C.c_int)
         _lib = handle
     return _lib
 

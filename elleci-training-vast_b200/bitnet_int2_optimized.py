@@ -48,6 +48,7 @@ class BitLinearInt2(nn.Module):
             self.extra_rmsnorm = _ExtraRMSNorm(in_features, eps=rmsnorm_eps)
         self.use_hadamard_smooth = False
         self.fuse_rmsnorm = True          # False: run the norm as separate tensor operations, as the reference does
+        self.fuse_swiglu = True           # False: a gated input (forward's `up`) runs silu and the product as tensor operations
         cls = Int2LinearTCWithGradHook if use_grad_hook else Int2LinearTC
         self.int2_layer = cls(in_features=in_features, out_features=out_features, bias=bias, threshold=threshold,
                               lr_scale=lr_scale, decay_rate=decay_rate, use_24_sparsity=use_24_sparsity,
@@ -68,10 +69,18 @@ class BitLinearInt2(nn.Module):
     def weight_packed(self):
         return self.int2_layer.W_packed
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, up: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """`up`: x is the output of a gate projection and the layer's input is `silu(x) * up` (the reference's SwiGLU
+        block, model/model.py:107-108); the product, the norm and the quantiser then run as one kernel."""
+        fusable = (self.int2_layer.quant_mode == "per_token"
+                   and (not self.use_extra_rmsnorm or self.extra_rmsnorm.weight.dtype == torch.float32))
+        if up is not None:
+            if self.fuse_swiglu and fusable and (self.fuse_rmsnorm or not self.use_extra_rmsnorm) and int2_tc_ops.swiglu_supported(x) \
+                    and up.dtype == x.dtype and up.shape == x.shape:
+                return self.int2_layer(x, pre_norm=self.extra_rmsnorm if self.use_extra_rmsnorm else None, up=up)
+            x = torch.nn.functional.silu(x) * up
         if self.use_extra_rmsnorm:
-            if (self.fuse_rmsnorm and self.int2_layer.quant_mode == "per_token" and self.extra_rmsnorm.weight.dtype == torch.float32
-                    and int2_tc_ops.rmsnorm_supported(x)):
+            if self.fuse_rmsnorm and fusable and int2_tc_ops.rmsnorm_supported(x):
                 # normalisation, quantisation (and their backward) as one kernel each instead of eight tensor passes
                 return self.int2_layer(x, pre_norm=self.extra_rmsnorm)
             x = self.extra_rmsnorm(x)
@@ -125,6 +134,25 @@ class BitLinearInt2(nn.Module):
 
     def extra_repr(self):
         return f"in={self.in_features}, out={self.out_features}, int2=tcgen05/{self.int2_layer.quant_mode}"
+
+
+class SwiGLUFFNInt2(nn.Module):
+    """The reference's feed-forward block over INT2 layers: `w3(silu(w1(x)) * w2(x))` with the hidden size rounded up
+    to a multiple of 256 (SwiGLUFFN, model/model.py:86-108; same submodule names, so its state dict keys carry over).
+    silu, the product, w3's pre-linear norm and w3's quantiser run as one kernel (and one in the backward pass);
+    `fuse_swiglu = False` on w3 runs them as tensor operations instead."""
+
+    def __init__(self, d_model: int, expansion_factor: float = 8 / 3, **layer_kwargs):
+        super().__init__()
+        hidden_dim = int(d_model * expansion_factor)
+        hidden_dim = 256 * ((hidden_dim + 256 - 1) // 256)
+        self.hidden_dim = hidden_dim
+        self.w1 = BitLinearInt2(d_model, hidden_dim, **layer_kwargs)     # gate projection
+        self.w2 = BitLinearInt2(d_model, hidden_dim, **layer_kwargs)     # up projection
+        self.w3 = BitLinearInt2(hidden_dim, d_model, **layer_kwargs)     # down projection
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.w3(self.w1(x), up=self.w2(x))
 
 
 def get_int2_layers(module: nn.Module) -> List[BitLinearInt2]:

@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libelleci_int2.so")
-SOURCES = ["api.cu", "pack_quant.cu", "hysteresis.cu", "gemm_simple.cu", "gemm_tc.cu", "gemm_tc2.cu", "decode_tc.cu", "gemv_small.cu", "gemv_mma.cu", "rmsnorm.cu", "peer_sync.cu"]
+SOURCES = ["api.cu", "pack_quant.cu", "hysteresis.cu", "gemm_simple.cu", "gemm_tc.cu", "gemm_tc2.cu", "decode_tc.cu", "gemv_small.cu", "gemv_mma.cu", "rmsnorm.cu", "swiglu.cu", "peer_sync.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-fmad=false",                       # the integer state must not depend on fused multiply-adds

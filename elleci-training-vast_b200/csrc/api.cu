@@ -41,6 +41,12 @@ int launch_rmsnorm_quantize_rows(const void* x, int dt, long long ldx, const flo
 size_t rmsnorm_backward_workspace_bytes(int K);
 int launch_rmsnorm_backward(const void* g, const void* x, int dt, const float* weight, const float* rstd, void* dx,
                             float* dweight, void* workspace, size_t workspace_bytes, int M, int K, cudaStream_t st);
+size_t swiglu_backward_workspace_bytes(int H);
+int launch_swiglu_quantize_rows(const void* gate, const void* up, int dt, long long ld, const float* weight, float norm_eps,
+                                int8_t* q, float* row_absmax, float* rstd, int M, int H, float quant_eps, cudaStream_t st);
+int launch_swiglu_backward(const void* gy, const void* gate, const void* up, int dt, long long ld, const float* weight,
+                           const float* rstd, void* d_gate, void* d_up, long long ld_d, float* dweight, void* workspace,
+                           size_t workspace_bytes, int M, int H, cudaStream_t st);
 int launch_peer_barrier(unsigned int* const* flags_all, int n_ranks, int rank, unsigned int epoch, int32_t* status,
                         cudaStream_t st);
 int launch_gemv_mma(const void* x, int x_dtype, const uint8_t* Wp, const EpiParams& epi, int M, int N, int K, cudaStream_t st,
@@ -235,6 +241,32 @@ int el_rmsnorm_backward(const void* g, const void* x, int dtype, const float* we
     if (!weight || !dweight || !workspace || (M > 0 && (!g || !x || !rstd || !dx))) return EL_ERR_NULL_PTR;
     return launch_rmsnorm_backward(g, x, dtype, weight, rstd, dx, dweight, workspace, workspace_bytes, M, K,
                                    (cudaStream_t)stream);
+}
+
+int el_swiglu_quantize_rows(const void* gate, const void* up, int dtype, long long ld, const float* norm_weight, float norm_eps,
+                            int8_t* q, float* row_absmax, float* rstd, int M, int H, float quant_eps, el_stream_t stream) {
+    if (M < 0 || H < 0 || !float_dtype(dtype) || ld < H) return EL_ERR_INVALID_ARG;
+    const int rc = require_sm100();
+    if (rc != EL_OK) return rc;
+    if (M == 0) return EL_OK;
+    if (!gate || !up || !q || !row_absmax || (norm_weight && !rstd)) return EL_ERR_NULL_PTR;
+    return launch_swiglu_quantize_rows(gate, up, dtype, ld, norm_weight, norm_eps, q, row_absmax, rstd, M, H, quant_eps,
+                                       (cudaStream_t)stream);
+}
+
+size_t el_swiglu_backward_workspace_bytes(int H) { return swiglu_backward_workspace_bytes(H); }
+
+int el_swiglu_backward(const void* gy, const void* gate, const void* up, int dtype, long long ld, const float* norm_weight,
+                       const float* rstd, void* d_gate, void* d_up, long long ld_d, float* d_norm_weight, void* workspace,
+                       size_t workspace_bytes, int M, int H, el_stream_t stream) {
+    if (M < 0 || H < 0 || !float_dtype(dtype) || ld < H || ld_d < H) return EL_ERR_INVALID_ARG;
+    const int rc = require_sm100();
+    if (rc != EL_OK) return rc;
+    if (H == 0) return EL_OK;
+    if ((norm_weight && (!d_norm_weight || !workspace || (M > 0 && !rstd))) || (M > 0 && (!gy || !gate || !up || !d_gate || !d_up)))
+        return EL_ERR_NULL_PTR;
+    return launch_swiglu_backward(gy, gate, up, dtype, ld, norm_weight, rstd, d_gate, d_up, ld_d, d_norm_weight, workspace,
+                                  workspace_bytes, M, H, (cudaStream_t)stream);
 }
 
 int el_gemm_fwd(const int8_t* Xq, const uint8_t* W_packed, void* Y, int out_dtype, const float* absmax, int absmax_stride,

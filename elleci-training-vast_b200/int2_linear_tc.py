@@ -48,11 +48,16 @@ class Int2LinearTCFunction(Function):
     @staticmethod
     def forward(ctx, X: torch.Tensor, W_packed: torch.Tensor, gamma: torch.Tensor, K: int,
                 gamma_cached: Optional[float] = None, layer: Optional["Int2LinearTC"] = None,
-                norm_weight: Optional[torch.Tensor] = None, norm_eps: float = 1e-6) -> torch.Tensor:
+                norm_weight: Optional[torch.Tensor] = None, norm_eps: float = 1e-6,
+                up: Optional[torch.Tensor] = None) -> torch.Tensor:
         """`norm_weight` (per-token mode): the weight of the reference's pre-linear RMSNorm
         (core/bitnet/bitnet_int2_optimized.py:72-86,203-204); normalisation and quantisation then run as one kernel
-        over X and the backward pass returns the gradients of X and of the norm weight."""
+        over X and the backward pass returns the gradients of X and of the norm weight.
+        `up` (per-token mode): X is the gate projection's output and the layer's input is `silu(X) * up`, the
+        reference's feed-forward expression (model/model.py:107-108); the product, the norm and the quantiser run as
+        one kernel, and the backward pass returns the gradients of X and of `up`."""
         ctx.has_norm = False
+        ctx.has_gate = False
         ctx.K = K
         ctx.gamma_cached = gamma_cached
         ctx.layer = layer
@@ -63,7 +68,17 @@ class Int2LinearTCFunction(Function):
             out_dtype = X.dtype if X.dtype in _FLOAT_IO else torch.bfloat16
             ctx.io_dtype = out_dtype
             Xin = X if X.dtype in _FLOAT_IO else X.to(out_dtype)
-            if norm_weight is not None:
+            if up is not None:
+                if up.dtype != Xin.dtype or up.shape != Xin.shape:
+                    raise RuntimeError("gate and up must have the same shape and dtype")
+                Xq, ax, rstd = int2_tc_ops.swiglu_quantize_rows(Xin, up, norm_weight, norm_eps, ACT_EPS)
+                ctx.has_gate = True
+                ctx.has_norm = norm_weight is not None
+                if ctx.has_norm:
+                    ctx.save_for_backward(W_packed, gamma, Xin, up, norm_weight, rstd)
+                else:
+                    ctx.save_for_backward(W_packed, gamma, Xin, up)
+            elif norm_weight is not None:
                 Xin = Xin.contiguous()
                 Xq, ax, rstd = int2_tc_ops.rmsnorm_quantize_rows(Xin, norm_weight, norm_eps, ACT_EPS)
                 ctx.has_norm = True
@@ -75,8 +90,8 @@ class Int2LinearTCFunction(Function):
                 layer._saved_input = (Xq, ax)
                 layer._saved_input_shape = X.shape
             return int2_tc_ops.matmul_rows(Xq, W_packed, ax, gamma_val, out_dtype)
-        if norm_weight is not None:
-            raise RuntimeError("the fused pre-linear RMSNorm needs quant_mode='per_token'")
+        if norm_weight is not None or up is not None:
+            raise RuntimeError("the fused pre-linear RMSNorm and SwiGLU gate need quant_mode='per_token'")
         ctx.save_for_backward(W_packed, gamma)
         X_half = X.half() if X.dtype != torch.float16 else X
         ctx.io_dtype = torch.float16
@@ -93,7 +108,8 @@ class Int2LinearTCFunction(Function):
         layer = ctx.layer
         dX = None
         d_norm_weight = None
-        if ctx.needs_input_grad[0] or (ctx.has_norm and ctx.needs_input_grad[6]):
+        d_up = None
+        if ctx.needs_input_grad[0] or (ctx.has_norm and ctx.needs_input_grad[6]) or (ctx.has_gate and ctx.needs_input_grad[8]):
             gamma_val = ctx.gamma_cached if ctx.gamma_cached is not None else gamma.item()
             if ctx.mode == "per_token":
                 cached = layer._take_dy_cache(dY) if layer is not None else None
@@ -108,12 +124,16 @@ class Int2LinearTCFunction(Function):
                 dY_int8, d_scale_dy = int2_tc_ops.quantize_activation_async(
                     dY_half.contiguous(), Int2LinearTCFunction._get_absmax_buf(dY.device))
                 dX = int2_tc_ops.backward_input_int8(dY_int8, W_packed, d_scale_dy, gamma_val, ctx.K)
-            if ctx.has_norm:
+            if ctx.has_gate:
+                gate, up = ctx.saved_tensors[2:4]
+                norm_weight, rstd = ctx.saved_tensors[4:6] if ctx.has_norm else (None, None)
+                dX, d_up, d_norm_weight = int2_tc_ops.swiglu_backward(dX.view_as(gate), gate, up, norm_weight, rstd)
+            elif ctx.has_norm:
                 Xin, norm_weight, rstd = ctx.saved_tensors[2:]
                 dX, d_norm_weight = int2_tc_ops.rmsnorm_backward(dX.view_as(Xin), Xin, norm_weight, rstd)
         if layer is not None:
             layer._run_pending_update()
-        return dX, None, None, None, None, None, d_norm_weight, None
+        return dX, None, None, None, None, None, d_norm_weight, None, d_up
 
 
 class Int2LinearTC(nn.Module):
@@ -190,15 +210,20 @@ class Int2LinearTC(nn.Module):
         self._step.fill_(self._step_py)
 
     # ---- forward ---------------------------------------------------------------------------------------------
-    def forward(self, x: torch.Tensor, pre_norm: Optional[nn.Module] = None) -> torch.Tensor:
-        """`pre_norm`: an RMSNorm module (`weight` float32 [K], `eps`) to apply to x first, fused with the quantiser."""
+    def forward(self, x: torch.Tensor, pre_norm: Optional[nn.Module] = None, up: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """`pre_norm`: an RMSNorm module (`weight` float32 [K], `eps`) to apply to x first, fused with the quantiser.
+        `up`: x is a gate and the layer's input is `silu(x) * up` (the reference's SwiGLU block), fused as well."""
         if not self._initialized:
             w_init = torch.randn(self.out_features, self.in_features, device=x.device, dtype=torch.float32) * (
                 1.0 / math.sqrt(self.in_features))
             self.init_from_float(w_init)
         if self._gamma_cached is None:
             self._gamma_cached = self.gamma.detach().item()
-        if pre_norm is not None:
+        if up is not None:
+            out = Int2LinearTCFunction.apply(x, self.W_packed, self.gamma, self.in_features, self._gamma_cached, self,
+                                             None if pre_norm is None else pre_norm.weight,
+                                             1e-6 if pre_norm is None else pre_norm.eps, up)
+        elif pre_norm is not None:
             out = Int2LinearTCFunction.apply(x, self.W_packed, self.gamma, self.in_features, self._gamma_cached, self,
                                              pre_norm.weight, pre_norm.eps)
         else:
@@ -296,8 +321,8 @@ class Int2LinearTCWithGradHook(Int2LinearTC):
     def disable_hysteresis(cls):
         Int2LinearTCWithGradHook._hysteresis_enabled = False
 
-    def forward(self, x: torch.Tensor, pre_norm: Optional[nn.Module] = None) -> torch.Tensor:
-        out = super().forward(x, pre_norm)
+    def forward(self, x: torch.Tensor, pre_norm: Optional[nn.Module] = None, up: Optional[torch.Tensor] = None) -> torch.Tensor:
+        out = super().forward(x, pre_norm, up)
         if self.training and out.requires_grad:
             out.register_hook(self._grad_hook)
         return out

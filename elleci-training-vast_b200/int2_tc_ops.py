@@ -311,6 +311,74 @@ def rmsnorm_backward(g: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, rst
     return dx.view_as(x), dw
 
 
+def _gate_up_views(gate: torch.Tensor, up: torch.Tensor):
+    """2-D views of gate and up with one common row pitch (the two halves of a [M, 2H] matrix qualify)."""
+    _require(gate.dtype == up.dtype and gate.shape == up.shape, "gate and up must have the same shape and dtype")
+    _require(gate.dtype in (torch.float16, torch.bfloat16, torch.float32), "gate and up must be float16, bfloat16 or float32")
+    gv, M, H, ld = _rows_view(gate)
+    uv, _, _, ld_u = _rows_view(up)
+    if ld_u != ld:
+        gv, uv, ld = gv.contiguous(), uv.contiguous(), H
+    return gv, uv, M, H, ld
+
+
+def swiglu_supported(gate: torch.Tensor) -> bool:
+    """Shapes the fused SwiGLU kernels take: a float CUDA tensor whose hidden size is a multiple of 8 (at most 25600)
+    and whose rows are 16-byte aligned."""
+    return rmsnorm_supported(gate)
+
+
+def swiglu_quantize_rows(gate: torch.Tensor, up: torch.Tensor, norm_weight: Optional[torch.Tensor] = None,
+                         norm_eps: float = NORM_EPS, quant_eps: float = ACT_EPS):
+    """`F.silu(gate) * up` of the reference's feed-forward block (model/model.py:107-108), the pre-linear RMSNorm of the
+    INT2 layer that consumes it (core/bitnet/bitnet_int2_optimized.py:201-204; skipped when `norm_weight` is None) and
+    the per-token quantiser, in one pass.  Returns (q int8 like gate, absmax float32 [M], rstd float32 [M] or None)."""
+    _cuda(gate, "gate"); _cuda(up, "up")
+    gv, uv, M, H, ld = _gate_up_views(gate, up)
+    if norm_weight is not None:
+        _require(norm_weight.dtype == torch.float32 and norm_weight.numel() == H and norm_weight.is_contiguous(),
+                 "norm_weight must be a contiguous float32 [H]")
+    q = torch.empty(*gate.shape[:-1], H, dtype=torch.int8, device=gate.device)
+    a = torch.empty(M, dtype=torch.float32, device=gate.device)
+    rstd = torch.empty(M, dtype=torch.float32, device=gate.device) if norm_weight is not None else None
+    call("el_swiglu_quantize_rows", gv.data_ptr(), uv.data_ptr(), _DT[gv.dtype], ld, _ptr(norm_weight), float(norm_eps),
+         q.data_ptr(), a.data_ptr(), _ptr(rstd), M, H, float(quant_eps), _stream())
+    return q, a, rstd
+
+
+def swiglu_backward(gy: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, norm_weight: Optional[torch.Tensor] = None,
+                    rstd: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None):
+    """Backward of swiglu_quantize_rows for the gradient gy with respect to the row that was quantised.  Returns
+    (d_gate, d_up, d_norm_weight or None); with `out` (a [M, 2H] tensor of the I/O type) the two gradients are written
+    into its halves (the gradient of a fused gate|up projection) and returned as views."""
+    _cuda(gy, "gy"); _cuda(gate, "gate"); _cuda(up, "up")
+    gv, uv, M, H, ld = _gate_up_views(gate, up)
+    _require(gy.dtype == gv.dtype and gy.numel() == M * H, "gy must have the shape and dtype of gate")
+    gyc = gy.contiguous()
+    if out is None:
+        d_gate, d_up, ld_d = torch.empty(M, H, dtype=gv.dtype, device=gv.device), torch.empty(M, H, dtype=gv.dtype, device=gv.device), H
+    else:
+        _require(out.dtype == gv.dtype and out.shape == (M, 2 * H) and out.is_contiguous(), "out must be a contiguous [M, 2H] tensor")
+        d_gate, d_up, ld_d = out[:, :H], out[:, H:], 2 * H
+    dw, ws, need = None, None, 0
+    if norm_weight is not None:
+        _require(norm_weight.dtype == torch.float32 and norm_weight.numel() == H, "norm_weight must be float32 [H]")
+        _require(rstd is not None and rstd.dtype == torch.float32 and rstd.numel() == M, "rstd must be float32 [M]")
+        need = _lib.lib().el_swiglu_backward_workspace_bytes(H)
+        key = (gv.device.index, H)
+        ws = _norm_ws.get(key)
+        if ws is None:
+            ws = torch.empty(need, dtype=torch.uint8, device=gv.device)
+            _norm_ws[key] = ws
+        dw = torch.empty(H, dtype=torch.float32, device=gv.device)
+        norm_weight = norm_weight.contiguous()
+    call("el_swiglu_backward", gyc.data_ptr(), gv.data_ptr(), uv.data_ptr(), _DT[gv.dtype], ld, _ptr(norm_weight), _ptr(rstd),
+         d_gate.data_ptr(), d_up.data_ptr(), ld_d, _ptr(dw), _ptr(ws), need, M, H, _stream())
+    if out is None:
+        return d_gate.view_as(gate), d_up.view_as(up), dw
+    return d_gate, d_up, dw
+
+
 def absmax_rows(x: torch.Tensor) -> torch.Tensor:
     """Raw max |x[m,:]| per row (float32 [M]), without the eps floor: the first half of quantize_rows for a
     column shard, to be max-reduced over ranks and passed back as `raw_absmax`."""

@@ -151,6 +151,35 @@ EL_API size_t el_rmsnorm_backward_workspace_bytes(int K);
 EL_API int el_rmsnorm_backward(const void* g, const void* x, int dtype, const float* weight, const float* rstd, void* dx,
                                float* dweight, void* workspace, size_t workspace_bytes, int M, int K, el_stream_t stream);
 
+/* ---- SwiGLU gate fused with the down projection's norm and quantiser ------------------------------- */
+
+/* The reference's feed-forward block is w3(silu(w1 x) * w2 x) (SwiGLUFFN.forward, model/model.py:107-108); its INT2
+ * layer then normalises and quantises that product (core/bitnet/bitnet_int2_optimized.py:201-210).  This call takes
+ * the outputs of the gate and up projections (gate, up: [M,H] of `dtype`, common row pitch ld elements, so they may
+ * be the two halves of one [M,2H] buffer) and writes what the down projection's GEMM reads:
+ *   s = dtype(gate * sigmoid(gate));  h = dtype(s * up);
+ *   y = dtype(dtype(h * rstd) * dtype(norm_weight)),  rstd[m] = 1/sqrt(mean_k h[m,k]^2 + norm_eps)   (y = h and rstd
+ *   untouched when norm_weight is NULL);  q, row_absmax = per-token quantisation of y as el_quantize_rows gives it.
+ * sigmoid(g) = 1/(1 + e^-g) in float32 with a fixed polynomial exponential (about 1 ulp), so the result is the same on
+ * every run and reproducible on a CPU; against a float32 library silu it differs by at most one unit of `dtype` on a
+ * small fraction of elements.  H % 8 == 0, 16-byte aligned rows. */
+EL_API int el_swiglu_quantize_rows(const void* gate, const void* up, int dtype, long long ld, const float* norm_weight,
+                                   float norm_eps, int8_t* q, float* row_absmax, float* rstd, int M, int H,
+                                   float quant_eps, el_stream_t stream);
+/* Backward of the call above for the gradient gy [M,H] (contiguous) with respect to y, following autograd through the
+ * reference's tensor operations (quantiser = straight-through estimator):
+ *   gn = dtype(gy*dtype(w));  c[m] = sum_k gn*h;  dh = dtype(gn*rstd - h*(rstd^3*c/H));  d_norm_weight[k] = sum_m
+ *   gy*dtype(h*rstd)  (dh = gy without a norm);  ds = dtype(dh*up);  d_up = dtype(dh*s);
+ *   d_gate = dtype((ds*sig) * (1 + gate*(1 - sig))).
+ * d_gate, d_up: [M,H] with common row pitch ld_d (may be the halves of one [M,2H] buffer: the gradient of the fused
+ * gate|up projection).  workspace: el_swiglu_backward_workspace_bytes(H) bytes, 16-byte aligned (unused without a
+ * norm).  H % 8 == 0; H <= 25600 with a norm. */
+EL_API size_t el_swiglu_backward_workspace_bytes(int H);
+EL_API int el_swiglu_backward(const void* gy, const void* gate, const void* up, int dtype, long long ld,
+                              const float* norm_weight, const float* rstd, void* d_gate, void* d_up, long long ld_d,
+                              float* d_norm_weight, void* workspace, size_t workspace_bytes, int M, int H,
+                              el_stream_t stream);
+
 /* ---- GEMMs ------------------------------------------------------------------------------------------- */
 
 /* Y[m,n] = out_dtype( float(sum_k Xq[m,k]*Wq[n,k]) * ((absmax[m*absmax_stride]/127) * gamma) ).

@@ -17,6 +17,7 @@ reference project root):
 * forward / dX integer GEMMs and their epilogue .. kernels/int2/int2_matmul_int8_tc_v2.cu:118-121,261
                                                    kernels/int2/int2_backward_int8_tc_v2.cu:88-92,233
 * hysteresis update .............................. kernels/int2/int2_hysteresis_v2.cu:54-152
+* SwiGLU gate (silu(w1 x) * w2 x) ................ model/model.py:86-108
 * pre-linear RMSNorm ............................. core/bitnet/bitnet_int2_optimized.py:72-86,
                                                    model/common/bitnet_legacy.py:10-25
 
@@ -436,6 +437,60 @@ def rmsnorm_backward(g: np.ndarray, x: np.ndarray, weight: np.ndarray, rstd: np.
     norm = _round_io((x * rstd[:, None]).astype(np.float32), io)
     dweight = (g * norm).astype(np.float32).astype(np.float64).sum(axis=0).astype(np.float32)
     return dx, dweight
+
+
+# ----------------------------------------------------------------------------------------------
+# SwiGLU gate in front of the down projection   (model/model.py:86-108: w3(silu(w1 x) * w2 x))
+# ----------------------------------------------------------------------------------------------
+
+def sigmoid_fixed(g: np.ndarray) -> np.ndarray:
+    """1/(1 + e^-g) in float32 with the fixed polynomial exponential of oracle/int2_oracle.c (the one
+    piece of this file that needs the C library: NumPy has no fused multiply-add)."""
+    from . import native
+    return native.c_sigmoid_fixed(np.asarray(g, dtype=np.float32))
+
+
+def swiglu_hidden(gate: np.ndarray, up: np.ndarray, io: str = "bf16"):
+    """`F.silu(gate) * up` as two tensor operations of the I/O type (model/model.py:107-108):
+    s = io(gate * sigmoid(gate)), h = io(s * up).  Returns (h, s, sig) as float32 arrays."""
+    g = _round_io(gate, io)
+    u = _round_io(up, io)
+    sig = sigmoid_fixed(g)
+    s = _round_io((g * sig).astype(np.float32), io)
+    h = _round_io((s * u).astype(np.float32), io)
+    return h, s, sig
+
+
+def swiglu_quantize_rows(gate, up, norm_weight=None, norm_eps: float = 1e-6, quant_eps: float = 1e-5, io: str = "bf16"):
+    """What the down projection's GEMM reads: the gated product, normalised by the layer's pre-linear
+    RMSNorm when `norm_weight` is given (core/bitnet/bitnet_int2_optimized.py:201-204), quantised per
+    token.  Returns (q int8 [M,H], absmax float32 [M], rstd float32 [M] or None)."""
+    h, _, _ = swiglu_hidden(gate, up, io)
+    if norm_weight is None:
+        q, a = quantize_rows(h, quant_eps)
+        return q, a, None
+    return rmsnorm_quantize_rows(h, norm_weight, norm_eps, quant_eps, io)
+
+
+def swiglu_backward(gy, gate, up, norm_weight=None, rstd=None, io: str = "bf16"):
+    """Gradients of swiglu_quantize_rows' input for the upstream gradient gy with respect to the quantised
+    row (straight-through quantiser), following autograd through the tensor operations:
+      dh = rmsnorm_backward(gy, h) (or gy);  ds = io(dh*up);  d_up = io(dh*s);
+      d_gate = io((ds*sig) * (1 + gate*(1 - sig)))     (torch's silu backward, float32)
+    Returns (d_gate, d_up, d_norm_weight or None)."""
+    g = _round_io(gate, io)
+    u = _round_io(up, io)
+    h, s, sig = swiglu_hidden(g, u, io)
+    if norm_weight is None:
+        dh, dweight = _round_io(gy, io), None
+    else:
+        dh, dweight = rmsnorm_backward(gy, h, norm_weight, rstd, io)
+    ds = _round_io((dh * u).astype(np.float32), io)
+    d_up = _round_io((dh * s).astype(np.float32), io)
+    one = np.float32(1.0)
+    t = (one + (g * (one - sig).astype(np.float32)).astype(np.float32)).astype(np.float32)
+    d_gate = _round_io(((ds * sig).astype(np.float32) * t).astype(np.float32), io)
+    return d_gate, d_up, dweight
 
 
 # ----------------------------------------------------------------------------------------------

@@ -92,3 +92,13 @@ def ref_hysteresis_step(dW, W_packed, H_packed, lr, lr_scale, threshold, decay, 
     W, H = padded(W_packed), padded(H_packed)
     lib.ref_hysteresis_v2_cpu(dW, W, H, lr, lr_scale, int(threshold), decay, int(step), N, K, int(bool(ftz)))
     return (W[: W_packed.size].reshape(W_packed.shape).copy(), H[: H_packed.size].reshape(H_packed.shape).copy())
+
+
+def c_sigmoid_fixed(g):
+    """sigmoid(g) in float32 with the fixed polynomial exponential (oracle/int2_oracle.c: exp_fixed)."""
+    g = np.ascontiguousarray(g, dtype=np.float32)
+    out = np.empty_like(g)
+    lib = oracle_lib()
+    lib.oracle_sigmoid_fixed.argtypes = [_f32p, _f32p, C.c_longlong]
+    lib.oracle_sigmoid_fixed(g.reshape(-1), out.reshape(-1), g.size)
+    return out

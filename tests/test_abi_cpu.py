@@ -46,6 +46,9 @@ def test_status_strings_and_host_side_argument_checks():
     assert handle.el_rmsnorm_quantize_rows(None, 9, 8, None, 1e-6, None, None, None, 1, 8, 1e-5, None) == lib.EL_ERR_INVALID_ARG
     assert handle.el_rmsnorm_quantize_rows(None, lib.EL_BF16, 4, None, 1e-6, None, None, None, 1, 8, 1e-5, None) == lib.EL_ERR_INVALID_ARG
     assert handle.el_rmsnorm_backward(None, None, 9, None, None, None, None, None, 0, 1, 8, None) == lib.EL_ERR_INVALID_ARG
+    assert handle.el_swiglu_quantize_rows(None, None, 9, 8, None, 1e-6, None, None, None, 1, 8, 1e-5, None) == lib.EL_ERR_INVALID_ARG
+    assert handle.el_swiglu_quantize_rows(None, None, lib.EL_BF16, 4, None, 1e-6, None, None, None, 1, 8, 1e-5, None) == lib.EL_ERR_INVALID_ARG
+    assert handle.el_swiglu_backward(None, None, None, lib.EL_F16, 8, None, None, None, None, 4, None, None, 0, 1, 8, None) == lib.EL_ERR_INVALID_ARG
     # tuning knobs: range-checked, process-wide
     assert handle.el_set_decode_gemv_max_tokens(9) == lib.EL_ERR_INVALID_ARG
     assert handle.el_set_decode_mma_max_tokens(33) == lib.EL_ERR_INVALID_ARG

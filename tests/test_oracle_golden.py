@@ -214,3 +214,57 @@ def test_package_unfused_rmsnorm_module_agrees_with_restatement(dtype):
         assert np.all(np.abs(a - b) <= unit * np.maximum(np.abs(b), np.abs(b).max() * 1e-3) * 1.01)
     ref_dw = norm.weight.grad.numpy()
     assert np.abs(dwo - ref_dw).max() <= (1e-2 if dtype == "bf16" else 1e-5) * np.abs(ref_dw).max()
+
+
+# ---- SwiGLU gate: the restatement against the reference's feed-forward expression -----------------------------------
+
+@pytest.mark.parametrize("i", range(5))
+def test_swiglu_restatement_matches_reference_expression(i):
+    """tests/golden/swiglu.npz holds what the reference's `SwiGLUFFN.forward` expression and autograd give for
+    gate|up inputs (followed by the INT2 layer's pre-linear norm, except in the last case).  The restatement fixes the
+    exponential and the order of the row sums, so values may differ by one unit of the I/O type on a small fraction of
+    the elements (bf16/fp16; the gate gradient passes through two more roundings: 2 %), fp32 within 1e-5."""
+    g = np.load(os.path.join(GOLDEN, "swiglu.npz"))
+    io, has_norm = str(g[f"io{i}"]), bool(g[f"norm{i}"])
+    gu, gy, eps = g[f"gu{i}"], g[f"gy{i}"], float(g[f"eps{i}"])
+    H = gu.shape[1] // 2
+    gate, up = np.ascontiguousarray(gu[:, :H]), np.ascontiguousarray(gu[:, H:])
+    w = g[f"w{i}"] if has_norm else None
+    unit = {"bf16": 2.0 ** -8, "f16": 2.0 ** -11, "f32": 1e-5}[io]
+
+    def close(a, b, frac=5e-3):
+        floor = 1.0 if io == "f32" else 1e-3        # fp32: error relative to the largest element
+        tol = unit * np.maximum(np.abs(b), np.abs(b).max() * floor) * 1.01
+        assert np.all(np.abs(a - b) <= tol)
+        if io != "f32":
+            assert (a != b).mean() <= frac
+
+    h, _, _ = O.swiglu_hidden(gate, up, io)
+    if has_norm:
+        y, rstd = O.rmsnorm_forward(h, w, eps, io)
+    else:
+        y, rstd = h, None
+    close(y, g[f"y{i}"])
+    q, a, rstd_q = O.swiglu_quantize_rows(gate, up, w, eps, 1e-5, io)
+    assert np.allclose(a, g[f"absmax{i}"], rtol=unit * 1.01, atol=0)
+    dq = np.abs(q.astype(np.int32) - g[f"q{i}"].astype(np.int32))
+    assert dq.max() <= 1 and (dq != 0).mean() <= 5e-3
+    if has_norm:
+        assert np.array_equal(rstd, rstd_q)
+    dg, du, dw = O.swiglu_backward(gy, gate, up, w, rstd, io)
+    close(du, g[f"dgu{i}"][:, H:], 1e-2)
+    close(dg, g[f"dgu{i}"][:, :H], 2e-2)
+    if has_norm:
+        dw_tol = {"bf16": 1e-2, "f16": 2e-3, "f32": 1e-5}[io]
+        assert np.abs(dw - g[f"dw{i}"]).max() <= dw_tol * np.abs(g[f"dw{i}"]).max()
+
+
+def test_sigmoid_fixed_accuracy_and_edges():
+    """The fixed exponential: within 3 float32 ulps of the exact sigmoid over the whole range, exact limits."""
+    x = np.concatenate([np.linspace(-87, 87, 400001), [0.0, -0.0, 104.0, -104.0, 1e30, -1e30, np.inf, -np.inf]]).astype(np.float32)
+    s = O.sigmoid_fixed(x)
+    with np.errstate(over="ignore"):
+        ref = 1.0 / (1.0 + np.exp(-x.astype(np.float64)[:-2]))
+    assert np.all(np.abs(s[:-2] - ref) <= 3 * np.spacing(ref.astype(np.float32)).astype(np.float64) + 1e-45)
+    assert s[-2] == 1.0 and s[-1] == 0.0 and s[400001] == 0.5
+    assert np.isnan(O.sigmoid_fixed(np.array([np.nan], np.float32))[0])
