@@ -698,7 +698,23 @@ def run_hbm_kernels(args):
         ops.hysteresis_step_v2(dW, Wp, Hp, 1e-2, 5.0, 3, 0.001, step[0])
 
     q8, sc = ops.quantize_activation_async(x16, gmax)
+    # SwiGLU gate in front of the 11008 -> 4096 down projection: gate|up as one [M, 2H] matrix
+    Hd = N
+    gu = torch.randn(M, 2 * Hd, generator=gen).to(torch.bfloat16).to(dev)
+    gyh = (torch.randn(M, Hd, generator=gen) * 1e-2).to(torch.bfloat16).to(dev)
+    dgu = torch.empty_like(gu)
+    nw = torch.ones(Hd, device=dev)
+    norm_mod = pkg.bitnet_int2_optimized._ExtraRMSNorm(Hd).to(dev)
+    rstd_h = ops.swiglu_quantize_rows(gu[:, :Hd], gu[:, Hd:], nw)[2]
+
+    def swiglu_unfused():
+        with torch.no_grad():
+            return ops.quantize_rows(norm_mod(torch.nn.functional.silu(gu[:, :Hd]) * gu[:, Hd:]))
+
     cases = {
+        "swiglu_quantize_rows (silu*up + norm + quantise)": (lambda: ops.swiglu_quantize_rows(gu[:, :Hd], gu[:, Hd:], nw), M * Hd * 5.0),
+        "swiglu_backward (norm + gate backward)": (lambda: ops.swiglu_backward(gyh, gu[:, :Hd], gu[:, Hd:], nw, rstd_h, out=dgu), M * Hd * 10.0),
+        "same forward as tensor operations + quantiser (bytes of the fused form)": (swiglu_unfused, M * Hd * 5.0),
         "hysteresis_from_dw": (hyst, N * K * 5.5),
         "ternarize_pack": (lambda: ops.ternarize_pack(W, gamma, out=Wp), N * K * 4.25),
         "unpack_int2": (lambda: ops.unpack_int2(Wp, w8, K), N * K * 1.25),

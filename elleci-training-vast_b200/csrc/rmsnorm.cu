@@ -62,8 +62,17 @@ rmsnorm_quantize_rows_kernel(const T* __restrict__ x, long long ldx, const float
 
     // y = io(io(x*r) * io(w))
     auto normed = [&](const float v[8], const float w[8], float y[8]) {
+        float wr[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) y[i] = Io<T>::round(__fmul_rn(Io<T>::round(__fmul_rn(v[i], r)), Io<T>::round(w[i])));
+        for (int i = 0; i < 8; ++i) {
+            y[i] = __fmul_rn(v[i], r);
+            wr[i] = w[i];
+        }
+        Io<T>::round8(y);
+        Io<T>::round8(wr);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) y[i] = __fmul_rn(y[i], wr[i]);
+        Io<T>::round8(y);
     };
 
     // ---- absmax of the normalised row ----------------------------------------------------------------------------------
@@ -161,22 +170,33 @@ rmsnorm_backward_kernel(const T* __restrict__ g, const T* __restrict__ x, const 
             Io<T>::load8(gr + k, gv);
             Io<T>::load8(xr + k, xv);
             load8_w(weight + k, w);
+            Io<T>::round8(w);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) c += (double)__fmul_rn(Io<T>::round(__fmul_rn(gv[i], Io<T>::round(w[i]))), xv[i]);
+            for (int i = 0; i < 8; ++i) gv[i] = __fmul_rn(gv[i], w[i]);
+            Io<T>::round8(gv);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) c += (double)__fmul_rn(gv[i], xv[i]);
         }
         c = block_sum(c, red_d);
         const float r3 = __fmul_rn(__fmul_rn(r, r), r);
         const float coef = __fdiv_rn(__fmul_rn(r3, (float)c), (float)K);
         for (int k = threadIdx.x * 8; k < K; k += RN_THREADS * 8) {
-            float gv[8], xv[8], w[8], o[8];
+            float gv[8], xv[8], w[8], o[8], gn[8], xn[8];
             Io<T>::load8(gr + k, gv);
             Io<T>::load8(xr + k, xv);
             load8_w(weight + k, w);
+            Io<T>::round8(w);
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                const float gn = Io<T>::round(__fmul_rn(gv[i], Io<T>::round(w[i])));
-                o[i] = __fsub_rn(__fmul_rn(gn, r), __fmul_rn(xv[i], coef));
-                col_sum[k + i] += (double)__fmul_rn(gv[i], Io<T>::round(__fmul_rn(xv[i], r)));
+                gn[i] = __fmul_rn(gv[i], w[i]);
+                xn[i] = __fmul_rn(xv[i], r);
+            }
+            Io<T>::round8(gn);
+            Io<T>::round8(xn);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                o[i] = __fsub_rn(__fmul_rn(gn[i], r), __fmul_rn(xv[i], coef));
+                col_sum[k + i] += (double)__fmul_rn(gv[i], xn[i]);
             }
             Io<T>::store8(dr + k, o);
         }

@@ -25,6 +25,7 @@ template <> struct Io<float> {
         return r;
     }
     static __device__ __forceinline__ float round(float v) { return v; }
+    static __device__ __forceinline__ void round8(float*) {}
     static __device__ __forceinline__ void load8(const float* p, float v[8]) {
         const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
         v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
@@ -50,6 +51,16 @@ template <> struct Io<__nv_bfloat16> {
         return Raw{make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]))};
     }
     static __device__ __forceinline__ float round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+    // Eight values rounded to bfloat16 in place, two per packed conversion (the single-value conversion runs on the
+    // slow conversion unit, the packed one does not).
+    static __device__ __forceinline__ void round8(float v[8]) {
+#pragma unroll
+        for (int i = 0; i < 8; i += 2) {
+            const uint32_t p = pack_bf16x2(v[i], v[i + 1]);
+            v[i] = __uint_as_float(p << 16);
+            v[i + 1] = __uint_as_float(p & 0xFFFF0000u);
+        }
+    }
     static __device__ __forceinline__ void load8(const __nv_bfloat16* p, float v[8]) { unpack(load_raw(p), v); }
     static __device__ __forceinline__ void store8(__nv_bfloat16* p, const float v[8]) {
         *reinterpret_cast<uint4*>(p) = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
@@ -72,6 +83,15 @@ template <> struct Io<__half> {
         return Raw{make_uint4(pack_f16x2(v[0], v[1]), pack_f16x2(v[2], v[3]), pack_f16x2(v[4], v[5]), pack_f16x2(v[6], v[7]))};
     }
     static __device__ __forceinline__ float round(float v) { return __half2float(__float2half_rn(v)); }
+    static __device__ __forceinline__ void round8(float v[8]) {
+#pragma unroll
+        for (int i = 0; i < 8; i += 2) {
+            const uint32_t p = pack_f16x2(v[i], v[i + 1]);
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&p));
+            v[i] = f.x;
+            v[i + 1] = f.y;
+        }
+    }
     static __device__ __forceinline__ void load8(const __half* p, float v[8]) { unpack(load_raw(p), v); }
     static __device__ __forceinline__ void store8(__half* p, const float v[8]) {
         *reinterpret_cast<uint4*>(p) = make_uint4(pack_f16x2(v[0], v[1]), pack_f16x2(v[2], v[3]), pack_f16x2(v[4], v[5]),

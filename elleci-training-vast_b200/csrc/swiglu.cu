@@ -22,13 +22,16 @@ namespace {
 
 using namespace rowio;
 
-// e^t in float32: t clamped to [-104, 89], n = rint(t*log2(e)), r = t - n*ln2 (two-step), degree-7 Taylor polynomial in
-// Horner form with fused multiply-adds, scaled by 2^n in two exact-exponent steps (so that results below the normal
-// range and above the largest float come out as IEEE multiplication rounds them).  About 1 ulp.
+// e^t in float32 for the sigmoid: t clamped to [-87, 88] (beyond it 1 + e^t no longer changes, or the sigmoid is below
+// 1e-38), n = round-half-even(t*log2(e)) taken by adding and subtracting 1.5*2^23 (its low mantissa bits are n as an
+// integer), r = t - n*ln2 in two fused steps, degree-7 Taylor polynomial in Horner form with fused multiply-adds, times
+// 2^n built in the exponent field.  About 1 ulp.  A NaN argument is clamped away (fmaxf returns the other operand); the
+// callers multiply by the argument afterwards, which brings the NaN back.
 __device__ __forceinline__ float exp_fixed(float t) {
-    if (t != t) return t;
-    t = fminf(fmaxf(t, -104.0f), 89.0f);
-    const float n = rintf(__fmul_rn(t, 1.44269504088896341f));
+    t = fminf(fmaxf(t, -87.0f), 88.0f);
+    const float magic = 12582912.0f;
+    const float nm = __fadd_rn(__fmul_rn(t, 1.44269504088896341f), magic);
+    const float n = __fsub_rn(nm, magic);
     float r = __fmaf_rn(n, -0.693145751953125f, t);
     r = __fmaf_rn(n, -1.42860682030941723e-6f, r);
     float p = 1.0f / 5040.0f;
@@ -39,21 +42,26 @@ __device__ __forceinline__ float exp_fixed(float t) {
     p = __fmaf_rn(p, r, 0.5f);
     p = __fmaf_rn(p, r, 1.0f);
     p = __fmaf_rn(p, r, 1.0f);
-    const int ni = (int)n;
-    const int n1 = ni >> 1, n2 = ni - n1;
-    const float s1 = __int_as_float((n1 + 127) << 23), s2 = __int_as_float((n2 + 127) << 23);
-    return __fmul_rn(__fmul_rn(p, s1), s2);
+    const float scale = __int_as_float((__float_as_int(nm) + 127) << 23);       // 2^n, n in [-126, 127]
+    return __fmul_rn(p, scale);
 }
 
 // sigmoid(g) = 1 / (1 + e^-g)
 __device__ __forceinline__ float sigmoid_fixed(float g) { return __frcp_rn(__fadd_rn(1.0f, exp_fixed(-g))); }
 
-// h = io( io(g * sigmoid(g)) * u ): silu rounded to the I/O type, then the product rounded to the I/O type, as the two
-// tensor operations of the reference round them.
+// Eight elements of the gate: sig = sigmoid(g), s = io(g * sig), h = io(s * u) - silu rounded to the I/O type, then the
+// product rounded to the I/O type, as the two tensor operations of the reference round them.
 template <typename T>
-__device__ __forceinline__ float gated(float g, float u) {
-    const float s = Io<T>::round(__fmul_rn(g, sigmoid_fixed(g)));
-    return Io<T>::round(__fmul_rn(s, u));
+__device__ __forceinline__ void gated8(const float g[8], const float u[8], float sig[8], float s[8], float h[8]) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        sig[i] = sigmoid_fixed(g[i]);
+        s[i] = __fmul_rn(g[i], sig[i]);
+    }
+    Io<T>::round8(s);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) h[i] = __fmul_rn(s[i], u[i]);
+    Io<T>::round8(h);
 }
 
 // One CTA per token.  H % 8 == 0, rows 16-byte aligned.  `weight` null: no normalisation (y = h, rstd is not written).
@@ -72,11 +80,10 @@ swiglu_quantize_rows_kernel(const T* __restrict__ gate, const T* __restrict__ up
     const bool has_norm = weight != nullptr;
 
     auto hidden = [&](int k, float h[8]) {
-        float g[8], u[8];
+        float g[8], u[8], sig[8], s[8];
         Io<T>::load8(gr + k, g);
         Io<T>::load8(ur + k, u);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) h[i] = gated<T>(g[i], u[i]);
+        gated8<T>(g, u, sig, s, h);
     };
 
     typename Io<T>::Raw cache[ROW_CACHE];
@@ -115,8 +122,13 @@ swiglu_quantize_rows_kernel(const T* __restrict__ gate, const T* __restrict__ up
         if (has_norm) {
             float w[8];
             Io<float>::load8(weight + k, w);
+            Io<T>::round8(w);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) y[i] = Io<T>::round(__fmul_rn(Io<T>::round(__fmul_rn(h[i], r)), Io<T>::round(w[i])));
+            for (int i = 0; i < 8; ++i) y[i] = __fmul_rn(h[i], r);
+            Io<T>::round8(y);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) y[i] = __fmul_rn(y[i], w[i]);
+            Io<T>::round8(y);
         } else {
 #pragma unroll
             for (int i = 0; i < 8; ++i) y[i] = h[i];
@@ -124,7 +136,9 @@ swiglu_quantize_rows_kernel(const T* __restrict__ gate, const T* __restrict__ up
     };
 
     // ---- absmax of the row that is quantised ---------------------------------------------------------------------------
-    float amax = 0.0f;
+    // Taken on the bit patterns of |y| as integers: the order of the finite values is the same, and an infinity or a NaN
+    // comes out on top, so one comparison at the end tells whether the row needs the checked passes.
+    int amax_bits = 0;
 #pragma unroll
     for (int c = 0; c < ROW_CACHE; ++c) {
         const int k = (threadIdx.x + c * RN_THREADS) * 8;
@@ -134,7 +148,7 @@ swiglu_quantize_rows_kernel(const T* __restrict__ gate, const T* __restrict__ up
             normed(h, k, y);
             cache[c] = Io<T>::pack(y);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(y[i]));
+            for (int i = 0; i < 8; ++i) amax_bits = max(amax_bits, __float_as_int(y[i]) & 0x7fffffff);
         }
     }
     for (int k = k_tail; k < H; k += RN_THREADS * 8) {
@@ -142,11 +156,11 @@ swiglu_quantize_rows_kernel(const T* __restrict__ gate, const T* __restrict__ up
         hidden(k, h);
         normed(h, k, y);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(y[i]));
+        for (int i = 0; i < 8; ++i) amax_bits = max(amax_bits, __float_as_int(y[i]) & 0x7fffffff);
     }
-    amax = block_max_f(amax, red_f);
-    const bool row_finite = amax <= 3.402823466e38f;
-    if (!row_finite) {        // fmaxf dropped NaN and kept infinities: redo the maximum over the finite values only
+    const bool row_finite = !__syncthreads_or(amax_bits >= 0x7f800000);     // same answer in every thread of the CTA
+    float amax = block_max_f(__int_as_float(amax_bits), red_f);              // used only when every thread's value is finite
+    if (!row_finite) {        // the row holds an infinity or a NaN: the maximum over its finite values only
         amax = 0.0f;
         for (int k = threadIdx.x * 8; k < H; k += RN_THREADS * 8) {
             float h[8], y[8];
@@ -167,8 +181,14 @@ swiglu_quantize_rows_kernel(const T* __restrict__ gate, const T* __restrict__ up
     // ---- quantise --------------------------------------------------------------------------------------------------------
     auto quantise_y = [&](const float y[8], int k) {
         int qi[8];
+        if (row_finite) {
+            // |y*s| <= 127: adding 1.5*2^23 rounds to the nearest even integer and leaves it in the low mantissa bits
 #pragma unroll
-        for (int i = 0; i < 8; ++i) qi[i] = q8_sat(__fmul_rn(row_finite ? y[i] : finite_or_nan(y[i]), s));
+            for (int i = 0; i < 8; ++i) qi[i] = __float_as_int(__fadd_rn(__fmul_rn(y[i], s), 12582912.0f));
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) qi[i] = q8_sat(__fmul_rn(finite_or_nan(y[i]), s));
+        }
         *reinterpret_cast<uint2*>(qr + k) = make_uint2(pack4_s8(qi[0], qi[1], qi[2], qi[3]), pack4_s8(qi[4], qi[5], qi[6], qi[7]));
     };
 #pragma unroll
@@ -196,7 +216,9 @@ swiglu_quantize_rows_kernel(const T* __restrict__ gate, const T* __restrict__ up
 //   ds = io(dh*u);  d_up = io(dh*s);  d_gate = io((ds*sig) * (1 + g*(1 - sig)))
 // CTA b takes the tokens b, b + gridDim.x, ...; a thread owns the same columns in every token, so the per-column sums of
 // dweight live in shared memory without any exchange, and the CTA writes its [H] partial sums to partial[b] at the end.
-template <typename T, bool NORM>
+// SIG_CACHE (with the norm only): vectors of 8 sigmoids a thread keeps in registers from the first pass (the row sum c) to
+// the second, so that the exponential is evaluated once per element for rows up to SIG_CACHE*2048 elements.
+template <typename T, bool NORM, int SIG_CACHE>
 __global__ void __launch_bounds__(RN_THREADS)
 swiglu_backward_kernel(const T* __restrict__ gy, const T* __restrict__ gate, const T* __restrict__ up, long long ld,
                        const float* __restrict__ weight, const float* __restrict__ rstd, T* __restrict__ d_gate,
@@ -209,6 +231,7 @@ swiglu_backward_kernel(const T* __restrict__ gy, const T* __restrict__ gate, con
             for (int i = 0; i < 8; ++i) col_sum[k + i] = 0.0;
         }
     }
+    const int k_tail = (threadIdx.x + SIG_CACHE * RN_THREADS) * 8;
     for (int m = blockIdx.x; m < M; m += gridDim.x) {
         const T* yr = gy + (size_t)m * H;
         const T* gr = gate + (size_t)m * ld;
@@ -216,46 +239,99 @@ swiglu_backward_kernel(const T* __restrict__ gy, const T* __restrict__ gate, con
         T* dgr = d_gate + (size_t)m * ld_d;
         T* dur = d_up + (size_t)m * ld_d;
         float r = 1.0f, coef = 0.0f;
-        if (NORM) {
-            r = rstd[m];
-            double c = 0.0;
-            for (int k = threadIdx.x * 8; k < H; k += RN_THREADS * 8) {
-                float yv[8], g[8], u[8], w[8];
-                Io<T>::load8(yr + k, yv);
-                Io<T>::load8(gr + k, g);
-                Io<T>::load8(ur + k, u);
-                Io<float>::load8(weight + k, w);
+        float sig_c[SIG_CACHE > 0 ? SIG_CACHE : 1][8];
+
+        // c += sum over the 8 elements at k of gn * h; hands back the sigmoids
+        auto row_dot = [&](int k, float sig[8]) -> double {
+            float yv[8], g[8], u[8], w[8];
+            Io<T>::load8(yr + k, yv);
+            Io<T>::load8(gr + k, g);
+            Io<T>::load8(ur + k, u);
+            Io<float>::load8(weight + k, w);
+            float sv[8], h[8];
+            gated8<T>(g, u, sig, sv, h);
+            Io<T>::round8(w);
 #pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    c += (double)__fmul_rn(Io<T>::round(__fmul_rn(yv[i], Io<T>::round(w[i]))), gated<T>(g[i], u[i]));
-            }
-            c = block_sum(c, red_d);
-            const float r3 = __fmul_rn(__fmul_rn(r, r), r);
-            coef = __fdiv_rn(__fmul_rn(r3, (float)c), (float)H);
-        }
-        for (int k = threadIdx.x * 8; k < H; k += RN_THREADS * 8) {
+            for (int i = 0; i < 8; ++i) yv[i] = __fmul_rn(yv[i], w[i]);
+            Io<T>::round8(yv);
+            double c = 0.0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) c += (double)__fmul_rn(yv[i], h[i]);
+            return c;
+        };
+        // the gradients of the 8 elements at k, given their sigmoids
+        auto row_grad = [&](int k, const float sig[8]) {
             float yv[8], g[8], u[8], w[8], og[8], ou[8];
             Io<T>::load8(yr + k, yv);
             Io<T>::load8(gr + k, g);
             Io<T>::load8(ur + k, u);
-            if (NORM) Io<float>::load8(weight + k, w);
+            float sv[8], dh[8], ds[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) sv[i] = __fmul_rn(g[i], sig[i]);
+            Io<T>::round8(sv);
+            if (NORM) {
+                float h[8], gn[8], hn[8];
+                Io<float>::load8(weight + k, w);
+                Io<T>::round8(w);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    h[i] = __fmul_rn(sv[i], u[i]);
+                    gn[i] = __fmul_rn(yv[i], w[i]);
+                }
+                Io<T>::round8(h);
+                Io<T>::round8(gn);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    dh[i] = __fsub_rn(__fmul_rn(gn[i], r), __fmul_rn(h[i], coef));
+                    hn[i] = __fmul_rn(h[i], r);
+                }
+                Io<T>::round8(dh);
+                Io<T>::round8(hn);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) col_sum[k + i] += (double)__fmul_rn(yv[i], hn[i]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) dh[i] = yv[i];
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ds[i] = __fmul_rn(dh[i], u[i]);
+            Io<T>::round8(ds);
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                const float sig = sigmoid_fixed(g[i]);
-                const float s = Io<T>::round(__fmul_rn(g[i], sig));
-                float dh = yv[i];
-                if (NORM) {
-                    const float h = Io<T>::round(__fmul_rn(s, u[i]));
-                    const float gn = Io<T>::round(__fmul_rn(yv[i], Io<T>::round(w[i])));
-                    dh = Io<T>::round(__fsub_rn(__fmul_rn(gn, r), __fmul_rn(h, coef)));
-                    col_sum[k + i] += (double)__fmul_rn(yv[i], Io<T>::round(__fmul_rn(h, r)));
-                }
-                const float ds = Io<T>::round(__fmul_rn(dh, u[i]));
-                ou[i] = __fmul_rn(dh, s);
-                og[i] = __fmul_rn(__fmul_rn(ds, sig), __fadd_rn(1.0f, __fmul_rn(g[i], __fsub_rn(1.0f, sig))));
+                ou[i] = __fmul_rn(dh[i], sv[i]);
+                og[i] = __fmul_rn(__fmul_rn(ds[i], sig[i]), __fadd_rn(1.0f, __fmul_rn(g[i], __fsub_rn(1.0f, sig[i]))));
             }
             Io<T>::store8(dgr + k, og);
             Io<T>::store8(dur + k, ou);
+        };
+
+        if (NORM) {
+            r = rstd[m];
+            double c = 0.0;
+#pragma unroll
+            for (int cv = 0; cv < SIG_CACHE; ++cv) {
+                const int k = (threadIdx.x + cv * RN_THREADS) * 8;
+                if (k < H) c += row_dot(k, sig_c[cv]);
+            }
+            for (int k = k_tail; k < H; k += RN_THREADS * 8) {
+                float sig[8];
+                c += row_dot(k, sig);
+            }
+            c = block_sum(c, red_d);
+            const float r3 = __fmul_rn(__fmul_rn(r, r), r);
+            coef = __fdiv_rn(__fmul_rn(r3, (float)c), (float)H);
+#pragma unroll
+            for (int cv = 0; cv < SIG_CACHE; ++cv) {
+                const int k = (threadIdx.x + cv * RN_THREADS) * 8;
+                if (k < H) row_grad(k, sig_c[cv]);
+            }
+        }
+        for (int k = NORM ? k_tail : threadIdx.x * 8; k < H; k += RN_THREADS * 8) {
+            float g[8], sig[8];
+            Io<T>::load8(gr + k, g);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) sig[i] = sigmoid_fixed(g[i]);
+            row_grad(k, sig);
         }
     }
     if (NORM) {
@@ -326,31 +402,41 @@ int launch_swiglu_quantize_rows(const void* gate, const void* up, int dt, long l
     return check_launch();
 }
 
-template <typename T>
-static int launch_swiglu_backward_t(const T* gy, const T* gate, const T* up, long long ld, const float* weight, const float* rstd,
-                                    T* d_gate, T* d_up, long long ld_d, float* dweight, double* partial, int M, int H,
-                                    cudaStream_t st) {
-    if (!weight) {
-        const int grid = backward_grid(M, H, false);
-        swiglu_backward_kernel<T, false><<<grid, RN_THREADS, 0, st>>>(gy, gate, up, ld, nullptr, nullptr, d_gate, d_up, ld_d,
-                                                                      nullptr, M, H);
-        return check_launch();
-    }
+template <typename T, int SIG_CACHE>
+static int launch_swiglu_backward_norm(const T* gy, const T* gate, const T* up, long long ld, const float* weight, const float* rstd,
+                                       T* d_gate, T* d_up, long long ld_d, float* dweight, double* partial, int M, int H,
+                                       cudaStream_t st) {
     const int grid = backward_grid(M, H, true);
     const size_t smem = (size_t)H * sizeof(double);
     static bool attr_set[64] = {};
     int dev = 0;
     EL_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-        EL_CUDA_TRY(cudaFuncSetAttribute(swiglu_backward_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        EL_CUDA_TRY(cudaFuncSetAttribute(swiglu_backward_kernel<T, true, SIG_CACHE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         200 * 1024));
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
-    swiglu_backward_kernel<T, true><<<grid, RN_THREADS, smem, st>>>(gy, gate, up, ld, weight, rstd, d_gate, d_up, ld_d, partial,
-                                                                    M, H);
+    swiglu_backward_kernel<T, true, SIG_CACHE><<<grid, RN_THREADS, smem, st>>>(gy, gate, up, ld, weight, rstd, d_gate, d_up, ld_d,
+                                                                               partial, M, H);
     int rc = check_launch();
     if (rc != EL_OK) return rc;
     swiglu_dweight_kernel<<<(H + 31) / 32, 256, 0, st>>>(partial, grid, dweight, H);
     return check_launch();
+}
+
+template <typename T>
+static int launch_swiglu_backward_t(const T* gy, const T* gate, const T* up, long long ld, const float* weight, const float* rstd,
+                                    T* d_gate, T* d_up, long long ld_d, float* dweight, double* partial, int M, int H,
+                                    cudaStream_t st) {
+    if (!weight) {
+        const int grid = backward_grid(M, H, false);
+        swiglu_backward_kernel<T, false, 0><<<grid, RN_THREADS, 0, st>>>(gy, gate, up, ld, nullptr, nullptr, d_gate, d_up, ld_d,
+                                                                         nullptr, M, H);
+        return check_launch();
+    }
+    // registers per thread that cost no occupancy: rows up to 4096 elements run four CTAs per SM, longer rows two or one
+    if (H <= 4096) return launch_swiglu_backward_norm<T, 2>(gy, gate, up, ld, weight, rstd, d_gate, d_up, ld_d, dweight, partial, M, H, st);
+    return launch_swiglu_backward_norm<T, 6>(gy, gate, up, ld, weight, rstd, d_gate, d_up, ld_d, dweight, partial, M, H, st);
 }
 
 int launch_swiglu_backward(const void* gy, const void* gate, const void* up, int dt, long long ld, const float* weight,

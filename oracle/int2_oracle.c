@@ -180,13 +180,17 @@ ORACLE_API void oracle_gemm_tn_i8(const int8_t* A, const int8_t* B, int32_t* C, 
 /* ---- sigmoid of the SwiGLU gate --------------------------------------------------------------------------
  * The reference's feed-forward block uses torch's silu (model/model.py:107-108): x * sigmoid(x), computed in
  * float32 with the platform's exponential, which is not reproducible across platforms.  The restatement fixes
- * the exponential: t clamped to [-104, 89], n = rint(t*log2(e)), r = t - n*ln2 in two fused steps, degree-7
- * Taylor polynomial in Horner form with fused multiply-adds, scaled by 2^n in two steps; every step one
- * correctly rounded float32 operation (fmaf is exact-then-rounded by definition).  About 1 ulp. */
+ * the exponential: t clamped to [-87, 88], n = round-half-even(t*log2(e)) taken by adding and subtracting
+ * 1.5*2^23, r = t - n*ln2 in two fused steps, degree-7 Taylor polynomial in Horner form with fused
+ * multiply-adds, times 2^n built in the exponent field; every step one correctly rounded float32 operation
+ * (fmaf is exact-then-rounded by definition).  About 1 ulp.  NaN is clamped away by fmaxf. */
 static inline float exp_fixed(float t) {
-    if (t != t) return t;
-    t = fminf(fmaxf(t, -104.0f), 89.0f);
-    const float n = rintf(t * 1.44269504088896341f);
+    t = fminf(fmaxf(t, -87.0f), 88.0f);
+    const float magic = 12582912.0f;
+    volatile float prod = t * 1.44269504088896341f;
+    volatile float nm = prod + magic;
+    const float nmv = nm;
+    const float n = nmv - magic;
     float r = fmaf(n, -0.693145751953125f, t);
     r = fmaf(n, -1.42860682030941723e-6f, r);
     float p = 1.0f / 5040.0f;
@@ -197,13 +201,10 @@ static inline float exp_fixed(float t) {
     p = fmaf(p, r, 0.5f);
     p = fmaf(p, r, 1.0f);
     p = fmaf(p, r, 1.0f);
-    const int ni = (int)n;
-    const int n1 = ni >> 1, n2 = ni - n1;
-    union { uint32_t u; float f; } s1, s2;
-    s1.u = (uint32_t)(n1 + 127) << 23;
-    s2.u = (uint32_t)(n2 + 127) << 23;
-    volatile float a = p * s1.f;      /* two separately rounded products */
-    return a * s2.f;
+    union { uint32_t u; float f; } bits, scale;
+    bits.f = nmv;
+    scale.u = (bits.u + 127u) << 23;
+    return p * scale.f;
 }
 
 /* sig[i] = 1 / (1 + e^-g[i]) in float32. */
