@@ -42,6 +42,7 @@ size_t rmsnorm_backward_workspace_bytes(int K);
 int launch_rmsnorm_backward(const void* g, const void* x, int dt, const float* weight, const float* rstd, void* dx,
                             float* dweight, void* workspace, size_t workspace_bytes, int M, int K, cudaStream_t st);
 size_t swiglu_backward_workspace_bytes(int H);
+int launch_sigmoid_fixed(const float* g, float* sig, long long n, cudaStream_t st);
 int launch_swiglu_quantize_rows(const void* gate, const void* up, int dt, long long ld, const float* weight, float norm_eps,
                                 int8_t* q, float* row_absmax, float* rstd, int M, int H, float quant_eps, cudaStream_t st);
 int launch_swiglu_backward(const void* gy, const void* gate, const void* up, int dt, long long ld, const float* weight,
@@ -252,6 +253,15 @@ int el_swiglu_quantize_rows(const void* gate, const void* up, int dtype, long lo
     if (!gate || !up || !q || !row_absmax || (norm_weight && !rstd)) return EL_ERR_NULL_PTR;
     return launch_swiglu_quantize_rows(gate, up, dtype, ld, norm_weight, norm_eps, q, row_absmax, rstd, M, H, quant_eps,
                                        (cudaStream_t)stream);
+}
+
+int el_sigmoid_fixed(const float* g, float* sig, long long n, el_stream_t stream) {
+    if (n < 0) return EL_ERR_INVALID_ARG;
+    const int rc = require_sm100();
+    if (rc != EL_OK) return rc;
+    if (n == 0) return EL_OK;
+    if (!g || !sig) return EL_ERR_NULL_PTR;
+    return launch_sigmoid_fixed(g, sig, n, (cudaStream_t)stream);
 }
 
 size_t el_swiglu_backward_workspace_bytes(int H) { return swiglu_backward_workspace_bytes(H); }

@@ -22,13 +22,13 @@ namespace {
 
 using namespace rowio;
 
-// e^t in float32 for the sigmoid: t clamped to [-87, 88] (beyond it 1 + e^t no longer changes, or the sigmoid is below
-// 1e-38), n = round-half-even(t*log2(e)) taken by adding and subtracting 1.5*2^23 (its low mantissa bits are n as an
+// e^t in float32 for the sigmoid: t clamped to [-87, 87] (beyond it 1 + e^t no longer changes, or the sigmoid is below
+// 2e-38), n = round-half-even(t*log2(e)) taken by adding and subtracting 1.5*2^23 (its low mantissa bits are n as an
 // integer), r = t - n*ln2 in two fused steps, degree-7 Taylor polynomial in Horner form with fused multiply-adds, times
 // 2^n built in the exponent field.  About 1 ulp.  A NaN argument is clamped away (fmaxf returns the other operand); the
 // callers multiply by the argument afterwards, which brings the NaN back.
 __device__ __forceinline__ float exp_fixed(float t) {
-    t = fminf(fmaxf(t, -87.0f), 88.0f);
+    t = fminf(fmaxf(t, -87.0f), 87.0f);
     const float magic = 12582912.0f;
     const float nm = __fadd_rn(__fmul_rn(t, 1.44269504088896341f), magic);
     const float n = __fsub_rn(nm, magic);
@@ -46,8 +46,18 @@ __device__ __forceinline__ float exp_fixed(float t) {
     return __fmul_rn(p, scale);
 }
 
+// 1/d correctly rounded for a d whose reciprocal is a normal number (here d = 1 + e^t lies in [1, 2^126]): the hardware
+// approximation and one Newton step in two fused multiply-adds - the general-purpose reciprocal is this sequence plus a
+// check and a branch for the arguments that cannot occur here.
+__device__ __forceinline__ float rcp_normal(float d) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(d));
+    const float e = __fmaf_rn(-d, r, 1.0f);
+    return __fmaf_rn(r, e, r);
+}
+
 // sigmoid(g) = 1 / (1 + e^-g)
-__device__ __forceinline__ float sigmoid_fixed(float g) { return __frcp_rn(__fadd_rn(1.0f, exp_fixed(-g))); }
+__device__ __forceinline__ float sigmoid_fixed(float g) { return rcp_normal(__fadd_rn(1.0f, exp_fixed(-g))); }
 
 // Eight elements of the gate: sig = sigmoid(g), s = io(g * sig), h = io(s * u) - silu rounded to the I/O type, then the
 // product rounded to the I/O type, as the two tensor operations of the reference round them.
@@ -379,9 +389,23 @@ int backward_grid(int M, int H, bool norm) {
     return M < grid ? (M < 1 ? 1 : M) : grid;
 }
 
+// sig[i] = sigmoid(g[i]) as the fused kernels compute it (a check of the fixed arithmetic against a CPU restatement).
+__global__ void __launch_bounds__(256) sigmoid_fixed_kernel(const float* __restrict__ g, float* __restrict__ sig, long long n) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        sig[i] = sigmoid_fixed(g[i]);
+}
+
 }  // namespace
 
 size_t swiglu_backward_workspace_bytes(int H) { return rmsnorm_backward_workspace_bytes(H); }
+
+int launch_sigmoid_fixed(const float* g, float* sig, long long n, cudaStream_t st) {
+    if (n == 0) return EL_OK;
+    int sms = 148;
+    device_sm_count(&sms);
+    sigmoid_fixed_kernel<<<sms * 8, 256, 0, st>>>(g, sig, n);
+    return check_launch();
+}
 
 int launch_swiglu_quantize_rows(const void* gate, const void* up, int dt, long long ld, const float* weight, float norm_eps,
                                 int8_t* q, float* row_absmax, float* rstd, int M, int H, float quant_eps, cudaStream_t st) {

@@ -328,6 +328,16 @@ def swiglu_supported(gate: torch.Tensor) -> bool:
     return rmsnorm_supported(gate)
 
 
+def sigmoid_fixed(g: torch.Tensor) -> torch.Tensor:
+    """sigmoid(g) for a float32 CUDA tensor, exactly as the fused SwiGLU kernels compute it."""
+    _cuda(g, "g")
+    _require(g.dtype == torch.float32, "g must be float32")
+    gc = g.contiguous()
+    out = torch.empty_like(gc)
+    call("el_sigmoid_fixed", gc.data_ptr(), out.data_ptr(), gc.numel(), _stream())
+    return out
+
+
 def swiglu_quantize_rows(gate: torch.Tensor, up: torch.Tensor, norm_weight: Optional[torch.Tensor] = None,
                          norm_eps: float = NORM_EPS, quant_eps: float = ACT_EPS):
     """`F.silu(gate) * up` of the reference's feed-forward block (model/model.py:107-108), the pre-linear RMSNorm of the

@@ -166,6 +166,10 @@ EL_API int el_rmsnorm_backward(const void* g, const void* x, int dtype, const fl
 EL_API int el_swiglu_quantize_rows(const void* gate, const void* up, int dtype, long long ld, const float* norm_weight,
                                    float norm_eps, int8_t* q, float* row_absmax, float* rstd, int M, int H,
                                    float quant_eps, el_stream_t stream);
+/* sig[i] = sigmoid(g[i]) in float32 exactly as the two SwiGLU calls compute it (fixed polynomial exponential, correctly
+ * rounded reciprocal): lets a port or a test check the arithmetic element by element.  torch's silu, which the
+ * reference calls (model/model.py:108), uses the platform's exponential instead. */
+EL_API int el_sigmoid_fixed(const float* g, float* sig, long long n, el_stream_t stream);
 /* Backward of the call above for the gradient gy [M,H] (contiguous) with respect to y, following autograd through the
  * reference's tensor operations (quantiser = straight-through estimator):
  *   gn = dtype(gy*dtype(w));  c[m] = sum_k gn*h;  dh = dtype(gn*rstd - h*(rstd^3*c/H));  d_norm_weight[k] = sum_m

@@ -180,12 +180,12 @@ ORACLE_API void oracle_gemm_tn_i8(const int8_t* A, const int8_t* B, int32_t* C, 
 /* ---- sigmoid of the SwiGLU gate --------------------------------------------------------------------------
  * The reference's feed-forward block uses torch's silu (model/model.py:107-108): x * sigmoid(x), computed in
  * float32 with the platform's exponential, which is not reproducible across platforms.  The restatement fixes
- * the exponential: t clamped to [-87, 88], n = round-half-even(t*log2(e)) taken by adding and subtracting
+ * the exponential: t clamped to [-87, 87], n = round-half-even(t*log2(e)) taken by adding and subtracting
  * 1.5*2^23, r = t - n*ln2 in two fused steps, degree-7 Taylor polynomial in Horner form with fused
  * multiply-adds, times 2^n built in the exponent field; every step one correctly rounded float32 operation
  * (fmaf is exact-then-rounded by definition).  About 1 ulp.  NaN is clamped away by fmaxf. */
 static inline float exp_fixed(float t) {
-    t = fminf(fmaxf(t, -87.0f), 88.0f);
+    t = fminf(fmaxf(t, -87.0f), 87.0f);
     const float magic = 12582912.0f;
     volatile float prod = t * 1.44269504088896341f;
     volatile float nm = prod + magic;
