@@ -1,6 +1,6 @@
 """Benchmark of the INT2 linear layer step on B200: forward + dX + dW/hysteresis tokens per second.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload config2|config4]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload config2|config4|config3|hbm|ffn]
 
 One "step" is one pass of the hot path over one batch of synthetic tokens: for every layer of the workload,
 per-token int8 quantisation of the activations, the forward GEMM, per-token quantisation of the output gradient,
@@ -741,13 +741,80 @@ def run_hbm_kernels(args):
     }))
 
 
+def run_ffn(args):
+    """The reference's feed-forward block at the 7B shape through the module API: `w3(silu(w1 x) * w2 x)` with
+    d_model 4096 and hidden size 11008 over INT2 layers (SwiGLUFFNInt2), forward + backward + the three weight updates
+    per step, M = 4096 tokens.  Timed with the gate fused into the down projection's quantiser and with the gate as tensor
+    operations (everything else identical); L2 flushed between steps, inputs resident."""
+    import torch
+    pkg = load_package()
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    peaks, peak_kind = measured_peaks()
+    M, D = 4096, 4096
+    gen = torch.Generator().manual_seed(11)
+    ffn = pkg.SwiGLUFFNInt2(D, threshold=3, hysteresis_order="after_dx").to(dev)
+    Hd = ffn.hidden_dim
+    for layer in (ffn.w1, ffn.w2, ffn.w3):
+        il = layer.int2_layer
+        il.init_from_float((torch.randn(il.out_features, il.in_features, generator=gen) * 0.02).to(dev))
+        counters = torch.randint(-3, 4, (il.out_features, il.in_features), generator=gen, dtype=torch.int16)
+        il.H_packed.copy_(((counters[:, 0::2] & 0xF) | ((counters[:, 1::2] & 0xF) << 4)).to(torch.uint8))
+    ffn.train()
+    pkg.set_all_int2_lr(ffn, 1e-2)
+    x = torch.randn(M, D, generator=gen).to(torch.bfloat16).to(dev).requires_grad_(True)
+    dY = (torch.randn(M, D, generator=gen) * 1e-3).to(torch.bfloat16).to(dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def step():
+        x.grad = None
+        ffn(x).backward(dY)
+
+    def timed(fused):
+        ffn.w3.fuse_swiglu = fused
+        for _ in range(max(args.warmup, 3)):
+            step()
+        total = 0.0
+        for _ in range(args.steps):
+            flush.fill_(1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            step()
+            e1.record()
+            torch.cuda.synchronize()
+            total += e0.elapsed_time(e1)
+        return total / args.steps
+
+    sampler = ClockSampler(dev.index or 0)
+    sampler.start()
+    fused_ms = timed(True)
+    clocks = sampler.stop()
+    unfused_ms = timed(False)
+    pkg.int2_tc_ops.check_device_status(dev)
+    ops_per_step = 3 * 3 * 2.0 * M * D * Hd
+    tops = ops_per_step / (fused_ms * 1e-3) / 1e12
+    peak = 2.0 * peaks["bf16_tflops_sustained"]
+    print(json.dumps({
+        "metric": "SwiGLU feed-forward block (3 INT2 layers) fwd+bwd+hysteresis tokens/s at the 7B shape", "value": M / (fused_ms * 1e-3),
+        "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": fused_ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8 x int2 -> int32, bf16 I/O",
+        "data": "synthetic",
+        "config": {"workload": f"ffn: M={M} tokens, d_model={D}, hidden={Hd}, module API with autograd, L2 flushed between steps",
+                   "threshold": 3, "hysteresis_order": "after_dx"},
+        "gate_as_tensor_operations": {"ms_per_step": unfused_ms, "tokens_per_s": M / (unfused_ms * 1e-3)},
+        "roofline": {"bound": "tensor", "achieved": tops, "peak": peak, "unit": "TOP/s", "frac": tops / peak, "traffic": None,
+                     "peak_source": f"2 x bf16_tflops_sustained ({peak_kind}); whole step including quantisers, gate and autograd"},
+        "clocks": clocks, "gpu_launches": (args.steps + max(args.warmup, 3)) * 26,
+    }))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="config2", choices=sorted(WORKLOADS) + ["config3", "hbm"])
+    ap.add_argument("--workload", default="config2", choices=sorted(WORKLOADS) + ["config3", "hbm", "ffn"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg of the default run")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
     ap.add_argument("--inline-kernel-events", action="store_true",
@@ -759,9 +826,9 @@ def main():
     ap.add_argument("--no-fused-gather", action="store_true",
                     help="N > 1: all-gather the output with NCCL instead of TMA stores from the GEMM epilogue")
     args = ap.parse_args()
-    if args.workload in ("config3", "hbm"):
+    if args.workload in ("config3", "hbm", "ffn"):
         if args.impl == "ours" and int(os.environ.get("RANK", "0")) == 0:
-            run_decode(args) if args.workload == "config3" else run_hbm_kernels(args)
+            {"config3": run_decode, "hbm": run_hbm_kernels, "ffn": run_ffn}[args.workload](args)
         return
     wl = WORKLOADS[args.workload]
     if args.impl == "reference":
