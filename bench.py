@@ -636,6 +636,43 @@ def run_decode(args):
     pkg._lib.lib().el_set_decode_gemv_max_tokens(2)
     pkg._lib.lib().el_set_decode_mma_max_tokens(32)
     ops.set_decode_overlap(False)
+    # The feed-forward block at decode through the module API: six blocks (203 MB of packed weights) rotated in one graph.
+    # Without gradient recording each layer is one small kernel (norm / gate) plus the decode call; with it, the training
+    # kernels (fused norm or gate + quantiser, then the tcgen05 GEMM).
+    ffns = []
+    for i in range(6):
+        f = pkg.SwiGLUFFNInt2(4096).to(dev).eval()
+        for layer in (f.w1, f.w2, f.w3):
+            il = layer.int2_layer
+            il.init_from_float(torch.randn(il.out_features, il.in_features, device=dev) * 0.02)
+        ffns.append(f)
+    module_cases = []
+    for M in (1, 8, 32):
+        xm = torch.randn(M, 4096, device=dev).to(torch.bfloat16)
+        row = {"M": M}
+        for name, ctx in (("inference_us", torch.no_grad), ("training_kernels_us", torch.enable_grad)):
+            with ctx():
+                for f in ffns[:2]:
+                    f(xm)
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    keep = [f(xm) for f in ffns]
+            for _ in range(3):
+                graph.replay()
+            torch.cuda.synchronize()
+            reps = max(args.steps, 10)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            row[name] = e0.elapsed_time(e1) * 1e3 / (reps * len(ffns))
+            del graph, keep
+        module_cases.append(row)
+    ops.check_device_status(dev)
+    del ffns
     head = next(c for c in cases if c["M"] == 1 and c["K"] == 4096 and c["overlap"])
     line = {
         "metric": "decode linear call (quantise + packed-weight GEMV), GB/s of algorithmic bytes", "value": head["GBps"],
@@ -646,7 +683,8 @@ def run_decode(args):
                                "buffers (> L2) in one CUDA graph; value = M=1, 4096->11008, dependent-launch overlap on"},
         "roofline": {"bound": "hbm", "achieved": head["GBps"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": head["GBps"] / peaks["hbm_gbs"], "traffic": None, "peak_source": f"hbm_gbs ({peak_kind})"},
-        "cases": cases, "copy_us_per_call": stream_us, "gpu_launches": 2 * nbuf * max(args.steps, 10),
+        "cases": cases, "copy_us_per_call": stream_us,
+        "ffn_block_4096_11008_module_api": module_cases, "gpu_launches": 2 * nbuf * max(args.steps, 10),
     }
     print(json.dumps(line))
 

@@ -46,6 +46,7 @@ SIGNATURES = {
     "el_swiglu_quantize_rows": [_vp, _vp, _i, C.c_longlong, _vp, _f, _vp, _vp, _vp, _i, _i, _f, _vp],
     "el_swiglu_backward_workspace_bytes": [_i],
     "el_sigmoid_fixed": [_vp, _vp, C.c_longlong, _vp],
+    "el_prelinear_rows": [_vp, _vp, _i, C.c_longlong, _vp, _f, _vp, _i, _i, _vp],
     "el_swiglu_backward": [_vp, _vp, _vp, _i, C.c_longlong, _vp, _vp, _vp, _vp, C.c_longlong, _vp, _vp, C.c_size_t, _i, _i, _vp],
     "el_rmsnorm_backward": [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, C.c_size_t, _i, _i, _vp],
     "el_set_decode_gemv_max_tokens": [_i],

@@ -43,6 +43,8 @@ int launch_rmsnorm_backward(const void* g, const void* x, int dt, const float* w
                             float* dweight, void* workspace, size_t workspace_bytes, int M, int K, cudaStream_t st);
 size_t swiglu_backward_workspace_bytes(int H);
 int launch_sigmoid_fixed(const float* g, float* sig, long long n, cudaStream_t st);
+int launch_prelinear_rows(const void* x, const void* up, int dt, long long ld, const float* weight, float norm_eps, void* y, int M,
+                          int K, cudaStream_t st);
 int launch_swiglu_quantize_rows(const void* gate, const void* up, int dt, long long ld, const float* weight, float norm_eps,
                                 int8_t* q, float* row_absmax, float* rstd, int M, int H, float quant_eps, cudaStream_t st);
 int launch_swiglu_backward(const void* gy, const void* gate, const void* up, int dt, long long ld, const float* weight,
@@ -129,8 +131,10 @@ static int gemm_dispatch(int mode, const int8_t* A, const void* B, int R, int C,
     const int elig = (D > 0) ? gemm_tc_eligible(mode, A, B, R, C, D) : EL_ERR_UNSUPPORTED_SHAPE;
     if (flags == EL_PATH_TC || flags == EL_PATH_TC_SINGLE)
         return elig != EL_OK ? elig : launch_tc(mode, flags == EL_PATH_TC_SINGLE, A, B, R, C, D, epi, status, st);
-    // auto: the tensor-core tiles are 128 rows deep; very small problems go to the CUDA-core kernel
-    if (elig == EL_OK && R >= 32) return launch_tc(mode, R <= 128, A, B, R, C, D, epi, status, st);
+    // auto: the tensor-core tiles are 128 rows deep; very small problems go to the CUDA-core kernel.  A few rows against a
+    // large weight matrix still belong on the tensor-core kernel: the call is then the time to stream the packed weights
+    // once, which the CUDA-core kernel takes twenty times longer for.
+    if (elig == EL_OK && (R >= 32 || (long long)C * D >= (1ll << 18))) return launch_tc(mode, R <= 128, A, B, R, C, D, epi, status, st);
     return launch_gemm_simple(mode, A, B, R, C, D, epi, st);
 }
 
@@ -253,6 +257,16 @@ int el_swiglu_quantize_rows(const void* gate, const void* up, int dtype, long lo
     if (!gate || !up || !q || !row_absmax || (norm_weight && !rstd)) return EL_ERR_NULL_PTR;
     return launch_swiglu_quantize_rows(gate, up, dtype, ld, norm_weight, norm_eps, q, row_absmax, rstd, M, H, quant_eps,
                                        (cudaStream_t)stream);
+}
+
+int el_prelinear_rows(const void* x, const void* up, int dtype, long long ld, const float* norm_weight, float norm_eps, void* y,
+                      int M, int K, el_stream_t stream) {
+    if (M < 0 || K < 0 || !float_dtype(dtype) || ld < K) return EL_ERR_INVALID_ARG;
+    const int rc = require_sm100();
+    if (rc != EL_OK) return rc;
+    if (M == 0) return EL_OK;
+    if (!x || !y) return EL_ERR_NULL_PTR;
+    return launch_prelinear_rows(x, up, dtype, ld, norm_weight, norm_eps, y, M, K, (cudaStream_t)stream);
 }
 
 int el_sigmoid_fixed(const float* g, float* sig, long long n, el_stream_t stream) {

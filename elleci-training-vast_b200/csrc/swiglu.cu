@@ -389,6 +389,61 @@ int backward_grid(int M, int H, bool norm) {
     return M < grid ? (M < 1 ? 1 : M) : grid;
 }
 
+// The layer's input as the fused training kernels form it, written out in the I/O type instead of being quantised: for
+// the small-M decode call, whose kernels quantise their few tokens themselves.  x is the layer input, or the gate when
+// `up` is given (h = io(io(x*sig(x))*up)); with `weight` the row is normalised (y = io(io(h*rstd)*io(w))).  One CTA per
+// token, same order of operations as swiglu_quantize_rows_kernel / rmsnorm_quantize_rows_kernel, so quantising y gives the
+// int8 row those kernels give.
+template <typename T>
+__global__ void __launch_bounds__(RN_THREADS)
+prelinear_rows_kernel(const T* __restrict__ x, const T* __restrict__ up, long long ld, const float* __restrict__ weight,
+                      T* __restrict__ y, int K, float norm_eps) {
+    __shared__ double red_d[RN_THREADS / 32];
+    const int m = blockIdx.x;
+    const T* xr = x + (size_t)m * ld;
+    const T* ur = up ? up + (size_t)m * ld : nullptr;
+    T* yr = y + (size_t)m * K;
+    auto hidden = [&](int k, float h[8]) {
+        Io<T>::load8(xr + k, h);
+        if (ur) {
+            float g[8], u[8], sig[8], s[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) g[i] = h[i];
+            Io<T>::load8(ur + k, u);
+            gated8<T>(g, u, sig, s, h);
+        }
+    };
+    float r = 1.0f;
+    if (weight) {
+        double ss = 0.0;
+        for (int k = threadIdx.x * 8; k < K; k += RN_THREADS * 8) {
+            float h[8];
+            hidden(k, h);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ss += (double)__fmul_rn(h[i], h[i]);
+        }
+        ss = block_sum(ss, red_d);
+        const float ms = __fdiv_rn((float)ss, (float)K);
+        r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(ms, norm_eps)));
+    }
+    for (int k = threadIdx.x * 8; k < K; k += RN_THREADS * 8) {
+        float h[8];
+        hidden(k, h);
+        if (weight) {
+            float w[8];
+            Io<float>::load8(weight + k, w);
+            Io<T>::round8(w);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) h[i] = __fmul_rn(h[i], r);
+            Io<T>::round8(h);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) h[i] = __fmul_rn(h[i], w[i]);
+            Io<T>::round8(h);
+        }
+        Io<T>::store8(yr + k, h);
+    }
+}
+
 // sig[i] = sigmoid(g[i]) as the fused kernels compute it (a check of the fixed arithmetic against a CPU restatement).
 __global__ void __launch_bounds__(256) sigmoid_fixed_kernel(const float* __restrict__ g, float* __restrict__ sig, long long n) {
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
@@ -398,6 +453,30 @@ __global__ void __launch_bounds__(256) sigmoid_fixed_kernel(const float* __restr
 }  // namespace
 
 size_t swiglu_backward_workspace_bytes(int H) { return rmsnorm_backward_workspace_bytes(H); }
+
+int launch_prelinear_rows(const void* x, const void* up, int dt, long long ld, const float* weight, float norm_eps, void* y, int M,
+                          int K, cudaStream_t st) {
+    if (M == 0) return EL_OK;
+    if (K <= 0 || K % 8 != 0) return EL_ERR_UNSUPPORTED_SHAPE;
+    const size_t esz = (dt == EL_F32) ? 4 : 2;
+    if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(up) & 15) || (reinterpret_cast<uintptr_t>(y) & 15) ||
+        ((size_t)ld * esz) % 16 != 0 || (reinterpret_cast<uintptr_t>(weight) & 15))
+        return EL_ERR_ALIGNMENT;
+    switch (dt) {
+        case EL_BF16:
+            prelinear_rows_kernel<__nv_bfloat16><<<M, RN_THREADS, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)up, ld, weight,
+                                                                           (__nv_bfloat16*)y, K, norm_eps);
+            break;
+        case EL_F16:
+            prelinear_rows_kernel<__half><<<M, RN_THREADS, 0, st>>>((const __half*)x, (const __half*)up, ld, weight, (__half*)y, K, norm_eps);
+            break;
+        case EL_F32:
+            prelinear_rows_kernel<float><<<M, RN_THREADS, 0, st>>>((const float*)x, (const float*)up, ld, weight, (float*)y, K, norm_eps);
+            break;
+        default: return EL_ERR_INVALID_ARG;
+    }
+    return check_launch();
+}
 
 int launch_sigmoid_fixed(const float* g, float* sig, long long n, cudaStream_t st) {
     if (n == 0) return EL_OK;

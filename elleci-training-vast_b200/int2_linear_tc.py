@@ -219,18 +219,42 @@ class Int2LinearTC(nn.Module):
             self.init_from_float(w_init)
         if self._gamma_cached is None:
             self._gamma_cached = self.gamma.detach().item()
-        if up is not None:
-            out = Int2LinearTCFunction.apply(x, self.W_packed, self.gamma, self.in_features, self._gamma_cached, self,
-                                             None if pre_norm is None else pre_norm.weight,
-                                             1e-6 if pre_norm is None else pre_norm.eps, up)
-        elif pre_norm is not None:
-            out = Int2LinearTCFunction.apply(x, self.W_packed, self.gamma, self.in_features, self._gamma_cached, self,
-                                             pre_norm.weight, pre_norm.eps)
-        else:
-            out = Int2LinearTCFunction.apply(x, self.W_packed, self.gamma, self.in_features, self._gamma_cached, self)
+        out = self._decode_forward(x, pre_norm, up)
+        if out is None:
+            args = (x, self.W_packed, self.gamma, self.in_features, self._gamma_cached, self)
+            if up is not None:
+                out = Int2LinearTCFunction.apply(*args, None if pre_norm is None else pre_norm.weight,
+                                                 1e-6 if pre_norm is None else pre_norm.eps, up)
+            elif pre_norm is not None:
+                out = Int2LinearTCFunction.apply(*args, pre_norm.weight, pre_norm.eps)
+            else:
+                out = Int2LinearTCFunction.apply(*args)
         if self.bias is not None:
             out = out + self.bias.to(out.dtype)
         return out
+
+    def _decode_forward(self, x: torch.Tensor, pre_norm: Optional[nn.Module], up: Optional[torch.Tensor]):
+        """Inference with a few tokens (no gradient recorded, 1..64 tokens, per-token mode): the layer input is formed by
+        one small kernel when a norm or a gate comes first, and the weight-streaming decode call does the rest - the
+        path of the reference's `generate` (model/model.py:505-623), where its own kernels fall back to a scalar loop
+        (kernels/int2/int2_matmul_int8_tc_v2.cu:452-473).  Same output as the training-time forward, bit for bit.
+        Returns None when the call does not qualify."""
+        K = self.in_features
+        if (torch.is_grad_enabled() or self.quant_mode != "per_token" or not x.is_cuda or x.dtype not in _FLOAT_IO or K % 64 != 0
+                or x.shape[-1] != K):
+            return None
+        M = x.numel() // K
+        if not 1 <= M <= 64:
+            return None
+        if pre_norm is not None and (pre_norm.weight.dtype != torch.float32 or not pre_norm.weight.is_contiguous()):
+            return None
+        if up is not None and (up.dtype != x.dtype or up.shape != x.shape):
+            return None
+        y = x
+        if pre_norm is not None or up is not None:
+            y = int2_tc_ops.prelinear_rows(x, up, None if pre_norm is None else pre_norm.weight,
+                                           1e-6 if pre_norm is None else pre_norm.eps)
+        return int2_tc_ops.linear_decode(y, self.W_packed, self._gamma_cached, x.dtype)
 
     # ---- weight update -----------------------------------------------------------------------------------------
     def _take_dy_cache(self, dY: torch.Tensor):

@@ -338,6 +338,27 @@ def sigmoid_fixed(g: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def prelinear_rows(x: torch.Tensor, up: Optional[torch.Tensor] = None, norm_weight: Optional[torch.Tensor] = None,
+                   norm_eps: float = NORM_EPS) -> torch.Tensor:
+    """The input of an INT2 layer as the fused training kernels form it (`silu(x) * up` when `up` is given, then the
+    pre-linear RMSNorm when `norm_weight` is given), written out in x's dtype: what `linear_decode` is fed at inference."""
+    _cuda(x, "x")
+    if up is not None:
+        _cuda(up, "up")
+        xv, uv, M, K, ld = _gate_up_views(x, up)
+    else:
+        _require(x.dtype in (torch.float16, torch.bfloat16, torch.float32), "x must be float16, bfloat16 or float32")
+        xv, M, K, ld = _rows_view(x)
+        uv = None
+    if norm_weight is not None:
+        _require(norm_weight.dtype == torch.float32 and norm_weight.numel() == K and norm_weight.is_contiguous(),
+                 "norm_weight must be a contiguous float32 [K]")
+    y = torch.empty(*x.shape[:-1], K, dtype=xv.dtype, device=x.device)
+    call("el_prelinear_rows", xv.data_ptr(), _ptr(uv), _DT[xv.dtype], ld, _ptr(norm_weight), float(norm_eps), y.data_ptr(), M, K,
+         _stream())
+    return y
+
+
 def swiglu_quantize_rows(gate: torch.Tensor, up: torch.Tensor, norm_weight: Optional[torch.Tensor] = None,
                          norm_eps: float = NORM_EPS, quant_eps: float = ACT_EPS):
     """`F.silu(gate) * up` of the reference's feed-forward block (model/model.py:107-108), the pre-linear RMSNorm of the

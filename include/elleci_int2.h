@@ -166,6 +166,15 @@ EL_API int el_rmsnorm_backward(const void* g, const void* x, int dtype, const fl
 EL_API int el_swiglu_quantize_rows(const void* gate, const void* up, int dtype, long long ld, const float* norm_weight,
                                    float norm_eps, int8_t* q, float* row_absmax, float* rstd, int M, int H,
                                    float quant_eps, el_stream_t stream);
+/* The input of an INT2 layer as el_rmsnorm_quantize_rows / el_swiglu_quantize_rows form it, written out in `dtype`
+ * (y [M,K], contiguous) instead of being quantised: x is the layer input, or the gate when `up` is not NULL
+ * (h = dtype(dtype(x*sigmoid(x))*up)); with norm_weight not NULL the row is normalised as _ExtraRMSNorm does
+ * (core/bitnet/bitnet_int2_optimized.py:72-86).  Feeding y to el_linear_decode gives, for 1..64 tokens, the output the
+ * training-time forward gives for them bit for bit (the decode kernels quantise their tokens themselves): the
+ * inference path of Elleci.generate (model/model.py:505-623) through normalised layers.  K % 8 == 0, 16-byte aligned
+ * rows. */
+EL_API int el_prelinear_rows(const void* x, const void* up, int dtype, long long ld, const float* norm_weight,
+                             float norm_eps, void* y, int M, int K, el_stream_t stream);
 /* sig[i] = sigmoid(g[i]) in float32 exactly as the two SwiGLU calls compute it (fixed polynomial exponential, correctly
  * rounded reciprocal): lets a port or a test check the arithmetic element by element.  torch's silu, which the
  * reference calls (model/model.py:108), uses the platform's exponential instead. */

@@ -250,6 +250,9 @@ SIMPLE_SHAPES = [(8, 8, 8), (256, 256, 256), (256, 260, 256), (128, 128, 130), (
 # tensor-core constraints: K % 64 == 0 (packed pitch), N % 16 == 0 (dYq / Gq pitch); M is free
 TC_SHAPES = [(128, 256, 128), (128, 256, 256), (256, 512, 384), (100, 304, 192), (1024, 1536, 1536), (160, 272, 1088),
              (37, 64, 64), (300, 1376, 4096), (129, 16, 64), (700, 528, 320),
+             # a handful of rows (the tile is mostly padding): what a small batch with gradients, or more than 64 tokens at
+             # inference, sends here
+             (1, 256, 128), (8, 512, 256), (31, 304, 192),
              # ragged tiles on a deeper reduction; more tiles (81) than CTA pairs, i.e. a partial second wave
              (600, 2000, 2048), (2304, 2304, 2048)]
 

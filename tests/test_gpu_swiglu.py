@@ -132,6 +132,50 @@ def test_sigmoid_fixed_bit_exact_over_the_range(ops):
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("gate,norm", [(True, True), (True, False), (False, True)])
+def test_prelinear_rows_bit_exact(ops, dtype, gate, norm):
+    """The layer input written out for the decode call equals the oracle's normalised (gated) row bit for bit."""
+    M, K = 9, 1536
+    gu, w, _ = _gate_up(M, K, dtype, 5)
+    d = gu.to(DEV)
+    y = ops.prelinear_rows(d[:, :K], d[:, K:] if gate else None, w.to(DEV) if norm else None, 1e-6)
+    io = _IO[dtype]
+    h = O.swiglu_hidden(t2n(gu[:, :K]), t2n(gu[:, K:]), io)[0] if gate else t2n(gu[:, :K])
+    want = O.rmsnorm_forward(h, w.numpy(), 1e-6, io)[0] if norm else h
+    assert y.dtype == dtype and np.array_equal(t2n(y), want)
+
+
+@pytest.mark.parametrize("M", [1, 2, 7, 33, 64, 65])
+@pytest.mark.parametrize("use_norm", [True, False])
+def test_inference_forward_takes_the_decode_kernels_and_matches_training_forward(pkg, ops, monkeypatch, M, use_norm):
+    """Without gradient recording, calls of up to 64 tokens go through the decode kernels (one small kernel forms the
+    normalised / gated input first); the output is the training-time forward's, bit for bit, for a plain layer and for
+    the feed-forward block."""
+    calls = []
+    real = ops.linear_decode
+    monkeypatch.setattr(ops, "linear_decode", lambda *a, **k: (calls.append(a[0].shape), real(*a, **k))[1])
+    gen = torch.Generator().manual_seed(M)
+    layer = pkg.BitLinearInt2(512, 384, use_extra_rmsnorm=use_norm).to(DEV)
+    layer.int2_layer.init_from_float((torch.randn(384, 512, generator=gen) * 0.03).to(DEV))
+    ffn = pkg.SwiGLUFFNInt2(256, use_extra_rmsnorm=use_norm).to(DEV)          # hidden size 768
+    for l, shape in ((ffn.w1, (768, 256)), (ffn.w2, (768, 256)), (ffn.w3, (256, 768))):
+        l.int2_layer.init_from_float((torch.randn(*shape, generator=gen) * 0.05).to(DEV))
+    if use_norm:
+        with torch.no_grad():
+            layer.extra_rmsnorm.weight.copy_(1.0 + 0.2 * torch.randn(512, generator=gen))
+            ffn.w3.extra_rmsnorm.weight.copy_(1.0 + 0.2 * torch.randn(768, generator=gen))
+    x = torch.randn(M, 512, generator=gen).to(torch.bfloat16).to(DEV)
+    xf = torch.randn(M, 256, generator=gen).to(torch.bfloat16).to(DEV)
+    layer.eval(); ffn.eval()
+    y_train, f_train = layer(x), ffn(xf)              # gradient recording on: the GEMM path
+    assert not calls
+    with torch.no_grad():
+        y_inf, f_inf = layer(x), ffn(xf)
+    assert len(calls) == (4 if M <= 64 else 0)
+    assert torch.equal(y_train, y_inf) and torch.equal(f_train, f_inf)
+
+
 def test_swiglu_rejects_what_it_cannot_run(ops, pkg):
     x = torch.zeros(4, 100, dtype=torch.bfloat16, device=DEV)        # H % 8 != 0
     with pytest.raises(pkg.ElleciError) as e:
