@@ -127,3 +127,25 @@ def test_quantisers_at_full_size(ops, M, K):
     Gq = ops.quantize_grad(dY.to(DEV), a, gmax)
     Gqo, go = O.grad_quantize(t2n(dY), ao)
     assert np.float32(gmax.item()) == np.float32(go) and np.array_equal(Gq.cpu().numpy(), Gqo)
+
+
+def test_swiglu_gate_at_full_size(ops):
+    """The fused SwiGLU gate of the 11008 -> 4096 down projection on 4096 tokens; tokens are independent of one another,
+    so the oracle re-computes 256 sampled tokens (every int8 value of theirs).  The backward kernel on 512 of the tokens
+    (the norm weight's gradient is a sum over the tokens given)."""
+    M, H = 4096, 11008
+    g = torch.Generator().manual_seed(31)
+    gu = (torch.randn(M, 2 * H, generator=g) * 1.5).to(torch.bfloat16)
+    w = (1.0 + 0.2 * torch.randn(H, generator=g)).float()
+    d = gu.to(DEV)
+    q, a, rstd = ops.swiglu_quantize_rows(d[:, :H], d[:, H:], w.to(DEV))
+    rows = _rows(M, 256, 2)
+    gate, up = t2n(gu[rows, :H]), t2n(gu[rows, H:])
+    qo, ao, ro = O.swiglu_quantize_rows(gate, up, w.numpy(), 1e-6, 1e-5, "bf16")
+    assert np.array_equal(rstd.cpu().numpy()[rows], ro) and np.array_equal(a.cpu().numpy()[rows], ao)
+    assert np.array_equal(q.cpu().numpy()[rows], qo)
+    Mb = 512
+    gy = (torch.randn(Mb, H, generator=g) * 1e-2).to(torch.bfloat16)
+    dg, du, dw = ops.swiglu_backward(gy.to(DEV), d[:Mb, :H], d[:Mb, H:], w.to(DEV), rstd[:Mb].contiguous())
+    dgo, duo, dwo = O.swiglu_backward(t2n(gy), t2n(gu[:Mb, :H]), t2n(gu[:Mb, H:]), w.numpy(), rstd[:Mb].cpu().numpy(), "bf16")
+    assert np.array_equal(t2n(dg), dgo) and np.array_equal(t2n(du), duo) and np.array_equal(dw.cpu().numpy(), dwo)
