@@ -24,7 +24,8 @@ int gemm_tc_eligible(int mode, const void* A, const void* B, int R, int C, int D
 int launch_gemm_tc(int mode, const int8_t* A, const void* B, int R, int C, int D, const EpiParams& epi, int32_t* status,
                    cudaStream_t st);
 int launch_gemm_tc2(int mode, const int8_t* A, const void* B, int R, int C, int D, const EpiParams& epi, int32_t* status,
-                    cudaStream_t st, void* const* dst, int n_dst, long long ld_total, long long col_offset, int rows_per_dst);
+                    cudaStream_t st, void* const* dst, int n_dst, long long ld_total, long long col_offset, int rows_per_dst,
+                    int first_dst);
 int launch_reduce_scale_gather(const int* parts, int n_parts, void* const* out_all, int n_ranks, long long row_offset,
                                long long rows_total, const EpiParams& epi, int Mr, int C, cudaStream_t st);
 int launch_dw_hysteresis_tc(const int8_t* Gq, const int8_t* Xq, const float* g_absmax, uint8_t* Wp, uint8_t* Hp,
@@ -119,7 +120,7 @@ static inline bool out_dtype_ok(int dt) { return dt == EL_F16 || dt == EL_BF16 |
 // Tensor-core launch: forward and dX run on CTA pairs unless the single-CTA kernel is asked for; dW has one kernel.
 static int launch_tc(int mode, bool single_cta, const int8_t* A, const void* B, int R, int C, int D, const EpiParams& epi,
                      int32_t* status, cudaStream_t st) {
-    if (mode != MODE_DW && !single_cta) return launch_gemm_tc2(mode, A, B, R, C, D, epi, status, st, nullptr, 0, 0, 0, 0);
+    if (mode != MODE_DW && !single_cta) return launch_gemm_tc2(mode, A, B, R, C, D, epi, status, st, nullptr, 0, 0, 0, 0, 0);
     return launch_gemm_tc(mode, A, B, R, C, D, epi, status, st);
 }
 
@@ -310,7 +311,7 @@ int el_gemm_fwd_gather(const int8_t* Xq, const uint8_t* W_packed, void* const* Y
     if (!Y_all || !absmax || !Xq || !W_packed) return EL_ERR_NULL_PTR;
     const EpiParams epi{nullptr, ld_total, out_dtype, absmax, absmax_stride, gamma};
     return launch_gemm_tc2(MODE_FWD, Xq, W_packed, M, N, K, epi, dev_status, (cudaStream_t)stream, Y_all, n_ranks, ld_total,
-                           col_offset, 0);
+                           col_offset, 0, 0);
 }
 
 int el_gemm_dx_scatter(const int8_t* dYq, const uint8_t* W_packed, void* const* parts_all, int n_ranks, int rank, int M, int N,
@@ -328,7 +329,7 @@ int el_gemm_dx_scatter(const int8_t* dYq, const uint8_t* W_packed, void* const* 
     const float one = 1.0f;
     (void)one;
     const EpiParams epi{nullptr, (long long)K, EL_I32, nullptr, 0, 1.0f};
-    return launch_gemm_tc2(MODE_DX, dYq, W_packed, M, K, N, epi, dev_status, (cudaStream_t)stream, dst, n_ranks, 0, 0, Mr);
+    return launch_gemm_tc2(MODE_DX, dYq, W_packed, M, K, N, epi, dev_status, (cudaStream_t)stream, dst, n_ranks, 0, 0, Mr, rank);
 }
 
 int el_reduce_scale_gather(const int32_t* parts, void* const* dX_all, int n_ranks, int rank, int out_dtype, const float* absmax,

@@ -55,6 +55,7 @@ struct Params {
     int tma_store;                      // the output takes TMA stores (16-byte aligned base and pitch)
     int n_dst;                          // destinations that receive every output block (1 unless gathered over ranks)
     int rows_per_dst;                   // > 0: scatter instead - rows [d*rows_per_dst, (d+1)*rows_per_dst) go to destination d only
+    int row_rotate;                     // scatter: row tiles are taken starting from this one (see tile_coords)
     int32_t* status;
 };
 
@@ -69,6 +70,10 @@ __device__ __forceinline__ void tile_coords(int t, const Params& p, int& tr, int
     const int rows_here = min(p.group_rows, p.tiles_r - first);
     tc = in / rows_here;
     tr = first + (in - tc * rows_here);
+    // Scatter over ranks: every rank walks the row tiles in the same cyclic order but starts at its own rows, so that at any
+    // time the ranks store into different owners (one sender per receiving link) instead of all into the same one.
+    tr += p.row_rotate;
+    if (tr >= p.tiles_r) tr -= p.tiles_r;
 }
 
 template <int MODE>
@@ -436,7 +441,7 @@ int gemm_tc_eligible(int mode, const void* A, const void* B, int R, int C, int D
 // rows [d*rows_per_dst, (d+1)*rows_per_dst) of the result (the reduce-scatter half of a cross-rank reduction of dX).
 int launch_gemm_tc2(int mode, const int8_t* A, const void* B, int R, int C, int D, const EpiParams& epi, int32_t* status,
                     cudaStream_t st, void* const* dst, int n_dst, long long ld_total, long long col_offset,
-                    int rows_per_dst) {
+                    int rows_per_dst, int first_dst) {
     if (mode != MODE_FWD && mode != MODE_DX) return EL_ERR_INVALID_ARG;
     int rc = gemm_tc_eligible(mode, A, B, R, C, D);
     if (rc != EL_OK) return rc;
@@ -457,6 +462,9 @@ int launch_gemm_tc2(int mode, const int8_t* A, const void* B, int R, int C, int 
         }
         p.n_dst = n_dst;
         p.rows_per_dst = rows_per_dst;
+        if (first_dst < 0 || first_dst >= n_dst) return EL_ERR_INVALID_ARG;
+        const int row_tiles = (R + 2 * tc2::BM - 1) / (2 * tc2::BM);
+        p.row_rotate = (int)(((long long)first_dst * rows_per_dst / (2 * tc2::BM)) % row_tiles);
         p.tma_store = 1;
         p.vec_ok = 1;
     } else if (dst != nullptr) {

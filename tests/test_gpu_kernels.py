@@ -478,3 +478,28 @@ def test_linear_decode_rejects_what_it_cannot_run(ops, pkg):
     with pytest.raises(pkg.ElleciError) as e:
         ops.linear_decode(torch.zeros(4, 100, dtype=torch.bfloat16, device=DEV), Wp, 1.0)        # K % 64 != 0
     assert e.value.status == pkg._lib.EL_ERR_UNSUPPORTED_SHAPE
+
+
+# ---- N-sharded dX: scatter of the partial sums, the ranks emulated one after the other on one GPU ------------------
+
+@pytest.mark.parametrize("g,M,K,N", [(2, 512, 256, 512), (4, 2048, 512, 1024), (8, 4096, 256, 2048), (8, 256, 128, 512)])
+def test_dx_scatter_of_all_ranks_adds_up_to_the_unsharded_sums(ops, g, M, K, N):
+    """Every rank's shard of the dX GEMM stores its int32 partial sums into slot `rank` of the owners' staging buffers
+    (each rank walks the row tiles from its own rows on); launched rank after rank on one device with local buffers,
+    the slots must add up to the unsharded integer sums, row block by row block."""
+    rng = np.random.default_rng(g * 1000 + M)
+    dYq = rng.integers(-128, 128, (M, N)).astype(np.int8)
+    Wp, _ = random_packed(N, K, 9)
+    Mr, Ns = M // g, N // g
+    parts = [torch.full((g, Mr, K), -7, dtype=torch.int32, device=DEV) for _ in range(g)]       # owner d: [source rank, rows, K]
+    ptrs = [p.data_ptr() for p in parts]
+    for r in range(g):
+        shard = _cuda(np.ascontiguousarray(dYq[:, r * Ns:(r + 1) * Ns]))
+        ops.backward_input_scatter(shard, _cuda(Wp[r * Ns:(r + 1) * Ns]), K, ptrs, r)
+    ops.check_device_status(torch.device(DEV))
+    want = O.gemm_dx_acc(dYq, Wp, K)
+    for d in range(g):
+        for r in range(g):
+            part = O.gemm_dx_acc(np.ascontiguousarray(dYq[d * Mr:(d + 1) * Mr, r * Ns:(r + 1) * Ns]), Wp[r * Ns:(r + 1) * Ns], K)
+            assert np.array_equal(parts[d][r].cpu().numpy(), part), (d, r)
+        assert np.array_equal(parts[d].sum(0).cpu().numpy(), want[d * Mr:(d + 1) * Mr])
