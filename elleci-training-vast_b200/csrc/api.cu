@@ -326,8 +326,6 @@ int el_gemm_dx_scatter(const int8_t* dYq, const uint8_t* W_packed, void* const* 
         if (!parts_all[d]) return EL_ERR_NULL_PTR;
         dst[d] = static_cast<char*>(parts_all[d]) + (size_t)rank * Mr * K * sizeof(int);     // slot `rank` of owner d
     }
-    const float one = 1.0f;
-    (void)one;
     const EpiParams epi{nullptr, (long long)K, EL_I32, nullptr, 0, 1.0f};
     return launch_gemm_tc2(MODE_DX, dYq, W_packed, M, K, N, epi, dev_status, (cudaStream_t)stream, dst, n_ranks, 0, 0, Mr, rank);
 }
