@@ -226,8 +226,9 @@ EL_API int el_gemm_dx(const int8_t* dYq, const uint8_t* W_packed, void* dX, int 
  * into slot `rank` of parts_all[d], rank d's staging buffer of shape [n_ranks, M/n_ranks, K] int32 (own buffer or a
  * peer mapping; TMA stores over NVLink).  After a barrier, rank d owns all partial sums of its rows:
  * el_reduce_scale_gather adds them (exact), scales by (absmax[m]/127)*gamma and writes the rows into every rank's
- * dX [M,K] (dX_all[r]), which completes the all-reduce.  Needs M % (32*n_ranks) == 0, N % 16 == 0, K % 64 == 0.
- * No counterpart in the reference (single-GPU). */
+ * dX [M,K] (dX_all[r]), which completes the all-reduce.  Rank r produces the token rows in cyclic order starting with
+ * its own, so that at any time the ranks store into different owners (one sender per receiving link).
+ * Needs M % (32*n_ranks) == 0, N % 16 == 0, K % 64 == 0.  No counterpart in the reference (single-GPU). */
 EL_API int el_gemm_dx_scatter(const int8_t* dYq, const uint8_t* W_packed, void* const* parts_all, int n_ranks, int rank,
                               int M, int N, int K, int32_t* dev_status, el_stream_t stream);
 EL_API int el_reduce_scale_gather(const int32_t* parts, void* const* dX_all, int n_ranks, int rank, int out_dtype,
