@@ -53,6 +53,9 @@ SIGNATURES = {
     "el_set_decode_overlap": [_i],
     "el_peer_barrier": [_vp, _i, _i, _u32, _vp, _vp],
     "el_set_decode_mma_max_tokens": [_i],
+    "el_set_peer_barrier_limit_us": [_ll],
+    "el_peer_put": [_vp, _vp, _i, C.c_size_t, C.c_size_t, _i, _vp],
+    "el_quantize_grad_scatter": [_vp, _i, _ll, _vp, _vp, _i, _vp, _vp, _i, _ll, _i, _i, _vp],
     "el_linear_decode": [_vp, _i, _vp, _vp, _i, _f, _vp, _vp, _vp, C.c_size_t, _i, _i, _i, _vp, _vp],
     "el_linear_decode_static": [_vp, _i, _vp, _vp, _i, _f, _i, _i, _i, _vp, _vp],
     "el_hysteresis_from_dw": [_vp, _vp, _vp, _f, _f, _i, _f, _i, _i, _i, _u32, _i, _vp],

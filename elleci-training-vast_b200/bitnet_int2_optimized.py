@@ -104,30 +104,34 @@ class BitLinearInt2(nn.Module):
         scale = max(w_init.abs().mean().item(), 1e-5)
         self.int2_layer.init_from_float(w_init.to(self.int2_layer.W_packed.device), scale=scale)
 
+    @staticmethod
+    def _source_weights(src: nn.Module, device: torch.device):
+        """(latent float32 weight [N,K] on `device`, ternarisation scale) of the module being converted.  A module with a
+        `master_weight` supplies it, and its `scale` tensor's mean when it has one (absmean of the weight otherwise); a
+        module without latent weights is re-initialised (Kaiming-normal, scale 1/sqrt(K)), as the reference's converter
+        does (core/bitnet/bitnet_int2_optimized.py:245-310).  The scale is floored at 1e-5."""
+        N, K = src.out_features, src.in_features
+        latent = getattr(src, "master_weight", None)
+        if latent is None:
+            weight = nn.init.kaiming_normal_(torch.empty(N, K, dtype=torch.float32, device=device), mode="fan_in",
+                                             nonlinearity="linear")
+            return weight, max(K ** -0.5, 1e-5)
+        weight = latent.detach().to(device=device, dtype=torch.float32)
+        stored = getattr(src, "scale", None)
+        scale = float(stored.detach().float().mean()) if stored is not None else float(weight.abs().mean())
+        return weight, max(scale, 1e-5)
+
     @classmethod
     def from_bitnetlinear(cls, bitlinear: nn.Module, use_24_sparsity: bool = False, **kwargs) -> "BitLinearInt2":
-        """Converts a BitNetLinear-style module (`master_weight`, optional `scale`) (bitnet_int2_optimized.py:245-310)."""
-        import math
+        """An INT2 layer on the GPU holding the ternarised weights (and the bias) of a BitNetLinear-style module."""
         device = torch.device("cuda")
-        new_layer = cls(in_features=bitlinear.in_features, out_features=bitlinear.out_features,
-                        bias=bitlinear.bias is not None, use_24_sparsity=use_24_sparsity, **kwargs).to(device)
+        has_bias = bitlinear.bias is not None
+        layer = cls(bitlinear.in_features, bitlinear.out_features, bias=has_bias, use_24_sparsity=use_24_sparsity, **kwargs).to(device)
         with torch.no_grad():
-            weight, scale = None, None
-            if getattr(bitlinear, "master_weight", None) is not None:
-                weight = bitlinear.master_weight.float().to(device)
-                if getattr(bitlinear, "scale", None) is not None:
-                    scale = bitlinear.scale.data.float().mean().item()
-            if weight is None:
-                weight = torch.empty(bitlinear.out_features, bitlinear.in_features, dtype=torch.float32, device=device)
-                nn.init.kaiming_normal_(weight, mode="fan_in", nonlinearity="linear")
-                scale = 1.0 / math.sqrt(bitlinear.in_features)
-            if scale is None:
-                scale = weight.abs().mean().item()
-            scale = max(scale, 1e-5)
-            new_layer.int2_layer.init_from_float(weight, scale=scale)
-            if bitlinear.bias is not None and new_layer.int2_layer.bias is not None:
-                new_layer.int2_layer.bias.data.copy_(bitlinear.bias.data.to(device))
-        return new_layer
+            layer.int2_layer.init_from_float(*cls._source_weights(bitlinear, device))
+            if has_bias and layer.int2_layer.bias is not None:
+                layer.int2_layer.bias.copy_(bitlinear.bias.detach().to(device))
+        return layer
 
     def memory_footprint(self):
         return self.int2_layer.memory_footprint()

@@ -53,6 +53,12 @@ int launch_swiglu_backward(const void* gy, const void* gate, const void* up, int
                            size_t workspace_bytes, int M, int H, cudaStream_t st);
 int launch_peer_barrier(unsigned int* const* flags_all, int n_ranks, int rank, unsigned int epoch, int32_t* status,
                         cudaStream_t st);
+int set_peer_barrier_limit_us(long long us);
+int launch_quantize_grad_scatter(const void* dY, int dt, long long ld, const float* xa, const float* g_slots, int n_slots,
+                                 float* g_out, void* const* Gq_all, int n_ranks, long long row_offset, int M, int N,
+                                 cudaStream_t st);
+int launch_peer_put(const void* src, void* const* dst_all, int n_dst, size_t dst_offset, size_t bytes, int max_ctas,
+                    cudaStream_t st);
 int launch_gemv_mma(const void* x, int x_dtype, const uint8_t* Wp, const EpiParams& epi, int M, int N, int K, cudaStream_t st,
                     bool overlap);
 bool gemv_mma_fits(int M, int K);
@@ -71,8 +77,7 @@ int check_launch() {
     return e == cudaSuccess ? EL_OK : record_cuda_error(e);
 }
 
-static int g_sm_count[64];
-static int g_cc_major[64];
+static std::atomic<int> g_dev_info[64];      // (compute capability major << 16) | SM count; 0 = not yet queried
 
 static int device_info(int* sms, int* major) {
     int dev = 0;
@@ -85,27 +90,30 @@ static int device_info(int* sms, int* major) {
         if (major) *major = b;
         return EL_OK;
     }
-    if (g_sm_count[dev] == 0) {   // benign race: every thread would store the same values
+    int info = g_dev_info[dev].load(std::memory_order_acquire);
+    if (info == 0) {   // threads that race here query and store the same word
         int a = 0, b = 0;
         EL_CUDA_TRY(cudaDeviceGetAttribute(&a, cudaDevAttrMultiProcessorCount, dev));
         EL_CUDA_TRY(cudaDeviceGetAttribute(&b, cudaDevAttrComputeCapabilityMajor, dev));
-        g_cc_major[dev] = b;
-        g_sm_count[dev] = a;
+        info = (b << 16) | (a & 0xFFFF);
+        g_dev_info[dev].store(info, std::memory_order_release);
     }
-    if (sms) *sms = g_sm_count[dev];
-    if (major) *major = g_cc_major[dev];
+    if (sms) *sms = info & 0xFFFF;
+    if (major) *major = info >> 16;
     return EL_OK;
 }
 
 int device_sm_count(int* out) { return device_info(out, nullptr); }
 
 // Token count up to which the decode call uses the CUDA-core GEMV (el_set_decode_gemv_max_tokens).
-static int g_gemv_max_tokens = 2;
-int decode_gemv_max_tokens() { return g_gemv_max_tokens; }
-static int g_mma_max_tokens = 32;
-int decode_mma_max_tokens() { return g_mma_max_tokens; }
-static int g_decode_overlap = 0;
-bool decode_overlap() { return g_decode_overlap != 0; }
+// The tuning knobs are process-wide atomics: a call reads each one once, so a setter that runs on another host thread
+// takes effect from some later call on, never halfway through one.
+static std::atomic<int> g_gemv_max_tokens{2};
+int decode_gemv_max_tokens() { return g_gemv_max_tokens.load(std::memory_order_relaxed); }
+static std::atomic<int> g_mma_max_tokens{32};
+int decode_mma_max_tokens() { return g_mma_max_tokens.load(std::memory_order_relaxed); }
+static std::atomic<int> g_decode_overlap{0};
+bool decode_overlap() { return g_decode_overlap.load(std::memory_order_relaxed) != 0; }
 
 int require_sm100() {
     int major = 0;
@@ -358,6 +366,23 @@ int el_peer_barrier(uint32_t* const* flags_all, int n_ranks, int rank, uint32_t 
                                (cudaStream_t)stream);
 }
 
+int el_quantize_grad_scatter(const void* dY, int dy_dtype, long long ld_dy, const float* x_absmax, const float* g_slots,
+                             int n_slots, float* g_absmax_out, void* const* Gq_all, int n_ranks, long long row_offset, int M,
+                             int N, el_stream_t stream) {
+    if (M < 0 || N < 0 || ld_dy < N || row_offset < 0 || !float_dtype(dy_dtype)) return EL_ERR_INVALID_ARG;
+    if (!Gq_all || !g_slots || (M > 0 && N > 0 && (!dY || !x_absmax))) return EL_ERR_NULL_PTR;
+    return launch_quantize_grad_scatter(dY, dy_dtype, ld_dy, x_absmax, g_slots, n_slots, g_absmax_out, Gq_all, n_ranks,
+                                        row_offset, M, N, (cudaStream_t)stream);
+}
+
+int el_peer_put(const void* src, void* const* dst, int n_dst, size_t dst_offset, size_t bytes, int max_ctas, el_stream_t stream) {
+    if (bytes > 0 && n_dst > 0 && (!src || !dst)) return EL_ERR_NULL_PTR;
+    if (max_ctas < 0) return EL_ERR_INVALID_ARG;
+    return launch_peer_put(src, dst, n_dst, dst_offset, bytes, max_ctas, (cudaStream_t)stream);
+}
+
+int el_set_peer_barrier_limit_us(long long microseconds) { return set_peer_barrier_limit_us(microseconds); }
+
 int el_gemm_dw(const int8_t* Gq, const int8_t* Xq, void* dW, int out_dtype, const float* g_absmax, int M, int N, int K,
                int flags, int32_t* dev_status, el_stream_t stream) {
     if (M < 0 || N < 0 || K < 0 || (out_dtype != EL_F32 && out_dtype != EL_I32)) return EL_ERR_INVALID_ARG;
@@ -391,18 +416,18 @@ int el_dw_hysteresis(const int8_t* Gq, const int8_t* Xq, const float* g_absmax, 
 
 int el_set_decode_gemv_max_tokens(int max_tokens) {
     if (max_tokens < 0 || max_tokens > 8) return EL_ERR_INVALID_ARG;
-    g_gemv_max_tokens = max_tokens;
+    g_gemv_max_tokens.store(max_tokens, std::memory_order_relaxed);
     return EL_OK;
 }
 
 int el_set_decode_mma_max_tokens(int max_tokens) {
     if (max_tokens < 0 || max_tokens > 32) return EL_ERR_INVALID_ARG;
-    g_mma_max_tokens = max_tokens;
+    g_mma_max_tokens.store(max_tokens, std::memory_order_relaxed);
     return EL_OK;
 }
 
 int el_set_decode_overlap(int enable) {
-    g_decode_overlap = enable ? 1 : 0;
+    g_decode_overlap.store(enable ? 1 : 0, std::memory_order_relaxed);
     return EL_OK;
 }
 

@@ -6,6 +6,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "../../include/elleci_int2.h"
 
 namespace el {
@@ -15,6 +17,17 @@ int record_cuda_error(cudaError_t e);   // stores e for el_last_cuda_error(), re
 int check_launch();                      // cudaGetLastError() -> EL_OK / EL_ERR_CUDA
 int device_sm_count(int* out);           // SM count of the current device (cached per device)
 int require_sm100();                     // EL_OK when the current device is compute capability 10.x
+
+// "Set up once per device" bookkeeping that host threads may race on.  The set-up calls guarded by it are idempotent
+// (a function attribute, a queried constant), so two threads that both find the flag clear simply both run them; the
+// flag itself is an atomic, published after the set-up returned.
+struct DeviceOnce {
+    std::atomic<int> done[64];
+    bool is_done(int dev) const { return dev >= 0 && dev < 64 && done[dev].load(std::memory_order_acquire) != 0; }
+    void mark(int dev) {
+        if (dev >= 0 && dev < 64) done[dev].store(1, std::memory_order_release);
+    }
+};
 
 #define EL_CUDA_TRY(call)                                          \
     do {                                                           \

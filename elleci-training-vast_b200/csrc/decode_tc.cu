@@ -267,12 +267,12 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
 template <int NU>
 static int launch_t(const CUtensorMap& tmW, const CUtensorMap& tmX, const Params& p, cudaStream_t st) {
     constexpr int smem = Cfg<NU>::SMEM_BYTES;
-    static bool attr_set[64] = {};
+    static DeviceOnce attr_once;
     int dev = 0;
     EL_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+    if (!attr_once.is_done(dev)) {
         EL_CUDA_TRY(cudaFuncSetAttribute(decode_tc_kernel<NU>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+        attr_once.mark(dev);
     }
     int sms = 0;
     const int rc = device_sm_count(&sms);
@@ -342,20 +342,21 @@ constexpr size_t STATIC_TOTAL_BYTES = STATIC_ABSMAX_OFFSET + 256;          // ab
 // cudaGetSymbolAddress; it is not a device address and must never be passed to a kernel as one.
 static __device__ __align__(256) unsigned char g_decode_scratch[STATIC_TOTAL_BYTES];
 
-static void* g_decode_scratch_ptr[64];    // device address of the array, per device ordinal (filled at set-up)
+static std::atomic<void*> g_decode_scratch_ptr[64];    // device address of the array, per device ordinal (filled at set-up)
 
-// Set-up for the current device: resolves the array's device address once.  Not an allocation.
+// Set-up for the current device: resolves the array's device address once.  Not an allocation.  Host threads that
+// race through the first call each resolve the same address and store the same value.
 static int decode_static_setup(unsigned char** out) {
     int dev = 0;
     EL_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return EL_ERR_DEVICE;
-    if (g_decode_scratch_ptr[dev] == nullptr) {
-        void* ptr = nullptr;
+    void* ptr = g_decode_scratch_ptr[dev].load(std::memory_order_acquire);
+    if (ptr == nullptr) {
         EL_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_decode_scratch));
         if (ptr == nullptr) return EL_ERR_DEVICE;
-        g_decode_scratch_ptr[dev] = ptr;
+        g_decode_scratch_ptr[dev].store(ptr, std::memory_order_release);
     }
-    *out = static_cast<unsigned char*>(g_decode_scratch_ptr[dev]);
+    *out = static_cast<unsigned char*>(ptr);
     return EL_OK;
 }
 
@@ -381,6 +382,11 @@ extern "C" EL_API int el_linear_decode_static(const void* x, int x_dtype, const 
     if (K == 0 || K % 64 != 0) return EL_ERR_UNSUPPORTED_SHAPE;
     if (!x || !W_packed || !Y) return EL_ERR_NULL_PTR;
     cudaStream_t st = (cudaStream_t)stream;
+    // Set-up comes first, whichever kernel this call ends up on: the first call on a device resolves the array's
+    // address even when it is a one-token warm-up, so no later call has to do it (inside a stream capture, say).
+    unsigned char* base = nullptr;
+    int rc = decode_static_setup(&base);
+    if (rc != EL_OK) return rc;
     if (M <= decode_gemv_max_tokens()) {      // the few-token kernel needs no scratch at all
         const EpiParams gepi{Y, (long long)N, out_dtype, nullptr, 0, gamma};
         return launch_gemv_small(x, x_dtype, W_packed, gepi, M, N, K, st, decode_overlap());
@@ -389,9 +395,6 @@ extern "C" EL_API int el_linear_decode_static(const void* x, int x_dtype, const 
         const EpiParams gepi{Y, (long long)N, out_dtype, nullptr, 0, gamma};
         return launch_gemv_mma(x, x_dtype, W_packed, gepi, M, N, K, st, decode_overlap());
     }
-    unsigned char* base = nullptr;
-    int rc = decode_static_setup(&base);
-    if (rc != EL_OK) return rc;
     int8_t* xq = reinterpret_cast<int8_t*>(base + STATIC_XQ_OFFSET);
     float* absmax = reinterpret_cast<float*>(base + STATIC_ABSMAX_OFFSET);
     // The array keeps whatever the previous call left.  The partial-sum rows and the tile counters this call will use

@@ -314,16 +314,15 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 static EncodeTiledFn get_encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static bool tried = false;
-    if (!tried) {
+    // resolved once; a function-local static is initialised under the language's own lock
+    static const EncodeTiledFn fn = []() -> EncodeTiledFn {
         void* ptr = nullptr;
         cudaDriverEntryPointQueryResult qres;
         if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
             qres == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(ptr);
-        tried = true;
-    }
+            return reinterpret_cast<EncodeTiledFn>(ptr);
+        return nullptr;
+    }();
     return fn;
 }
 
@@ -364,12 +363,12 @@ int make_map_out(CUtensorMap* m, const void* base, uint64_t cols, uint64_t rows,
 template <int MODE, int BN, int EPI>
 static int launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB, Params& p, cudaStream_t st) {
     constexpr int smem = Cfg<BN>::SMEM_BYTES(MODE);
-    static bool attr_set[64] = {};
+    static DeviceOnce attr_once;
     int dev = 0;
     EL_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+    if (!attr_once.is_done(dev)) {
         EL_CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<MODE, BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+        attr_once.mark(dev);
     }
     int sms = 0;
     int rc = device_sm_count(&sms);

@@ -379,8 +379,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 
 template <int MODE>
 static int launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB, const OutMaps& outs, Params& p, cudaStream_t st) {
-    static bool attr_set[64] = {};
-    static int max_pairs[64] = {};
+    static std::atomic<int> max_pairs[64];      // co-resident CTA pairs per device; 0 = not yet queried
     int dev = 0;
     EL_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return EL_ERR_DEVICE;
@@ -395,7 +394,8 @@ static int launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB, const OutMap
     cfg.stream = st;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (!attr_set[dev]) {
+    int dev_pairs = max_pairs[dev].load(std::memory_order_acquire);
+    if (dev_pairs == 0) {       // host threads may race here: both then query and store the same number
         EL_CUDA_TRY(cudaFuncSetAttribute(gemm_tc2_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         int sms = 0;
         const int rc = device_sm_count(&sms);
@@ -404,8 +404,8 @@ static int launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB, const OutMap
         int clusters = 0;
         EL_CUDA_TRY(cudaOccupancyMaxActiveClusters(&clusters, gemm_tc2_kernel<MODE>, &cfg));
         if (clusters < 1) return EL_ERR_DEVICE;
-        max_pairs[dev] = clusters < sms / 2 ? clusters : sms / 2;
-        attr_set[dev] = true;
+        dev_pairs = clusters < sms / 2 ? clusters : sms / 2;
+        max_pairs[dev].store(dev_pairs, std::memory_order_release);
     }
     p.tiles_r = (p.R + 2 * BM - 1) / (2 * BM);
     p.tiles_c = (p.C + BN - 1) / BN;
@@ -418,7 +418,7 @@ static int launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB, const OutMap
     const long long tiles = (long long)p.tiles_r * p.tiles_c;
     if (tiles == 0) return EL_OK;
     if (p.k_blocks == 0) return EL_ERR_UNSUPPORTED_SHAPE;
-    const int pairs = (int)(tiles < max_pairs[dev] ? tiles : max_pairs[dev]);
+    const int pairs = (int)(tiles < dev_pairs ? tiles : dev_pairs);
     cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
     EL_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<MODE>, tmA, tmB, outs, p));
     return check_launch();

@@ -238,12 +238,12 @@ int launch_gemv_mma_t(const T* x, const uint8_t* Wp, const EpiParams& epi, int M
     int sms = 0;
     const int rc = device_sm_count(&sms);
     if (rc != EL_OK) return rc;
-    static bool attr_set[64] = {};
+    static DeviceOnce attr_once;
     int dev = 0;
     EL_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+    if (!attr_once.is_done(dev)) {
         EL_CUDA_TRY(cudaFuncSetAttribute(gemv_mma_kernel<T, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+        attr_once.mark(dev);
     }
     const int row_groups = (N + 15) / 16;
     cudaLaunchConfig_t cfg = {};

@@ -256,12 +256,12 @@ gemv_small_kernel(const T* __restrict__ x, const uint8_t* __restrict__ Wp, EpiPa
 template <typename T, int MT, int RB, int THREADS>
 static int launch_gemv_rb(const T* x, const uint8_t* Wp, const EpiParams& epi, int M, int N, int K, size_t smem, int grid,
                           cudaStream_t st, bool overlap) {
-    static bool attr_set[64] = {};
+    static DeviceOnce attr_once;
     int dev = 0;
     EL_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+    if (!attr_once.is_done(dev)) {
         EL_CUDA_TRY(cudaFuncSetAttribute(gemv_small_kernel<T, MT, RB, THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+        attr_once.mark(dev);
     }
     // overlap: programmatic dependent launch.  The kernel may start while earlier work of the stream still runs; it only
     // loads packed weights until its griddepcontrol.wait, which returns once that earlier work has completed.

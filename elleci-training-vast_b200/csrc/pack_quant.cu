@@ -384,6 +384,70 @@ quantize_grad_kernel(const T* __restrict__ dY, long long ld, const float* __rest
     }
 }
 
+// The same quantisation for a token-sharded layer: this rank holds the gradient rows of its own tokens, and the weight
+// gradient of output features [d*win, (d+1)*win) is formed on rank d.  The row is quantised once and each column window
+// is stored straight into its owner's receive buffer (own memory or a peer mapping: plain stores over NVLink) at row
+// row_offset + m, so the all-to-all of the int8 gradient is this kernel's output.  The per-tensor maximum is the largest
+// of the ranks' partial maxima in g_slots; block 0 also leaves it in g_out for the weight-gradient kernel.
+struct ScatterDst {
+    int8_t* p[8];
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+quantize_grad_scatter_kernel(const T* __restrict__ dY, long long ld, const float* __restrict__ x_absmax,
+                             const float* __restrict__ g_slots, int n_slots, float* __restrict__ g_out, ScatterDst dst,
+                             int win, long long row_offset, int N) {
+    const int m = blockIdx.x;
+    float g = 0.0f;
+    for (int i = 0; i < n_slots; ++i) g = fmaxf(g, g_slots[i]);
+    if (m == 0 && threadIdx.x == 0 && g_out != nullptr) *g_out = g;
+    const float inv = (g >= 1e-30f) ? __fdiv_rn(127.0f, g) : 0.0f;
+    const float sx = __fdiv_rn(x_absmax[m], 127.0f);
+    const T* yr = dY + (size_t)m * ld;
+    for (int k = threadIdx.x * 8; k < N; k += blockDim.x * 8) {
+        float v[8];
+        load8<T>(yr + k, v);
+        int qi[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            qi[i] = max(-127, q8_sat(__fmul_rn(__fmul_rn(finite_or_nan(v[i]), sx), inv)));
+        const int d = k / win, c = k - d * win;                 // win % 8 == 0: the eight values share one window
+        int8_t* out = dst.p[d] + (size_t)(row_offset + m) * win + c;
+        *reinterpret_cast<uint2*>(out) = make_uint2(pack4_s8(qi[0], qi[1], qi[2], qi[3]), pack4_s8(qi[4], qi[5], qi[6], qi[7]));
+    }
+}
+
+// Copy of a local block into the same offset of several buffers (peer mappings): the push half of an all-gather.
+struct PutDst {
+    char* p[8];
+};
+
+__global__ void __launch_bounds__(256)
+peer_put_vec_kernel(const uint4* __restrict__ src, PutDst dst, int n_dst, size_t n_vec) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += 4 * stride) {
+        uint4 v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            if (i + j * stride < n_vec) v[j] = __ldg(src + i + j * stride);
+        for (int d = 0; d < n_dst; ++d) {
+            uint4* out = reinterpret_cast<uint4*>(dst.p[d]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (i + j * stride < n_vec) out[i + j * stride] = v[j];
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256)
+peer_put_word_kernel(const uint32_t* __restrict__ src, PutDst dst, int n_dst, size_t n_words) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_words; i += (size_t)gridDim.x * blockDim.x) {
+        const uint32_t v = src[i];
+        for (int d = 0; d < n_dst; ++d) reinterpret_cast<uint32_t*>(dst.p[d])[i] = v;
+    }
+}
+
 // ---------------------------------------------------------------------------------------------------------
 // launchers
 // ---------------------------------------------------------------------------------------------------------
@@ -513,6 +577,62 @@ int launch_quantize_grad(const void* dY, int dt, long long ld, const float* xa, 
         case EL_F32: return launch_quantize_grad_t((const float*)dY, ld, xa, ga, Gq, M, N, st);
         default: return EL_ERR_INVALID_ARG;
     }
+}
+
+template <typename T>
+static int launch_quantize_grad_scatter_t(const T* dY, long long ld, const float* xa, const float* g_slots, int n_slots,
+                                          float* g_out, const ScatterDst& dst, int win, long long row_offset, int M, int N,
+                                          cudaStream_t st) {
+    quantize_grad_scatter_kernel<T><<<M, 256, 0, st>>>(dY, ld, xa, g_slots, n_slots, g_out, dst, win, row_offset, N);
+    return check_launch();
+}
+
+int launch_quantize_grad_scatter(const void* dY, int dt, long long ld, const float* xa, const float* g_slots, int n_slots,
+                                 float* g_out, void* const* Gq_all, int n_ranks, long long row_offset, int M, int N,
+                                 cudaStream_t st) {
+    if (n_ranks < 1 || n_ranks > 8 || n_slots < 1 || N % n_ranks != 0) return EL_ERR_INVALID_ARG;
+    const int win = N / n_ranks;
+    if (win % 8 != 0 || ld % 8 != 0) return EL_ERR_UNSUPPORTED_SHAPE;
+    if (reinterpret_cast<uintptr_t>(dY) & 15) return EL_ERR_ALIGNMENT;
+    ScatterDst dst{};
+    for (int d = 0; d < n_ranks; ++d) {
+        if (Gq_all[d] == nullptr) return EL_ERR_NULL_PTR;
+        if (reinterpret_cast<uintptr_t>(Gq_all[d]) & 7) return EL_ERR_ALIGNMENT;
+        dst.p[d] = static_cast<int8_t*>(Gq_all[d]);
+    }
+    if (M == 0 || N == 0) return EL_OK;
+    switch (dt) {
+        case EL_F16: return launch_quantize_grad_scatter_t((const __half*)dY, ld, xa, g_slots, n_slots, g_out, dst, win, row_offset, M, N, st);
+        case EL_BF16: return launch_quantize_grad_scatter_t((const __nv_bfloat16*)dY, ld, xa, g_slots, n_slots, g_out, dst, win, row_offset, M, N, st);
+        case EL_F32: return launch_quantize_grad_scatter_t((const float*)dY, ld, xa, g_slots, n_slots, g_out, dst, win, row_offset, M, N, st);
+        default: return EL_ERR_INVALID_ARG;
+    }
+}
+
+int launch_peer_put(const void* src, void* const* dst_all, int n_dst, size_t dst_offset, size_t bytes, int max_ctas,
+                    cudaStream_t st) {
+    if (n_dst < 0 || n_dst > 8) return EL_ERR_INVALID_ARG;
+    if (n_dst == 0 || bytes == 0) return EL_OK;
+    if ((reinterpret_cast<uintptr_t>(src) & 3) || (dst_offset & 3) || (bytes & 3)) return EL_ERR_ALIGNMENT;
+    PutDst dst{};
+    bool vec = ((reinterpret_cast<uintptr_t>(src) | dst_offset | bytes) & 15) == 0;
+    for (int d = 0; d < n_dst; ++d) {
+        if (dst_all[d] == nullptr) return EL_ERR_NULL_PTR;
+        if (reinterpret_cast<uintptr_t>(dst_all[d]) & 3) return EL_ERR_ALIGNMENT;
+        vec = vec && (reinterpret_cast<uintptr_t>(dst_all[d]) & 15) == 0;
+        dst.p[d] = static_cast<char*>(dst_all[d]) + dst_offset;
+    }
+    int sms = 148;
+    device_sm_count(&sms);
+    const int cap = max_ctas > 0 ? max_ctas : 4 * sms;
+    if (vec) {
+        const size_t n = bytes / 16;
+        peer_put_vec_kernel<<<grid_for((long long)((n + 3) / 4), 256, cap), 256, 0, st>>>(static_cast<const uint4*>(src), dst, n_dst, n);
+    } else {
+        const size_t n = bytes / 4;
+        peer_put_word_kernel<<<grid_for((long long)n, 256, cap), 256, 0, st>>>(static_cast<const uint32_t*>(src), dst, n_dst, n);
+    }
+    return check_launch();
 }
 
 // int32 sums -> scaled output, four columns per thread

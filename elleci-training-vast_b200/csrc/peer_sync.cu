@@ -3,8 +3,9 @@
 // Every rank owns an array of n_ranks 32-bit flags in peer-mapped memory.  In barrier number `epoch` (1, 2, ... in the
 // same order on every rank) rank r stores `epoch` into slot r of every rank's array (st.release.sys: its earlier work on
 // the stream, including stores into peer memory, is visible before the flag) and then waits until all slots of its OWN
-// array have reached `epoch`.  The wait only reads this GPU's memory, is bounded (about four seconds of cycles) and
-// reports a rank that never arrives through the caller's status word instead of hanging.
+// array have reached `epoch`.  The wait only reads this GPU's memory, is bounded (about four seconds of cycles unless
+// el_set_peer_barrier_limit_us says otherwise) and reports a rank that never arrives through the caller's status word
+// instead of hanging.
 // The epilogue-store collectives of the sharded layer (el_gemm_fwd_gather, el_gemm_dx_scatter,
 // el_reduce_scale_gather) need exactly this: "all stores into my buffers have landed".  No counterpart in the reference.
 #include "common.cuh"
@@ -15,13 +16,14 @@ namespace {
 
 constexpr int PEER_MAX = 8;
 constexpr long long PEER_WAIT_CYCLES = 1LL << 33;
+std::atomic<long long> g_wait_limit_us{0};       // 0 = the default above
 
 struct PeerFlags {
     unsigned int* p[PEER_MAX];
 };
 
 __global__ void __launch_bounds__(32)
-peer_barrier_kernel(PeerFlags flags, int n_ranks, int rank, unsigned int epoch, int32_t* status) {
+peer_barrier_kernel(PeerFlags flags, int n_ranks, int rank, unsigned int epoch, long long limit_cycles, int32_t* status) {
     const int i = threadIdx.x;
     if (i >= n_ranks) return;
     __threadfence_system();
@@ -32,7 +34,7 @@ peer_barrier_kernel(PeerFlags flags, int n_ranks, int rank, unsigned int epoch, 
         unsigned int v;
         asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
         if ((int)(v - epoch) >= 0) break;            // wrap-safe "v >= epoch"
-        if (clock64() - t0 > PEER_WAIT_CYCLES) {
+        if (clock64() - t0 > limit_cycles) {
             if (status != nullptr) atomicCAS(status, 0, 40 + i);      // rank i did not arrive
             break;
         }
@@ -40,6 +42,12 @@ peer_barrier_kernel(PeerFlags flags, int n_ranks, int rank, unsigned int epoch, 
 }
 
 }  // namespace
+
+int set_peer_barrier_limit_us(long long us) {
+    if (us < 0) return EL_ERR_INVALID_ARG;
+    g_wait_limit_us.store(us, std::memory_order_relaxed);
+    return EL_OK;
+}
 
 int launch_peer_barrier(unsigned int* const* flags_all, int n_ranks, int rank, unsigned int epoch, int32_t* status,
                         cudaStream_t st) {
@@ -50,7 +58,15 @@ int launch_peer_barrier(unsigned int* const* flags_all, int n_ranks, int rank, u
         if (reinterpret_cast<uintptr_t>(flags_all[i]) & 3) return EL_ERR_ALIGNMENT;
         f.p[i] = flags_all[i];
     }
-    peer_barrier_kernel<<<1, 32, 0, st>>>(f, n_ranks, rank, epoch, status);
+    long long limit = PEER_WAIT_CYCLES;
+    const long long us = g_wait_limit_us.load(std::memory_order_relaxed);
+    if (us > 0) {
+        int dev = 0, khz = 0;
+        EL_CUDA_TRY(cudaGetDevice(&dev));
+        EL_CUDA_TRY(cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, dev));     // the SM clock's maximum, kHz
+        limit = us * (long long)(khz > 0 ? khz : 2000000) / 1000;
+    }
+    peer_barrier_kernel<<<1, 32, 0, st>>>(f, n_ranks, rank, epoch, limit, status);
     return check_launch();
 }
 

@@ -275,12 +275,12 @@ static int launch_rmsnorm_backward_t(const T* g, const T* x, const float* weight
                                      double* partial, int M, int K, cudaStream_t st) {
     const int grid = backward_grid(M, K);
     const size_t smem = (size_t)K * sizeof(double);
-    static bool attr_set[64] = {};
+    static DeviceOnce attr_once;
     int dev = 0;
     EL_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+    if (!attr_once.is_done(dev)) {
         EL_CUDA_TRY(cudaFuncSetAttribute(rmsnorm_backward_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+        attr_once.mark(dev);
     }
     rmsnorm_backward_kernel<T><<<grid, RN_THREADS, smem, st>>>(g, x, weight, rstd, dx, partial, M, K);
     int rc = check_launch();

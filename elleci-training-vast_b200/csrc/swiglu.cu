@@ -511,13 +511,13 @@ static int launch_swiglu_backward_norm(const T* gy, const T* gate, const T* up, 
                                        cudaStream_t st) {
     const int grid = backward_grid(M, H, true);
     const size_t smem = (size_t)H * sizeof(double);
-    static bool attr_set[64] = {};
+    static DeviceOnce attr_once;
     int dev = 0;
     EL_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+    if (!attr_once.is_done(dev)) {
         EL_CUDA_TRY(cudaFuncSetAttribute(swiglu_backward_kernel<T, true, SIG_CACHE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          200 * 1024));
-        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+        attr_once.mark(dev);
     }
     swiglu_backward_kernel<T, true, SIG_CACHE><<<grid, RN_THREADS, smem, st>>>(gy, gate, up, ld, weight, rstd, d_gate, d_up, ld_d,
                                                                                partial, M, H);

@@ -54,10 +54,15 @@ def device_status(device: torch.device) -> torch.Tensor:
 
 
 def check_device_status(device: torch.device) -> None:
-    """Synchronises and raises if a tensor-core kernel reported a failed wait."""
+    """Synchronises and raises if a tensor-core kernel reported a failed wait.  A kernel that gave up may have left
+    partial sums in a decode workspace, which every call expects to find zeroed: the cached workspaces of the device are
+    dropped, so the next decode call starts from a fresh zeroed one."""
     code = int(device_status(device).item())
     if code != 0:
         device_status(device).zero_()
+        index = device.index if device.index is not None else torch.cuda.current_device()
+        for key in [k for k in _decode_ws if k[0] == index]:
+            del _decode_ws[key]
         raise ElleciError("tensor-core kernel", code, f"a bounded barrier wait gave up (code {code})")
 
 
@@ -234,15 +239,21 @@ def _rows_view(t: torch.Tensor):
 
 
 def quantize_rows(x: torch.Tensor, eps: float = ACT_EPS, fold_absmax: Optional[torch.Tensor] = None,
-                  raw_absmax: Optional[torch.Tensor] = None):
+                  raw_absmax: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None):
     """Per-token absmax int8 quantisation.  Returns (q int8, absmax float32 [M]) and, when `fold_absmax` [M] is
     given, also max_m(rawmax[m]*fold_absmax[m]/127) as a float32 [1] tensor.  `raw_absmax` [M] supplies row
     maxima found elsewhere (reduced over the ranks of a column-sharded tensor); it is floored at eps in place
-    and returned as the absmax.  A 2-D column window `x[:, a:b]` is read in place."""
+    and returned as the absmax.  A 2-D column window `x[:, a:b]` is read in place.  `out` (contiguous int8, M*K
+    elements: a row block of a larger buffer, say) receives the quantised rows instead of a new tensor."""
     _cuda(x, "x")
     _require(x.dtype in _DT and x.dtype != torch.int32, "x must be float16, bfloat16 or float32")
     xv, M, K, ld = _rows_view(x)
-    q = torch.empty(*x.shape[:-1], K, dtype=torch.int8, device=x.device)
+    if out is None:
+        q = torch.empty(*x.shape[:-1], K, dtype=torch.int8, device=x.device)
+    else:
+        _require(out.is_cuda and out.dtype == torch.int8 and out.is_contiguous() and out.numel() == M * K,
+                 "out must be a contiguous int8 CUDA tensor of M*K elements")
+        q = out
     if raw_absmax is None:
         a = torch.empty(M, dtype=torch.float32, device=x.device)
         mode = _lib.EL_QUANT_FULL
@@ -299,7 +310,7 @@ def rmsnorm_backward(g: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, rst
     _require(weight.dtype == torch.float32 and weight.numel() == K, "weight must be float32 [K]")
     _require(rstd.dtype == torch.float32 and rstd.numel() == M, "rstd must be float32 [M]")
     need = _lib.lib().el_rmsnorm_backward_workspace_bytes(K)
-    key = (x.device.index, K)
+    key = (x.device.index, _stream(), K)       # one scratch buffer per stream: calls on different streams may overlap
     ws = _norm_ws.get(key)
     if ws is None:
         ws = torch.empty(need, dtype=torch.uint8, device=x.device)
@@ -396,7 +407,7 @@ def swiglu_backward(gy: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, norm
         _require(norm_weight.dtype == torch.float32 and norm_weight.numel() == H, "norm_weight must be float32 [H]")
         _require(rstd is not None and rstd.dtype == torch.float32 and rstd.numel() == M, "rstd must be float32 [M]")
         need = _lib.lib().el_swiglu_backward_workspace_bytes(H)
-        key = (gv.device.index, H)
+        key = (gv.device.index, _stream(), H)
         ws = _norm_ws.get(key)
         if ws is None:
             ws = torch.empty(need, dtype=torch.uint8, device=gv.device)
@@ -521,6 +532,32 @@ def quantize_grad(dY: torch.Tensor, x_absmax: torch.Tensor, g_absmax: torch.Tens
     return Gq
 
 
+def quantize_grad_scatter(dY: torch.Tensor, x_absmax: torch.Tensor, g_slots: torch.Tensor, recv_ptrs, row_offset: int,
+                          g_out: Optional[torch.Tensor] = None) -> None:
+    """quantize_grad of this rank's gradient rows whose output is the all-to-all: column window d of every row goes to row
+    `row_offset + m` of rank d's receive buffer [M_total, N/g] (`recv_ptrs`: device addresses, own buffer and peer
+    mappings).  `g_slots` holds the ranks' partial maxima; their maximum is the scale and lands in `g_out` [1]."""
+    _cuda(dY, "dY")
+    yv, M, N, ld = _rows_view(dY)
+    _require(x_absmax.dtype == torch.float32 and x_absmax.numel() == M, "x_absmax must be float32 [M]")
+    _require(g_slots.dtype == torch.float32 and g_slots.is_contiguous(), "g_slots must be a contiguous float32 tensor")
+    keep, arr = _ptr_array(recv_ptrs)
+    call("el_quantize_grad_scatter", yv.data_ptr(), _DT[yv.dtype], ld, x_absmax.data_ptr(), g_slots.data_ptr(), g_slots.numel(),
+         _ptr(g_out), arr, len(recv_ptrs), int(row_offset), M, N, _stream())
+
+
+def peer_put(src: torch.Tensor, dst_ptrs, dst_offset_bytes: int, max_ctas: int = 0) -> None:
+    """Copies the contiguous tensor `src` to byte offset `dst_offset_bytes` of every buffer in `dst_ptrs` (device
+    addresses of peer mappings): one rank's push of an all-gather, as plain stores over NVLink from one kernel."""
+    _cuda(src, "src")
+    _require(src.is_contiguous(), "src must be contiguous")
+    if len(dst_ptrs) == 0 or src.numel() == 0:
+        return
+    keep, arr = _ptr_array(dst_ptrs)
+    call("el_peer_put", src.data_ptr(), arr, len(dst_ptrs), int(dst_offset_bytes), src.numel() * src.element_size(),
+         int(max_ctas), _stream())
+
+
 def weight_grad(Gq: torch.Tensor, Xq: torch.Tensor, g_absmax: torch.Tensor, raw: bool = False,
                 path: int = EL_PATH_AUTO) -> torch.Tensor:
     """dW[n,k] = (sum_m Gq[m,n]*Xq[m,k]) * (g_absmax/127) as float32 [N,K] (int32 sums when raw=True)."""
@@ -573,7 +610,7 @@ def linear_decode(x: torch.Tensor, W_packed: torch.Tensor, gamma: float, out_dty
                   workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Small-M layer call (1 <= M <= 64 tokens): per-token quantisation + the weight-streaming tensor-core kernel.
     Same integers and rounding as quantize_rows + matmul_rows.  `workspace` (uint8, zero before first use, left
-    zero) defaults to a cached per-device, per-N buffer; calls sharing it must be stream-ordered."""
+    zero) defaults to a cached buffer per device, stream and N, so calls on different streams never share one."""
     _cuda(x, "x"); _cuda(W_packed, "W_packed")
     _require(x.dtype in (torch.float16, torch.bfloat16, torch.float32), "x must be float16, bfloat16 or float32")
     _require(W_packed.dtype == torch.uint8 and W_packed.dim() == 2, "W_packed must be uint8 [N, ceil(K/4)]")
@@ -586,7 +623,7 @@ def linear_decode(x: torch.Tensor, W_packed: torch.Tensor, gamma: float, out_dty
     out_dtype = out_dtype or x.dtype
     need = _lib.lib().el_decode_workspace_bytes(N)
     if workspace is None:
-        key = (x.device.index, N)
+        key = (x.device.index, _stream(), N)       # per stream: calls that share a workspace must be stream-ordered
         workspace = _decode_ws.get(key)
         if workspace is None:
             workspace = torch.zeros(need, dtype=torch.uint8, device=x.device)

@@ -51,7 +51,7 @@ class _ShardedLinearFn(Function):
         x2 = x.reshape(-1, K)
         Xq, ax = ops.quantize_rows(x2 if x2.dtype in _FLOAT_IO else x2.to(io), ACT_EPS)
         M = x2.shape[0]
-        if g > 1 and layer.fused_gather:
+        if g > 1 and layer.fused_gather and layer.fused_forward_ok():
             # Two output buffers alternate between calls.  A rank can only start call i+1 after the barrier of call i,
             # by which time every rank has issued (in stream order) its reads of the buffer of call i-1: no barrier is
             # needed before overwriting that buffer.
@@ -97,6 +97,7 @@ class _ShardedLinearFn(Function):
 
         def update():
             layer._step_py += 1
+            layer._step.fill_(layer._step_py)       # the buffer follows the counter, so a plain state_dict() resumes exactly
             Gq = ops.quantize_grad(window, ax, gmax)
             idx_base = layer.row_start * K
             if ops.dw_hysteresis_supported(Nl, K):
@@ -195,6 +196,22 @@ class ShardedInt2Linear(nn.Module):
 
     def set_lr(self, lr: float):
         self._lr = lr
+
+    def fused_forward_ok(self) -> bool:
+        """The epilogue-store all-gather needs the tensor-core kernel (K % 64 == 0) and a shard whose 32-column store
+        boxes stay inside its own column window; other shapes take the NCCL all-gather."""
+        return self.in_features % 64 == 0 and self.local_out_features % 32 == 0
+
+    def sync_step_buffer(self):
+        """Writes the Python step counter into the `_step` buffer (done after every update as well)."""
+        self._step.fill_(self._step_py)
+
+    def _load_from_state_dict(self, state_dict, prefix, *args, **kwargs):
+        super()._load_from_state_dict(state_dict, prefix, *args, **kwargs)
+        # the random numbers of the next update continue from the restored counter; gamma's cache follows the parameter
+        if prefix + "_step" in state_dict:
+            self._step_py = int(self._step.item())
+        self._gamma_cached = None
 
     def _side_stream(self):
         if self._side is None:

@@ -1,0 +1,317 @@
+"""INT2 linear layer run token-parallel over the GPUs of one node.
+
+Every rank keeps a full replica of `W_packed` and runs the forward and dX GEMMs on ITS OWN tokens: the layer's input,
+output and input gradient are token-sharded and need no communication at all.  The weight update is split by rows, as in
+the N-sharded layer (sharded.py): rank r owns rows [r*N/g, (r+1)*N/g) of `W_packed` / `H_packed`, forms their weight
+gradient over ALL tokens and runs their hysteresis update.  For that it receives int8 operands only:
+
+  Xq      the other ranks' quantised tokens            all-gather, int8 [M, K]            (pushed during the forward GEMM)
+  gmax    one float per rank (partial maximum)        all-gather of g floats, max taken by the consumer
+  Gq      its column window of every rank's folded,   all-to-all, int8 [M, N/g]
+          quantised output gradient
+  W rows  the updated rows of every other rank        all-gather, uint8 [N, K/4]          (before the next forward)
+
+Against N-sharding (replicated activations, bf16 Y all-gathered, int32 dX partial sums reduced) this moves about a fifth
+of the bytes, and the per-token quantisers run on M/g tokens per rank instead of on all of them.  The integers are those
+of the single-GPU layer: a token's scales depend on its own row only, the per-tensor gradient maximum is a maximum of
+maxima, the weight gradient is an exact int32 sum over all tokens, and the per-weight random numbers use the global row
+index.  The reference has no multi-GPU code (README.md:58); the single-GPU contract kept here is
+Int2LinearTCFunction's (core/bitnet/int2_linear_tc.py:255-305) with the hook's update
+(core/bitnet/int2_linear_tc_offload.py:210-285).
+
+Two data paths.  `fused=False`: torch.distributed collectives (NCCL on GPUs; gloo in the CPU tests, where a stand-in for
+the operator module is injected).  `fused=True` (CUDA): no collective kernel moves data; all buffers that peers write
+live in symmetric memory and the library's own kernels store into them over NVLink (el_peer_put, el_quantize_grad_scatter),
+ordered by el_peer_barrier.  Only stores cross NVLink; nothing loads from a peer.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+from torch.autograd import Function
+
+from .int2_tc_ops import ACT_EPS, GRAD_EPS
+from .sharded import shard_rows
+
+_FLOAT_IO = (torch.float16, torch.bfloat16, torch.float32)
+
+
+class PeerGroup:
+    """The barrier of the fused path, shared by all token-parallel layers of one process group on one device: a flag
+    array per rank in symmetric memory and a common epoch counter.  Because the epochs are shared, a barrier that one
+    layer queues also serves every other layer that was waiting for "a barrier after my last push"."""
+
+    _cache: dict = {}
+
+    def __init__(self, group, device: torch.device, ops):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group if group is not None else dist.group.WORLD
+        self.ops, self.device = ops, device
+        self.rank = dist.get_rank(self.group)
+        self.flags = symm_mem.empty((8,), dtype=torch.int32, device=device)
+        self.flags.zero_()
+        self.handle = symm_mem.rendezvous(self.flags, self.group)
+        self.handle.barrier(channel=0)              # every rank's flags are zero before anybody signals
+        self.epoch = 0
+        self.side = torch.cuda.Stream(device=device)
+
+    @classmethod
+    def get(cls, group, device: torch.device, ops) -> "PeerGroup":
+        key = (id(group) if group is not None else None, device.index)
+        if key not in cls._cache:
+            cls._cache[key] = cls(group, device, ops)
+        return cls._cache[key]
+
+    def barrier(self) -> None:
+        """All ranks have finished the work queued on their main streams so far, peer stores included."""
+        self.epoch += 1
+        self.ops.peer_barrier(self.handle.buffer_ptrs, self.rank, self.epoch, self.device)
+
+
+class _TokenParallelFn(Function):
+    @staticmethod
+    def forward(ctx, x: torch.Tensor, gamma: torch.Tensor, layer: "TokenParallelInt2Linear") -> torch.Tensor:
+        ops, K, N = layer.ops, layer.in_features, layer.out_features
+        io = x.dtype if x.dtype in _FLOAT_IO else torch.bfloat16
+        x2 = x.reshape(-1, K)
+        if x2.dtype not in _FLOAT_IO:
+            x2 = x2.to(io)
+        Ml = x2.shape[0]
+        will_update = layer.training and layer.hysteresis_enabled
+        run = layer._run
+        if will_update:
+            bufs = layer._exchange_buffers(Ml)
+            own = bufs["xq_all"][layer.rank * Ml:(layer.rank + 1) * Ml]         # this rank's rows of the gathered tokens
+            Xq, ax = run("quantize_rows", ops.quantize_rows, x2, ACT_EPS, out=own)
+        else:
+            bufs = None
+            Xq, ax = run("quantize_rows", ops.quantize_rows, x2, ACT_EPS)
+        layer._weights_ready()                  # the other ranks' updated rows of W_packed have landed
+        if will_update and layer.world > 1:
+            layer._share_tokens(bufs, own, Ml)
+        y = run("gemm_fwd", ops.matmul_rows, Xq, layer.W_packed, ax, layer.gamma_value(), io)
+        ctx.layer, ctx.io, ctx.x_shape = layer, io, x.shape
+        ctx.saved = (bufs, ax) if will_update else None
+        return y.view(*x.shape[:-1], N)
+
+    @staticmethod
+    def backward(ctx, dY: torch.Tensor):
+        layer = ctx.layer
+        ops, K, N = layer.ops, layer.in_features, layer.out_features
+        run = layer._run
+        dY2 = dY.reshape(-1, N)
+        if dY2.dtype not in _FLOAT_IO:
+            dY2 = dY2.to(ctx.io)
+        if not dY2.is_contiguous():
+            dY2 = dY2.contiguous()
+        do_update = ctx.saved is not None and layer.training and layer.hysteresis_enabled
+        if do_update:
+            bufs, ax = ctx.saved
+            dYq, ady, gloc = run("quantize_rows_dy", ops.quantize_rows, dY2, GRAD_EPS, fold_absmax=ax)
+        else:
+            dYq, ady = run("quantize_rows_dy", ops.quantize_rows, dY2, GRAD_EPS)
+
+        def input_grad():
+            if not ctx.needs_input_grad[0]:
+                return None
+            dX = run("gemm_dx", ops.backward_input_rows, dYq, layer.W_packed, ady, layer.gamma_value(), K, ctx.io)
+            return dX.view(ctx.x_shape)
+
+        if do_update and layer.hysteresis_order == "reference":
+            layer._update(bufs, dY2, ax, gloc)             # as the reference's hook: before dX ...
+            layer._weights_ready()                         # ... which then reads every rank's updated rows
+            dX = input_grad()
+        else:
+            dX = input_grad()
+            if do_update:
+                layer._update(bufs, dY2, ax, gloc)
+        return dX, None, None
+
+
+class TokenParallelInt2Linear(nn.Module):
+    """One rank of a token-parallel INT2 linear layer.  `W_packed` is the full [N, ceil(K/4)] matrix (a replica per
+    rank); `H_packed` holds the counters of the rows this rank updates; `gamma`, `_step` as in Int2LinearTC.  Call it
+    with this rank's tokens; every rank must pass the same number of tokens per call."""
+
+    def __init__(self, in_features: int, out_features: int, group: Optional[dist.ProcessGroup] = None, threshold: int = 7,
+                 lr_scale: float = 5.0, decay_rate: float = 0.001, hysteresis_order: str = "after_dx", ops=None,
+                 fused: bool = False, push_ctas: int = 32):
+        super().__init__()
+        if ops is None:
+            from . import int2_tc_ops as ops_mod
+            ops = ops_mod
+        if hysteresis_order not in ("reference", "after_dx"):
+            raise ValueError("hysteresis_order must be 'reference' or 'after_dx'")
+        self.ops, self.group = ops, group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.in_features, self.out_features = in_features, out_features
+        self.row_start, self.row_stop = shard_rows(out_features, self.world, self.rank)
+        self.local_out_features = self.row_stop - self.row_start
+        self.threshold, self.lr_scale, self.decay_rate = threshold, lr_scale, decay_rate
+        self.hysteresis_order = hysteresis_order
+        self.hysteresis_enabled = True
+        self.fused = fused
+        # CTAs of the token push that runs on a side stream beside the forward GEMM: few, so the GEMM keeps its SMs
+        self.push_ctas = push_ctas
+        self._lr = 0.001
+        self._step_py = 0
+        self._gamma_cached: Optional[float] = None
+        self._peer: Optional[PeerGroup] = None
+        self._w_handle = None
+        self._w_ready_epoch = 0                 # fused path: W_packed is complete once the group's epoch has reached this
+        self._tokens_pushed = None              # event on the side stream: this step's token push has been queued
+        self._bufs: dict = {}
+        self._run = lambda name, fn, *a, **k: fn(*a, **k)       # a benchmark replaces this to time the calls by name
+        self.register_buffer("W_packed", torch.zeros(out_features, (in_features + 3) // 4, dtype=torch.uint8))
+        self.register_buffer("H_packed", torch.zeros(self.local_out_features, (in_features + 1) // 2, dtype=torch.uint8))
+        self.gamma = nn.Parameter(torch.ones(1))
+        self.register_buffer("_step", torch.tensor(0, dtype=torch.int64))
+
+    # ---- state -------------------------------------------------------------------------------------------------------
+    def set_lr(self, lr: float):
+        self._lr = lr
+
+    def gamma_value(self) -> float:
+        if self._gamma_cached is None:
+            self._gamma_cached = self.gamma.detach().item()
+        return self._gamma_cached
+
+    def sync_step_buffer(self):
+        self._step.fill_(self._step_py)
+
+    def _load_from_state_dict(self, state_dict, prefix, *args, **kwargs):
+        super()._load_from_state_dict(state_dict, prefix, *args, **kwargs)
+        if prefix + "_step" in state_dict:
+            self._step_py = int(self._step.item())
+        self._gamma_cached = None
+
+    def init_from_float(self, weight_full: torch.Tensor, scale: Optional[float] = None):
+        """Ternarises the full [N,K] weight (every rank holds all of it); counters start at zero."""
+        assert weight_full.shape == (self.out_features, self.in_features)
+        if scale is None:
+            scale = max(weight_full.abs().mean().item(), 1e-5)
+        self.W_packed.copy_(self.ops.ternarize_pack(weight_full.to(self.W_packed.device), scale))
+        self.gamma.data.fill_(scale)
+        self._gamma_cached = scale
+        self.H_packed.zero_()
+
+    def load_full(self, W_packed_full: torch.Tensor, H_packed_full: torch.Tensor, gamma: float):
+        """Takes the state of an unsharded layer: all of its weights, and the counters of this rank's rows."""
+        self.W_packed.copy_(W_packed_full)
+        self.H_packed.copy_(H_packed_full[self.row_start:self.row_stop])
+        self.gamma.data.fill_(gamma)
+        self._gamma_cached = float(gamma)
+
+    def owned_rows(self) -> torch.Tensor:
+        """The rows of the replica this rank updates (a view)."""
+        return self.W_packed[self.row_start:self.row_stop]
+
+    # ---- exchange plumbing ---------------------------------------------------------------------------------------------
+    def _use_fused(self) -> bool:
+        return self.fused and self.world > 1 and self.W_packed.is_cuda
+
+    def _symm(self, shape, dtype):
+        import torch.distributed._symmetric_memory as symm_mem
+        t = symm_mem.empty(shape, dtype=dtype, device=self.W_packed.device)
+        return t, symm_mem.rendezvous(t, self.group if self.group is not None else dist.group.WORLD)
+
+    def _fused_setup(self):
+        """First use of the fused path (collective: every rank gets here in its first forward): the barrier group, and
+        the weight replica moved into symmetric memory so that peers can store their updated rows into it."""
+        if self._peer is None:
+            self._peer = PeerGroup.get(self.group, self.W_packed.device, self.ops)
+            w, self._w_handle = self._symm(tuple(self.W_packed.shape), torch.uint8)
+            w.copy_(self.W_packed)
+            self._buffers["W_packed"] = w
+            self._peer.barrier()
+
+    def _exchange_buffers(self, Ml: int) -> dict:
+        """Receive buffers for a call with Ml tokens per rank: the gathered int8 tokens [g*Ml, K], this rank's column
+        window of every rank's quantised gradient [g*Ml, N/g], the partial maxima [g] and the reduced maximum [1]."""
+        if self._use_fused():
+            self._fused_setup()
+        if Ml not in self._bufs:
+            g, dev = self.world, self.W_packed.device
+            if self._use_fused():
+                xq_all, hx = self._symm((g * Ml, self.in_features), torch.int8)
+                gq_recv, hg = self._symm((g * Ml, self.local_out_features), torch.int8)
+                slots, hs = self._symm((8,), torch.float32)
+                slots.zero_()
+                self._bufs[Ml] = dict(xq_all=xq_all, hx=hx, gq_recv=gq_recv, hg=hg, slots=slots, hs=hs,
+                                      gmax=torch.zeros(1, dtype=torch.float32, device=dev))
+                self._peer.barrier()            # nobody pushes into buffers that a rank has not created yet
+            else:
+                self._bufs[Ml] = dict(xq_all=torch.empty(g * Ml, self.in_features, dtype=torch.int8, device=dev))
+        return self._bufs[Ml]
+
+    def _weights_ready(self):
+        """Before a GEMM reads the replica: the rows the other ranks updated last must have landed.  On the fused path
+        that is any barrier queued after this rank's last push; one is queued here only if none has been since."""
+        if self._use_fused() and self._peer is not None and self._peer.epoch < self._w_ready_epoch:
+            self._run("barrier_weights", self._peer.barrier)
+
+    def _share_tokens(self, bufs: dict, own: torch.Tensor, Ml: int):
+        """All-gather of the int8 tokens; on the fused path a push to the peers on a side stream, beside the forward GEMM."""
+        if self._use_fused():
+            main, side = torch.cuda.current_stream(), self._peer.side
+            side.wait_stream(main)
+            peers = [p for i, p in enumerate(bufs["hx"].buffer_ptrs) if i != self.rank]
+            with torch.cuda.stream(side):
+                self._run("push_tokens", self.ops.peer_put, own, peers, self.rank * Ml * self.in_features, self.push_ctas)
+                self._tokens_pushed = torch.cuda.Event()
+                self._tokens_pushed.record(side)
+        else:
+            self._run("all_gather_tokens", dist.all_gather_into_tensor, bufs["xq_all"], own.clone(), group=self.group)
+
+    def _update(self, bufs: dict, dY2: torch.Tensor, ax: torch.Tensor, gloc: torch.Tensor):
+        """The weight update of this rank's rows from all ranks' tokens, then the push of the new rows to the replicas."""
+        ops, run = self.ops, self._run
+        g, r, K, Nl = self.world, self.rank, self.in_features, self.local_out_features
+        Ml = dY2.shape[0]
+        self._step_py += 1
+        self._step.fill_(self._step_py)
+        if g == 1:
+            gmax = gloc
+            gq = run("quantize_grad", ops.quantize_grad, dY2, ax, gmax)
+        elif self._use_fused():
+            peer = self._peer
+            run("push_gmax", ops.peer_put, gloc, list(bufs["hs"].buffer_ptrs), 4 * r)     # slot r of every rank
+            if self._tokens_pushed is not None:
+                torch.cuda.current_stream().wait_event(self._tokens_pushed)                # the token push precedes the barrier
+                self._tokens_pushed = None
+            run("barrier_gmax", peer.barrier)           # all partial maxima and all tokens have landed
+            gmax = bufs["gmax"]
+            run("quantize_grad", ops.quantize_grad_scatter, dY2, ax, bufs["slots"][:g], list(bufs["hg"].buffer_ptrs), r * Ml, gmax)
+            run("barrier_grad", peer.barrier)           # every rank's window of the gradient has landed
+            gq = bufs["gq_recv"]
+        else:
+            gmax = gloc.clone()
+            run("all_reduce_gmax", dist.all_reduce, gmax, op=dist.ReduceOp.MAX, group=self.group)
+            full = run("quantize_grad", ops.quantize_grad, dY2, ax, gmax)
+            send = full.view(Ml, g, Nl).permute(1, 0, 2).contiguous()           # [destination rank, token, window column]
+            gq = torch.empty(g * Ml, Nl, dtype=torch.int8, device=full.device)  # [source rank * Ml + token, window column]
+            run("all_to_all_grad", dist.all_to_all_single, gq, send, group=self.group)
+        own = self.owned_rows()
+        idx_base = self.row_start * K
+        if ops.dw_hysteresis_supported(Nl, K):
+            run("gemm_dw_hysteresis", ops.dw_hysteresis, gq, bufs["xq_all"], gmax, own, self.H_packed, self._lr, self.lr_scale,
+                self.threshold, self.decay_rate, self._step_py, idx_base)
+        else:
+            dW = run("gemm_dw", ops.weight_grad, gq, bufs["xq_all"], gmax)
+            run("hysteresis", ops.hysteresis_step_v2, dW, own, self.H_packed, self._lr, self.lr_scale, self.threshold,
+                self.decay_rate, self._step_py, idx_base)
+        if g == 1:
+            return
+        if self._use_fused():
+            peers = [p for i, p in enumerate(self._w_handle.buffer_ptrs) if i != r]
+            run("push_weights", ops.peer_put, own, peers, self.row_start * self.W_packed.shape[1])
+            self._w_ready_epoch = self._peer.epoch + 1          # complete after the next barrier, whoever queues it
+        else:
+            run("all_gather_weights", dist.all_gather_into_tensor, self.W_packed, own.clone(), group=self.group)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return _TokenParallelFn.apply(x, self.gamma, self)

@@ -5,7 +5,9 @@
  * Nothing here allocates, synchronises or prints.  Every function returns EL_OK (0) or a negative
  * EL_ERR_* code; el_status_string() names it and el_last_cuda_error() gives the CUDA error code behind
  * EL_ERR_CUDA on the calling thread.  All calls are asynchronous on `stream` and re-entrant across
- * streams and devices (there is no hidden scratch memory).
+ * host threads, streams and devices: there is no hidden scratch memory, with one documented exception,
+ * el_linear_decode_static, whose scratch is a static device array shared by all calls on a device.
+ * The el_set_* tuning calls are process-wide and take effect for calls made after they return.
  *
  * Each declaration cites the interface of the reference project (step325/Elleci-Training-Vast,
  * paths relative to its root) that it replaces.
@@ -242,6 +244,31 @@ EL_API int el_reduce_scale_gather(const int32_t* parts, void* const* dX_all, int
  * code 40 + its index in *dev_status.  No counterpart in the reference. */
 EL_API int el_peer_barrier(uint32_t* const* flags_all, int n_ranks, int rank, uint32_t epoch, int32_t* dev_status,
                            el_stream_t stream);
+/* Bound of el_peer_barrier's wait, process-wide, for barriers queued from now on: microseconds > 0 sets it, 0 restores
+ * the default of a few seconds.  A health check (or a test) that wants a missing rank reported within a millisecond
+ * instead of seconds sets it; the barrier then returns with code 40 + rank in *dev_status and the device stays usable. */
+EL_API int el_set_peer_barrier_limit_us(long long microseconds);
+
+/* ---- token-parallel layer: every GPU runs forward and dX on its own tokens, the weight update is split by rows ---- */
+
+/* Pushes `bytes` bytes of local memory `src` to byte offset dst_offset of each of the n_dst (<= 8) buffers dst[d] (own
+ * memory or peer mappings; plain 16-byte stores over NVLink when everything is 16-byte aligned, 4-byte stores otherwise;
+ * 4-byte alignment is the minimum).  The building block of the layer's all-gathers (the int8 tokens every rank needs for
+ * its rows of the weight gradient; the updated rows of W_packed every replica needs): each rank pushes its block, a
+ * barrier (el_peer_barrier) completes the exchange.  max_ctas > 0 caps the grid, so that a push running beside a GEMM
+ * takes few SMs; 0 picks a size that saturates the links.  No counterpart in the reference (single-GPU, README.md:58). */
+EL_API int el_peer_put(const void* src, void* const* dst, int n_dst, size_t dst_offset, size_t bytes, int max_ctas,
+                       el_stream_t stream);
+
+/* el_quantize_grad for a token-sharded layer, fused with the all-to-all of its result: this rank's M gradient rows
+ * dY[M,N] are quantised exactly as el_quantize_grad does, and the column window [d*N/n_ranks, (d+1)*N/n_ranks) of row m is
+ * stored at row row_offset + m of Gq_all[d], rank d's receive buffer of shape [M_total, N/n_ranks] int8 (own memory or a
+ * peer mapping).  The per-tensor maximum is max(g_slots[0..n_slots)), the ranks' partial maxima exchanged beforehand; it
+ * is also written to g_absmax_out[0] (may be NULL) for el_dw_hysteresis.  Needs (N/n_ranks) % 8 == 0, ld_dy % 8 == 0 and a
+ * 16-byte aligned dY.  No counterpart in the reference. */
+EL_API int el_quantize_grad_scatter(const void* dY, int dy_dtype, long long ld_dy, const float* x_absmax, const float* g_slots,
+                                    int n_slots, float* g_absmax_out, void* const* Gq_all, int n_ranks, long long row_offset,
+                                    int M, int N, el_stream_t stream);
 
 /* dW[n,k] = float(sum_m Gq[m,n]*Xq[m,k]) * (g_absmax[0]/127)   (out_dtype EL_F32, or EL_I32 for the raw sums).
  * Tensor-core path needs N % 16 == 0 and K % 16 == 0.  Replaces `torch.mm(dY_2d.t(), X_2d).float()`

@@ -11,12 +11,13 @@
 #                        its own flags (-O3 --use_fast_math), as a torch extension module that the
 #                        GPU tests load to compare kernels on the same device.
 #
-# usage: oracle/build_ref.sh [--cuda] [REFERENCE_ROOT]
+# usage: oracle/build_ref.sh [--cuda] REFERENCE_ROOT      (or REFERENCE_ROOT in the environment)
 set -euo pipefail
 HERE="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
 WITH_CUDA=0
 if [[ "${1:-}" == "--cuda" ]]; then WITH_CUDA=1; shift; fi
-REF="${1:-/root/reference}"
+REF="${1:-${REFERENCE_ROOT:-}}"
+[[ -n "$REF" ]] || { echo "usage: $0 [--cuda] REFERENCE_ROOT (the checkout of the reference project)" >&2; exit 2; }
 SRC="$REF/kernels/int2"
 OUT="$HERE/_ref"
 [[ -d "$SRC" ]] || { echo "reference sources not found at $SRC" >&2; exit 3; }

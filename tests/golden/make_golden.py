@@ -22,7 +22,9 @@ import types
 import numpy as np
 import torch
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("REFERENCE_ROOT")
+if not REF:
+    raise SystemExit("usage: %s REFERENCE_ROOT   (the checkout of the reference project; or set REFERENCE_ROOT)" % sys.argv[0])
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 from oracle import native  # noqa: E402

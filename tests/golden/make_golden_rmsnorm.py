@@ -1,8 +1,8 @@
 """Generates tests/golden/rmsnorm.npz from the reference's own pre-linear RMSNorm.
 
-Run where the reference checkout is available (its path in the environment variable REFERENCE_ROOT):
+Run where the reference checkout is available (its path as the argument, or in REFERENCE_ROOT):
 
-    python tests/golden/make_golden_rmsnorm.py
+    python tests/golden/make_golden_rmsnorm.py REFERENCE_ROOT
 
 What is imported from the reference (nothing is copied into this repository):
   * model/common/bitnet_legacy.py   _RMSNorm (the same expression as _ExtraRMSNorm of
@@ -15,12 +15,15 @@ activation_quant makes of the normalised output.
 """
 import importlib.util
 import os
+import sys
 
 import numpy as np
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = os.environ.get("REFERENCE_ROOT", "/root/reference")
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("REFERENCE_ROOT")
+if not REF:
+    raise SystemExit("usage: %s REFERENCE_ROOT   (the checkout of the reference project; or set REFERENCE_ROOT)" % sys.argv[0])
 
 
 def main():

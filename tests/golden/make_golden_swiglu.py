@@ -25,7 +25,9 @@ import torch
 import torch.nn as nn
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = os.environ.get("REFERENCE_ROOT", "/root/reference")
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("REFERENCE_ROOT")
+if not REF:
+    raise SystemExit("usage: %s REFERENCE_ROOT   (the checkout of the reference project; or set REFERENCE_ROOT)" % sys.argv[0])
 
 
 class _Half(nn.Module):

@@ -19,21 +19,24 @@ def ternarize_pack(weight, gamma):
     return torch.from_numpy(O.pack_ternary(O.ternarize(_n(weight), gamma), pad_code=0))
 
 
-def quantize_rows(x, eps=1e-5, fold_absmax=None, raw_absmax=None):
+def quantize_rows(x, eps=1e-5, fold_absmax=None, raw_absmax=None, out=None):
     xn = _n(x)
     xn = np.where(np.isfinite(xn), xn, np.float32(0))
     raw = np.abs(xn).max(axis=1).astype(np.float32) if raw_absmax is None else _n(raw_absmax).copy()
     a = np.maximum(raw, np.float32(eps)).astype(np.float32)
     s = (np.float32(127.0) / a).astype(np.float32)
     q = np.clip(np.rint(xn * s[:, None]), -128, 127).astype(np.int8)
+    if out is not None:
+        out.copy_(torch.from_numpy(q))
     if raw_absmax is not None:
         raw_absmax.copy_(torch.from_numpy(a))
     at = raw_absmax if raw_absmax is not None else torch.from_numpy(a)
+    qt = out if out is not None else torch.from_numpy(q)
     if fold_absmax is None:
-        return torch.from_numpy(q), at
+        return qt, at
     sx = (_n(fold_absmax) / np.float32(127.0)).astype(np.float32)
     g = np.float32((raw * sx).astype(np.float32).max())
-    return torch.from_numpy(q), at, torch.tensor([g], dtype=torch.float32)
+    return qt, at, torch.tensor([g], dtype=torch.float32)
 
 
 def absmax_rows(x):

@@ -54,9 +54,35 @@ def test_status_strings_and_host_side_argument_checks():
     assert handle.el_set_decode_mma_max_tokens(33) == lib.EL_ERR_INVALID_ARG
     assert handle.el_set_decode_gemv_max_tokens(2) == lib.EL_OK and handle.el_set_decode_mma_max_tokens(32) == lib.EL_OK
     assert handle.el_set_decode_overlap(0) == lib.EL_OK
+    assert handle.el_set_peer_barrier_limit_us(-5) == lib.EL_ERR_INVALID_ARG
+    assert handle.el_set_peer_barrier_limit_us(1000) == lib.EL_OK and handle.el_set_peer_barrier_limit_us(0) == lib.EL_OK
     try:
         lib.check("el_gemm_fwd", lib.EL_ERR_ALIGNMENT)
     except pkg.ElleciError as e:
         assert e.status == lib.EL_ERR_ALIGNMENT and "alignment" in str(e)
     else:
         raise AssertionError("check() must raise")
+
+
+def test_tuning_setters_from_several_threads_leave_a_valid_value():
+    """The knobs are process-wide atomics: setters racing on several host threads must each succeed and leave one of
+    the values that was set (checked through the range check of a follow-up call, since there is no getter)."""
+    import threading
+    pkg = load_package()
+    handle = pkg._lib.lib()
+    rcs = []
+
+    def hammer(v):
+        for _ in range(2000):
+            rcs.append(handle.el_set_decode_gemv_max_tokens(v))
+            rcs.append(handle.el_set_decode_mma_max_tokens(8 * v))
+            rcs.append(handle.el_set_decode_overlap(v & 1))
+
+    threads = [threading.Thread(target=hammer, args=(v,)) for v in (1, 2, 3, 4)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert set(rcs) == {0}
+    assert handle.el_set_decode_gemv_max_tokens(2) == 0 and handle.el_set_decode_mma_max_tokens(32) == 0
+    assert handle.el_set_decode_overlap(0) == 0

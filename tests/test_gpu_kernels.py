@@ -503,3 +503,222 @@ def test_dx_scatter_of_all_ranks_adds_up_to_the_unsharded_sums(ops, g, M, K, N):
             part = O.gemm_dx_acc(np.ascontiguousarray(dYq[d * Mr:(d + 1) * Mr, r * Ns:(r + 1) * Ns]), Wp[r * Ns:(r + 1) * Ns], K)
             assert np.array_equal(parts[d][r].cpu().numpy(), part), (d, r)
         assert np.array_equal(parts[d].sum(0).cpu().numpy(), want[d * Mr:(d + 1) * Mr])
+
+
+# ---- N-sharded forward and the owner's half of the dX exchange, ranks emulated one after the other on one GPU --------
+
+@pytest.mark.parametrize("g,M,K,N", [(2, 512, 256, 512), (4, 300, 512, 1024), (8, 1024, 256, 2048), (8, 256, 128, 256)])
+def test_fwd_gather_of_all_ranks_fills_every_output_buffer(ops, g, M, K, N):
+    """Every rank's shard of the forward GEMM writes its [M, N/g] block at column r*N/g of ALL g output buffers (the
+    all-gather is the epilogue's TMA stores).  Launched rank after rank on one device with g local buffers standing in
+    for the ranks' buffers, every buffer must end up holding the unsharded layer's output, and nothing else is touched."""
+    rng = np.random.default_rng(g * 100 + M)
+    x = torch.from_numpy(rng.standard_normal((M, K)).astype(np.float32)).to(torch.bfloat16)
+    Wp, _ = random_packed(N, K, 21)
+    gamma = 0.0173
+    Xq, ax = O.quantize_rows(t2n(x))
+    want = O.to_bf16(O.scale_rows(O.gemm_fwd_acc(Xq, Wp, K), ax, gamma))
+    Ns = N // g
+    pad = 64                                                    # guard columns right of the matrix: must stay untouched
+    bufs = [torch.full((M, N + pad), 3.0, dtype=torch.bfloat16, device=DEV) for _ in range(g)]
+    Xd, ad = _cuda(Xq), _cuda(ax)
+    for r in range(g):
+        ops.matmul_rows_gather(Xd, _cuda(Wp[r * Ns:(r + 1) * Ns]), ad, gamma, [b.data_ptr() for b in bufs], N + pad, r * Ns,
+                               torch.bfloat16)
+    ops.check_device_status(torch.device(DEV))
+    for d in range(g):
+        got = t2n(bufs[d])
+        assert np.array_equal(got[:, :N], want), d
+        assert np.all(got[:, N:] == 3.0), d
+
+
+@pytest.mark.parametrize("g,M,K", [(2, 512, 256), (4, 2048, 512), (8, 256, 128), (8, 4096, 1024)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_reduce_scale_gather_of_all_owners_completes_dx(ops, g, M, K, dtype):
+    """Owner d adds the g slots of its staging buffer, scales the rows it owns and writes them into every rank's dX.
+    With all owners launched one after the other on one device, every dX buffer must equal scale_rows of the summed
+    partial sums (integer addition first, one rounding at the end), whichever owner produced a row."""
+    rng = np.random.default_rng(g + M + K)
+    Mr = M // g
+    parts = rng.integers(-(1 << 20), 1 << 20, (g, g, Mr, K)).astype(np.int32)          # [owner, source rank, rows, K]
+    ax = (rng.random(M).astype(np.float32) + 0.25)
+    gamma = 0.0211
+    total = parts.astype(np.int64).sum(1).reshape(M, K)
+    assert np.abs(total).max() < 2 ** 31
+    want = O.scale_rows(total.astype(np.int32), ax, gamma)
+    want = O.to_bf16(want) if dtype == torch.bfloat16 else want.astype(np.float32)
+    outs = [torch.full((M, K), -5.0, dtype=dtype, device=DEV) for _ in range(g)]
+    ad = _cuda(ax)
+    for d in range(g):
+        ops.reduce_scale_gather(_cuda(parts[d]), [o.data_ptr() for o in outs], d, ad, gamma, M, K, dtype)
+    for r in range(g):
+        assert np.array_equal(t2n(outs[r]), want), r
+
+
+# ---- bounded device-side waits and first calls from several host threads -----------------------------------------
+
+def test_peer_barrier_reports_a_rank_that_never_arrives_and_leaves_the_device_usable(ops, pkg):
+    """Two ranks' flag arrays live on this one device; only rank 0 ever launches.  With the wait limit set to a
+    millisecond the barrier must come back by itself, name the missing rank (code 40 + 1) in the status word and leave
+    the context healthy.  A barrier whose partner has already signalled (its flag written beforehand) passes at once."""
+    dev = torch.device(DEV)
+    handle = pkg._lib.lib()
+    flags = [torch.zeros(8, dtype=torch.int32, device=DEV) for _ in range(2)]
+    ptrs = [f.data_ptr() for f in flags]
+    status = ops.device_status(dev)
+    status.zero_()
+    assert handle.el_set_peer_barrier_limit_us(1000) == 0
+    try:
+        t0 = torch.cuda.Event(enable_timing=True)
+        t1 = torch.cuda.Event(enable_timing=True)
+        t0.record()
+        ops.peer_barrier(ptrs, 0, 1, dev)                   # rank 1 never signals
+        t1.record()
+        torch.cuda.synchronize()
+        assert t0.elapsed_time(t1) < 500.0                  # a millisecond of cycles, not the default of seconds
+        assert int(status.item()) == 41
+        with pytest.raises(pkg.ElleciError):
+            ops.check_device_status(dev)                    # raises and clears the word
+        assert int(status.item()) == 0
+        assert flags[0][0].item() == 1 and flags[1][0].item() == 1      # rank 0 did publish its epoch everywhere
+        # the partner's arrival written by hand: epoch 2 passes without a wait
+        flags[0][1] = 2
+        ops.peer_barrier(ptrs, 0, 2, dev)
+        torch.cuda.synchronize()
+        ops.check_device_status(dev)
+        # and the device still computes
+        Wp, w = random_packed(64, 64, 5)
+        out = torch.empty(64, 64, dtype=torch.int8, device=DEV)
+        ops.unpack_int2(_cuda(Wp), out, 64)
+        assert np.array_equal(out.cpu().numpy(), w)
+    finally:
+        assert handle.el_set_peer_barrier_limit_us(0) == 0
+        status.zero_()
+    assert handle.el_set_peer_barrier_limit_us(-1) == pkg._lib.EL_ERR_INVALID_ARG
+
+
+def test_calls_from_two_host_threads_agree_with_one(ops):
+    """The library promises re-entrancy across host threads, including the per-device set-up a launcher does on its
+    first call.  Two threads, each on its own stream, run the forward and dX GEMMs and a decode call at shapes no other
+    test of this file uses first; both must return what the oracle gives."""
+    import threading
+    M, N, K = 384, 640, 320
+    Xq, dYq, Wp, ax, ay = _gemm_inputs(M, N, K, seed=4242)
+    gamma = 0.019
+    want_y = O.to_bf16(O.scale_rows(O.gemm_fwd_acc(Xq, Wp, K), ax, gamma))
+    want_dx = O.to_bf16(O.scale_rows(O.gemm_dx_acc(dYq, Wp, K), ay, gamma))
+    xs = torch.from_numpy(np.random.default_rng(1).standard_normal((5, K)).astype(np.float32)).to(torch.bfloat16)
+    q5, a5 = O.quantize_rows(t2n(xs))
+    want_dec = O.to_bf16(O.scale_rows(O.gemm_fwd_acc(q5, Wp, K), a5, gamma))
+    Xd, Yd, Wd, axd, ayd, xsd = _cuda(Xq), _cuda(dYq), _cuda(Wp), _cuda(ax), _cuda(ay), xs.to(DEV)
+    torch.cuda.synchronize()
+    results, errors = [None, None], []
+    gate = threading.Barrier(2)
+
+    def worker(i):
+        try:
+            torch.cuda.set_device(0)
+            s = torch.cuda.Stream()
+            gate.wait()
+            with torch.cuda.stream(s):
+                y = ops.matmul_rows(Xd, Wd, axd, gamma, torch.bfloat16)
+                dx = ops.backward_input_rows(Yd, Wd, ayd, gamma, K, torch.bfloat16)
+                ws = torch.zeros(ops._lib.lib().el_decode_workspace_bytes(N), dtype=torch.uint8, device=DEV)
+                dec = ops.linear_decode(xsd, Wd, gamma, workspace=ws)
+            s.synchronize()
+            results[i] = (t2n(y), t2n(dx), t2n(dec))
+        except Exception as e:  # noqa: BLE001 - reported by the asserting thread
+            errors.append(e)
+
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    for y, dx, dec in results:
+        assert np.array_equal(y, want_y) and np.array_equal(dx, want_dx) and np.array_equal(dec, want_dec)
+    ops.check_device_status(torch.device(DEV))
+
+
+# ---- token-parallel layer: its exchange kernels with the ranks emulated one after the other on one GPU ---------------
+
+@pytest.mark.parametrize("nbytes,offset", [(4, 8), (48, 16), (4096, 0), (1 << 20, 4096), (100, 4), (3 * (1 << 20) + 16, 32)])
+def test_peer_put_copies_the_block_into_every_destination(ops, nbytes, offset):
+    """The push half of an all-gather: one local block lands at the same byte offset of every destination buffer (16-byte
+    stores when everything is aligned, 4-byte stores otherwise) and nothing around it changes."""
+    src = torch.randint(0, 256, (nbytes,), dtype=torch.uint8, device=DEV)
+    dsts = [torch.full((offset + nbytes + 64,), 7, dtype=torch.uint8, device=DEV) for _ in range(3)]
+    ops.peer_put(src, [d.data_ptr() for d in dsts], offset, max_ctas=5)
+    ops.peer_put(src, [dsts[2].data_ptr()], offset)                      # default grid size
+    for d in dsts:
+        assert torch.equal(d[offset:offset + nbytes], src)
+        assert bool((d[:offset] == 7).all()) and bool((d[offset + nbytes:] == 7).all())
+
+
+def test_peer_put_rejects_misaligned_blocks(ops, pkg):
+    src = torch.zeros(64, dtype=torch.uint8, device=DEV)
+    dst = torch.zeros(64, dtype=torch.uint8, device=DEV)
+    for args in ((src[1:9], [dst.data_ptr()], 0), (src[:8], [dst.data_ptr()], 2), (src[:6], [dst.data_ptr()], 0)):
+        with pytest.raises(pkg.ElleciError) as e:
+            ops.peer_put(*args)
+        assert e.value.status == pkg._lib.EL_ERR_ALIGNMENT
+
+
+@pytest.mark.parametrize("g,Ml,K,N,thr", [(2, 128, 256, 512, 2), (4, 64, 128, 256, 3), (8, 96, 256, 1024, 2)])
+def test_token_parallel_update_of_all_ranks_equals_the_single_gpu_update(ops, g, Ml, K, N, thr):
+    """The weight update of a token-parallel layer, its g ranks emulated one after the other on one device with local
+    buffers standing in for the peers': every rank quantises its own tokens into its row block of the gathered token
+    buffers, leaves its partial gradient maximum in its slot, scatters the column windows of its quantised gradient to
+    the owners (el_quantize_grad_scatter), and every owner runs the fused weight-gradient + hysteresis kernel on its rows
+    of a replica.  The assembled weights and counters must equal the single-GPU update over all g*Ml tokens bit for bit,
+    and so must the intermediate integers against the oracle."""
+    M = g * Ml
+    d = make_layer_inputs(M, K, N, seed=g + Ml, dtype=torch.bfloat16, dy_std=1e-2, counters=thr)
+    x, dY = d["x"].to(DEV), d["dY"].to(DEV)
+    Nl = N // g
+    lr, lr_scale, decay, step = 0.5, 5.0, 0.001, 3
+    # single-GPU update
+    Xq1, ax1 = ops.quantize_rows(x)
+    _, _, gmax1 = ops.quantize_rows(dY, ops.GRAD_EPS, fold_absmax=ax1)
+    Gq1 = ops.quantize_grad(dY, ax1, gmax1)
+    W1, H1 = _cuda(d["Wp"]), _cuda(d["Hp"])
+    ops.dw_hysteresis(Gq1, Xq1, gmax1, W1, H1, lr, lr_scale, thr, decay, step)
+    # emulated ranks
+    xq_all = [torch.zeros(M, K, dtype=torch.int8, device=DEV) for _ in range(g)]           # every rank's gathered tokens
+    gq_recv = [torch.full((M, Nl), 99, dtype=torch.int8, device=DEV) for _ in range(g)]    # owner d: [source rank * Ml + token, window]
+    slots = [torch.zeros(8, dtype=torch.float32, device=DEV) for _ in range(g)]
+    axs = []
+    for r in range(g):
+        rows = slice(r * Ml, (r + 1) * Ml)
+        own = xq_all[r][rows]
+        _, ax = ops.quantize_rows(x[rows], out=own)
+        ops.peer_put(own, [xq_all[p].data_ptr() for p in range(g) if p != r], r * Ml * K)
+        _, _, gloc = ops.quantize_rows(dY[rows], ops.GRAD_EPS, fold_absmax=ax)
+        ops.peer_put(gloc, [s.data_ptr() for s in slots], 4 * r)
+        axs.append(ax)
+    gmaxes = []
+    for r in range(g):
+        rows = slice(r * Ml, (r + 1) * Ml)
+        gmax = torch.zeros(1, dtype=torch.float32, device=DEV)
+        ops.quantize_grad_scatter(dY[rows], axs[r], slots[r][:g], [b.data_ptr() for b in gq_recv], r * Ml, gmax)
+        gmaxes.append(gmax)
+    Wr = [_cuda(d["Wp"]) for _ in range(g)]                                                # one replica per rank
+    Hr = [_cuda(d["Hp"][r * Nl:(r + 1) * Nl]) for r in range(g)]
+    for r in range(g):
+        own_rows = Wr[r][r * Nl:(r + 1) * Nl]
+        ops.dw_hysteresis(gq_recv[r], xq_all[r], gmaxes[r], own_rows, Hr[r], lr, lr_scale, thr, decay, step, idx_base=r * Nl * K)
+        ops.peer_put(own_rows, [Wr[p].data_ptr() for p in range(g) if p != r], r * Nl * (K // 4))
+    ops.check_device_status(torch.device(DEV))
+    for r in range(g):
+        assert torch.equal(xq_all[r], Xq1), r
+        assert float(gmaxes[r].item()) == float(gmax1.item())
+        assert torch.equal(gq_recv[r], Gq1[:, r * Nl:(r + 1) * Nl].contiguous()), r
+        assert torch.equal(Wr[r], W1), r
+        assert torch.equal(Hr[r], H1[r * Nl:(r + 1) * Nl]), r
+    # the intermediate integers against the oracle
+    xq_o, ax_o = O.quantize_rows(t2n(d["x"]))
+    assert np.array_equal(Xq1.cpu().numpy(), xq_o)
+    Gq_o, g_o = O.grad_quantize(t2n(d["dY"]), ax_o)
+    assert np.array_equal(Gq1.cpu().numpy(), Gq_o) and np.float32(gmax1.item()) == g_o
+    assert not torch.equal(W1.cpu(), torch.from_numpy(d["Wp"]))

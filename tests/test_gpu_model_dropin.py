@@ -9,6 +9,7 @@ import pytest
 import torch
 import torch.nn as nn
 import torch.nn.functional as F
+import torch.utils.checkpoint
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
@@ -66,6 +67,15 @@ class _Ffn(nn.Module):
 
 
 class _Mini(nn.Module):
+    # None: plain blocks; True / False: every block under torch.utils.checkpoint with that `use_reentrant`
+    # (the reference's model wraps its blocks with use_reentrant=False, model/model.py:422-424)
+    checkpoint_blocks = None
+
+    def _block(self, block, x):
+        if self.checkpoint_blocks is None or not self.training:
+            return block(x)
+        return torch.utils.checkpoint.checkpoint(block, x, use_reentrant=self.checkpoint_blocks)
+
     def __init__(self, fused_gate):
         super().__init__()
         self.in_norm = nn.LayerNorm(D)
@@ -74,9 +84,9 @@ class _Mini(nn.Module):
 
     def forward(self, x):
         x = self.in_norm(x.float()).to(torch.bfloat16)          # the INT2 layers see bfloat16, as under the trainer's autocast
-        x = x + self.mla(x)
-        x = x + self.mamba(x)
-        x = x + self.ffn(x)
+        x = x + self._block(self.mla, x)
+        x = x + self._block(self.mamba, x)
+        x = x + self._block(self.ffn, x)
         return self.lm_head(x.float())
 
 
@@ -187,3 +197,38 @@ def test_converted_block_trains_and_resumes_bit_for_bit(pkg, fused_gate):
     ref_state = torch.load(io.BytesIO(buf.getvalue()), map_location="cpu")["int2_state"]
     for i, l in enumerate(layers3):
         assert torch.equal(l.int2_layer.W_packed.cpu(), ref_state[f"layer_{i}"]["W_packed"]) and l.int2_layer._step_py == 2
+
+
+@pytest.mark.parametrize("tokens", [(2, 16), (4, 32)])          # 32 tokens per call (decode-sized) and 128
+@pytest.mark.parametrize("use_reentrant", [False, True])
+def test_blocks_under_activation_checkpointing_train_like_plain_blocks(pkg, use_reentrant, tokens):
+    """Per-block activation checkpointing runs every layer's forward twice.  With use_reentrant=False (what the
+    reference's model uses) both passes record gradients and the recompute starts inside the backward pass, after the
+    last layer's update hook has already fired; with use_reentrant=True the first pass runs without gradient recording
+    (calls of at most 64 tokens then take the decode kernels and save nothing) and the hook exists only on the recompute
+    pass (core/bitnet/int2_linear_tc_offload.py:338-344).  Either way two optimiser steps with accumulation must leave
+    the same losses, packed weights, counters, step counters and other parameters as the same model without
+    checkpointing."""
+    B, T = tokens
+
+    def batches(seed):
+        g = torch.Generator().manual_seed(seed)
+        return [(torch.randn(B, T, D, generator=g).to(torch.bfloat16).to(DEV), torch.randint(0, 64, (B, T), generator=g).to(DEV))
+                for _ in range(2)]
+
+    plain, ckpt = _build(pkg, True), _build(pkg, True)
+    ckpt.checkpoint_blocks = use_reentrant
+    tp, tc = _Trainer(pkg, plain), _Trainer(pkg, ckpt)
+    for s in range(2):
+        lp, lc = tp.optimizer_step(batches(40 + s)), tc.optimizer_step(batches(40 + s))
+        assert lp == lc, (s, lp, lc)
+    torch.cuda.synchronize()
+    pkg.int2_tc_ops.check_device_status(torch.device(DEV))
+    changed = 0
+    for a, b in zip(tp.int2_layers, tc.int2_layers):
+        assert a.int2_layer._step_py == 2 and b.int2_layer._step_py == 2
+        assert torch.equal(a.int2_layer.W_packed, b.int2_layer.W_packed) and torch.equal(a.int2_layer.H_packed, b.int2_layer.H_packed)
+        changed += int(bool((a.int2_layer.H_packed != 0).any()))
+    assert changed >= 10
+    for (n, p), (_, q) in zip(plain.named_parameters(), ckpt.named_parameters()):
+        assert torch.equal(p, q), n

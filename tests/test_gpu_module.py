@@ -206,3 +206,38 @@ def test_bitlinear_fused_rmsnorm_matches_oracle_and_unfused_module(pkg, M, K, N,
     assert rel(yf, yu) <= tol
     assert rel(xf.grad, xu.grad) <= tol
     assert rel(mf.extra_rmsnorm.weight.grad, mu.extra_rmsnorm.weight.grad) <= tol
+
+
+def test_from_bitnetlinear_takes_weights_scale_and_bias_of_the_source_module(pkg):
+    """The converter of BitNetLinear-style modules (core/bitnet/bitnet_int2_optimized.py:245-310): latent `master_weight`
+    ternarised with the mean of the module's `scale` tensor when it has one, with the weight's absmean otherwise; a module
+    without latent weights is re-initialised with scale 1/sqrt(K); the bias is carried over."""
+    K, N = 128, 48
+    g = torch.Generator().manual_seed(8)
+
+    class Src(nn.Module):
+        def __init__(self, with_weight, with_scale, with_bias):
+            super().__init__()
+            self.in_features, self.out_features = K, N
+            self.master_weight = nn.Parameter(torch.randn(N, K, generator=g) * 0.05) if with_weight else None
+            self.scale = nn.Parameter(torch.full((N,), 0.031)) if with_scale else None
+            self.bias = nn.Parameter(torch.randn(N, generator=g)) if with_bias else None
+
+    for with_weight, with_scale, with_bias in [(True, True, True), (True, False, False), (False, False, True)]:
+        src = Src(with_weight, with_scale, with_bias)
+        layer = pkg.BitLinearInt2.from_bitnetlinear(src, threshold=3)
+        il = layer.int2_layer
+        assert il.W_packed.is_cuda and il.threshold == 3 and (il.bias is not None) == with_bias
+        if with_bias:
+            assert torch.equal(il.bias.detach().cpu(), src.bias.detach())
+        if with_weight:
+            w = src.master_weight.detach().float().numpy()
+            scale = 0.031 if with_scale else float(np.abs(w).mean())
+            assert abs(il.gamma.item() - scale) < 1e-7
+            want = O.pack_ternary(O.ternarize(w, np.float32(il.gamma.item())), pad_code=0)
+            assert np.array_equal(il.W_packed.cpu().numpy(), want)
+        else:
+            assert abs(il.gamma.item() - K ** -0.5) < 1e-7
+            codes = il.W_packed.cpu().numpy()
+            assert len(np.unique(O.unpack_ternary(codes, K))) == 3
+        assert int(il.H_packed.abs().sum().item()) == 0

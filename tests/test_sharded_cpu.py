@@ -83,3 +83,39 @@ def test_shard_rows_rejects_uneven_split():
     with pytest.raises(ValueError):
         pkg.sharded.shard_rows(100, 8, 0)
     assert pkg.sharded.shard_rows(11008, 8, 3) == (4128, 5504)
+
+
+def test_sharded_layer_resumes_from_plain_state_dict():
+    """The `_step` buffer follows the Python counter, so state_dict() -> load_state_dict() on a fresh layer continues
+    with the next step's random numbers instead of replaying the first step's."""
+    pkg = load_package()
+    sys.path.insert(0, HERE)
+    import oracle_ops
+    M, K, N = 32, 64, 64
+    d = make_layer_inputs(M, K, N, seed=2, dtype=torch.float32, dy_std=1e-2, counters=1)
+
+    def make():
+        layer = pkg.sharded.ShardedInt2Linear(K, N, threshold=2, ops=oracle_ops)
+        layer.set_lr(0.5)
+        return layer.train()
+
+    def step(layer):
+        x = d["x"].clone().requires_grad_(True)
+        layer(x).backward(d["dY"])
+
+    a = make()
+    a.load_shard(torch.from_numpy(d["Wp"]), torch.from_numpy(d["Hp"]), d["gamma"])
+    step(a)
+    assert int(a._step.item()) == 1
+    b = make()
+    b.load_state_dict(a.state_dict())
+    assert b._step_py == 1 and abs(b.gamma_value() - d["gamma"]) < 1e-9
+    step(a)
+    step(b)
+    assert torch.equal(a.W_packed, b.W_packed) and torch.equal(a.H_packed, b.H_packed)
+    c = make()                                   # a layer that replays step 1's random numbers ends up elsewhere
+    c.load_state_dict(b.state_dict())
+    c._step_py = 0
+    step(c)
+    step(a)
+    assert not torch.equal(a.H_packed, c.H_packed)

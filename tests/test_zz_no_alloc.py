@@ -10,7 +10,9 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import random_packed
+from oracle import int2_oracle as O
+
+from helpers import random_packed, t2n
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
@@ -60,6 +62,32 @@ def test_static_scratch_decode_matches_regular_entry_point_twice_in_a_row(pkg):
         torch.cuda.synchronize()
         assert torch.equal(y1, r1) and torch.equal(y2, r2)
         assert not torch.equal(y1, y2) and float(y1.float().abs().max()) > 0.0
+
+
+def test_static_scratch_is_really_used_and_shared_between_shapes(pkg):
+    """Calls that need the array (more than 32 tokens, or tokens that do not fit in shared memory): the stated capacity
+    M=64 at N=16384, a 40-token call, then a small-N call whose tile counters sit where the large call kept partial
+    sums, then the large one again.  The first call of the sequence is a one-token call, which touches no scratch but
+    must already have resolved the array's address.  Every result is checked against the regular entry point and
+    against the CPU oracle."""
+    gamma = 0.0157
+    seq = [(1, 4096, 16384), (64, 4096, 16384), (33, 1024, 640), (40, 4096, 16384), (48, 256, 128), (64, 4096, 16384)]
+    weights = {}
+    for i, (M, K, N) in enumerate(seq):
+        if (K, N) not in weights:
+            Wp, _ = random_packed(N, K, seed=K + N)
+            weights[(K, N)] = (Wp, torch.from_numpy(Wp).to(DEV))
+        Wp, W = weights[(K, N)]
+        x = (torch.randn(M, K, generator=torch.Generator().manual_seed(100 + i)) * (1.0 + i)).to(torch.bfloat16)
+        xd = x.to(DEV)
+        y = _static(pkg, xd, W, gamma, torch.bfloat16)
+        r = _regular(pkg, xd, W, gamma, torch.bfloat16)
+        torch.cuda.synchronize()
+        Xq, ax = O.quantize_rows(t2n(x))
+        want = O.to_bf16(O.scale_rows(O.gemm_fwd_acc(Xq, Wp, K), ax, gamma))
+        assert torch.equal(y, r), (M, K, N)
+        assert np.array_equal(t2n(y), want), (M, K, N)
+    pkg.int2_tc_ops.check_device_status(torch.device(DEV))
 
 
 def test_static_scratch_decode_refuses_sizes_beyond_its_capacity(pkg):
