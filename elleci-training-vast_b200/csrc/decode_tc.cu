@@ -102,6 +102,12 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
 
     if (warp == WARP_TMA) {
         // ================= producer: packed weight tile + token tile of every unit =================
+        // The ring holds eight units (32 KB of packed weights) per SM, too few bytes in flight to keep HBM busy; so all
+        // of this CTA's weight tiles are first requested into L2 (the whole matrix is a fraction of it), and the ring's
+        // loads then find them there.
+        for (long long u = u_lo + lane; u < u_hi; u += 32)
+            tma_prefetch_2d(&tmW, (int)(u % p.k_blocks) * (BK / 4), (int)(u / p.k_blocks) * TILE_N);
+        __syncwarp();
         if (lane == 0) {
             int sp = 0;
             uint32_t php = 0;

@@ -104,7 +104,8 @@ class Int2LinearTCFunction(Function):
 
     @staticmethod
     def backward(ctx, dY: torch.Tensor) -> Tuple[Optional[torch.Tensor], ...]:
-        W_packed, gamma = ctx.saved_tensors[:2]
+        saved = ctx.saved_tensors        # read once: under activation checkpointing a second read is an error
+        W_packed, gamma = saved[:2]
         layer = ctx.layer
         dX = None
         d_norm_weight = None
@@ -125,11 +126,11 @@ class Int2LinearTCFunction(Function):
                     dY_half.contiguous(), Int2LinearTCFunction._get_absmax_buf(dY.device))
                 dX = int2_tc_ops.backward_input_int8(dY_int8, W_packed, d_scale_dy, gamma_val, ctx.K)
             if ctx.has_gate:
-                gate, up = ctx.saved_tensors[2:4]
-                norm_weight, rstd = ctx.saved_tensors[4:6] if ctx.has_norm else (None, None)
+                gate, up = saved[2:4]
+                norm_weight, rstd = saved[4:6] if ctx.has_norm else (None, None)
                 dX, d_up, d_norm_weight = int2_tc_ops.swiglu_backward(dX.view_as(gate), gate, up, norm_weight, rstd)
             elif ctx.has_norm:
-                Xin, norm_weight, rstd = ctx.saved_tensors[2:]
+                Xin, norm_weight, rstd = saved[2:]
                 dX, d_norm_weight = int2_tc_ops.rmsnorm_backward(dX.view_as(Xin), Xin, norm_weight, rstd)
         if layer is not None:
             layer._run_pending_update()

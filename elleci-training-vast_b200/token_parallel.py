@@ -71,64 +71,74 @@ class PeerGroup:
         self.ops.peer_barrier(self.handle.buffer_ptrs, self.rank, self.epoch, self.device)
 
 
+def _forward_impl(layer: "TokenParallelInt2Linear", x: torch.Tensor):
+    """Quantise this rank's tokens (into its row block of the gathered-token buffer when an update will follow), start
+    their all-gather, run the forward GEMM.  Returns (y [Ml, N], saved state for the backward pass or None, I/O dtype)."""
+    ops, K = layer.ops, layer.in_features
+    io = x.dtype if x.dtype in _FLOAT_IO else torch.bfloat16
+    x2 = x.reshape(-1, K)
+    if x2.dtype not in _FLOAT_IO:
+        x2 = x2.to(io)
+    Ml = x2.shape[0]
+    will_update = layer.training and layer.hysteresis_enabled
+    run = layer._run
+    if will_update:
+        bufs = layer._exchange_buffers(Ml)
+        own = bufs["xq_all"][layer.rank * Ml:(layer.rank + 1) * Ml]         # this rank's rows of the gathered tokens
+        Xq, ax = run("quantize_rows", ops.quantize_rows, x2, ACT_EPS, out=own)
+    else:
+        bufs = None
+        Xq, ax = run("quantize_rows", ops.quantize_rows, x2, ACT_EPS)
+    layer._weights_ready()                  # the other ranks' updated rows of W_packed have landed
+    if will_update and layer.world > 1:
+        layer._share_tokens(bufs, own, Ml)
+    y = run("gemm_fwd", ops.matmul_rows, Xq, layer.W_packed, ax, layer.gamma_value(), io)
+    return y, ((bufs, ax) if will_update else None), io
+
+
+def _backward_impl(layer: "TokenParallelInt2Linear", saved, dY: torch.Tensor, io: torch.dtype, need_dx: bool):
+    """Quantise this rank's gradient rows, run the dX GEMM on them and the weight update of this rank's rows, in the
+    layer's order.  Returns dX [Ml, K] or None."""
+    ops, K, N = layer.ops, layer.in_features, layer.out_features
+    run = layer._run
+    dY2 = dY.reshape(-1, N)
+    if dY2.dtype not in _FLOAT_IO:
+        dY2 = dY2.to(io)
+    if not dY2.is_contiguous():
+        dY2 = dY2.contiguous()
+    do_update = saved is not None and layer.training and layer.hysteresis_enabled
+    if do_update:
+        bufs, ax = saved
+        dYq, ady, gloc = run("quantize_rows_dy", ops.quantize_rows, dY2, GRAD_EPS, fold_absmax=ax)
+    else:
+        dYq, ady = run("quantize_rows_dy", ops.quantize_rows, dY2, GRAD_EPS)
+
+    def input_grad():
+        if not need_dx:
+            return None
+        return run("gemm_dx", ops.backward_input_rows, dYq, layer.W_packed, ady, layer.gamma_value(), K, io)
+
+    if do_update and layer.hysteresis_order == "reference":
+        layer._update(bufs, dY2, ax, gloc)             # as the reference's hook: before dX ...
+        layer._weights_ready()                         # ... which then reads every rank's updated rows
+        return input_grad()
+    dX = input_grad()
+    if do_update:
+        layer._update(bufs, dY2, ax, gloc)
+    return dX
+
+
 class _TokenParallelFn(Function):
     @staticmethod
     def forward(ctx, x: torch.Tensor, gamma: torch.Tensor, layer: "TokenParallelInt2Linear") -> torch.Tensor:
-        ops, K, N = layer.ops, layer.in_features, layer.out_features
-        io = x.dtype if x.dtype in _FLOAT_IO else torch.bfloat16
-        x2 = x.reshape(-1, K)
-        if x2.dtype not in _FLOAT_IO:
-            x2 = x2.to(io)
-        Ml = x2.shape[0]
-        will_update = layer.training and layer.hysteresis_enabled
-        run = layer._run
-        if will_update:
-            bufs = layer._exchange_buffers(Ml)
-            own = bufs["xq_all"][layer.rank * Ml:(layer.rank + 1) * Ml]         # this rank's rows of the gathered tokens
-            Xq, ax = run("quantize_rows", ops.quantize_rows, x2, ACT_EPS, out=own)
-        else:
-            bufs = None
-            Xq, ax = run("quantize_rows", ops.quantize_rows, x2, ACT_EPS)
-        layer._weights_ready()                  # the other ranks' updated rows of W_packed have landed
-        if will_update and layer.world > 1:
-            layer._share_tokens(bufs, own, Ml)
-        y = run("gemm_fwd", ops.matmul_rows, Xq, layer.W_packed, ax, layer.gamma_value(), io)
-        ctx.layer, ctx.io, ctx.x_shape = layer, io, x.shape
-        ctx.saved = (bufs, ax) if will_update else None
-        return y.view(*x.shape[:-1], N)
+        y, ctx.saved, ctx.io = _forward_impl(layer, x)
+        ctx.layer, ctx.x_shape = layer, x.shape
+        return y.view(*x.shape[:-1], layer.out_features)
 
     @staticmethod
     def backward(ctx, dY: torch.Tensor):
-        layer = ctx.layer
-        ops, K, N = layer.ops, layer.in_features, layer.out_features
-        run = layer._run
-        dY2 = dY.reshape(-1, N)
-        if dY2.dtype not in _FLOAT_IO:
-            dY2 = dY2.to(ctx.io)
-        if not dY2.is_contiguous():
-            dY2 = dY2.contiguous()
-        do_update = ctx.saved is not None and layer.training and layer.hysteresis_enabled
-        if do_update:
-            bufs, ax = ctx.saved
-            dYq, ady, gloc = run("quantize_rows_dy", ops.quantize_rows, dY2, GRAD_EPS, fold_absmax=ax)
-        else:
-            dYq, ady = run("quantize_rows_dy", ops.quantize_rows, dY2, GRAD_EPS)
-
-        def input_grad():
-            if not ctx.needs_input_grad[0]:
-                return None
-            dX = run("gemm_dx", ops.backward_input_rows, dYq, layer.W_packed, ady, layer.gamma_value(), K, ctx.io)
-            return dX.view(ctx.x_shape)
-
-        if do_update and layer.hysteresis_order == "reference":
-            layer._update(bufs, dY2, ax, gloc)             # as the reference's hook: before dX ...
-            layer._weights_ready()                         # ... which then reads every rank's updated rows
-            dX = input_grad()
-        else:
-            dX = input_grad()
-            if do_update:
-                layer._update(bufs, dY2, ax, gloc)
-        return dX, None, None
+        dX = _backward_impl(ctx.layer, ctx.saved, dY, ctx.io, ctx.needs_input_grad[0])
+        return (None if dX is None else dX.view(ctx.x_shape)), None, None
 
 
 class TokenParallelInt2Linear(nn.Module):
@@ -315,3 +325,11 @@ class TokenParallelInt2Linear(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return _TokenParallelFn.apply(x, self.gamma, self)
+
+    def train_step(self, x: torch.Tensor, dY: torch.Tensor, need_dx: bool = True):
+        """Forward, dX and the weight update for this rank's tokens x [Ml, K] with the output gradient dY [Ml, N], without
+        the autograd machinery around them (a trainer that schedules the layer itself; the benchmark).  Same kernels, same
+        order and same results as `layer(x)` followed by `backward(dY)`.  Returns (y, dX)."""
+        y, saved, io = _forward_impl(self, x)
+        dX = _backward_impl(self, saved, dY, io, need_dx)
+        return y, dX

@@ -5,10 +5,14 @@ absmax fake-quantisation of the activations, absmean ternary fake-quantisation o
 straight-through backward giving dX and dW), followed by the C restatement of the hysteresis kernel
 (oracle/int2_oracle.c, after kernels/int2/int2_hysteresis_v2.cu:54-152), which the reference only has in CUDA.
 The layer's RMSNorm is left out on both sides of the comparison: the GPU step starts at the quantiser too.
-Runs on all host threads torch and OpenMP give it.
+Every step is timed on ALL tokens of the workload (nothing is extrapolated), in bfloat16 and in float32 (the
+reference's layer is not tied to a dtype, and host cores without bfloat16 units run float32 faster); the caller
+reports the faster one.  The thread count is set explicitly, because launchers such as torch.distributed.run export
+OMP_NUM_THREADS=1.
 """
 from __future__ import annotations
 
+import os
 import time
 
 import numpy as np
@@ -17,6 +21,14 @@ import torch.nn.functional as F
 
 from . import int2_oracle as O
 from . import native
+
+
+def use_all_cores() -> int:
+    """All host cores for torch's and the C library's loops; returns the count in use."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    torch.set_num_threads(n)
+    native.oracle_lib().oracle_set_num_threads(n)
+    return n
 
 
 def _activation_quant(x: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
@@ -36,24 +48,31 @@ def _weight_quant(w: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
 class CpuLayer:
     """One [N,K] layer: latent float weights for the torch part, packed state for the hysteresis part."""
 
-    def __init__(self, K: int, N: int, dtype: torch.dtype, seed: int, counters: int = 3):
+    def __init__(self, K: int, N: int, seed: int, counters: int = 3):
         g = torch.Generator().manual_seed(seed)
-        self.K, self.N, self.dtype = K, N, dtype
-        self.weight = (torch.randn(N, K, generator=g) * 0.02).to(dtype).requires_grad_(True)
-        w32 = self.weight.detach().float().numpy()
+        self.K, self.N = K, N
+        self.master = torch.randn(N, K, generator=g) * 0.02
+        self.weights = {}
+        w32 = self.master.numpy()
         gamma = O.absmean_scale(w32)
         self.W_packed = O.pack_ternary(O.ternarize(w32, gamma))
         rng = np.random.default_rng(seed)
         self.H_packed = O.pack_counters(rng.integers(-counters, counters + 1, (N, K)).astype(np.int8))
         self.step = 0
 
+    def weight(self, dtype: torch.dtype) -> torch.Tensor:
+        if dtype not in self.weights:
+            self.weights[dtype] = self.master.to(dtype).requires_grad_(True)
+        return self.weights[dtype]
+
     def gemm_part(self, x: torch.Tensor, dY: torch.Tensor):
         """forward + backward (dX, dW) on the given tokens; returns dW float32 [N,K]."""
-        self.weight.grad = None
+        w = self.weight(x.dtype)
+        w.grad = None
         xin = x.detach().requires_grad_(True)
-        y = F.linear(_activation_quant(xin), _weight_quant(self.weight))
+        y = F.linear(_activation_quant(xin), _weight_quant(w))
         y.backward(dY)
-        return self.weight.grad.float().numpy()
+        return w.grad.float().numpy()
 
     def hysteresis_part(self, dW: np.ndarray, lr: float, threshold: int):
         self.step += 1
@@ -62,24 +81,19 @@ class CpuLayer:
                                    int(threshold), 0.001, self.step, self.N, self.K, 0, 1)
 
 
-def time_step(layers, M_full: int, M_sample: int, dtype: torch.dtype, lr: float = 1e-2, threshold: int = 3, seed: int = 0):
-    """Times one layer step on a bounded sample: the torch part (forward, dX, dW) on M_sample tokens, scaled to
-    M_full tokens, plus the hysteresis update of the whole weight matrix (its cost does not depend on M).
-    Returns (seconds per full step, seconds of CPU time actually spent)."""
+def time_step(layers, M: int, dtype: torch.dtype, lr: float = 1e-2, threshold: int = 3, seed: int = 0, dy_std: float = 1e-3):
+    """One full layer step on all M tokens in `dtype`: forward, dX, dW (torch) and the hysteresis update of every weight
+    (C).  Returns the wall-clock seconds of the step (input generation excluded)."""
     g = torch.Generator().manual_seed(seed)
-    t_gemm = 0.0
-    t_hyst = 0.0
+    total = 0.0
     for layer in layers:
-        x = torch.randn(M_sample, layer.K, generator=g).to(dtype)
-        dY = (torch.randn(M_sample, layer.N, generator=g) * 1e-3).to(dtype)
+        x = torch.randn(M, layer.K, generator=g).to(dtype)
+        dY = (torch.randn(M, layer.N, generator=g) * dy_std).to(dtype)
         t0 = time.perf_counter()
         dW = layer.gemm_part(x, dY)
-        t1 = time.perf_counter()
         layer.hysteresis_part(dW, lr, threshold)
-        t2 = time.perf_counter()
-        t_gemm += t1 - t0
-        t_hyst += t2 - t1
-    return t_gemm * (M_full / M_sample) + t_hyst, t_gemm + t_hyst
+        total += time.perf_counter() - t0
+    return total
 
 
 def cores_used() -> int:

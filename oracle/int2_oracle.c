@@ -44,6 +44,15 @@ ORACLE_API int oracle_num_threads(void) {
 #endif
 }
 
+/* Sets the number of worker threads of the OpenMP loops (a launcher may have exported OMP_NUM_THREADS=1). */
+ORACLE_API void oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 /*
  * Hysteresis update of an [N,K] weight matrix from a float32 gradient, in place.
  * idx_base offsets the random-number counter for a row shard of a larger matrix.
