@@ -128,8 +128,10 @@ static inline bool out_dtype_ok(int dt) { return dt == EL_F16 || dt == EL_BF16 |
 // Tensor-core launch: forward and dX run on CTA pairs unless the single-CTA kernel is asked for; dW has one kernel.
 static int launch_tc(int mode, bool single_cta, const int8_t* A, const void* B, int R, int C, int D, const EpiParams& epi,
                      int32_t* status, cudaStream_t st) {
-    if (mode != MODE_DW && !single_cta) return launch_gemm_tc2(mode, A, B, R, C, D, epi, status, st, nullptr, 0, 0, 0, 0, 0);
-    return launch_gemm_tc(mode, A, B, R, C, D, epi, status, st);
+    // The weight-gradient GEMM has one kernel: a CTA-pair version of it (half of the Xq columns per CTA) was built and
+    // measured 8-10 % slower than the single-CTA kernel at every size, and dropped.
+    if (single_cta || mode == MODE_DW) return launch_gemm_tc(mode, A, B, R, C, D, epi, status, st);
+    return launch_gemm_tc2(mode, A, B, R, C, D, epi, status, st, nullptr, 0, 0, 0, 0, 0);
 }
 
 static int gemm_dispatch(int mode, const int8_t* A, const void* B, int R, int C, int D, const EpiParams& epi, int flags,
@@ -143,7 +145,8 @@ static int gemm_dispatch(int mode, const int8_t* A, const void* B, int R, int C,
     // auto: the tensor-core tiles are 128 rows deep; very small problems go to the CUDA-core kernel.  A few rows against a
     // large weight matrix still belong on the tensor-core kernel: the call is then the time to stream the packed weights
     // once, which the CUDA-core kernel takes twenty times longer for.
-    if (elig == EL_OK && (R >= 32 || (long long)C * D >= (1ll << 18))) return launch_tc(mode, R <= 128, A, B, R, C, D, epi, status, st);
+    if (elig == EL_OK && (R >= 32 || (long long)C * D >= (1ll << 18)))
+        return launch_tc(mode, R <= 128, A, B, R, C, D, epi, status, st);
     return launch_gemm_simple(mode, A, B, R, C, D, epi, st);
 }
 

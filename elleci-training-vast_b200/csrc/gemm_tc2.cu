@@ -6,15 +6,20 @@
 // 128 bytes per reduction block) and one thread of the leader CTA issues 256-row MMAs that read both halves, so the
 // expansion work per MMA cycle is halved.  Per CTA and 128-deep reduction block:
 //   A   16 KB  activations, TMA, 128-byte swizzle, K-major           (counted on the leader's "a_full" barrier)
-//   P    4 KB  packed weights, TMA                                     (local "p_full" / "p_empty" barriers)
+//   P    4 KB  packed weights, plain 16-byte global loads into the transform warp's registers, one block ahead
 //   B   16 KB  expanded weights                                         (one arrival per CTA on the leader's "ready")
-// Three rings: A 5 deep, B and P 6 deep.  Each reduction block is expanded by ONE transform warp per CTA into
-// that warp's own B slot (six blocks are in flight on six warps), so a block's barrier, fence and signalling
-// latency overlaps with the other blocks' work.
+// Two rings: A and B, 6 deep each.  Each reduction block is expanded by ONE transform warp per CTA into that warp's own
+// B slot (six blocks are in flight on six warps), so a block's barrier, fence and signalling latency overlaps with
+// the other blocks' work.
+// The packed tile deliberately does NOT come through TMA.  A tile load costs the TMA unit about 2.5 cycles per box row
+// whatever the row's width (measured: with all MMAs removed the kernel still took 0.9 of its time, and 256 box rows per
+// block - 128 rows of 128 activation bytes and 128 rows of 32 packed bytes - came to ~690 cycles against the 512 cycles
+// the block's MMAs need).  The 32-byte packed rows cost as much as the 128-byte activation rows and carry a quarter of
+// the bytes, so they go through the load/store unit instead and the TMA unit only moves activations.
 // FWD reads B K-major (rows = output features n); DX reads the same image MN-major (rows = reduction index n,
 // 128 output columns k per CTA).  DX expands without the final byte interleave (decode16_deint), which permutes the
 // output columns inside groups of 16; the epilogue undoes that while the sums are in registers.
-// The leader commits each stage to the "empty" barriers of both CTAs, and each tile to both "tmem_full" barriers; no
+// The leader commits each stage to the "empty" barriers of both CTAs and each tile to both "tmem_full" barriers; no
 // cluster-multicast load or commit is used.  Every mbarrier wait is bounded (tc_ptx.cuh).
 #include "common.cuh"
 #include "epilogue.cuh"
@@ -31,14 +36,13 @@ using namespace tc;
 constexpr int BM = 128;            // rows per CTA (the pair covers 256)
 constexpr int BN = 256;            // output columns per pair tile (128 expanded per CTA)
 constexpr int BK = 128;
-constexpr int DA = 5;              // depth of the activation ring
+constexpr int DA = 6;              // depth of the activation ring
 constexpr int DB = 6;              // depth of the expanded-weight ring: one slot per transform warp
-constexpr int DP = 6;              // depth of the packed-tile ring: one slot per transform warp
-constexpr int A_BYTES = BM * BK, B_BYTES = 128 * BK, P_BYTES = 128 * BK / 4;
+constexpr int A_BYTES = BM * BK, B_BYTES = 128 * BK;
 constexpr int E_BYTES = 4 * 4096;   // epilogue staging for TMA stores: 4 KB per epilogue warp
-constexpr int SMEM_BYTES = DA * A_BYTES + DB * B_BYTES + DP * P_BYTES + E_BYTES + 1024 + 512;
-constexpr int WARP_TMA = 0, WARP_MMA = 1, NUM_EPI_WARPS = 4, WARP_PTMA = 6, WARP_XF0 = 7, NUM_XF_WARPS = 6;   // warps 2-5: epilogue
-constexpr int NUM_THREADS = (WARP_XF0 + NUM_XF_WARPS) * 32;     // 416
+constexpr int SMEM_BYTES = DA * A_BYTES + DB * B_BYTES + E_BYTES + 1024 + 512;
+constexpr int WARP_TMA = 0, WARP_MMA = 1, NUM_EPI_WARPS = 4, WARP_XF0 = 6, NUM_XF_WARPS = 6;   // warps 2-5: epilogue
+constexpr int NUM_THREADS = (WARP_XF0 + NUM_XF_WARPS) * 32;     // 384
 constexpr uint32_t TMEM_COLS = 2 * BN;
 
 constexpr int MAX_DST = 8;         // output destinations of one launch (the ranks of an N-sharded layer)
@@ -56,6 +60,8 @@ struct Params {
     int n_dst;                          // destinations that receive every output block (1 unless gathered over ranks)
     int rows_per_dst;                   // > 0: scatter instead - rows [d*rows_per_dst, (d+1)*rows_per_dst) go to destination d only
     int row_rotate;                     // scatter: row tiles are taken starting from this one (see tile_coords)
+    const uint8_t* Wp;                  // packed weights, row pitch ldw bytes: rows are output features (FWD) or the
+    long long ldw;                      // reduction index (DX); a row holds 4 weights per byte along the other index
     int32_t* status;
 };
 
@@ -78,25 +84,29 @@ __device__ __forceinline__ void tile_coords(int t, const Params& p, int& tr, int
 
 template <int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                const __grid_constant__ OutMaps outs, const Params p) {
+gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ OutMaps outs, const Params p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
     const uint32_t ring_b = smem_base + DA * A_BYTES;
-    const uint32_t ring_p = ring_b + DB * B_BYTES;
-    const uint32_t ring_e = ring_p + DP * P_BYTES;
+    const uint32_t ring_e = ring_b + DB * B_BYTES;
     const uint32_t bars = ring_e + E_BYTES;
-    uint8_t* bars_gen = smem_gen + DA * A_BYTES + DB * B_BYTES + DP * P_BYTES + E_BYTES;
-    auto bar_afull = [&](int s) { return bars + 8u * s; };                         // leader: both CTAs' A tiles landed
-    auto bar_aempty = [&](int s) { return bars + 8u * (DA + s); };                 // local: MMAs done with the A slot
-    auto bar_ready = [&](int s) { return bars + 8u * (2 * DA + s); };              // leader: both halves expanded
-    auto bar_bempty = [&](int s) { return bars + 8u * (2 * DA + DB + s); };        // local: MMAs done with the B slot
-    auto bar_pfull = [&](int s) { return bars + 8u * (2 * DA + 2 * DB + s); };     // local: packed tile landed
-    auto bar_pempty = [&](int s) { return bars + 8u * (2 * DA + 2 * DB + DP + s); };   // local: packed tile read
-    auto bar_tfull = [&](int a) { return bars + 8u * (2 * DA + 2 * DB + 2 * DP + a); };        // local: accumulator complete
-    auto bar_tempty = [&](int a) { return bars + 8u * (2 * DA + 2 * DB + 2 * DP + 2 + a); };   // leader: both epilogues done
-    volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(bars_gen + 8 * (2 * DA + 2 * DB + 2 * DP + 4));
+    uint8_t* bars_gen = smem_gen + DA * A_BYTES + DB * B_BYTES + E_BYTES;
+    // Stage s of the two rings is one unit: its A tile and its expanded B tile are filled, consumed and released together.
+    //   full   (leader's copy is used) one phase = both CTAs' A tiles landed (transaction bytes) + both halves expanded
+    //          (one arrival per CTA's transform warp) + the leader producer's expect-arrival
+    //   empty  (local) the MMAs that read stage s have completed
+    // With every data movement and every MMA removed, the handshakes of this kernel alone took more than half of its time
+    // when the MMA-issuing thread waited on two barriers and made four commits per block; it now waits on ONE barrier and
+    // makes TWO commits per block (one per CTA).  Passing the peer's release through the leader's producer instead of a
+    // second commit was tried and lost a third of the throughput: the handshake chain is latency-bound, and the relay
+    // added a hop to it.
+    auto bar_full = [&](int s) { return bars + 8u * s; };
+    auto bar_empty = [&](int s) { return bars + 8u * (DA + s); };
+    static_assert(DA == DB, "the A and B rings advance in lockstep");
+    auto bar_tfull = [&](int a) { return bars + 8u * (2 * DA + a); };        // local: accumulator complete
+    auto bar_tempty = [&](int a) { return bars + 8u * (2 * DA + 2 + a); };   // leader: both epilogues done
+    volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(bars_gen + 8 * (2 * DA + 4));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();            // 0 = leader
@@ -105,16 +115,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < DA; ++s) {
-            mbar_init(bar_afull(s), 1);
-            mbar_init(bar_aempty(s), 1);
-        }
-        for (int s = 0; s < DB; ++s) {
-            mbar_init(bar_ready(s), 2);
-            mbar_init(bar_bempty(s), 1);
-        }
-        for (int s = 0; s < DP; ++s) {
-            mbar_init(bar_pfull(s), 1);
-            mbar_init(bar_pempty(s), 1);
+            mbar_init(bar_full(s), 3);
+            mbar_init(bar_empty(s), 1);
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(bar_tfull(a), 1);
@@ -138,7 +140,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 
     if (warp == WARP_TMA) {
         // ================= activation producer: this CTA's 128 rows of every reduction block =================
-        if (lane == 0) {
+        // The whole warp waits (a warp whose lanes all wait on the barrier is woken sooner than a single waiting lane);
+        // lane 0 issues the copy.
+        {
             int s = 0;
             uint32_t ph = 0;
             for (int t = pair; t < num_tiles && !failed; t += num_pairs) {
@@ -146,67 +150,50 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 tile_coords(t, p, trow, tcol);
                 const int r0 = trow * (2 * BM) + (int)rank * BM;
                 for (int kb = 0; kb < p.k_blocks; ++kb) {
-                    if (!mbar_wait_cluster(bar_aempty(s), ph ^ 1u, p.status, 21)) { failed = true; break; }
-                    if (rank == 0) mbar_expect_tx(bar_afull(s), 2 * A_BYTES);
-                    tma_load_2d_pair(smem_base + s * A_BYTES, &tmA, mapa_u32(bar_afull(s), 0), kb * BK, r0);
+                    if (!mbar_wait_cluster_warp(bar_empty(s), ph ^ 1u, p.status, 21)) { failed = true; break; }
+                    if (lane == 0) {
+                        if (rank == 0) mbar_expect_tx(bar_full(s), 2 * A_BYTES);
+                        tma_load_2d_pair(smem_base + s * A_BYTES, &tmA, mapa_u32(bar_full(s), 0), kb * BK, r0);
+                    }
+                    __syncwarp();
                     if (++s == DA) { s = 0; ph ^= 1u; }
                 }
             }
         }
-    } else if (warp == WARP_PTMA) {
-        // ================= packed-weight producer: this CTA's half of the weight tile, running far ahead =================
-        if (lane == 0) {
-            int s = 0;
-            uint32_t ph = 0;
-            for (int t = pair; t < num_tiles && !failed; t += num_pairs) {
-                int trow, tcol;
-                tile_coords(t, p, trow, tcol);
-                const int c0 = tcol * BN + (int)rank * 128;     // this CTA's 128 output columns
-                for (int kb = 0; kb < p.k_blocks; ++kb) {
-                    if (!mbar_wait(bar_pempty(s), ph ^ 1u, p.status, 27)) { failed = true; break; }
-                    const uint32_t sp = ring_p + s * P_BYTES;
-                    const int d0 = kb * BK;
-                    mbar_expect_tx(bar_pfull(s), P_BYTES);
-                    if (MODE == MODE_FWD) tma_load_2d(sp, &tmB, bar_pfull(s), d0 >> 2, c0);     // rows n, 32 B of k
-                    else tma_load_2d(sp, &tmB, bar_pfull(s), c0 >> 2, d0);                      // rows n (reduction), 32 B of k
-                    if (++s == DP) { s = 0; ph ^= 1u; }
-                }
-            }
-        }
     } else if (warp == WARP_MMA) {
-        // ================= MMA issuer (leader CTA only) =================
-        if (lane == 0 && rank == 0) {
+        // ================= MMA issuer (leader CTA only): the whole warp waits, lane 0 issues =================
+        if (rank == 0) {
             constexpr uint32_t idesc = make_idesc(0, MODE == MODE_DX, BN, 2 * BM);
-            int sa = 0, sb = 0, it = 0;
-            uint32_t pha = 0, phb = 0;
+            int s = 0, it = 0;
+            uint32_t ph = 0;
             for (int t = pair; t < num_tiles && !failed; t += num_pairs, ++it) {
                 const int acc = it & 1;
                 const uint32_t acc_ph = (uint32_t)(it >> 1) & 1u;
-                if (!mbar_wait_cluster(bar_tempty(acc), acc_ph ^ 1u, p.status, 22)) { failed = true; break; }
+                if (!mbar_wait_cluster_warp(bar_tempty(acc), acc_ph ^ 1u, p.status, 22)) { failed = true; break; }
                 tcgen05_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
                 for (int kb = 0; kb < p.k_blocks; ++kb) {
-                    if (!mbar_wait_cluster(bar_afull(sa), pha, p.status, 23)) { failed = true; break; }
-                    if (!mbar_wait_cluster(bar_ready(sb), phb, p.status, 24)) { failed = true; break; }
+                    if (!mbar_wait_cluster_warp(bar_full(s), ph, p.status, 23)) { failed = true; break; }
                     tcgen05_fence_after();
-                    const uint32_t a_addr = smem_base + sa * A_BYTES, b_addr = ring_b + sb * B_BYTES;
+                    if (lane == 0) {
+                        const uint32_t a_addr = smem_base + s * A_BYTES, b_addr = ring_b + s * B_BYTES;
 #pragma unroll
-                    for (int k = 0; k < BK / 32; ++k) {
-                        const uint64_t da = make_desc(a_addr + k * 32, 16);
-                        const uint64_t db = (MODE == MODE_FWD) ? make_desc(b_addr + k * 32, 16) : make_desc(b_addr + k * 4096, 16384);
-                        umma_i8_pair(d_tmem, da, db, idesc, (kb | k) != 0);
+                        for (int k = 0; k < BK / 32; ++k) {
+                            const uint64_t da = make_desc(a_addr + k * 32, 16);
+                            const uint64_t db = (MODE == MODE_FWD) ? make_desc(b_addr + k * 32, 16) : make_desc(b_addr + k * 4096, 16384);
+                            umma_i8_pair(d_tmem, da, db, idesc, (kb | k) != 0);
+                        }
+                        umma_commit_pair(mapa_u32(bar_empty(s), 0));
+                        umma_commit_pair(mapa_u32(bar_empty(s), 1));
                     }
-                    umma_commit_pair(mapa_u32(bar_aempty(sa), 0));
-                    umma_commit_pair(mapa_u32(bar_aempty(sa), 1));
-                    umma_commit_pair(mapa_u32(bar_bempty(sb), 0));
-                    umma_commit_pair(mapa_u32(bar_bempty(sb), 1));
-                    if (++sa == DA) { sa = 0; pha ^= 1u; }
-                    if (++sb == DB) { sb = 0; phb ^= 1u; }
+                    __syncwarp();
+                    if (++s == DA) { s = 0; ph ^= 1u; }
                 }
-                if (!failed) {
+                if (!failed && lane == 0) {
                     umma_commit_pair(mapa_u32(bar_tfull(acc), 0));
                     umma_commit_pair(mapa_u32(bar_tfull(acc), 1));
                 }
+                __syncwarp();
             }
         }
     } else if (warp < WARP_XF0) {
@@ -228,7 +215,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             const float sc = row_ok ? epi_row_scale(p.epi, row) : 0.0f;
             const bool two_byte = (p.epi.out_dtype == EL_BF16 || p.epi.out_dtype == EL_F16);
             const uint32_t stage = ring_e + quarter * 4096;        // this warp's staging area
-            uint8_t* stage_gen = smem_gen + DA * A_BYTES + DB * B_BYTES + DP * P_BYTES + quarter * 4096;
+            uint8_t* stage_gen = smem_gen + DA * A_BYTES + DB * B_BYTES + quarter * 4096;
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
                 uint32_t v[32];
@@ -320,45 +307,67 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         if (lane == 0) bulk_wait_all();      // this warp's TMA stores have left shared memory and reached global memory
     } else {
         // ================= transform: 128 packed rows of 32 bytes -> 128 rows of 128 int8, swizzled =================
-        // Warp w expands the reduction blocks g = w, w+6, ... of this CTA's sequence on its own; lane l takes the
-        // 16-byte segments l, l+32, ... (row = segment/2) of the packed tile.
+        // Warp w expands the reduction blocks g = w, w+6, ... of this CTA's sequence (tile after tile, block after block)
+        // on its own; lane l takes the 16-byte segments l, l+32, ... (row = segment/2) of the packed tile, straight from
+        // global memory.  The loads of the warp's next block are issued before the current one is expanded, so their
+        // latency runs under five other blocks' worth of work.
         const int xw = warp - WARP_XF0;
-        int g = 0;
-        for (int t = pair; t < num_tiles && !failed; t += num_pairs) {
-            for (int kb = 0; kb < p.k_blocks; ++kb, ++g) {
-                if (g % NUM_XF_WARPS != xw) continue;
-                // Block g uses this warp's own packed slot and B slot (g % 6 == xw).  A barrier only tells the parity of
-                // its phase, so a waiter must never be two phases away from it: with one slot per warp the previous
-                // use of either slot was this warp's previous block (g-6).
-                static_assert(DP == NUM_XF_WARPS && DB == NUM_XF_WARPS, "one packed slot and one B slot per transform warp");
-                const int sp = xw, sb_i = xw;
-                const uint32_t php = (uint32_t)(g / DP) & 1u, phb = (uint32_t)(g / DB) & 1u;
-                if (!mbar_wait_warp(bar_pfull(sp), php, p.status, 26)) { failed = true; break; }
-                const uint8_t* src = smem_gen + DA * A_BYTES + DB * B_BYTES + sp * P_BYTES;
-                uint4 pk[8];
+        static_assert(DB == NUM_XF_WARPS, "one B slot per transform warp");
+        const int my_tiles = (num_tiles > pair) ? (num_tiles - pair + num_pairs - 1) / num_pairs : 0;
+        const long long total = (long long)my_tiles * p.k_blocks;
+        const uint4 zero_codes = make_uint4(0x55555555u, 0x55555555u, 0x55555555u, 0x55555555u);     // sixteen weights 0 per word
+        auto load_block = [&](long long g, uint4 (&pk)[8]) {
+            const int i = (int)(g / p.k_blocks), kb = (int)(g - (long long)i * p.k_blocks);
+            int trow, tcol;
+            tile_coords(pair + i * num_pairs, p, trow, tcol);
+            const int c0 = tcol * BN + (int)rank * 128;             // this CTA's 128 output columns
 #pragma unroll
-                for (int j = 0; j < 8; ++j) pk[j] = *reinterpret_cast<const uint4*>(src + (lane + 32 * j) * 16);
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar_pempty(sp));
-                if (!mbar_wait_warp(bar_bempty(sb_i), phb ^ 1u, p.status, 28)) { failed = true; break; }
-                uint8_t* sb = smem_gen + DA * A_BYTES + sb_i * B_BYTES;
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const int item = lane + 32 * j, row = item >> 1, seg = item & 1;
-                    const uint32_t px[4] = {pk[j].x, pk[j].y, pk[j].z, pk[j].w};
-                    uint8_t* dst_row = sb + row * 128;
-#pragma unroll
-                    for (int w = 0; w < 4; ++w) {
-                        uint32_t o[4];
-                        if (MODE == MODE_DX) decode16_deint(px[w], o);
-                        else decode16(px[w], o);
-                        const int chunk = seg * 4 + w;
-                        *reinterpret_cast<uint4*>(dst_row + ((chunk ^ (row & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
-                    }
+            for (int j = 0; j < 8; ++j) {
+                const int item = lane + 32 * j, row = item >> 1, seg = item & 1;
+                const uint8_t* src;
+                bool ok;
+                if (MODE == MODE_FWD) {         // rows = output features c0 + row, bytes = reduction indices kb*128 + seg*64 ..
+                    ok = (c0 + row < p.C) && (kb * BK + seg * 64 < p.D);
+                    src = p.Wp + (long long)(c0 + row) * p.ldw + kb * (BK / 4) + seg * 16;
+                } else {                        // rows = reduction indices kb*128 + row, bytes = output columns c0 + seg*64 ..
+                    ok = (kb * BK + row < p.D) && (c0 + seg * 64 < p.C);
+                    src = p.Wp + (long long)(kb * BK + row) * p.ldw + (c0 >> 2) + seg * 16;
                 }
-                fence_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(mapa_u32(bar_ready(sb_i), 0));
+                pk[j] = ok ? __ldg(reinterpret_cast<const uint4*>(src)) : zero_codes;
+            }
+        };
+        uint4 cur[8], nxt[8];
+        if (xw < total) load_block(xw, cur);
+        for (long long g = xw; g < total && !failed; g += NUM_XF_WARPS) {
+            const bool more = g + NUM_XF_WARPS < total;
+            if (more) load_block(g + NUM_XF_WARPS, nxt);
+            // Block g uses this warp's own B slot (g % 6 == xw).  A barrier only tells the parity of its phase, so a
+            // waiter must never be two phases away from it: with one slot per warp the previous use of the slot was this
+            // warp's previous block (g-6).
+            const int sb_i = xw;
+            const uint32_t phb = (uint32_t)(g / DB) & 1u;
+            if (!mbar_wait_warp(bar_empty(sb_i), phb ^ 1u, p.status, 28)) { failed = true; break; }
+            uint8_t* sb = smem_gen + DA * A_BYTES + sb_i * B_BYTES;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int item = lane + 32 * j, row = item >> 1, seg = item & 1;
+                const uint32_t px[4] = {cur[j].x, cur[j].y, cur[j].z, cur[j].w};
+                uint8_t* dst_row = sb + row * 128;
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    uint32_t o[4];
+                    if (MODE == MODE_DX) decode16_deint(px[w], o);
+                    else decode16(px[w], o);
+                    const int chunk = seg * 4 + w;
+                    *reinterpret_cast<uint4*>(dst_row + ((chunk ^ (row & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                }
+            }
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(mapa_u32(bar_full(sb_i), 0));
+            if (more) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) cur[j] = nxt[j];
             }
         }
     }
@@ -378,7 +387,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 }
 
 template <int MODE>
-static int launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB, const OutMaps& outs, Params& p, cudaStream_t st) {
+static int launch_t(const CUtensorMap& tmA, const OutMaps& outs, Params& p, cudaStream_t st) {
     static std::atomic<int> max_pairs[64];      // co-resident CTA pairs per device; 0 = not yet queried
     int dev = 0;
     EL_CUDA_TRY(cudaGetDevice(&dev));
@@ -420,7 +429,7 @@ static int launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB, const OutMap
     if (p.k_blocks == 0) return EL_ERR_UNSUPPORTED_SHAPE;
     const int pairs = (int)(tiles < dev_pairs ? tiles : dev_pairs);
     cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
-    EL_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<MODE>, tmA, tmB, outs, p));
+    EL_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<MODE>, tmA, outs, p));
     return check_launch();
 }
 
@@ -453,7 +462,7 @@ int launch_gemm_tc2(int mode, const int8_t* A, const void* B, int R, int C, int 
     p.status = status;
     const int esz = (epi.out_dtype == EL_BF16 || epi.out_dtype == EL_F16) ? 2 : 4;
     tc2::OutMaps outs{};
-    CUtensorMap tmA, tmB;
+    CUtensorMap tmA;
     if (dst != nullptr && rows_per_dst > 0) {
         if (n_dst < 1 || n_dst > tc2::MAX_DST || rows_per_dst % 32 != 0 || (long long)rows_per_dst * n_dst < R) return EL_ERR_INVALID_ARG;
         for (int d = 0; d < n_dst; ++d) {
@@ -485,12 +494,13 @@ int launch_gemm_tc2(int mode, const int8_t* A, const void* B, int R, int C, int 
         if (p.tma_store && (rc = tc::make_map_out(&outs.m[0], epi.out, C, R, (uint64_t)epi.ldo * esz, esz, 128 / esz)) != EL_OK) return rc;
     }
     if ((rc = tc::make_map(&tmA, A, D, R, D, 128, 128, true)) != EL_OK) return rc;
+    p.Wp = static_cast<const uint8_t*>(B);
     if (mode == MODE_FWD) {
-        if ((rc = tc::make_map(&tmB, B, D / 4, C, D / 4, 32, 128, false)) != EL_OK) return rc;
-        return tc2::launch_t<MODE_FWD>(tmA, tmB, outs, p, st);
+        p.ldw = D / 4;              // [C output features, D/4 bytes]
+        return tc2::launch_t<MODE_FWD>(tmA, outs, p, st);
     }
-    if ((rc = tc::make_map(&tmB, B, C / 4, D, C / 4, 32, 128, false)) != EL_OK) return rc;
-    return tc2::launch_t<MODE_DX>(tmA, tmB, outs, p, st);
+    p.ldw = C / 4;                  // [D reduction rows, C/4 bytes]
+    return tc2::launch_t<MODE_DX>(tmA, outs, p, st);
 }
 
 }  // namespace el

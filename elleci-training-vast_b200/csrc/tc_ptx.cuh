@@ -51,7 +51,8 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int32_t
     }
 }
 // The same for a whole warp: every lane polls, and the warp agrees on the outcome before it goes on to
-// warp-wide (.sync.aligned) instructions.
+// warp-wide (.sync.aligned) instructions.  (Polling with one lane and broadcasting the result was measured: the
+// forward GEMM lost a fifth of its throughput.  A waiting warp is woken sooner when all of its lanes wait.)
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, int32_t* status, int code) {
     const bool ok = mbar_wait(bar, parity, status, code);
     return __all_sync(0xffffffffu, ok);
@@ -180,6 +181,11 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
             }
         }
     }
+}
+// Whole-warp form of the cluster-scope wait (see mbar_wait_warp).
+__device__ __forceinline__ bool mbar_wait_cluster_warp(uint32_t bar, uint32_t parity, int32_t* status, int code) {
+    const bool ok = mbar_wait_cluster(bar, parity, status, code);
+    return __all_sync(0xffffffffu, ok);
 }
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");

@@ -175,6 +175,8 @@ class TokenParallelInt2Linear(nn.Module):
         self._w_ready_epoch = 0                 # fused path: W_packed is complete once the group's epoch has reached this
         self._tokens_pushed = None              # event on the side stream: this step's token push has been queued
         self._bufs: dict = {}
+        self._plans: dict = {}
+        self._step_dirty = False                # the `_step` buffer lags the Python counter (synced when the state is saved)
         self._run = lambda name, fn, *a, **k: fn(*a, **k)       # a benchmark replaces this to time the calls by name
         self.register_buffer("W_packed", torch.zeros(out_features, (in_features + 3) // 4, dtype=torch.uint8))
         self.register_buffer("H_packed", torch.zeros(self.local_out_features, (in_features + 1) // 2, dtype=torch.uint8))
@@ -329,7 +331,123 @@ class TokenParallelInt2Linear(nn.Module):
     def train_step(self, x: torch.Tensor, dY: torch.Tensor, need_dx: bool = True):
         """Forward, dX and the weight update for this rank's tokens x [Ml, K] with the output gradient dY [Ml, N], without
         the autograd machinery around them (a trainer that schedules the layer itself; the benchmark).  Same kernels, same
-        order and same results as `layer(x)` followed by `backward(dY)`.  Returns (y, dX)."""
+        order and same results as `layer(x)` followed by `backward(dY)`.  Returns (y, dX).  On the fused CUDA path the
+        step is issued from a prepared plan (buffers allocated once per token count, one library call per kernel), and
+        the returned tensors are the plan's own: they are overwritten by the next call with the same token count."""
+        if (self._use_fused() and self.training and self.hysteresis_enabled and x.dim() == 2 and dY.dim() == 2
+                and x.dtype in _FLOAT_IO and dY.dtype == x.dtype and x.is_contiguous() and dY.is_contiguous()
+                and self.ops.dw_hysteresis_supported(self.local_out_features, self.in_features)):
+            return self._planned_step(x, dY, need_dx)
         y, saved, io = _forward_impl(self, x)
         dX = _backward_impl(self, saved, dY, io, need_dx)
         return y, dX
+
+    # ---- the fused step from a prepared plan ---------------------------------------------------------------------------
+    def _make_plan(self, Ml: int, io: torch.dtype):
+        import ctypes
+        from types import SimpleNamespace
+        ops = self.ops
+        lib = ops._lib
+        dev = self.W_packed.device
+        g, r, K, N, Nl = self.world, self.rank, self.in_features, self.out_features, self.local_out_features
+        bufs = self._exchange_buffers(Ml)
+        P = SimpleNamespace()
+        P.lib, P.bufs, P.dt = lib.lib(), bufs, {torch.float16: lib.EL_F16, torch.bfloat16: lib.EL_BF16, torch.float32: lib.EL_F32}[io]
+        P.y = torch.empty(Ml, N, dtype=io, device=dev)
+        P.dx = torch.empty(Ml, K, dtype=io, device=dev)
+        P.ax = torch.empty(Ml, dtype=torch.float32, device=dev)
+        P.ady = torch.empty(Ml, dtype=torch.float32, device=dev)
+        P.dyq = torch.empty(Ml, N, dtype=torch.int8, device=dev)
+        P.gloc = torch.zeros(1, dtype=torch.float32, device=dev)
+        P.own = bufs["xq_all"][r * Ml:(r + 1) * Ml]
+        P.status = ops.device_status(dev).data_ptr()
+
+        def arr(ptrs):
+            a = (ctypes.c_void_p * len(ptrs))(*[int(p) for p in ptrs])
+            return a, ctypes.cast(a, ctypes.c_void_p)
+
+        P.keep = []
+        for name, ptrs in (("peers_x", [p for i, p in enumerate(bufs["hx"].buffer_ptrs) if i != r]),
+                           ("all_slots", list(bufs["hs"].buffer_ptrs)), ("all_gq", list(bufs["hg"].buffer_ptrs)),
+                           ("peers_w", [p for i, p in enumerate(self._w_handle.buffer_ptrs) if i != r]),
+                           ("flags", list(self._peer.handle.buffer_ptrs))):
+            a, c = arr(ptrs)
+            P.keep.append(a)
+            setattr(P, name, c)
+        return P
+
+    def _planned_step(self, x: torch.Tensor, dY: torch.Tensor, need_dx: bool):
+        Ml = x.shape[0]
+        key = (Ml, x.dtype)
+        P = self._plans.get(key)
+        if P is None:
+            P = self._plans[key] = self._make_plan(Ml, x.dtype)
+        lib, run, peer, bufs = P.lib, self._run, self._peer, P.bufs
+        g, r, K, N, Nl = self.world, self.rank, self.in_features, self.out_features, self.local_out_features
+        gam = self.gamma_value()
+        main = torch.cuda.current_stream()
+        st = main.cuda_stream
+        W, own_w = self.W_packed.data_ptr(), self.W_packed.data_ptr() + self.row_start * self.W_packed.shape[1]
+
+        def call(name, fn, *a):
+            rc = run(name, fn, *a)
+            if rc != 0:
+                self.ops._lib.check(name, rc)
+
+        def barrier(name):
+            peer.epoch += 1
+            call(name, lib.el_peer_barrier, P.flags, g, r, peer.epoch & 0xFFFFFFFF, P.status, st)
+
+        # forward: quantise into this rank's rows of the gathered tokens, push them to the peers beside the GEMM
+        call("quantize_rows", lib.el_quantize_rows, x.data_ptr(), P.dt, K, P.own.data_ptr(), P.ax.data_ptr(), Ml, K, ACT_EPS, 0,
+             None, None, st)
+        if peer.epoch < self._w_ready_epoch:
+            barrier("barrier_weights")
+        side = peer.side
+        side.wait_stream(main)
+        call("push_tokens", lib.el_peer_put, P.own.data_ptr(), P.peers_x, g - 1, r * Ml * K, Ml * K, self.push_ctas, side.cuda_stream)
+        pushed = torch.cuda.Event()
+        pushed.record(side)
+        call("gemm_fwd", lib.el_gemm_fwd, P.own.data_ptr(), W, P.y.data_ptr(), P.dt, P.ax.data_ptr(), 1, gam, Ml, N, K, 0, P.status, st)
+        # backward: quantise the gradient rows (with the fold that yields this rank's partial maximum)
+        P.gloc.zero_()
+        call("quantize_rows_dy", lib.el_quantize_rows, dY.data_ptr(), P.dt, N, P.dyq.data_ptr(), P.ady.data_ptr(), Ml, N, GRAD_EPS, 0,
+             P.ax.data_ptr(), P.gloc.data_ptr(), st)
+
+        def input_grad():
+            if need_dx:
+                call("gemm_dx", lib.el_gemm_dx, P.dyq.data_ptr(), W, P.dx.data_ptr(), P.dt, P.ady.data_ptr(), 1, gam, Ml, N, K, 0,
+                     P.status, st)
+
+        def update():
+            self._step_py += 1
+            self._step_dirty = True
+            call("push_gmax", lib.el_peer_put, P.gloc.data_ptr(), P.all_slots, g, 4 * r, 4, 0, st)
+            main.wait_event(pushed)
+            barrier("barrier_gmax")
+            call("quantize_grad", lib.el_quantize_grad_scatter, dY.data_ptr(), P.dt, N, P.ax.data_ptr(), bufs["slots"].data_ptr(), g,
+                 bufs["gmax"].data_ptr(), P.all_gq, g, r * Ml, Ml, N, st)
+            barrier("barrier_grad")
+            step32 = self._step_py & 0xFFFFFFFF
+            call("gemm_dw_hysteresis", lib.el_dw_hysteresis, bufs["gq_recv"].data_ptr(), bufs["xq_all"].data_ptr(),
+                 bufs["gmax"].data_ptr(), own_w, self.H_packed.data_ptr(), float(self._lr), float(self.lr_scale), int(self.threshold),
+                 float(self.decay_rate), step32 - (1 << 32) if step32 >= (1 << 31) else step32,
+                 (self.row_start * K) & 0xFFFFFFFF, g * Ml, Nl, K, P.status, st)
+            call("push_weights", lib.el_peer_put, own_w, P.peers_w, g - 1, self.row_start * self.W_packed.shape[1],
+                 Nl * self.W_packed.shape[1], 0, st)
+            self._w_ready_epoch = peer.epoch + 1
+
+        if self.hysteresis_order == "reference":
+            update()
+            barrier("barrier_weights")
+            input_grad()
+        else:
+            input_grad()
+            update()
+        return P.y, (P.dx if need_dx else None)
+
+    def _save_to_state_dict(self, destination, prefix, keep_vars):
+        if self._step_dirty:
+            self._step.fill_(self._step_py)
+            self._step_dirty = False
+        super()._save_to_state_dict(destination, prefix, keep_vars)

@@ -114,19 +114,25 @@ def _tp_worker(rank, world, port, order, out_dir, fused):
         for li, layer in enumerate(layers):
             x = d["x"][rows].to(dev).requires_grad_(True)
             outs.append([layer, x, None])
+        dy = d["dY"][rows].to(dev)
+        grads = [None, None]
         for _ in range(STEPS):
-            for o in outs:
+            for li, o in enumerate(outs):
                 layer, x, _ = o
-                x.grad = None
-                y = layer(x)
-                y.backward(d["dY"][rows].to(dev))
-                o[2] = y
+                if li == 0:                              # through autograd
+                    x.grad = None
+                    y = layer(x)
+                    y.backward(dy)
+                    o[2], grads[li] = y.detach(), x.grad
+                else:                                    # the same step issued directly (from the prepared plan when fused)
+                    o[2], grads[li] = layer.train_step(x.detach(), dy)
         for o in outs:
             o[0]._weights_ready()                        # the last pushes of updated rows have landed in this replica
         torch.cuda.synchronize()
         pkg.int2_tc_ops.check_device_status(dev)
-        torch.save([{"y": y.detach().cpu(), "dx": x.grad.cpu(), "W": layer.W_packed.cpu(), "H": layer.H_packed.cpu(),
-                     "rows": (layer.row_start, layer.row_stop)} for layer, x, y in outs], os.path.join(out_dir, f"rank{rank}.pt"))
+        torch.save([{"y": y.cpu(), "dx": grads[li].cpu(), "W": layer.W_packed.cpu(), "H": layer.H_packed.cpu(),
+                     "rows": (layer.row_start, layer.row_stop), "step": int(layer.state_dict()["_step"])}
+                    for li, (layer, x, y) in enumerate(outs)], os.path.join(out_dir, f"rank{rank}.pt"))
     finally:
         dist.destroy_process_group()
 
@@ -169,3 +175,4 @@ def test_token_parallel_steps_on_gpus_equal_single_gpu(tmp_path, order, fused):
             assert torch.equal(res[li]["dx"], x.grad.cpu()[r * Ml:(r + 1) * Ml]), (r, li)
             assert torch.equal(res[li]["W"], ref.W_packed.cpu()), (r, li)
             assert torch.equal(res[li]["H"], ref.H_packed.cpu()[a:b]), (r, li)
+            assert res[li]["step"] == STEPS
