@@ -52,6 +52,7 @@ SIGNATURES = {
     "el_set_decode_gemv_max_tokens": [_i],
     "el_set_decode_overlap": [_i],
     "el_peer_barrier": [_vp, _i, _i, _u32, _vp, _vp],
+    "el_peer_barrier_put": [_vp, _i, _i, _u32, _vp, _vp, _vp, C.c_size_t, _vp],
     "el_set_decode_mma_max_tokens": [_i],
     "el_set_peer_barrier_limit_us": [_ll],
     "el_peer_put": [_vp, _vp, _i, C.c_size_t, C.c_size_t, _i, _vp],

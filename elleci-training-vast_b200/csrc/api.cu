@@ -52,7 +52,7 @@ int launch_swiglu_backward(const void* gy, const void* gate, const void* up, int
                            const float* rstd, void* d_gate, void* d_up, long long ld_d, float* dweight, void* workspace,
                            size_t workspace_bytes, int M, int H, cudaStream_t st);
 int launch_peer_barrier(unsigned int* const* flags_all, int n_ranks, int rank, unsigned int epoch, int32_t* status,
-                        cudaStream_t st);
+                        cudaStream_t st, const void* put_src, void* const* put_dst_all, size_t put_offset);
 int set_peer_barrier_limit_us(long long us);
 int launch_quantize_grad_scatter(const void* dY, int dt, long long ld, const float* xa, const float* g_slots, int n_slots,
                                  float* g_out, void* const* Gq_all, int n_ranks, long long row_offset, int M, int N,
@@ -366,7 +366,16 @@ int el_peer_barrier(uint32_t* const* flags_all, int n_ranks, int rank, uint32_t 
     const int rc = require_sm100();
     if (rc != EL_OK) return rc;
     return launch_peer_barrier(reinterpret_cast<unsigned int* const*>(flags_all), n_ranks, rank, epoch, dev_status,
-                               (cudaStream_t)stream);
+                               (cudaStream_t)stream, nullptr, nullptr, 0);
+}
+
+int el_peer_barrier_put(uint32_t* const* flags_all, int n_ranks, int rank, uint32_t epoch, int32_t* dev_status, const void* word,
+                        void* const* dst_all, size_t dst_offset, el_stream_t stream) {
+    if (!flags_all || !word || !dst_all) return EL_ERR_NULL_PTR;
+    const int rc = require_sm100();
+    if (rc != EL_OK) return rc;
+    return launch_peer_barrier(reinterpret_cast<unsigned int* const*>(flags_all), n_ranks, rank, epoch, dev_status,
+                               (cudaStream_t)stream, word, dst_all, dst_offset);
 }
 
 int el_quantize_grad_scatter(const void* dY, int dy_dtype, long long ld_dy, const float* x_absmax, const float* g_slots,

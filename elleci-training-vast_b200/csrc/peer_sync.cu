@@ -20,12 +20,15 @@ std::atomic<long long> g_wait_limit_us{0};       // 0 = the default above
 
 struct PeerFlags {
     unsigned int* p[PEER_MAX];
+    unsigned int* put_dst[PEER_MAX];     // optional payload: one 32-bit word delivered to every rank ahead of the flag
 };
 
 __global__ void __launch_bounds__(32)
-peer_barrier_kernel(PeerFlags flags, int n_ranks, int rank, unsigned int epoch, long long limit_cycles, int32_t* status) {
+peer_barrier_kernel(PeerFlags flags, int n_ranks, int rank, unsigned int epoch, long long limit_cycles, int32_t* status,
+                    const unsigned int* put_src) {
     const int i = threadIdx.x;
     if (i >= n_ranks) return;
+    if (put_src != nullptr) *flags.put_dst[i] = *put_src;      // ordered before the flag by the fence and the release below
     __threadfence_system();
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags.p[i] + rank), "r"(epoch) : "memory");
     const unsigned int* mine = flags.p[rank] + i;
@@ -50,13 +53,20 @@ int set_peer_barrier_limit_us(long long us) {
 }
 
 int launch_peer_barrier(unsigned int* const* flags_all, int n_ranks, int rank, unsigned int epoch, int32_t* status,
-                        cudaStream_t st) {
+                        cudaStream_t st, const void* put_src, void* const* put_dst_all, size_t put_offset) {
     if (n_ranks < 1 || n_ranks > PEER_MAX || rank < 0 || rank >= n_ranks) return EL_ERR_INVALID_ARG;
+    if ((put_src != nullptr) != (put_dst_all != nullptr)) return EL_ERR_INVALID_ARG;
+    if (put_src != nullptr && ((reinterpret_cast<uintptr_t>(put_src) | put_offset) & 3)) return EL_ERR_ALIGNMENT;
     PeerFlags f{};
     for (int i = 0; i < n_ranks; ++i) {
         if (flags_all[i] == nullptr) return EL_ERR_NULL_PTR;
         if (reinterpret_cast<uintptr_t>(flags_all[i]) & 3) return EL_ERR_ALIGNMENT;
         f.p[i] = flags_all[i];
+        if (put_src != nullptr) {
+            if (put_dst_all[i] == nullptr) return EL_ERR_NULL_PTR;
+            if (reinterpret_cast<uintptr_t>(put_dst_all[i]) & 3) return EL_ERR_ALIGNMENT;
+            f.put_dst[i] = reinterpret_cast<unsigned int*>(static_cast<char*>(put_dst_all[i]) + put_offset);
+        }
     }
     long long limit = PEER_WAIT_CYCLES;
     const long long us = g_wait_limit_us.load(std::memory_order_relaxed);
@@ -66,7 +76,7 @@ int launch_peer_barrier(unsigned int* const* flags_all, int n_ranks, int rank, u
         EL_CUDA_TRY(cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, dev));     // the SM clock's maximum, kHz
         limit = us * (long long)(khz > 0 ? khz : 2000000) / 1000;
     }
-    peer_barrier_kernel<<<1, 32, 0, st>>>(f, n_ranks, rank, epoch, limit, status);
+    peer_barrier_kernel<<<1, 32, 0, st>>>(f, n_ranks, rank, epoch, limit, status, static_cast<const unsigned int*>(put_src));
     return check_launch();
 }
 

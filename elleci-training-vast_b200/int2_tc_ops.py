@@ -513,6 +513,18 @@ def peer_barrier(flag_ptrs, rank: int, epoch: int, device: torch.device) -> None
     call("el_peer_barrier", arr, len(flag_ptrs), int(rank), int(epoch) & 0xFFFFFFFF, st.data_ptr(), _stream())
 
 
+def peer_barrier_put(flag_ptrs, rank: int, epoch: int, device: torch.device, word: torch.Tensor, dst_ptrs, dst_offset_bytes: int) -> None:
+    """peer_barrier that first delivers the 4-byte tensor `word` to byte offset `dst_offset_bytes` of every rank's buffer in
+    `dst_ptrs`: after it, every rank holds every rank's word."""
+    _cuda(word, "word")
+    _require(word.numel() * word.element_size() == 4, "word must hold exactly four bytes")
+    keep, arr = _ptr_array(flag_ptrs)
+    keep2, arr2 = _ptr_array(dst_ptrs)
+    st = device_status(device)
+    call("el_peer_barrier_put", arr, len(flag_ptrs), int(rank), int(epoch) & 0xFFFFFFFF, st.data_ptr(), word.data_ptr(), arr2,
+         int(dst_offset_bytes), _stream())
+
+
 def backward_input_rows(dYq: torch.Tensor, W_packed: torch.Tensor, row_absmax: torch.Tensor, gamma: float, K: int,
                         out_dtype: torch.dtype = torch.bfloat16, path: int = EL_PATH_AUTO) -> torch.Tensor:
     """dX[m,:] = (dYq[m,:] @ W) * (row_absmax[m]/127) * gamma: the dX GEMM with per-token scales."""

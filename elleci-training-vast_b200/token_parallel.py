@@ -57,6 +57,7 @@ class PeerGroup:
         self.handle.barrier(channel=0)              # every rank's flags are zero before anybody signals
         self.epoch = 0
         self.side = torch.cuda.Stream(device=device)
+        self.pending = None             # event of the last push queued on the side stream and not yet joined
 
     @classmethod
     def get(cls, group, device: torch.device, ops) -> "PeerGroup":
@@ -65,10 +66,22 @@ class PeerGroup:
             cls._cache[key] = cls(group, device, ops)
         return cls._cache[key]
 
-    def barrier(self) -> None:
-        """All ranks have finished the work queued on their main streams so far, peer stores included."""
+    def join_side(self) -> None:
+        """Pushes queued on the side stream are ordered before whatever the main stream does next (a barrier)."""
+        if self.pending is not None:
+            torch.cuda.current_stream().wait_event(self.pending)
+            self.pending = None
+
+    def barrier(self, word: Optional[torch.Tensor] = None, dst_ptrs=None, dst_offset: int = 0) -> None:
+        """All ranks have finished the work queued on their main streams so far - and on the side stream before this
+        call - peer stores included.  With `word` (4 bytes) the barrier also delivers it to `dst_offset` of every rank's
+        buffer in `dst_ptrs`."""
+        self.join_side()
         self.epoch += 1
-        self.ops.peer_barrier(self.handle.buffer_ptrs, self.rank, self.epoch, self.device)
+        if word is None:
+            self.ops.peer_barrier(self.handle.buffer_ptrs, self.rank, self.epoch, self.device)
+        else:
+            self.ops.peer_barrier_put(self.handle.buffer_ptrs, self.rank, self.epoch, self.device, word, dst_ptrs, dst_offset)
 
 
 def _forward_impl(layer: "TokenParallelInt2Linear", x: torch.Tensor):
@@ -173,7 +186,6 @@ class TokenParallelInt2Linear(nn.Module):
         self._peer: Optional[PeerGroup] = None
         self._w_handle = None
         self._w_ready_epoch = 0                 # fused path: W_packed is complete once the group's epoch has reached this
-        self._tokens_pushed = None              # event on the side stream: this step's token push has been queued
         self._bufs: dict = {}
         self._plans: dict = {}
         self._step_dirty = False                # the `_step` buffer lags the Python counter (synced when the state is saved)
@@ -274,8 +286,8 @@ class TokenParallelInt2Linear(nn.Module):
             peers = [p for i, p in enumerate(bufs["hx"].buffer_ptrs) if i != self.rank]
             with torch.cuda.stream(side):
                 self._run("push_tokens", self.ops.peer_put, own, peers, self.rank * Ml * self.in_features, self.push_ctas)
-                self._tokens_pushed = torch.cuda.Event()
-                self._tokens_pushed.record(side)
+                self._peer.pending = torch.cuda.Event()
+                self._peer.pending.record(side)
         else:
             self._run("all_gather_tokens", dist.all_gather_into_tensor, bufs["xq_all"], own.clone(), group=self.group)
 
@@ -291,11 +303,9 @@ class TokenParallelInt2Linear(nn.Module):
             gq = run("quantize_grad", ops.quantize_grad, dY2, ax, gmax)
         elif self._use_fused():
             peer = self._peer
-            run("push_gmax", ops.peer_put, gloc, list(bufs["hs"].buffer_ptrs), 4 * r)     # slot r of every rank
-            if self._tokens_pushed is not None:
-                torch.cuda.current_stream().wait_event(self._tokens_pushed)                # the token push precedes the barrier
-                self._tokens_pushed = None
-            run("barrier_gmax", peer.barrier)           # all partial maxima and all tokens have landed
+            # the barrier carries this rank's partial maximum to slot r of every rank; after it all maxima and (the side
+            # stream is joined first) all tokens have landed
+            run("barrier_gmax", peer.barrier, gloc, list(bufs["hs"].buffer_ptrs), 4 * r)
             gmax = bufs["gmax"]
             run("quantize_grad", ops.quantize_grad_scatter, dY2, ax, bufs["slots"][:g], list(bufs["hg"].buffer_ptrs), r * Ml, gmax)
             run("barrier_grad", peer.barrier)           # every rank's window of the gradient has landed
@@ -319,8 +329,14 @@ class TokenParallelInt2Linear(nn.Module):
         if g == 1:
             return
         if self._use_fused():
+            # the updated rows go out on the side stream, under whatever the main stream does until the next barrier
             peers = [p for i, p in enumerate(self._w_handle.buffer_ptrs) if i != r]
-            run("push_weights", ops.peer_put, own, peers, self.row_start * self.W_packed.shape[1])
+            main, side = torch.cuda.current_stream(), self._peer.side
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                run("push_weights", ops.peer_put, own, peers, self.row_start * self.W_packed.shape[1], self.push_ctas)
+                self._peer.pending = torch.cuda.Event()
+                self._peer.pending.record(side)
             self._w_ready_epoch = self._peer.epoch + 1          # complete after the next barrier, whoever queues it
         else:
             run("all_gather_weights", dist.all_gather_into_tensor, self.W_packed, own.clone(), group=self.group)
@@ -394,9 +410,14 @@ class TokenParallelInt2Linear(nn.Module):
             if rc != 0:
                 self.ops._lib.check(name, rc)
 
-        def barrier(name):
+        def barrier(name, with_gmax=False):
+            peer.join_side()
             peer.epoch += 1
-            call(name, lib.el_peer_barrier, P.flags, g, r, peer.epoch & 0xFFFFFFFF, P.status, st)
+            if with_gmax:       # the barrier carries this rank's partial maximum to slot r of every rank
+                call(name, lib.el_peer_barrier_put, P.flags, g, r, peer.epoch & 0xFFFFFFFF, P.status, P.gloc.data_ptr(),
+                     P.all_slots, 4 * r, st)
+            else:
+                call(name, lib.el_peer_barrier, P.flags, g, r, peer.epoch & 0xFFFFFFFF, P.status, st)
 
         # forward: quantise into this rank's rows of the gathered tokens, push them to the peers beside the GEMM
         call("quantize_rows", lib.el_quantize_rows, x.data_ptr(), P.dt, K, P.own.data_ptr(), P.ax.data_ptr(), Ml, K, ACT_EPS, 0,
@@ -405,9 +426,10 @@ class TokenParallelInt2Linear(nn.Module):
             barrier("barrier_weights")
         side = peer.side
         side.wait_stream(main)
-        call("push_tokens", lib.el_peer_put, P.own.data_ptr(), P.peers_x, g - 1, r * Ml * K, Ml * K, self.push_ctas, side.cuda_stream)
-        pushed = torch.cuda.Event()
-        pushed.record(side)
+        with torch.cuda.stream(side):
+            call("push_tokens", lib.el_peer_put, P.own.data_ptr(), P.peers_x, g - 1, r * Ml * K, Ml * K, self.push_ctas, side.cuda_stream)
+        peer.pending = torch.cuda.Event()
+        peer.pending.record(side)
         call("gemm_fwd", lib.el_gemm_fwd, P.own.data_ptr(), W, P.y.data_ptr(), P.dt, P.ax.data_ptr(), 1, gam, Ml, N, K, 0, P.status, st)
         # backward: quantise the gradient rows (with the fold that yields this rank's partial maximum)
         P.gloc.zero_()
@@ -422,9 +444,7 @@ class TokenParallelInt2Linear(nn.Module):
         def update():
             self._step_py += 1
             self._step_dirty = True
-            call("push_gmax", lib.el_peer_put, P.gloc.data_ptr(), P.all_slots, g, 4 * r, 4, 0, st)
-            main.wait_event(pushed)
-            barrier("barrier_gmax")
+            barrier("barrier_gmax", with_gmax=True)
             call("quantize_grad", lib.el_quantize_grad_scatter, dY.data_ptr(), P.dt, N, P.ax.data_ptr(), bufs["slots"].data_ptr(), g,
                  bufs["gmax"].data_ptr(), P.all_gq, g, r * Ml, Ml, N, st)
             barrier("barrier_grad")
@@ -433,8 +453,12 @@ class TokenParallelInt2Linear(nn.Module):
                  bufs["gmax"].data_ptr(), own_w, self.H_packed.data_ptr(), float(self._lr), float(self.lr_scale), int(self.threshold),
                  float(self.decay_rate), step32 - (1 << 32) if step32 >= (1 << 31) else step32,
                  (self.row_start * K) & 0xFFFFFFFF, g * Ml, Nl, K, P.status, st)
-            call("push_weights", lib.el_peer_put, own_w, P.peers_w, g - 1, self.row_start * self.W_packed.shape[1],
-                 Nl * self.W_packed.shape[1], 0, st)
+            side.wait_stream(main)          # the updated rows go out on the side stream, under the main stream's next work
+            with torch.cuda.stream(side):
+                call("push_weights", lib.el_peer_put, own_w, P.peers_w, g - 1, self.row_start * self.W_packed.shape[1],
+                     Nl * self.W_packed.shape[1], self.push_ctas, side.cuda_stream)
+            peer.pending = torch.cuda.Event()
+            peer.pending.record(side)
             self._w_ready_epoch = peer.epoch + 1
 
         if self.hysteresis_order == "reference":

@@ -244,6 +244,12 @@ EL_API int el_reduce_scale_gather(const int32_t* parts, void* const* dX_all, int
  * code 40 + its index in *dev_status.  No counterpart in the reference. */
 EL_API int el_peer_barrier(uint32_t* const* flags_all, int n_ranks, int rank, uint32_t epoch, int32_t* dev_status,
                            el_stream_t stream);
+/* el_peer_barrier that also delivers one 32-bit word: before it publishes its epoch, the rank copies `word` (device
+ * memory, 4 bytes) to byte offset dst_offset of every rank's buffer dst_all[i]; after the barrier every rank holds every
+ * rank's word (each rank passes its own offset).  The token-parallel layer exchanges its partial gradient maxima this
+ * way, in the barrier it needs anyway, instead of with a launch of its own.  No counterpart in the reference. */
+EL_API int el_peer_barrier_put(uint32_t* const* flags_all, int n_ranks, int rank, uint32_t epoch, int32_t* dev_status,
+                               const void* word, void* const* dst_all, size_t dst_offset, el_stream_t stream);
 /* Bound of el_peer_barrier's wait, process-wide, for barriers queued from now on: microseconds > 0 sets it, 0 restores
  * the default of a few seconds.  A health check (or a test) that wants a missing rank reported within a millisecond
  * instead of seconds sets it; the barrier then returns with code 40 + rank in *dev_status and the device stays usable. */

@@ -586,6 +586,16 @@ def test_peer_barrier_reports_a_rank_that_never_arrives_and_leaves_the_device_us
         ops.peer_barrier(ptrs, 0, 2, dev)
         torch.cuda.synchronize()
         ops.check_device_status(dev)
+        # a barrier that carries a word: rank 0's value lands at its offset of every rank's buffer before the epoch does
+        word = torch.tensor([3.25], dtype=torch.float32, device=DEV)
+        slots = [torch.zeros(8, dtype=torch.float32, device=DEV) for _ in range(2)]
+        flags[0][1] = 3
+        ops.peer_barrier_put(ptrs, 0, 3, dev, word, [s_.data_ptr() for s_ in slots], 4 * 5)
+        torch.cuda.synchronize()
+        ops.check_device_status(dev)
+        for s_ in slots:
+            assert s_[5].item() == 3.25 and float(s_.sum()) == 3.25
+        assert flags[0][0].item() == 3 and flags[1][0].item() == 3
         # and the device still computes
         Wp, w = random_packed(64, 64, 5)
         out = torch.empty(64, 64, dtype=torch.int8, device=DEV)
