@@ -35,6 +35,9 @@ SIGNATURES = {
     "el_quantize_grad": [_vp, _i, _ll, _vp, _vp, _vp, _i, _i, _vp],
     "el_scale_rows": [_vp, _vp, _i, _vp, _i, _f, _i, _i, _vp],
     "el_gemm_fwd": [_vp, _vp, _vp, _i, _vp, _i, _f, _i, _i, _i, _i, _vp, _vp],
+    "el_gemm_workspace_bytes": [_i, _i, _i, _i],
+    "el_gemm_fwd_ws": [_vp, _vp, _vp, _i, _vp, _i, _f, _i, _i, _i, _i, _vp, C.c_size_t, _vp, _vp],
+    "el_gemm_dx_ws": [_vp, _vp, _vp, _i, _vp, _i, _f, _i, _i, _i, _i, _vp, C.c_size_t, _vp, _vp],
     "el_gemm_fwd_gather": [_vp, _vp, _vp, _i, _ll, _ll, _i, _vp, _i, _f, _i, _i, _i, _vp, _vp],
     "el_gemm_dx_scatter": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp],
     "el_reduce_scale_gather": [_vp, _vp, _i, _i, _i, _vp, _f, _i, _i, _vp],
@@ -88,7 +91,8 @@ def lib() -> C.CDLL:
             fn = getattr(handle, name)
             fn.argtypes = argtypes
             fn.restype = (C.c_char_p if name == "el_status_string" else
-                          C.c_size_t if name in ("el_decode_workspace_bytes", "el_rmsnorm_backward_workspace_bytes", "el_swiglu_backward_workspace_bytes") else C.c_int)
+                          C.c_size_t if name in ("el_decode_workspace_bytes", "el_rmsnorm_backward_workspace_bytes", "el_swiglu_backward_workspace_bytes",
+                                                "el_gemm_workspace_bytes") else C.c_int)
         _lib = handle
     return _lib
 

@@ -53,6 +53,7 @@ struct OutMaps {
 struct Params {
     int R, C, D;
     int tiles_r, tiles_c, k_blocks;     // tiles_r counts 256-row pair tiles
+    int k_split, kbp;                   // reduction split: k_split work items of kbp blocks per output tile (1, k_blocks = none)
     int group_rows;                     // row tiles per band of the tile order (see tile_coords)
     EpiParams epi;
     int vec_ok;
@@ -80,6 +81,15 @@ __device__ __forceinline__ void tile_coords(int t, const Params& p, int& tr, int
     // time the ranks store into different owners (one sender per receiving link) instead of all into the same one.
     tr += p.row_rotate;
     if (tr >= p.tiles_r) tr -= p.tiles_r;
+}
+
+// Work item w -> output tile and the first reduction block of its part.  With a split reduction the parts of one tile
+// are num_tiles items apart, so they run on different pairs at the same time; part q writes its int32 partial sums
+// to output q, and a second pass adds the parts and scales.
+__device__ __forceinline__ void item_coords(int w, int num_tiles, const Params& p, int& tr, int& tc, int& part, int& kb0) {
+    part = w / num_tiles;
+    tile_coords(w - part * num_tiles, p, tr, tc);
+    kb0 = part * p.kbp;
 }
 
 template <int MODE>
@@ -112,6 +122,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const uint32_t rank = cluster_ctarank();            // 0 = leader
     const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
     const int num_tiles = p.tiles_r * p.tiles_c;
+    const int num_items = num_tiles * p.k_split;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < DA; ++s) {
@@ -145,11 +156,11 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         {
             int s = 0;
             uint32_t ph = 0;
-            for (int t = pair; t < num_tiles && !failed; t += num_pairs) {
-                int trow, tcol;
-                tile_coords(t, p, trow, tcol);
+            for (int w = pair; w < num_items && !failed; w += num_pairs) {
+                int trow, tcol, part, kb0;
+                item_coords(w, num_tiles, p, trow, tcol, part, kb0);
                 const int r0 = trow * (2 * BM) + (int)rank * BM;
-                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                for (int kb = kb0; kb < kb0 + p.kbp; ++kb) {
                     if (!mbar_wait_cluster_warp(bar_empty(s), ph ^ 1u, p.status, 21)) { failed = true; break; }
                     if (lane == 0) {
                         if (rank == 0) mbar_expect_tx(bar_full(s), 2 * A_BYTES);
@@ -166,13 +177,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             constexpr uint32_t idesc = make_idesc(0, MODE == MODE_DX, BN, 2 * BM);
             int s = 0, it = 0;
             uint32_t ph = 0;
-            for (int t = pair; t < num_tiles && !failed; t += num_pairs, ++it) {
+            for (int w = pair; w < num_items && !failed; w += num_pairs, ++it) {
                 const int acc = it & 1;
                 const uint32_t acc_ph = (uint32_t)(it >> 1) & 1u;
                 if (!mbar_wait_cluster_warp(bar_tempty(acc), acc_ph ^ 1u, p.status, 22)) { failed = true; break; }
                 tcgen05_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                for (int kb = 0; kb < p.kbp; ++kb) {          // the item's own blocks: the first one starts the sums
                     if (!mbar_wait_cluster_warp(bar_full(s), ph, p.status, 23)) { failed = true; break; }
                     tcgen05_fence_after();
                     if (lane == 0) {
@@ -201,9 +212,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const int quarter = warp & 3;
         const int row_in_tile = quarter * 32 + lane;
         int it = 0;
-        for (int t = pair; t < num_tiles && !failed; t += num_pairs, ++it) {
-            int trow, tcol;
-            tile_coords(t, p, trow, tcol);
+        for (int w = pair; w < num_items && !failed; w += num_pairs, ++it) {
+            int trow, tcol, part, kb0;
+            item_coords(w, num_tiles, p, trow, tcol, part, kb0);
             const int r0 = trow * (2 * BM) + (int)rank * BM, c0 = tcol * BN;
             const int acc = it & 1;
             const uint32_t acc_ph = (uint32_t)(it >> 1) & 1u;
@@ -287,7 +298,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         __syncwarp();
                         if (lane == 0) {
                             const int rb = r0 + quarter * 32;
-                            if (p.rows_per_dst > 0) {
+                            if (p.k_split > 1) {                   // split reduction: part q's sums go to partial output q
+                                tma_store_2d(&outs.m[part], stage, col0, rb);
+                            } else if (p.rows_per_dst > 0) {
                                 const int d = rb / p.rows_per_dst;
                                 if (d < p.n_dst) tma_store_2d(&outs.m[d], stage, col0, rb - d * p.rows_per_dst);
                             } else {
@@ -313,13 +326,14 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         // latency runs under five other blocks' worth of work.
         const int xw = warp - WARP_XF0;
         static_assert(DB == NUM_XF_WARPS, "one B slot per transform warp");
-        const int my_tiles = (num_tiles > pair) ? (num_tiles - pair + num_pairs - 1) / num_pairs : 0;
-        const long long total = (long long)my_tiles * p.k_blocks;
+        const int my_items = (num_items > pair) ? (num_items - pair + num_pairs - 1) / num_pairs : 0;
+        const long long total = (long long)my_items * p.kbp;
         const uint4 zero_codes = make_uint4(0x55555555u, 0x55555555u, 0x55555555u, 0x55555555u);     // sixteen weights 0 per word
         auto load_block = [&](long long g, uint4 (&pk)[8]) {
-            const int i = (int)(g / p.k_blocks), kb = (int)(g - (long long)i * p.k_blocks);
-            int trow, tcol;
-            tile_coords(pair + i * num_pairs, p, trow, tcol);
+            const int i = (int)(g / p.kbp);
+            int trow, tcol, part, kb0;
+            item_coords(pair + i * num_pairs, num_tiles, p, trow, tcol, part, kb0);
+            const int kb = kb0 + (int)(g - (long long)i * p.kbp);
             const int c0 = tcol * BN + (int)rank * 128;             // this CTA's 128 output columns
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
@@ -427,7 +441,10 @@ static int launch_t(const CUtensorMap& tmA, const OutMaps& outs, Params& p, cuda
     const long long tiles = (long long)p.tiles_r * p.tiles_c;
     if (tiles == 0) return EL_OK;
     if (p.k_blocks == 0) return EL_ERR_UNSUPPORTED_SHAPE;
-    const int pairs = (int)(tiles < dev_pairs ? tiles : dev_pairs);
+    if (p.k_split < 1 || p.k_blocks % p.k_split != 0) p.k_split = 1;
+    p.kbp = p.k_blocks / p.k_split;
+    const long long items = tiles * p.k_split;
+    const int pairs = (int)(items < dev_pairs ? items : dev_pairs);
     cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
     EL_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<MODE>, tmA, outs, p));
     return check_launch();
@@ -441,6 +458,26 @@ int make_map(CUtensorMap* m, const void* base, uint64_t cols, uint64_t rows, uin
 int make_map_out(CUtensorMap* m, const void* base, uint64_t cols, uint64_t rows, uint64_t pitch_bytes, int esz, int box_cols);
 }
 int gemm_tc_eligible(int mode, const void* A, const void* B, int R, int C, int D);
+int launch_reduce_scale_gather(const int* parts, int n_parts, void* const* out_all, int n_ranks, long long row_offset,
+                               long long rows_total, const EpiParams& epi, int Mr, int C, cudaStream_t st);
+
+// A problem with few output tiles leaves most CTA pairs idle (4096 -> 512 at 4096 tokens is 32 tiles for 74 pairs).  Its
+// reduction is then cut into q parts that run on different pairs at the same time; each part stores its int32 partial
+// sums and a second pass adds them (exact) and applies the epilogue.  Returns q (1 = no split): the largest q <= 8 that
+// keeps all parts in one wave, divides the number of reduction blocks and leaves at least 16 blocks per part, for
+// reductions of at least 48 blocks.  (Shorter reductions gain nothing: at 4096 -> 512 and 32 blocks the second pass and
+// its int32 round trip cost what the shorter main loop saves, measured.)
+int gemm_tc2_k_split(int R, int C, int D) {
+    int sms = 0;
+    if (device_sm_count(&sms) != EL_OK || sms < 2) return 1;
+    const long long pairs = sms / 2;
+    const long long tiles = (long long)((R + 2 * tc2::BM - 1) / (2 * tc2::BM)) * ((C + tc2::BN - 1) / tc2::BN);
+    const int k_blocks = (D + tc2::BK - 1) / tc2::BK;
+    int best = 1;
+    for (int q = 2; q <= 8; ++q)
+        if (tiles * q <= pairs && k_blocks >= 48 && k_blocks % q == 0 && k_blocks / q >= 16) best = q;
+    return best;
+}
 
 // Forward (mode 0) and dX (mode 1) on CTA pairs; same eligibility as the single-CTA kernel.
 // `dst` (optional): n_dst base pointers of [R, ld_total] output matrices that all receive this launch's [R, C] result
@@ -450,7 +487,7 @@ int gemm_tc_eligible(int mode, const void* A, const void* B, int R, int C, int D
 // rows [d*rows_per_dst, (d+1)*rows_per_dst) of the result (the reduce-scatter half of a cross-rank reduction of dX).
 int launch_gemm_tc2(int mode, const int8_t* A, const void* B, int R, int C, int D, const EpiParams& epi, int32_t* status,
                     cudaStream_t st, void* const* dst, int n_dst, long long ld_total, long long col_offset,
-                    int rows_per_dst, int first_dst) {
+                    int rows_per_dst, int first_dst, void* workspace, size_t workspace_bytes) {
     if (mode != MODE_FWD && mode != MODE_DX) return EL_ERR_INVALID_ARG;
     int rc = gemm_tc_eligible(mode, A, B, R, C, D);
     if (rc != EL_OK) return rc;
@@ -460,6 +497,7 @@ int launch_gemm_tc2(int mode, const int8_t* A, const void* B, int R, int C, int 
     p.R = R; p.C = C; p.D = D;
     p.epi = epi;
     p.status = status;
+    p.k_split = 1;
     const int esz = (epi.out_dtype == EL_BF16 || epi.out_dtype == EL_F16) ? 2 : 4;
     tc2::OutMaps outs{};
     CUtensorMap tmA;
@@ -491,16 +529,33 @@ int launch_gemm_tc2(int mode, const int8_t* A, const void* B, int R, int C, int 
         p.vec_ok = ((reinterpret_cast<uintptr_t>(epi.out) & 15) == 0) && ((epi.ldo * esz) % 16 == 0);
         p.tma_store = p.vec_ok;
         p.n_dst = 1;
-        if (p.tma_store && (rc = tc::make_map_out(&outs.m[0], epi.out, C, R, (uint64_t)epi.ldo * esz, esz, 128 / esz)) != EL_OK) return rc;
+        // split reduction: needs the caller's workspace, a dense scaled output and 8-column vectors in the second pass
+        const int q = (workspace != nullptr && epi.out_dtype != EL_I32 && p.vec_ok && epi.ldo == C && C % 8 == 0 &&
+                       (reinterpret_cast<uintptr_t>(workspace) & 15) == 0) ? gemm_tc2_k_split(R, C, D) : 1;
+        if (q > 1 && (size_t)q * R * C * sizeof(int) <= workspace_bytes) {
+            p.k_split = q;
+            p.epi.out_dtype = EL_I32;                   // the parts are raw int32 sums; the second pass scales
+            p.epi.absmax = nullptr;
+            for (int part = 0; part < q; ++part) {
+                char* base = static_cast<char*>(workspace) + (size_t)part * R * C * sizeof(int);
+                if ((rc = tc::make_map_out(&outs.m[part], base, C, R, (uint64_t)C * 4, 4, 32)) != EL_OK) return rc;
+            }
+        } else if (p.tma_store && (rc = tc::make_map_out(&outs.m[0], epi.out, C, R, (uint64_t)epi.ldo * esz, esz, 128 / esz)) != EL_OK) {
+            return rc;
+        }
     }
     if ((rc = tc::make_map(&tmA, A, D, R, D, 128, 128, true)) != EL_OK) return rc;
     p.Wp = static_cast<const uint8_t*>(B);
     if (mode == MODE_FWD) {
         p.ldw = D / 4;              // [C output features, D/4 bytes]
-        return tc2::launch_t<MODE_FWD>(tmA, outs, p, st);
+        rc = tc2::launch_t<MODE_FWD>(tmA, outs, p, st);
+    } else {
+        p.ldw = C / 4;              // [D reduction rows, C/4 bytes]
+        rc = tc2::launch_t<MODE_DX>(tmA, outs, p, st);
     }
-    p.ldw = C / 4;                  // [D reduction rows, C/4 bytes]
-    return tc2::launch_t<MODE_DX>(tmA, outs, p, st);
+    if (rc != EL_OK || p.k_split == 1) return rc;
+    void* out_one[1] = {epi.out};
+    return launch_reduce_scale_gather(static_cast<const int*>(workspace), p.k_split, out_one, 1, 0, R, epi, R, C, st);
 }
 
 }  // namespace el

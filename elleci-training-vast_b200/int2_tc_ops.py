@@ -108,6 +108,24 @@ def dequantize_activation(input_int8: torch.Tensor, scale: torch.Tensor, dtype: 
     return out
 
 
+_gemm_ws: dict = {}
+
+
+def _gemm_workspace(device: torch.device, mode: int, M: int, N: int, K: int):
+    """(pointer, bytes) of the scratch a GEMM with few output tiles uses to split its reduction over idle CTA pairs, or
+    (None, 0) when the shape is not split.  One buffer per device and stream, grown on demand; calls on one stream are
+    ordered, so they can share it."""
+    need = _lib.lib().el_gemm_workspace_bytes(mode, M, N, K)
+    if need == 0:
+        return None, 0
+    key = (device.index if device.index is not None else torch.cuda.current_device(), _stream())
+    buf = _gemm_ws.get(key)
+    if buf is None or buf.numel() < need:
+        buf = torch.empty(need, dtype=torch.uint8, device=device)
+        _gemm_ws[key] = buf
+    return buf.data_ptr(), buf.numel()
+
+
 def _gemm_fwd(Xq, W_packed, absmax, stride, gamma, out_dtype, path=EL_PATH_AUTO):
     _cuda(Xq, "X_int8"); _cuda(W_packed, "W_packed"); _cuda(absmax, "d_scale_x")
     _require(Xq.dtype == torch.int8, "X_int8 must be int8")
@@ -124,8 +142,9 @@ def _gemm_fwd(Xq, W_packed, absmax, stride, gamma, out_dtype, path=EL_PATH_AUTO)
     Wc = W_packed.contiguous()
     Y = torch.empty(M, N, dtype=out_dtype, device=Xq.device)
     st = device_status(Xq.device)
-    call("el_gemm_fwd", Xf.data_ptr(), Wc.data_ptr(), Y.data_ptr(), _DT[out_dtype], absmax.data_ptr(), stride,
-         float(gamma), M, N, K, path, st.data_ptr(), _stream())
+    ws, ws_bytes = _gemm_workspace(Xq.device, 0, M, N, K) if path in (EL_PATH_AUTO, EL_PATH_TC) else (None, 0)
+    call("el_gemm_fwd_ws", Xf.data_ptr(), Wc.data_ptr(), Y.data_ptr(), _DT[out_dtype], absmax.data_ptr(), stride,
+         float(gamma), M, N, K, path, ws, ws_bytes, st.data_ptr(), _stream())
     _maybe_check(Xq.device)
     return Y.view(*Xq.shape[:-1], N)
 
@@ -144,8 +163,9 @@ def _gemm_dx(dYq, W_packed, absmax, stride, gamma, K, out_dtype, path=EL_PATH_AU
     Wc = W_packed.contiguous()
     dX = torch.empty(M, K, dtype=out_dtype, device=dYq.device)
     st = device_status(dYq.device)
-    call("el_gemm_dx", Yf.data_ptr(), Wc.data_ptr(), dX.data_ptr(), _DT[out_dtype], absmax.data_ptr(), stride,
-         float(gamma), M, N, int(K), path, st.data_ptr(), _stream())
+    ws, ws_bytes = _gemm_workspace(dYq.device, 1, M, N, int(K)) if path in (EL_PATH_AUTO, EL_PATH_TC) else (None, 0)
+    call("el_gemm_dx_ws", Yf.data_ptr(), Wc.data_ptr(), dX.data_ptr(), _DT[out_dtype], absmax.data_ptr(), stride,
+         float(gamma), M, N, int(K), path, ws, ws_bytes, st.data_ptr(), _stream())
     _maybe_check(dYq.device)
     return dX.view(*dYq.shape[:-1], K)
 

@@ -161,7 +161,7 @@ class TokenParallelInt2Linear(nn.Module):
 
     def __init__(self, in_features: int, out_features: int, group: Optional[dist.ProcessGroup] = None, threshold: int = 7,
                  lr_scale: float = 5.0, decay_rate: float = 0.001, hysteresis_order: str = "after_dx", ops=None,
-                 fused: bool = False, push_ctas: int = 32):
+                 fused: bool = False, push_ctas: int = 296):
         super().__init__()
         if ops is None:
             from . import int2_tc_ops as ops_mod
@@ -178,7 +178,9 @@ class TokenParallelInt2Linear(nn.Module):
         self.hysteresis_order = hysteresis_order
         self.hysteresis_enabled = True
         self.fused = fused
-        # CTAs of the token push that runs on a side stream beside the forward GEMM: few, so the GEMM keeps its SMs
+        # CTAs of the pushes that run on a side stream beside the GEMMs.  They hold no shared memory, so they sit on the SMs
+        # next to the GEMM's CTAs; NVLink needs a few megabytes of stores in flight to run at rate (32 CTAs moved 140-310
+        # GB/s, a fifth of the link), hence two CTAs per SM.
         self.push_ctas = push_ctas
         self._lr = 0.001
         self._step_py = 0
@@ -377,6 +379,10 @@ class TokenParallelInt2Linear(nn.Module):
         P.gloc = torch.zeros(1, dtype=torch.float32, device=dev)
         P.own = bufs["xq_all"][r * Ml:(r + 1) * Ml]
         P.status = ops.device_status(dev).data_ptr()
+        # scratch for the split reduction of GEMMs with few output tiles (a rank's share of a small batch): see el_gemm_fwd_ws
+        need = max(P.lib.el_gemm_workspace_bytes(0, Ml, N, K), P.lib.el_gemm_workspace_bytes(1, Ml, N, K))
+        P.ws = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)
+        P.ws_bytes = need
 
         def arr(ptrs):
             a = (ctypes.c_void_p * len(ptrs))(*[int(p) for p in ptrs])
@@ -430,7 +436,8 @@ class TokenParallelInt2Linear(nn.Module):
             call("push_tokens", lib.el_peer_put, P.own.data_ptr(), P.peers_x, g - 1, r * Ml * K, Ml * K, self.push_ctas, side.cuda_stream)
         peer.pending = torch.cuda.Event()
         peer.pending.record(side)
-        call("gemm_fwd", lib.el_gemm_fwd, P.own.data_ptr(), W, P.y.data_ptr(), P.dt, P.ax.data_ptr(), 1, gam, Ml, N, K, 0, P.status, st)
+        call("gemm_fwd", lib.el_gemm_fwd_ws, P.own.data_ptr(), W, P.y.data_ptr(), P.dt, P.ax.data_ptr(), 1, gam, Ml, N, K, 0,
+             P.ws.data_ptr(), P.ws_bytes, P.status, st)
         # backward: quantise the gradient rows (with the fold that yields this rank's partial maximum)
         P.gloc.zero_()
         call("quantize_rows_dy", lib.el_quantize_rows, dY.data_ptr(), P.dt, N, P.dyq.data_ptr(), P.ady.data_ptr(), Ml, N, GRAD_EPS, 0,
@@ -438,8 +445,8 @@ class TokenParallelInt2Linear(nn.Module):
 
         def input_grad():
             if need_dx:
-                call("gemm_dx", lib.el_gemm_dx, P.dyq.data_ptr(), W, P.dx.data_ptr(), P.dt, P.ady.data_ptr(), 1, gam, Ml, N, K, 0,
-                     P.status, st)
+                call("gemm_dx", lib.el_gemm_dx_ws, P.dyq.data_ptr(), W, P.dx.data_ptr(), P.dt, P.ady.data_ptr(), 1, gam, Ml, N, K, 0,
+                     P.ws.data_ptr(), P.ws_bytes, P.status, st)
 
         def update():
             self._step_py += 1

@@ -205,6 +205,24 @@ EL_API int el_gemm_fwd(const int8_t* Xq, const uint8_t* W_packed, void* Y, int o
                 int absmax_stride, float gamma, int M, int N, int K, int flags, int32_t* dev_status,
                 el_stream_t stream);
 
+/* el_gemm_fwd / el_gemm_dx with a caller-owned workspace that lets a problem with few output tiles use the whole GPU.
+ * A GEMM whose output has fewer 256 x 256 tiles than half the GPU's CTA pairs and whose reduction is long (512 tokens
+ * through 11008 -> 4096: 32 tiles for 74 pairs, 86 reduction blocks; the per-rank GEMMs of a layer split over eight
+ * GPUs) is cut along its reduction into q <= 8 parts
+ * that run side by side; each part stores int32 partial sums in the workspace and a second small kernel adds them
+ * (exact: the result is bit-identical to the unsplit GEMM) and applies the scaling epilogue.  el_gemm_workspace_bytes
+ * (mode 0 = forward, 1 = dX) says how many bytes that takes for a shape, 0 when the shape is not split; with workspace
+ * NULL or too small the call runs unsplit, as el_gemm_fwd / el_gemm_dx do.  The workspace (16-byte aligned) needs no
+ * initialisation and holds nothing between calls; calls that share one must not overlap on the GPU.  No counterpart in
+ * the reference. */
+EL_API size_t el_gemm_workspace_bytes(int mode, int M, int N, int K);
+EL_API int el_gemm_fwd_ws(const int8_t* Xq, const uint8_t* W_packed, void* Y, int out_dtype, const float* absmax,
+                          int absmax_stride, float gamma, int M, int N, int K, int flags, void* workspace,
+                          size_t workspace_bytes, int32_t* dev_status, el_stream_t stream);
+EL_API int el_gemm_dx_ws(const int8_t* dYq, const uint8_t* W_packed, void* dX, int out_dtype, const float* absmax,
+                         int absmax_stride, float gamma, int M, int N, int K, int flags, void* workspace,
+                         size_t workspace_bytes, int32_t* dev_status, el_stream_t stream);
+
 /* Forward GEMM of one N-shard fused with the all-gather of the output: the [M,N] result of el_gemm_fwd (N = this
  * rank's rows of W_packed) is written at column col_offset of EVERY matrix Y_all[r] (r < n_ranks <= 8, each [M, ld_total]
  * of out_dtype): the rank's own buffer and the peer-mapped buffers of the other ranks (symmetric memory / IPC

@@ -732,3 +732,48 @@ def test_token_parallel_update_of_all_ranks_equals_the_single_gpu_update(ops, g,
     Gq_o, g_o = O.grad_quantize(t2n(d["dY"]), ax_o)
     assert np.array_equal(Gq1.cpu().numpy(), Gq_o) and np.float32(gmax1.item()) == g_o
     assert not torch.equal(W1.cpu(), torch.from_numpy(d["Wp"]))
+
+
+# ---- split reduction of GEMMs with few output tiles ---------------------------------------------------------------------
+
+@pytest.mark.parametrize("M,N,K", [(512, 4096, 11008), (512, 11008, 4096), (256, 512, 8192), (300, 520, 8192), (1024, 8192, 1024)])
+def test_split_reduction_gemms_equal_the_unsplit_ones(ops, pkg, M, N, K):
+    """Shapes with at most 37 output tiles (forward, dX or both) run with their reduction cut into parts on otherwise
+    idle CTA pairs, the int32 partial sums added by a second kernel: the outputs must equal the oracle's and the unsplit
+    kernel's bit for bit (bf16 and float32), also for ragged edges and per-tensor scales."""
+    lib = pkg._lib.lib()
+    Xq, dYq, Wp, ax, ay = _gemm_inputs(M, N, K, seed=M + N)
+    gamma = 0.0173
+    assert lib.el_gemm_workspace_bytes(0, M, N, K) > 0 or lib.el_gemm_workspace_bytes(1, M, N, K) > 0
+    dXq, ddY, dWp, dax, day = _cuda(Xq), _cuda(dYq), _cuda(Wp), _cuda(ax), _cuda(ay)
+    acc_f, acc_x = O.gemm_fwd_acc(Xq, Wp, K), O.gemm_dx_acc(dYq, Wp, K)
+    for dt, rnd in ((torch.float32, lambda v: v), (torch.bfloat16, O.to_bf16)):
+        y = ops.matmul_rows(dXq, dWp, dax, gamma, dt)
+        assert np.array_equal(t2n(y), rnd(O.scale_rows(acc_f, ax, gamma)))
+        dx = ops.backward_input_rows(ddY, dWp, day, gamma, K, dt)
+        assert np.array_equal(t2n(dx), rnd(O.scale_rows(acc_x, ay, gamma)))
+        # the same calls without a workspace run unsplit
+        y0 = torch.empty_like(y)
+        dx0 = torch.empty_like(dx)
+        st = ops.device_status(torch.device(DEV))
+        cs = torch.cuda.current_stream().cuda_stream
+        edt = pkg._lib.EL_F32 if dt == torch.float32 else pkg._lib.EL_BF16
+        pkg._lib.call("el_gemm_fwd", dXq.data_ptr(), dWp.data_ptr(), y0.data_ptr(), edt, dax.data_ptr(), 1, gamma, M, N, K, 0,
+                      st.data_ptr(), cs)
+        pkg._lib.call("el_gemm_dx", ddY.data_ptr(), dWp.data_ptr(), dx0.data_ptr(), edt, day.data_ptr(), 1, gamma, M, N, K, 0,
+                      st.data_ptr(), cs)
+        assert torch.equal(y, y0) and torch.equal(dx, dx0)
+    s1 = torch.tensor([2.5], device=DEV)
+    yt = ops.matmul_int8(dXq, dWp, s1, gamma)
+    assert np.array_equal(t2n(yt), O.to_f16(O.scale_rows(acc_f, np.float32(2.5), gamma)))
+    ops.check_device_status(torch.device(DEV))
+
+
+def test_split_reduction_is_chosen_for_the_shapes_it_is_meant_for(pkg):
+    lib = pkg._lib.lib()
+    assert lib.el_gemm_workspace_bytes(0, 4096, 512, 4096) == 0                            # 32 tiles but only 32 reduction blocks
+    assert lib.el_gemm_workspace_bytes(0, 4096, 11008, 4096) == 0                          # 688 tiles: no split
+    assert lib.el_gemm_workspace_bytes(1, 512, 11008, 4096) == 2 * 512 * 4096 * 4         # dX of 512 tokens: 32 tiles, 86 blocks
+    assert lib.el_gemm_workspace_bytes(0, 512, 4096, 11008) == 2 * 512 * 4096 * 4         # 86 reduction blocks = 2 x 43
+    assert lib.el_gemm_workspace_bytes(0, 256, 256, 8192) == 4 * 256 * 256 * 4            # one tile, 64 blocks: four parts of 16
+    assert lib.el_gemm_workspace_bytes(0, 0, 64, 64) == 0 and lib.el_gemm_workspace_bytes(7, 64, 64, 64) == 0
