@@ -17,6 +17,7 @@ EL_ERR_INVALID_ARG, EL_ERR_NULL_PTR, EL_ERR_ALIGNMENT, EL_ERR_UNSUPPORTED_SHAPE 
 EL_ERR_CUDA, EL_ERR_DEVICE, EL_ERR_DRIVER, EL_ERR_TOO_LARGE = -5, -6, -7, -8
 EL_F16, EL_BF16, EL_F32, EL_I32 = 0, 1, 2, 3
 EL_PATH_AUTO, EL_PATH_SIMPLE, EL_PATH_TC, EL_PATH_TC_SINGLE = 0, 1, 2, 3
+EL_FLAG_LEAN = 0x100
 EL_QUANT_FULL, EL_QUANT_ABSMAX_ONLY, EL_QUANT_WITH_ABSMAX = 0, 1, 2
 
 _vp, _i, _f, _ll, _u32 = C.c_void_p, C.c_int, C.c_float, C.c_longlong, C.c_uint32

@@ -25,7 +25,7 @@ int launch_gemm_tc(int mode, const int8_t* A, const void* B, int R, int C, int D
                    cudaStream_t st);
 int launch_gemm_tc2(int mode, const int8_t* A, const void* B, int R, int C, int D, const EpiParams& epi, int32_t* status,
                     cudaStream_t st, void* const* dst, int n_dst, long long ld_total, long long col_offset, int rows_per_dst,
-                    int first_dst, void* workspace, size_t workspace_bytes);
+                    int first_dst, void* workspace, size_t workspace_bytes, bool lean);
 int gemm_tc2_k_split(int R, int C, int D);
 int launch_reduce_scale_gather(const int* parts, int n_parts, void* const* out_all, int n_ranks, long long row_offset,
                                long long rows_total, const EpiParams& epi, int Mr, int C, cudaStream_t st);
@@ -128,26 +128,28 @@ static inline bool out_dtype_ok(int dt) { return dt == EL_F16 || dt == EL_BF16 |
 
 // Tensor-core launch: forward and dX run on CTA pairs unless the single-CTA kernel is asked for; dW has one kernel.
 static int launch_tc(int mode, bool single_cta, const int8_t* A, const void* B, int R, int C, int D, const EpiParams& epi,
-                     int32_t* status, cudaStream_t st, void* ws = nullptr, size_t ws_bytes = 0) {
+                     int32_t* status, cudaStream_t st, void* ws = nullptr, size_t ws_bytes = 0, bool lean = false) {
     // The weight-gradient GEMM has one kernel: a CTA-pair version of it (half of the Xq columns per CTA) was built and
     // measured 8-10 % slower than the single-CTA kernel at every size, and dropped.
     if (single_cta || mode == MODE_DW) return launch_gemm_tc(mode, A, B, R, C, D, epi, status, st);
-    return launch_gemm_tc2(mode, A, B, R, C, D, epi, status, st, nullptr, 0, 0, 0, 0, 0, ws, ws_bytes);
+    return launch_gemm_tc2(mode, A, B, R, C, D, epi, status, st, nullptr, 0, 0, 0, 0, 0, ws, ws_bytes, lean);
 }
 
 static int gemm_dispatch(int mode, const int8_t* A, const void* B, int R, int C, int D, const EpiParams& epi, int flags,
                          int32_t* status, cudaStream_t st, void* ws = nullptr, size_t ws_bytes = 0) {
+    const bool lean = (flags & EL_FLAG_LEAN) != 0;
+    flags &= ~EL_FLAG_LEAN;
     if (flags < EL_PATH_AUTO || flags > EL_PATH_TC_SINGLE) return EL_ERR_INVALID_ARG;
     if (R == 0 || C == 0) return EL_OK;
     if (flags == EL_PATH_SIMPLE) return launch_gemm_simple(mode, A, B, R, C, D, epi, st);
     const int elig = (D > 0) ? gemm_tc_eligible(mode, A, B, R, C, D) : EL_ERR_UNSUPPORTED_SHAPE;
     if (flags == EL_PATH_TC || flags == EL_PATH_TC_SINGLE)
-        return elig != EL_OK ? elig : launch_tc(mode, flags == EL_PATH_TC_SINGLE, A, B, R, C, D, epi, status, st, ws, ws_bytes);
+        return elig != EL_OK ? elig : launch_tc(mode, flags == EL_PATH_TC_SINGLE, A, B, R, C, D, epi, status, st, ws, ws_bytes, lean);
     // auto: the tensor-core tiles are 128 rows deep; very small problems go to the CUDA-core kernel.  A few rows against a
     // large weight matrix still belong on the tensor-core kernel: the call is then the time to stream the packed weights
     // once, which the CUDA-core kernel takes twenty times longer for.
     if (elig == EL_OK && (R >= 32 || (long long)C * D >= (1ll << 18)))
-        return launch_tc(mode, R <= 128, A, B, R, C, D, epi, status, st, ws, ws_bytes);
+        return launch_tc(mode, R <= 128, A, B, R, C, D, epi, status, st, ws, ws_bytes, lean);
     return launch_gemm_simple(mode, A, B, R, C, D, epi, st);
 }
 
@@ -350,7 +352,7 @@ int el_gemm_fwd_gather(const int8_t* Xq, const uint8_t* W_packed, void* const* Y
     if (!Y_all || !absmax || !Xq || !W_packed) return EL_ERR_NULL_PTR;
     const EpiParams epi{nullptr, ld_total, out_dtype, absmax, absmax_stride, gamma};
     return launch_gemm_tc2(MODE_FWD, Xq, W_packed, M, N, K, epi, dev_status, (cudaStream_t)stream, Y_all, n_ranks, ld_total,
-                           col_offset, 0, 0, nullptr, 0);
+                           col_offset, 0, 0, nullptr, 0, false);
 }
 
 int el_gemm_dx_scatter(const int8_t* dYq, const uint8_t* W_packed, void* const* parts_all, int n_ranks, int rank, int M, int N,
@@ -367,7 +369,7 @@ int el_gemm_dx_scatter(const int8_t* dYq, const uint8_t* W_packed, void* const* 
     }
     const EpiParams epi{nullptr, (long long)K, EL_I32, nullptr, 0, 1.0f};
     return launch_gemm_tc2(MODE_DX, dYq, W_packed, M, K, N, epi, dev_status, (cudaStream_t)stream, dst, n_ranks, 0, 0, Mr, rank,
-                           nullptr, 0);
+                           nullptr, 0, false);
 }
 
 int el_reduce_scale_gather(const int32_t* parts, void* const* dX_all, int n_ranks, int rank, int out_dtype, const float* absmax,

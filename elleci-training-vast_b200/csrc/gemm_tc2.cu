@@ -92,8 +92,13 @@ __device__ __forceinline__ void item_coords(int w, int num_tiles, const Params& 
     kb0 = part * p.kbp;
 }
 
-template <int MODE>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+// LEAN = false: the transform warps hold two register images of a packed block (the loads run a whole block ahead),
+// 160 registers per thread: the CTA fills the SM's register file.  LEAN = true: one image, the next block's loads issued
+// right after the current one has been expanded, at most 128 registers: a quarter of the register file stays free and a
+// kernel that needs no shared memory (the peer pushes of a multi-GPU step, on a side stream) can run beside this
+// persistent one.  The lean form is about 9 % slower on its own (2140 against 2350 TOP/s at 4096 -> 11008).
+template <int MODE, bool LEAN>
+__global__ void __maxnreg__(LEAN ? 128 : 168)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ OutMaps outs, const Params p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -233,16 +238,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 tmem_ld32(taddr + c * 32, v);
                 tmem_ld_wait();
                 const int col0 = c0 + c * 32;
-                if (MODE == MODE_DX) {
-                    // column 16g+p of the tile holds output column 16g + KPERM16[p] (de-interleaved expansion)
-                    uint32_t w[32];
-#pragma unroll
-                    for (int g = 0; g < 2; ++g)
-#pragma unroll
-                        for (int q = 0; q < 16; ++q) w[16 * g + ((q < 8) ? 2 * q : 2 * (q - 8) + 1)] = v[16 * g + q];
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = w[i];
-                }
+                // DX: column 16g+p of the tile holds output column 16g + KPERM16[p] (de-interleaved expansion), so output column
+                // i of the chunk is read from register SRC(i); with the loops below unrolled this is a renaming, not a copy.
+#define EL_SRC(i) ((MODE == MODE_DX) ? (((i) & ~15) + ((((i) & 15) & 1) ? 8 + (((i) & 15) >> 1) : (((i) & 15) >> 1))) : (i))
                 if (p.tma_store) {
                     if (col0 >= p.C) continue;
                     // The warp's 32 rows go to shared memory in the tensor map's 128-byte swizzle (32 columns of four-byte
@@ -261,7 +259,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                             uint32_t o[4];
 #pragma unroll
                             for (int i = 0; i < 4; ++i) {
-                                const float lo = __fmul_rn((float)(int)v[8 * j + 2 * i], sc), hi = __fmul_rn((float)(int)v[8 * j + 2 * i + 1], sc);
+                                const float lo = __fmul_rn((float)(int)v[EL_SRC(8 * j + 2 * i)], sc),
+                                            hi = __fmul_rn((float)(int)v[EL_SRC(8 * j + 2 * i + 1)], sc);
                                 o[i] = (p.epi.out_dtype == EL_BF16) ? pack_bf16x2(lo, hi) : pack_f16x2(lo, hi);
                             }
                             *reinterpret_cast<uint4*>(buf + (((4 * h + j) ^ (lane & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
@@ -289,7 +288,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                             uint32_t o[4];
 #pragma unroll
                             for (int i = 0; i < 4; ++i) {
-                                const int a = (int)v[4 * j + i];
+                                const int a = (int)v[EL_SRC(4 * j + i)];
                                 o[i] = (p.epi.out_dtype == EL_F32) ? __float_as_uint(__fmul_rn((float)a, sc)) : (uint32_t)a;
                             }
                             *reinterpret_cast<uint4*>(buf + ((j ^ (lane & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
@@ -309,9 +308,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                             bulk_commit();
                         }
                     }
-                } else if (row_ok && col0 < p.C) {
-                    epi_store_chunk32(p.epi, row, col0, p.C, v, sc, false);
+                } else if (row_ok && col0 < p.C) {        // unaligned output: plain stores (rare)
+                    uint32_t w[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) w[i] = v[EL_SRC(i)];
+                    epi_store_chunk32(p.epi, row, col0, p.C, w, sc, false);
                 }
+#undef EL_SRC
             }
             tcgen05_fence_before();
             __syncwarp();
@@ -353,11 +356,11 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         uint4 cur[8], nxt[8];
         if (xw < total) load_block(xw, cur);
         for (long long g = xw; g < total && !failed; g += NUM_XF_WARPS) {
-            const bool more = g + NUM_XF_WARPS < total;
-            if (more) load_block(g + NUM_XF_WARPS, nxt);
             // Block g uses this warp's own B slot (g % 6 == xw).  A barrier only tells the parity of its phase, so a
             // waiter must never be two phases away from it: with one slot per warp the previous use of the slot was this
             // warp's previous block (g-6).
+            const bool more = g + NUM_XF_WARPS < total;
+            if (!LEAN && more) load_block(g + NUM_XF_WARPS, nxt);        // a whole block ahead, into the second image
             const int sb_i = xw;
             const uint32_t phb = (uint32_t)(g / DB) & 1u;
             if (!mbar_wait_warp(bar_empty(sb_i), phb ^ 1u, p.status, 28)) { failed = true; break; }
@@ -376,10 +379,14 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     *reinterpret_cast<uint4*>(dst_row + ((chunk ^ (row & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
                 }
             }
+            if (LEAN) {
+                asm volatile("" ::: "memory");  // keeps the compiler from starting the next loads while `cur` is still needed
+                if (more) load_block(g + NUM_XF_WARPS, cur);        // into the one image, as soon as it is free
+            }
             fence_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(mapa_u32(bar_full(sb_i), 0));
-            if (more) {
+            if (!LEAN && more) {
 #pragma unroll
                 for (int j = 0; j < 8; ++j) cur[j] = nxt[j];
             }
@@ -400,7 +407,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     }
 }
 
-template <int MODE>
+template <int MODE, bool LEAN>
 static int launch_t(const CUtensorMap& tmA, const OutMaps& outs, Params& p, cudaStream_t st) {
     static std::atomic<int> max_pairs[64];      // co-resident CTA pairs per device; 0 = not yet queried
     int dev = 0;
@@ -419,13 +426,13 @@ static int launch_t(const CUtensorMap& tmA, const OutMaps& outs, Params& p, cuda
     cfg.numAttrs = 1;
     int dev_pairs = max_pairs[dev].load(std::memory_order_acquire);
     if (dev_pairs == 0) {       // host threads may race here: both then query and store the same number
-        EL_CUDA_TRY(cudaFuncSetAttribute(gemm_tc2_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        EL_CUDA_TRY(cudaFuncSetAttribute(gemm_tc2_kernel<MODE, LEAN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         int sms = 0;
         const int rc = device_sm_count(&sms);
         if (rc != EL_OK) return rc;
         cfg.gridDim = dim3((unsigned)(sms & ~1), 1, 1);
         int clusters = 0;
-        EL_CUDA_TRY(cudaOccupancyMaxActiveClusters(&clusters, gemm_tc2_kernel<MODE>, &cfg));
+        EL_CUDA_TRY(cudaOccupancyMaxActiveClusters(&clusters, gemm_tc2_kernel<MODE, LEAN>, &cfg));
         if (clusters < 1) return EL_ERR_DEVICE;
         dev_pairs = clusters < sms / 2 ? clusters : sms / 2;
         max_pairs[dev].store(dev_pairs, std::memory_order_release);
@@ -446,7 +453,7 @@ static int launch_t(const CUtensorMap& tmA, const OutMaps& outs, Params& p, cuda
     const long long items = tiles * p.k_split;
     const int pairs = (int)(items < dev_pairs ? items : dev_pairs);
     cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
-    EL_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<MODE>, tmA, outs, p));
+    EL_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<MODE, LEAN>, tmA, outs, p));
     return check_launch();
 }
 
@@ -487,7 +494,7 @@ int gemm_tc2_k_split(int R, int C, int D) {
 // rows [d*rows_per_dst, (d+1)*rows_per_dst) of the result (the reduce-scatter half of a cross-rank reduction of dX).
 int launch_gemm_tc2(int mode, const int8_t* A, const void* B, int R, int C, int D, const EpiParams& epi, int32_t* status,
                     cudaStream_t st, void* const* dst, int n_dst, long long ld_total, long long col_offset,
-                    int rows_per_dst, int first_dst, void* workspace, size_t workspace_bytes) {
+                    int rows_per_dst, int first_dst, void* workspace, size_t workspace_bytes, bool lean) {
     if (mode != MODE_FWD && mode != MODE_DX) return EL_ERR_INVALID_ARG;
     int rc = gemm_tc_eligible(mode, A, B, R, C, D);
     if (rc != EL_OK) return rc;
@@ -548,10 +555,10 @@ int launch_gemm_tc2(int mode, const int8_t* A, const void* B, int R, int C, int 
     p.Wp = static_cast<const uint8_t*>(B);
     if (mode == MODE_FWD) {
         p.ldw = D / 4;              // [C output features, D/4 bytes]
-        rc = tc2::launch_t<MODE_FWD>(tmA, outs, p, st);
+        rc = lean ? tc2::launch_t<MODE_FWD, true>(tmA, outs, p, st) : tc2::launch_t<MODE_FWD, false>(tmA, outs, p, st);
     } else {
         p.ldw = C / 4;              // [D reduction rows, C/4 bytes]
-        rc = tc2::launch_t<MODE_DX>(tmA, outs, p, st);
+        rc = lean ? tc2::launch_t<MODE_DX, true>(tmA, outs, p, st) : tc2::launch_t<MODE_DX, false>(tmA, outs, p, st);
     }
     if (rc != EL_OK || p.k_split == 1) return rc;
     void* out_one[1] = {epi.out};

@@ -17,7 +17,7 @@ from typing import Optional, Tuple
 import torch
 
 from . import _lib
-from ._lib import EL_BF16, EL_F16, EL_F32, EL_I32, EL_PATH_AUTO, EL_PATH_SIMPLE, EL_PATH_TC, ElleciError, call
+from ._lib import EL_BF16, EL_F16, EL_F32, EL_FLAG_LEAN, EL_I32, EL_PATH_AUTO, EL_PATH_SIMPLE, EL_PATH_TC, ElleciError, call
 
 _DT = {torch.float16: EL_F16, torch.bfloat16: EL_BF16, torch.float32: EL_F32, torch.int32: EL_I32}
 GRAD_EPS = 1e-30          # floor of a gradient row's absmax (an all-zero row quantises to zeros)
@@ -142,7 +142,7 @@ def _gemm_fwd(Xq, W_packed, absmax, stride, gamma, out_dtype, path=EL_PATH_AUTO)
     Wc = W_packed.contiguous()
     Y = torch.empty(M, N, dtype=out_dtype, device=Xq.device)
     st = device_status(Xq.device)
-    ws, ws_bytes = _gemm_workspace(Xq.device, 0, M, N, K) if path in (EL_PATH_AUTO, EL_PATH_TC) else (None, 0)
+    ws, ws_bytes = _gemm_workspace(Xq.device, 0, M, N, K) if (path & ~EL_FLAG_LEAN) in (EL_PATH_AUTO, EL_PATH_TC) else (None, 0)
     call("el_gemm_fwd_ws", Xf.data_ptr(), Wc.data_ptr(), Y.data_ptr(), _DT[out_dtype], absmax.data_ptr(), stride,
          float(gamma), M, N, K, path, ws, ws_bytes, st.data_ptr(), _stream())
     _maybe_check(Xq.device)
@@ -163,7 +163,7 @@ def _gemm_dx(dYq, W_packed, absmax, stride, gamma, K, out_dtype, path=EL_PATH_AU
     Wc = W_packed.contiguous()
     dX = torch.empty(M, K, dtype=out_dtype, device=dYq.device)
     st = device_status(dYq.device)
-    ws, ws_bytes = _gemm_workspace(dYq.device, 1, M, N, int(K)) if path in (EL_PATH_AUTO, EL_PATH_TC) else (None, 0)
+    ws, ws_bytes = _gemm_workspace(dYq.device, 1, M, N, int(K)) if (path & ~EL_FLAG_LEAN) in (EL_PATH_AUTO, EL_PATH_TC) else (None, 0)
     call("el_gemm_dx_ws", Yf.data_ptr(), Wc.data_ptr(), dX.data_ptr(), _DT[out_dtype], absmax.data_ptr(), stride,
          float(gamma), M, N, int(K), path, ws, ws_bytes, st.data_ptr(), _stream())
     _maybe_check(dYq.device)

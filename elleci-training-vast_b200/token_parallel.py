@@ -105,7 +105,7 @@ def _forward_impl(layer: "TokenParallelInt2Linear", x: torch.Tensor):
     layer._weights_ready()                  # the other ranks' updated rows of W_packed have landed
     if will_update and layer.world > 1:
         layer._share_tokens(bufs, own, Ml)
-    y = run("gemm_fwd", ops.matmul_rows, Xq, layer.W_packed, ax, layer.gamma_value(), io)
+    y = run("gemm_fwd", ops.matmul_rows, Xq, layer.W_packed, ax, layer.gamma_value(), io, layer.gemm_path)
     return y, ((bufs, ax) if will_update else None), io
 
 
@@ -129,7 +129,7 @@ def _backward_impl(layer: "TokenParallelInt2Linear", saved, dY: torch.Tensor, io
     def input_grad():
         if not need_dx:
             return None
-        return run("gemm_dx", ops.backward_input_rows, dYq, layer.W_packed, ady, layer.gamma_value(), K, io)
+        return run("gemm_dx", ops.backward_input_rows, dYq, layer.W_packed, ady, layer.gamma_value(), K, io, layer.gemm_path)
 
     if do_update and layer.hysteresis_order == "reference":
         layer._update(bufs, dY2, ax, gloc)             # as the reference's hook: before dX ...
@@ -182,6 +182,10 @@ class TokenParallelInt2Linear(nn.Module):
         # next to the GEMM's CTAs; NVLink needs a few megabytes of stores in flight to run at rate (32 CTAs moved 140-310
         # GB/s, a fifth of the link), hence two CTAs per SM.
         self.push_ctas = push_ctas
+        # From four ranks on, the pushes are a large enough share of the step that they must overlap with the GEMMs: the
+        # forward and dX GEMMs then run in their register-lean form (EL_FLAG_LEAN), which leaves room on the SMs for the
+        # push kernel of the side stream.  With two ranks the faster form wins (measured).
+        self.gemm_path = getattr(ops, "EL_FLAG_LEAN", 0) if (fused and self.world >= 4) else 0
         self._lr = 0.001
         self._step_py = 0
         self._gamma_cached: Optional[float] = None
@@ -436,8 +440,8 @@ class TokenParallelInt2Linear(nn.Module):
             call("push_tokens", lib.el_peer_put, P.own.data_ptr(), P.peers_x, g - 1, r * Ml * K, Ml * K, self.push_ctas, side.cuda_stream)
         peer.pending = torch.cuda.Event()
         peer.pending.record(side)
-        call("gemm_fwd", lib.el_gemm_fwd_ws, P.own.data_ptr(), W, P.y.data_ptr(), P.dt, P.ax.data_ptr(), 1, gam, Ml, N, K, 0,
-             P.ws.data_ptr(), P.ws_bytes, P.status, st)
+        call("gemm_fwd", lib.el_gemm_fwd_ws, P.own.data_ptr(), W, P.y.data_ptr(), P.dt, P.ax.data_ptr(), 1, gam, Ml, N, K,
+             self.gemm_path, P.ws.data_ptr(), P.ws_bytes, P.status, st)
         # backward: quantise the gradient rows (with the fold that yields this rank's partial maximum)
         P.gloc.zero_()
         call("quantize_rows_dy", lib.el_quantize_rows, dY.data_ptr(), P.dt, N, P.dyq.data_ptr(), P.ady.data_ptr(), Ml, N, GRAD_EPS, 0,
@@ -445,8 +449,8 @@ class TokenParallelInt2Linear(nn.Module):
 
         def input_grad():
             if need_dx:
-                call("gemm_dx", lib.el_gemm_dx_ws, P.dyq.data_ptr(), W, P.dx.data_ptr(), P.dt, P.ady.data_ptr(), 1, gam, Ml, N, K, 0,
-                     P.ws.data_ptr(), P.ws_bytes, P.status, st)
+                call("gemm_dx", lib.el_gemm_dx_ws, P.dyq.data_ptr(), W, P.dx.data_ptr(), P.dt, P.ady.data_ptr(), 1, gam, Ml, N, K,
+                     self.gemm_path, P.ws.data_ptr(), P.ws_bytes, P.status, st)
 
         def update():
             self._step_py += 1

@@ -62,6 +62,9 @@ typedef void* el_stream_t;
 #define EL_PATH_SIMPLE 1   /* force the CUDA-core kernel (any shape) */
 #define EL_PATH_TC     2   /* require the tcgen05 kernel; EL_ERR_UNSUPPORTED_SHAPE / EL_ERR_ALIGNMENT if it cannot run */
 #define EL_PATH_TC_SINGLE 3 /* as EL_PATH_TC, but forward / dX on the single-CTA kernel instead of CTA pairs */
+/* May be OR-ed into the path: the CTA-pair kernels keep to 128 registers per thread, so that a kernel which needs no
+ * shared memory (el_peer_put on another stream) can run on the same SMs beside them; about 9 % slower on their own. */
+#define EL_FLAG_LEAN   0x100
 
 EL_API int el_version(void);
 EL_API const char* el_status_string(int status);

@@ -777,3 +777,20 @@ def test_split_reduction_is_chosen_for_the_shapes_it_is_meant_for(pkg):
     assert lib.el_gemm_workspace_bytes(0, 512, 4096, 11008) == 2 * 512 * 4096 * 4         # 86 reduction blocks = 2 x 43
     assert lib.el_gemm_workspace_bytes(0, 256, 256, 8192) == 4 * 256 * 256 * 4            # one tile, 64 blocks: four parts of 16
     assert lib.el_gemm_workspace_bytes(0, 0, 64, 64) == 0 and lib.el_gemm_workspace_bytes(7, 64, 64, 64) == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(600, 2000, 2048), (2304, 2304, 2048), (512, 4096, 11008)])
+def test_register_lean_pair_kernels_bit_exact(ops, pkg, M, N, K):
+    """EL_FLAG_LEAN selects the form of the CTA-pair kernels that leaves register-file room for a co-resident push kernel:
+    same integers, same rounding (also through the split reduction)."""
+    Xq, dYq, Wp, ax, ay = _gemm_inputs(M, N, K, seed=7 + M)
+    gamma = 0.0173
+    path = pkg._lib.EL_PATH_TC | pkg._lib.EL_FLAG_LEAN
+    dXq, ddY, dWp, dax, day = _cuda(Xq), _cuda(dYq), _cuda(Wp), _cuda(ax), _cuda(ay)
+    acc_f, acc_x = O.gemm_fwd_acc(Xq, Wp, K), O.gemm_dx_acc(dYq, Wp, K)
+    assert np.array_equal(ops.matmul_rows(dXq, dWp, dax, gamma, torch.int32, path).cpu().numpy(), acc_f)
+    assert np.array_equal(ops.backward_input_rows(ddY, dWp, day, gamma, K, torch.int32, path).cpu().numpy(), acc_x)
+    assert np.array_equal(t2n(ops.matmul_rows(dXq, dWp, dax, gamma, torch.bfloat16, path)), O.to_bf16(O.scale_rows(acc_f, ax, gamma)))
+    assert np.array_equal(t2n(ops.backward_input_rows(ddY, dWp, day, gamma, K, torch.bfloat16, path)),
+                          O.to_bf16(O.scale_rows(acc_x, ay, gamma)))
+    ops.check_device_status(torch.device(DEV))
