@@ -5,17 +5,16 @@
 // 256 x 256 output tile: each loads its own 128 activation rows, expands only HALF of the weight tile (128 rows of
 // 128 bytes per reduction block) and one thread of the leader CTA issues 256-row MMAs that read both halves, so the
 // expansion work per MMA cycle is halved.  Per CTA and 128-deep reduction block:
-//   A   16 KB  activations, TMA, 128-byte swizzle, K-major           (counted on the leader's "a_full" barrier)
+//   A   16 KB  activations, TMA, 128-byte swizzle, K-major           (bytes counted on the leader's "full" barrier)
 //   P    4 KB  packed weights, plain 16-byte global loads into the transform warp's registers, one block ahead
-//   B   16 KB  expanded weights                                         (one arrival per CTA on the leader's "ready")
+//   B   16 KB  expanded weights                                         (one arrival per CTA on the leader's "full")
 // Two rings: A and B, 6 deep each.  Each reduction block is expanded by ONE transform warp per CTA into that warp's own
 // B slot (six blocks are in flight on six warps), so a block's barrier, fence and signalling latency overlaps with
 // the other blocks' work.
-// The packed tile deliberately does NOT come through TMA.  A tile load costs the TMA unit about 2.5 cycles per box row
-// whatever the row's width (measured: with all MMAs removed the kernel still took 0.9 of its time, and 256 box rows per
-// block - 128 rows of 128 activation bytes and 128 rows of 32 packed bytes - came to ~690 cycles against the 512 cycles
-// the block's MMAs need).  The 32-byte packed rows cost as much as the 128-byte activation rows and carry a quarter of
-// the bytes, so they go through the load/store unit instead and the TMA unit only moves activations.
+// The packed tile does not come through TMA and shared memory: a transform warp reads its block's 4 KB straight into
+// registers.  That removes a third ring with its two barrier types and its producer warp and frees 24 KB for a sixth
+// activation stage; on its own it changed the speed by nothing, but it lets a stage have one "full" and one "empty"
+// barrier (see the kernel), which did (+8 % forward).
 // FWD reads B K-major (rows = output features n); DX reads the same image MN-major (rows = reduction index n,
 // 128 output columns k per CTA).  DX expands without the final byte interleave (decode16_deint), which permutes the
 // output columns inside groups of 16; the epilogue undoes that while the sums are in registers.
