@@ -989,10 +989,11 @@ def run_decode(args):
         # overlap: the GEMV issued as a programmatic dependent launch (weights constant, as at inference), so that a
         # call's weight loads start under the tail of the previous call
         # columns: tokens, limit of the CUDA-core GEMV, limit of the warp-MMA kernel (tcgen05 stream-K above it), overlap
-        for M, gemv_max, mma_max, overlap in ((1, 1, 32, False), (1, 1, 32, True), (1, 0, 32, True), (2, 2, 32, True),
-                                              (2, 1, 32, True), (4, 4, 32, True), (4, 1, 32, False), (4, 1, 32, True),
-                                              (8, 8, 32, True), (8, 1, 32, False), (8, 1, 32, True), (8, 0, 0, False),
-                                              (16, 1, 32, True), (32, 1, 32, True), (32, 1, 0, False), (64, 1, 32, False)):
+        for M, gemv_max, mma_max, overlap in ((1, 1, 64, False), (1, 1, 64, True), (1, 0, 64, True), (2, 2, 64, True),
+                                              (2, 1, 64, True), (4, 4, 64, True), (4, 1, 64, False), (4, 1, 64, True),
+                                              (8, 8, 64, True), (8, 1, 64, False), (8, 1, 64, True), (8, 0, 0, False),
+                                              (16, 1, 64, True), (16, 0, 0, False), (32, 1, 64, True), (32, 1, 0, False),
+                                              (64, 1, 64, False), (64, 1, 0, False)):
             pkg._lib.lib().el_set_decode_gemv_max_tokens(gemv_max)
             pkg._lib.lib().el_set_decode_mma_max_tokens(mma_max)
             ops.set_decode_overlap(overlap)
@@ -1017,14 +1018,15 @@ def run_decode(args):
             us = e0.elapsed_time(e1) * 1e3 / (reps * nbuf)
             nbytes = N * K // 4 + 2 * M * K + 2 * M * N
             gbs = nbytes / (us * 1e-6) / 1e9
-            fits_mma = M <= mma_max and M * K <= 190 * 1024 * (M / (8 if M <= 8 else 16 if M <= 16 else 32))
-            kernel = "gemv" if M <= gemv_max else ("mma" if fits_mma else "tcgen05")
+            mt = 8 if M <= 8 else (16 if M <= 16 else 32)      # tokens per launch of the warp-MMA kernel, padded
+            fits_mma = M <= mma_max and 256 + ((K + 255) // 256) * 16 * mt * 16 + 2 * 16 * mt * 4 <= 200 * 1024
+            kernel = "gemv" if M <= gemv_max else (("mma" if M <= 8 else "mma_preq") if fits_mma else "tcgen05")
             cases.append({"M": M, "K": K, "N": N, "kernel": kernel, "overlap": overlap, "us_per_call": us, "GBps": gbs, "frac_of_hbm": gbs / peaks["hbm_gbs"],
                           "algorithmic_bytes": nbytes})
         ops.check_device_status(dev)
         del Ws
     pkg._lib.lib().el_set_decode_gemv_max_tokens(2)
-    pkg._lib.lib().el_set_decode_mma_max_tokens(32)
+    pkg._lib.lib().el_set_decode_mma_max_tokens(64)
     ops.set_decode_overlap(False)
     # The feed-forward block at decode through the module API: six blocks (203 MB of packed weights) rotated in one graph.
     # Without gradient recording each layer is one small kernel (norm / gate) plus the decode call; with it, the training

@@ -65,6 +65,9 @@ int launch_gemv_mma(const void* x, int x_dtype, const uint8_t* Wp, const EpiPara
 bool gemv_mma_fits(int M, int K);
 int launch_gemv_small(const void* x, int x_dtype, const uint8_t* Wp, const EpiParams& epi, int M, int N, int K, cudaStream_t st, bool overlap);
 int decode_gemv_max_tokens();
+bool gemv_mma_preq_fits(int M, int K);
+int launch_gemv_mma_preq(const int8_t* xq, const float* amax, const uint8_t* Wp, const EpiParams& epi, int M, int N, int K,
+                         cudaStream_t st);
 
 static thread_local int g_last_cuda_error = 0;
 
@@ -111,7 +114,7 @@ int device_sm_count(int* out) { return device_info(out, nullptr); }
 // takes effect from some later call on, never halfway through one.
 static std::atomic<int> g_gemv_max_tokens{2};
 int decode_gemv_max_tokens() { return g_gemv_max_tokens.load(std::memory_order_relaxed); }
-static std::atomic<int> g_mma_max_tokens{32};
+static std::atomic<int> g_mma_max_tokens{64};
 int decode_mma_max_tokens() { return g_mma_max_tokens.load(std::memory_order_relaxed); }
 static std::atomic<int> g_decode_overlap{0};
 bool decode_overlap() { return g_decode_overlap.load(std::memory_order_relaxed) != 0; }
@@ -464,7 +467,7 @@ int el_set_decode_gemv_max_tokens(int max_tokens) {
 }
 
 int el_set_decode_mma_max_tokens(int max_tokens) {
-    if (max_tokens < 0 || max_tokens > 32) return EL_ERR_INVALID_ARG;
+    if (max_tokens < 0 || max_tokens > 64) return EL_ERR_INVALID_ARG;
     g_mma_max_tokens.store(max_tokens, std::memory_order_relaxed);
     return EL_OK;
 }
@@ -488,9 +491,17 @@ int el_linear_decode(const void* x, int x_dtype, const uint8_t* W_packed, void* 
         const EpiParams gepi{Y, (long long)N, out_dtype, nullptr, 0, gamma};
         return launch_gemv_small(x, x_dtype, W_packed, gepi, M, N, K, (cudaStream_t)stream, decode_overlap());
     }
-    if (M <= decode_mma_max_tokens() && gemv_mma_fits(M, K)) {      // up to 32 tokens that fit in shared memory: one warp-MMA launch
+    if (M <= DECODE_MMA_SINGLE_MAX && M <= decode_mma_max_tokens() && gemv_mma_fits(M, K)) {
+        // up to 8 tokens that fit in shared memory: one warp-MMA launch that quantises the tokens itself
         const EpiParams gepi{Y, (long long)N, out_dtype, nullptr, 0, gamma};
         return launch_gemv_mma(x, x_dtype, W_packed, gepi, M, N, K, (cudaStream_t)stream, decode_overlap());
+    }
+    if (M <= decode_mma_max_tokens() && gemv_mma_preq_fits(M, K)) {
+        // more tokens: quantise them once, then the warp-MMA kernel on the quantised tokens, 32 at a time
+        int rc = launch_quantize_rows_perm(x, x_dtype, K, xq_scratch, absmax, M, K, 1e-5f, (cudaStream_t)stream);
+        if (rc != EL_OK) return rc;
+        const EpiParams gepi{Y, (long long)N, out_dtype, nullptr, 0, gamma};
+        return launch_gemv_mma_preq(xq_scratch, absmax, W_packed, gepi, M, N, K, (cudaStream_t)stream);
     }
     int rc = launch_quantize_rows_perm(x, x_dtype, K, xq_scratch, absmax, M, K, 1e-5f, (cudaStream_t)stream);
     if (rc != EL_OK) return rc;

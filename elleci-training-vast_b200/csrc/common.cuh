@@ -21,6 +21,10 @@ int require_sm100();                     // EL_OK when the current device is com
 // "Set up once per device" bookkeeping that host threads may race on.  The set-up calls guarded by it are idempotent
 // (a function attribute, a queried constant), so two threads that both find the flag clear simply both run them; the
 // flag itself is an atomic, published after the set-up returned.
+// Decode calls of up to this many tokens use the warp-MMA kernel in its single-launch form (every CTA quantises the tokens
+// itself); larger ones quantise once and run it on the quantised tokens.
+constexpr int DECODE_MMA_SINGLE_MAX = 8;
+
 struct DeviceOnce {
     std::atomic<int> done[64];
     bool is_done(int dev) const { return dev >= 0 && dev < 64 && done[dev].load(std::memory_order_acquire) != 0; }

@@ -157,6 +157,12 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         // ================= epilogue: partial sums -> workspace; last contributor of a tile finishes it =========
         const int quarter = warp & 3;
         const int n_in_tile = quarter * 32 + lane;
+        // The tokens' scales, two per lane (tokens `lane` and `lane + 32`), handed out by shuffle.  Loading a scale inside
+        // the store loops would put a global load and a division behind every store (the compiler must assume the two
+        // alias), one trip to L2 per token: that chain was a sixth of the call at 64 tokens.
+        const float sc_lo = (lane < p.M) ? epi_row_scale(p.epi, lane) : 0.0f;
+        const float sc_hi = (lane + 32 < p.M) ? epi_row_scale(p.epi, lane + 32) : 0.0f;
+        auto scale_of = [&](int m) { return __shfl_sync(0xffffffffu, m < 32 ? sc_lo : sc_hi, m & 31); };
         int it = 0;
         for (long long u = u_lo; u < u_hi && !failed; ++it) {
             const int t = (int)(u / p.k_blocks), kb0 = (int)(u % p.k_blocks);
@@ -170,25 +176,24 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
             const bool n_ok = n < p.N;
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * NU);
             const bool whole = (cnt == p.k_blocks);      // this CTA holds the complete sums of the tile
-#pragma unroll 1
-            for (int c = 0; c < NU / 16; ++c) {
-                uint32_t v[16];
-                tmem_ld16(taddr + c * 16, v);
-                tmem_ld_wait();
-                if (n_ok) {
+            uint32_t v[NU];                               // the whole accumulator row: every load in flight, one wait
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int m = c * 16 + j;
-                        if (m < p.M) {
-                            if (whole) epi_store_one(p.epi, m, n, (int)v[j], epi_row_scale(p.epi, m));
-                            else atomicAdd(p.acc_ws + (size_t)m * p.N + n, (int)v[j]);
-                        }
+            for (int c = 0; c < NU / 16; ++c) tmem_ld16(taddr + c * 16, *reinterpret_cast<uint32_t(*)[16]>(&v[c * 16]));
+            tmem_ld_wait();
+            tcgen05_fence_before();                       // the sums are in registers: hand the accumulator back first
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_tempty(acc));
+#pragma unroll
+            for (int m = 0; m < NU; ++m) {
+                if (m < p.M) {
+                    if (whole) {
+                        const float sc = scale_of(m);
+                        if (n_ok) epi_store_one(p.epi, m, n, (int)v[m], sc);
+                    } else if (n_ok) {
+                        atomicAdd(p.acc_ws + (size_t)m * p.N + n, (int)v[m]);
                     }
                 }
             }
-            tcgen05_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_tempty(acc));
             if (!whole) {
                 // Publish this warp's partial sums, then count the segment's reduction blocks towards this quarter
                 // of the tile.  Each quarter (32 weight rows) has its own counter, so no warp waits for another:
@@ -201,17 +206,18 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
                 before = __shfl_sync(0xffffffffu, before, 0);
                 if (before + cnt == p.k_blocks) {
                     __threadfence();
-                    if (n_ok) {
-                        for (int m0 = 0; m0 < p.M; m0 += 8) {       // eight independent loads in flight per lane
-                            int sum[8];
+                    for (int m0 = 0; m0 < p.M; m0 += 32) {      // 32 independent loads in flight per lane
+                        int sum[32];
 #pragma unroll
-                            for (int j = 0; j < 8; ++j)
-                                sum[j] = (m0 + j < p.M) ? __ldcg(p.acc_ws + (size_t)(m0 + j) * p.N + n) : 0;
+                        for (int j = 0; j < 32; ++j)
+                            sum[j] = (n_ok && m0 + j < p.M) ? __ldcg(p.acc_ws + (size_t)(m0 + j) * p.N + n) : 0;
 #pragma unroll
-                            for (int j = 0; j < 8; ++j) {
-                                if (m0 + j < p.M) {
-                                    epi_store_one(p.epi, m0 + j, n, sum[j], epi_row_scale(p.epi, m0 + j));
+                        for (int j = 0; j < 32; ++j) {
+                            if (m0 + j < p.M) {
+                                const float sc = scale_of(m0 + j);
+                                if (n_ok) {
                                     __stcg(p.acc_ws + (size_t)(m0 + j) * p.N + n, 0);
+                                    epi_store_one(p.epi, m0 + j, n, sum[j], sc);
                                 }
                             }
                         }
@@ -372,6 +378,9 @@ int launch_gemv_small(const void* x, int x_dtype, const uint8_t* Wp, const EpiPa
 int launch_gemv_mma(const void* x, int x_dtype, const uint8_t* Wp, const EpiParams& epi, int M, int N, int K, cudaStream_t st,
                     bool overlap);
 bool gemv_mma_fits(int M, int K);
+bool gemv_mma_preq_fits(int M, int K);
+int launch_gemv_mma_preq(const int8_t* xq, const float* amax, const uint8_t* Wp, const EpiParams& epi, int M, int N, int K,
+                         cudaStream_t st);
 bool decode_overlap();
 int decode_gemv_max_tokens();
 int decode_mma_max_tokens();
@@ -397,12 +406,18 @@ extern "C" EL_API int el_linear_decode_static(const void* x, int x_dtype, const 
         const EpiParams gepi{Y, (long long)N, out_dtype, nullptr, 0, gamma};
         return launch_gemv_small(x, x_dtype, W_packed, gepi, M, N, K, st, decode_overlap());
     }
-    if (M <= decode_mma_max_tokens() && gemv_mma_fits(M, K)) {      // neither does the warp-MMA kernel
+    if (M <= DECODE_MMA_SINGLE_MAX && M <= decode_mma_max_tokens() && gemv_mma_fits(M, K)) {      // neither does the warp-MMA kernel
         const EpiParams gepi{Y, (long long)N, out_dtype, nullptr, 0, gamma};
         return launch_gemv_mma(x, x_dtype, W_packed, gepi, M, N, K, st, decode_overlap());
     }
     int8_t* xq = reinterpret_cast<int8_t*>(base + STATIC_XQ_OFFSET);
     float* absmax = reinterpret_cast<float*>(base + STATIC_ABSMAX_OFFSET);
+    if (M <= decode_mma_max_tokens() && gemv_mma_preq_fits(M, K)) {      // the warp-MMA kernel on tokens quantised once
+        rc = launch_quantize_rows_perm(x, x_dtype, K, xq, absmax, M, K, 1e-5f, st);
+        if (rc != EL_OK) return rc;
+        const EpiParams gepi{Y, (long long)N, out_dtype, nullptr, 0, gamma};
+        return launch_gemv_mma_preq(xq, absmax, W_packed, gepi, M, N, K, st);
+    }
     // The array keeps whatever the previous call left.  The partial-sum rows and the tile counters this call will use
     // must start at zero, so they are cleared here on the caller's stream (the rest of the array is overwritten
     // before it is read).

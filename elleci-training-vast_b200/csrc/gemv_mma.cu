@@ -82,9 +82,12 @@ __device__ __forceinline__ void mma_s8(int d[4], const uint32_t a[4], uint32_t b
 // NT token groups of 8.  Shared memory: [0,256) absmax floats; then the tokens as B fragments, uint4 index
 // ((kb*4 + w)*MT + m)*4 + s for the 16 indices 256*kb + 64*s + 16*w .. of token m (a quarter-warp then reads eight
 // consecutive uint4: no bank conflicts); then two [16][MT] int32 accumulators for the cross-warp sums.
-template <typename T, int NT>
+// PREQ: the tokens arrive quantised (xq int8 [M,K] in the permuted order, amax_in [M], written by the launch before this
+// one) and are only copied into shared memory; otherwise every CTA quantises x itself.
+template <typename T, int NT, bool PREQ>
 __global__ void __launch_bounds__(GM_THREADS, 1)
-gemv_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ Wp, EpiParams epi, int M, int N, int K, float eps) {
+gemv_mma_kernel(const T* __restrict__ x, const int8_t* xq, const float* amax_in, const uint8_t* __restrict__ Wp, EpiParams epi,
+                int M, int N, int K, float eps) {
     constexpr int MT = NT * 8;
     extern __shared__ uint4 gm_smem[];
     float* s_amax = reinterpret_cast<float*>(gm_smem);
@@ -132,43 +135,55 @@ gemv_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ Wp, EpiPara
     const int groups = K >> 4;
     for (int i = tid; i < 2 * 16 * MT; i += GM_THREADS) acc_sm[i] = 0;
     if (tid == 0) s_checked = 0;
-    __syncthreads();
-    for (int m = warp; m < M; m += GM_WARPS) {
-        float amax = 0.0f;
-        for (int g = lane; g < groups; g += 32) {
-            float v[16];
-            gm_load16<T>(x + (size_t)m * K + g * 16, v);
-#pragma unroll
-            for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));        // drops NaN, keeps infinities
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-        if (!(amax <= 3.402823466e38f)) {
-            // the token holds an infinity: redo its maximum with non-finite values counted as zero
-            amax = 0.0f;
+    if (PREQ) {
+        if (tid < MT) s_amax[tid] = tid < M ? __ldcg(amax_in + tid) : 1.0f;
+    } else {
+        __syncthreads();
+        for (int m = warp; m < M; m += GM_WARPS) {
+            float amax = 0.0f;
             for (int g = lane; g < groups; g += 32) {
                 float v[16];
                 gm_load16<T>(x + (size_t)m * K + g * 16, v);
 #pragma unroll
-                for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(finite_or_zero(v[i])));
+                for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));        // drops NaN, keeps infinities
             }
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-            if (lane == 0) s_checked = 1;
+            if (!(amax <= 3.402823466e38f)) {
+                // the token holds an infinity: redo its maximum with non-finite values counted as zero
+                amax = 0.0f;
+                for (int g = lane; g < groups; g += 32) {
+                    float v[16];
+                    gm_load16<T>(x + (size_t)m * K + g * 16, v);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(finite_or_zero(v[i])));
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+                if (lane == 0) s_checked = 1;
+            }
+            if (lane == 0) s_amax[m] = fmaxf(amax, eps);
         }
-        if (lane == 0) s_amax[m] = fmaxf(amax, eps);
     }
     __syncthreads();
     const bool checked = s_checked != 0;
-    const int groups_padded = kblocks * 16;
-    for (int i = tid; i < MT * groups_padded; i += GM_THREADS) {
-        const int m = i / groups_padded, g = i - m * groups_padded;
-        const int kb = g >> 4, sg = (g >> 2) & 3, w = g & 3;
+    // A warp fills, per step, the 16 groups of one 256-block for a pair of tokens: two 256-byte runs of global memory,
+    // and shared-memory addresses that fall four to each 16-byte bank group (the uint4 index is ... + m*4 + s).
+    const int work = kblocks * (MT / 2) * 32;
+    for (int i = tid; i < work; i += GM_THREADS) {
+        const int l = i & 31, chunk = i >> 5;
+        const int kb = chunk / (MT / 2), m = (chunk - kb * (MT / 2)) * 2 + (l >> 4);
+        const int g = kb * 16 + (l & 15);
+        const int sg = (g >> 2) & 3, w = g & 3;
         uint4 v = make_uint4(0u, 0u, 0u, 0u);                  // padding tokens and indices beyond K multiply by zero
         if (m < M && g < groups) {
-            const float s = __fdiv_rn(127.0f, s_amax[m]);
-            const T* src = x + (size_t)m * K + g * 16;
-            v = checked ? gm_quant16<T, true>(src, s) : gm_quant16<T, false>(src, s);
+            if (PREQ) {
+                v = __ldcg(reinterpret_cast<const uint4*>(xq + (size_t)m * K) + g);
+            } else {
+                const float s = __fdiv_rn(127.0f, s_amax[m]);
+                const T* src = x + (size_t)m * K + g * 16;
+                v = checked ? gm_quant16<T, true>(src, s) : gm_quant16<T, false>(src, s);
+            }
         }
         xs[((kb * 4 + w) * MT + m) * 4 + sg] = v;
     }
@@ -229,8 +244,9 @@ gemv_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ Wp, EpiPara
     }
 }
 
-template <typename T, int NT>
-int launch_gemv_mma_t(const T* x, const uint8_t* Wp, const EpiParams& epi, int M, int N, int K, cudaStream_t st, bool overlap) {
+template <typename T, int NT, bool PREQ>
+int launch_gemv_mma_t(const T* x, const int8_t* xq, const float* amax, const uint8_t* Wp, const EpiParams& epi, int M, int N,
+                      int K, cudaStream_t st, bool overlap) {
     constexpr int MT = NT * 8;
     const int kblocks = (K + 255) >> 8;
     const size_t smem = 256 + (size_t)kblocks * 16 * MT * sizeof(uint4) + 2 * 16 * MT * sizeof(int);
@@ -242,7 +258,7 @@ int launch_gemv_mma_t(const T* x, const uint8_t* Wp, const EpiParams& epi, int M
     int dev = 0;
     EL_CUDA_TRY(cudaGetDevice(&dev));
     if (!attr_once.is_done(dev)) {
-        EL_CUDA_TRY(cudaFuncSetAttribute(gemv_mma_kernel<T, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        EL_CUDA_TRY(cudaFuncSetAttribute(gemv_mma_kernel<T, NT, PREQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         attr_once.mark(dev);
     }
     const int row_groups = (N + 15) / 16;
@@ -256,15 +272,15 @@ int launch_gemv_mma_t(const T* x, const uint8_t* Wp, const EpiParams& epi, int M
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = overlap ? 1 : 0;
-    EL_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_mma_kernel<T, NT>, x, Wp, epi, M, N, K, 1e-5f));
+    EL_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_mma_kernel<T, NT, PREQ>, x, xq, amax, Wp, epi, M, N, K, 1e-5f));
     return check_launch();
 }
 
 template <typename T>
 int launch_gemv_mma_m(const T* x, const uint8_t* Wp, const EpiParams& epi, int M, int N, int K, cudaStream_t st, bool overlap) {
-    if (M <= 8) return launch_gemv_mma_t<T, 1>(x, Wp, epi, M, N, K, st, overlap);
-    if (M <= 16) return launch_gemv_mma_t<T, 2>(x, Wp, epi, M, N, K, st, overlap);
-    return launch_gemv_mma_t<T, 4>(x, Wp, epi, M, N, K, st, overlap);
+    if (M <= 8) return launch_gemv_mma_t<T, 1, false>(x, nullptr, nullptr, Wp, epi, M, N, K, st, overlap);
+    if (M <= 16) return launch_gemv_mma_t<T, 2, false>(x, nullptr, nullptr, Wp, epi, M, N, K, st, overlap);
+    return launch_gemv_mma_t<T, 4, false>(x, nullptr, nullptr, Wp, epi, M, N, K, st, overlap);
 }
 
 }  // namespace
@@ -288,6 +304,39 @@ int launch_gemv_mma(const void* x, int x_dtype, const uint8_t* Wp, const EpiPara
         case EL_F32: return launch_gemv_mma_m((const float*)x, Wp, epi, M, N, K, st, overlap);
         default: return EL_ERR_INVALID_ARG;
     }
+}
+
+// The same kernel on tokens that launch_quantize_rows_perm has already quantised on this stream (xq int8 [M,K], amax [M]):
+// no CTA repeats the quantisation, which is what the single-launch form spends most of its time on from about 16 tokens
+// up (148 CTAs each converting all M*K values).  The launch is a programmatic dependent of the quantiser: its CTAs
+// request their first weight fragments while the quantiser still runs and read the tokens after it has completed.  That
+// is safe whatever else the stream holds, because the quantiser itself started after all earlier work had finished.
+// Any number of tokens: they are taken 32 (or 16, or 8) at a time, one launch each; the weights of the later launches
+// come from L2.
+bool gemv_mma_preq_fits(int M, int K) {
+    if (M < 1 || K <= 0 || K % 64 != 0) return false;
+    return gemv_mma_fits(M < 32 ? M : 32, K);
+}
+
+int launch_gemv_mma_preq(const int8_t* xq, const float* amax, const uint8_t* Wp, const EpiParams& epi, int M, int N, int K,
+                         cudaStream_t st) {
+    if (!gemv_mma_preq_fits(M, K)) return EL_ERR_UNSUPPORTED_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(xq) & 15) || (reinterpret_cast<uintptr_t>(Wp) & 15)) return EL_ERR_ALIGNMENT;
+    const size_t out_bytes = (epi.out_dtype == EL_F16 || epi.out_dtype == EL_BF16) ? 2 : 4;
+    for (int m0 = 0; m0 < M; m0 += 32) {
+        const int mc = (M - m0) < 32 ? (M - m0) : 32;
+        EpiParams e = epi;
+        e.out = static_cast<unsigned char*>(epi.out) + (size_t)m0 * epi.ldo * out_bytes;
+        const int8_t* q = xq + (size_t)m0 * K;
+        const float* a = amax + m0;
+        const __nv_bfloat16* none = nullptr;
+        int rc;
+        if (mc <= 8) rc = launch_gemv_mma_t<__nv_bfloat16, 1, true>(none, q, a, Wp, e, mc, N, K, st, true);
+        else if (mc <= 16) rc = launch_gemv_mma_t<__nv_bfloat16, 2, true>(none, q, a, Wp, e, mc, N, K, st, true);
+        else rc = launch_gemv_mma_t<__nv_bfloat16, 4, true>(none, q, a, Wp, e, mc, N, K, st, true);
+        if (rc != EL_OK) return rc;
+    }
+    return EL_OK;
 }
 
 }  // namespace el

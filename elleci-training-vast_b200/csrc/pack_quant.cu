@@ -265,6 +265,9 @@ __global__ void __launch_bounds__(256)
 quantize_rows_perm_kernel(const T* __restrict__ x, long long ldx, int8_t* __restrict__ q, float* __restrict__ row_absmax,
                           int K, float eps) {
     __shared__ float red[8];
+    // A kernel launched behind this one as a programmatic dependent may start its own preamble now (it waits for this
+    // grid to complete before it reads q or row_absmax); without such a dependent this does nothing.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int m = blockIdx.x;
     const T* xr = x + (size_t)m * ldx;
     int8_t* qr = q + (size_t)m * K;

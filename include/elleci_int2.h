@@ -337,9 +337,11 @@ EL_API size_t el_decode_workspace_bytes(int N);
 /* Tuning: calls with at most `max_tokens` tokens (0..8, default 2) take a single-launch CUDA-core GEMV that
  * quantises the tokens itself and touches no scratch; larger ones take the tensor-core kernel.  Process-wide. */
 EL_API int el_set_decode_gemv_max_tokens(int max_tokens);
-/* Tuning: calls with more tokens than the limit above and at most `max_tokens` (0..32, default 32) whose int8 tokens
- * fit in shared memory (M*K up to about 190 KB) take a single-launch kernel on the warp-level int8 MMA that also
- * quantises the tokens itself and touches no scratch; the rest take the tcgen05 stream-K kernel.  Process-wide. */
+/* Tuning: calls with more tokens than the limit above and at most `max_tokens` (0..64, default 64) whose int8 tokens,
+ * taken 32 at a time, fit in shared memory (up to 32*K of about 190 KB) run on the warp-level int8 MMA: up to 8 tokens as
+ * one launch that quantises the tokens itself and touches no scratch; more tokens as the row quantiser (into xq_scratch
+ * and absmax) followed by one launch per 32 tokens on the quantised tokens, each a programmatic dependent of the launch
+ * before it.  The rest take the tcgen05 stream-K kernel.  Process-wide. */
 EL_API int el_set_decode_mma_max_tokens(int max_tokens);
 /* Tuning, off by default: with `enable` != 0 the single-launch GEMV of el_linear_decode is issued as a programmatic
  * dependent launch.  It may then start while earlier work of the stream still runs; until that work has completed it

@@ -51,8 +51,8 @@ def test_status_strings_and_host_side_argument_checks():
     assert handle.el_swiglu_backward(None, None, None, lib.EL_F16, 8, None, None, None, None, 4, None, None, 0, 1, 8, None) == lib.EL_ERR_INVALID_ARG
     # tuning knobs: range-checked, process-wide
     assert handle.el_set_decode_gemv_max_tokens(9) == lib.EL_ERR_INVALID_ARG
-    assert handle.el_set_decode_mma_max_tokens(33) == lib.EL_ERR_INVALID_ARG
-    assert handle.el_set_decode_gemv_max_tokens(2) == lib.EL_OK and handle.el_set_decode_mma_max_tokens(32) == lib.EL_OK
+    assert handle.el_set_decode_mma_max_tokens(65) == lib.EL_ERR_INVALID_ARG
+    assert handle.el_set_decode_gemv_max_tokens(2) == lib.EL_OK and handle.el_set_decode_mma_max_tokens(64) == lib.EL_OK
     assert handle.el_set_decode_overlap(0) == lib.EL_OK
     assert handle.el_set_peer_barrier_limit_us(-5) == lib.EL_ERR_INVALID_ARG
     assert handle.el_set_peer_barrier_limit_us(1000) == lib.EL_OK and handle.el_set_peer_barrier_limit_us(0) == lib.EL_OK
@@ -84,5 +84,5 @@ def test_tuning_setters_from_several_threads_leave_a_valid_value():
     for t in threads:
         t.join()
     assert set(rcs) == {0}
-    assert handle.el_set_decode_gemv_max_tokens(2) == 0 and handle.el_set_decode_mma_max_tokens(32) == 0
+    assert handle.el_set_decode_gemv_max_tokens(2) == 0 and handle.el_set_decode_mma_max_tokens(64) == 0
     assert handle.el_set_decode_overlap(0) == 0

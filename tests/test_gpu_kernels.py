@@ -368,12 +368,13 @@ def test_fused_dw_hysteresis_bit_exact(ops, M, N, K, thr):
 @pytest.fixture
 def gemv_threshold(ops):
     """Lets a test choose between the few-token CUDA-core GEMV (up to `v` tokens), the warp-MMA kernel (up to `mma`
-    tokens) and the tcgen05 stream-K kernel (the rest)."""
+    tokens: one launch up to 8, quantiser + kernel on the quantised tokens beyond) and the tcgen05 stream-K kernel (the
+    rest)."""
     def set_(v, mma=0):
         assert ops._lib.lib().el_set_decode_gemv_max_tokens(v) == 0
         assert ops._lib.lib().el_set_decode_mma_max_tokens(mma) == 0
     yield set_
-    set_(2, 32)
+    set_(2, 64)
 
 
 @pytest.mark.parametrize("gemv_max", [0, 8, "mma"])
@@ -390,7 +391,7 @@ def test_linear_decode_bit_exact(ops, gemv_threshold, M, K, N, gemv_max):
     want = O.to_bf16(O.scale_rows(O.gemm_fwd_acc(Xq, Wp, K), ax, gamma))
     # 0: tcgen05 kernel for every M; 8: CUDA-core GEMV up to 8 tokens; "mma": warp-MMA kernel wherever the tokens fit
     if gemv_max == "mma":
-        gemv_threshold(0, 32)
+        gemv_threshold(0, 64)
     else:
         gemv_threshold(gemv_max)
     ws = torch.zeros(ops._lib.lib().el_decode_workspace_bytes(N), dtype=torch.uint8, device=DEV)
@@ -410,7 +411,7 @@ def test_linear_decode_counts_non_finite_tokens_as_zero(ops, gemv_threshold, M, 
     K, N = 1024, 328
     g = torch.Generator().manual_seed(90 + M)
     if gemv_max == "mma":
-        gemv_threshold(0, 32)
+        gemv_threshold(0, 64)
     else:
         gemv_threshold(gemv_max)
     Wp, _ = random_packed(N, K, seed=77)

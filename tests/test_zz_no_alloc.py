@@ -64,14 +64,26 @@ def test_static_scratch_decode_matches_regular_entry_point_twice_in_a_row(pkg):
         assert not torch.equal(y1, y2) and float(y1.float().abs().max()) > 0.0
 
 
-def test_static_scratch_is_really_used_and_shared_between_shapes(pkg):
-    """Calls that need the array (more than 32 tokens, or tokens that do not fit in shared memory): the stated capacity
-    M=64 at N=16384, a 40-token call, then a small-N call whose tile counters sit where the large call kept partial
-    sums, then the large one again.  The first call of the sequence is a one-token call, which touches no scratch but
-    must already have resolved the array's address.  Every result is checked against the regular entry point and
-    against the CPU oracle."""
+@pytest.mark.parametrize("mma_max", [64, 0])
+def test_static_scratch_is_really_used_and_shared_between_shapes(pkg, mma_max):
+    """Calls that need the array (more than 8 tokens): the stated capacity M=64 at N=16384, a 40-token call, then a
+    small-N call whose tile counters sit where the large call kept partial sums, then the large one again, then tokens
+    that do not fit in shared memory.  With the default limits the quantised tokens and their scales live in the array
+    and the warp-MMA kernel reads them (the last case takes the tcgen05 kernel and its partial-sum area); with the
+    warp-MMA kernel switched off (`mma_max` 0) every case takes the tcgen05 kernel.  The first call of the sequence is
+    a one-token call, which touches no scratch but must already have resolved the array's address.  Every result is
+    checked against the regular entry point and against the CPU oracle."""
+    assert pkg._lib.lib().el_set_decode_mma_max_tokens(mma_max) == 0
+    try:
+        _static_sequence(pkg)
+    finally:
+        assert pkg._lib.lib().el_set_decode_mma_max_tokens(64) == 0
+
+
+def _static_sequence(pkg):
     gamma = 0.0157
-    seq = [(1, 4096, 16384), (64, 4096, 16384), (33, 1024, 640), (40, 4096, 16384), (48, 256, 128), (64, 4096, 16384)]
+    seq = [(1, 4096, 16384), (64, 4096, 16384), (33, 1024, 640), (40, 4096, 16384), (48, 256, 128), (64, 4096, 16384),
+           (40, 11008, 512)]
     weights = {}
     for i, (M, K, N) in enumerate(seq):
         if (K, N) not in weights:
