@@ -60,6 +60,87 @@ __global__ void unpack_kernel(const uint8_t* __restrict__ Wp, OutT* __restrict__
     }
 }
 
+// Vector forms for matrices whose rows are whole 16-weight words (K % 16 == 0) at 16-byte aligned addresses: a thread
+// takes one 32-bit word of codes (16 weights), consecutive threads consecutive words, so a warp reads 128 and writes 512
+// (int8) to 2048 (float32) contiguous bytes per step; four steps are in flight per thread.
+template <typename OutT> __device__ __forceinline__ void store16_ternary(OutT* out, const uint32_t w[4]);
+template <> __device__ __forceinline__ void store16_ternary<int8_t>(int8_t* out, const uint32_t w[4]) {
+    *reinterpret_cast<uint4*>(out) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+__device__ __forceinline__ float s8_of(uint32_t word, int i) { return (float)(int)(int8_t)(word >> (8 * i)); }
+template <> __device__ __forceinline__ void store16_ternary<__nv_bfloat16>(__nv_bfloat16* out, const uint32_t w[4]) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+        reinterpret_cast<uint4*>(out)[h] =
+            make_uint4(pack_bf16x2(s8_of(w[2 * h], 0), s8_of(w[2 * h], 1)), pack_bf16x2(s8_of(w[2 * h], 2), s8_of(w[2 * h], 3)),
+                       pack_bf16x2(s8_of(w[2 * h + 1], 0), s8_of(w[2 * h + 1], 1)), pack_bf16x2(s8_of(w[2 * h + 1], 2), s8_of(w[2 * h + 1], 3)));
+}
+template <> __device__ __forceinline__ void store16_ternary<__half>(__half* out, const uint32_t w[4]) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+        reinterpret_cast<uint4*>(out)[h] =
+            make_uint4(pack_f16x2(s8_of(w[2 * h], 0), s8_of(w[2 * h], 1)), pack_f16x2(s8_of(w[2 * h], 2), s8_of(w[2 * h], 3)),
+                       pack_f16x2(s8_of(w[2 * h + 1], 0), s8_of(w[2 * h + 1], 1)), pack_f16x2(s8_of(w[2 * h + 1], 2), s8_of(w[2 * h + 1], 3)));
+}
+template <> __device__ __forceinline__ void store16_ternary<float>(float* out, const uint32_t w[4]) {
+#pragma unroll
+    for (int h = 0; h < 4; ++h)
+        reinterpret_cast<float4*>(out)[h] = make_float4(s8_of(w[h], 0), s8_of(w[h], 1), s8_of(w[h], 2), s8_of(w[h], 3));
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(256)
+unpack_vec_kernel(const uint32_t* __restrict__ Wp, OutT* __restrict__ out, long long n_words) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_words; i += 4 * stride) {
+        uint32_t code[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) code[j] = (i + j * stride < n_words) ? __ldg(Wp + i + j * stride) : 0u;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (i + j * stride < n_words) {
+                uint32_t w[4];
+                decode16(code[j], w);
+                store16_ternary<OutT>(out + (i + j * stride) * 16, w);
+            }
+        }
+    }
+}
+
+// Ternarise + pack, vector form (K % 16 == 0, 16-byte aligned rows): a thread takes 16 consecutive weights as four
+// 16-byte loads, interleaved over the warp so that every load instruction reads 512 contiguous bytes, and writes the
+// four packed bytes it produced (byte j*32 + lane of the warp's 128-byte output run).
+__global__ void __launch_bounds__(256)
+ternarize_pack_vec_kernel(const float4* __restrict__ src, float gamma, uint8_t* __restrict__ Wp, long long n_bytes) {
+    const int lane = threadIdx.x & 31;
+    const long long warp_id = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const long long n_warps = ((long long)gridDim.x * blockDim.x) >> 5;
+    for (long long b0 = warp_id * 128; b0 < n_bytes; b0 += n_warps * 128) {      // 128 packed bytes = 512 weights per warp and step
+        float4 v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const long long b = b0 + j * 32 + lane;
+            v[j] = (b < n_bytes) ? __ldg(src + b) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const long long b = b0 + j * 32 + lane;
+            if (b < n_bytes) {
+                const float w4[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+                uint32_t byte = 0;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    float r = rintf(__fdiv_rn(w4[i], gamma));     // round half to even
+                    r = fminf(1.0f, fmaxf(-1.0f, r));
+                    const int q = (r != r) ? 0 : (int)r;
+                    byte |= (uint32_t)(q + 1) << (2 * i);
+                }
+                Wp[b] = (uint8_t)byte;
+            }
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------------------------------
 // per-token quantisation: one CTA per row
 // ---------------------------------------------------------------------------------------------------------
@@ -316,27 +397,52 @@ quantize_rows_perm_kernel(const T* __restrict__ x, long long ldx, int8_t* __rest
 // per-tensor quantisation (the reference CUDA path's rule)
 // ---------------------------------------------------------------------------------------------------------
 
+// The three per-tensor kernels take the tensor as 16-element vectors (two 16-byte loads of 16-bit data, one 16-byte
+// store of int8) over the part that allows it (`n_vec` vectors: the whole tensor when its base is 16-byte aligned, less
+// the tail) and element by element over the rest.
 template <typename T>
 __global__ void __launch_bounds__(256)
-tensor_absmax_kernel(const T* __restrict__ x, float* __restrict__ absmax, long long size) {
+tensor_absmax_kernel(const T* __restrict__ x, float* __restrict__ absmax, long long size, long long n_vec) {
     __shared__ float red[8];
     float amax = 0.0f;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < size; i += (long long)gridDim.x * blockDim.x)
-        amax = fmaxf(amax, fabsf(finite_or_zero(to_float<T>(x[i]))));
+    const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, stride = (long long)gridDim.x * blockDim.x;
+#pragma unroll 4
+    for (long long i = tid; i < n_vec; i += stride) {
+        float v[16];
+        load8<T>(x + i * 16, v);
+        load8<T>(x + i * 16 + 8, v + 8);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(finite_or_zero(v[j])));
+    }
+    for (long long i = n_vec * 16 + tid; i < size; i += stride) amax = fmaxf(amax, fabsf(finite_or_zero(to_float<T>(x[i]))));
     amax = block_max(amax, red);
     if (threadIdx.x == 0 && amax > 0.0f) atomicMax(reinterpret_cast<int*>(absmax), __float_as_int(amax));
 }
 
+__device__ __forceinline__ int tensor_q8(float v, float inv) {
+    const float r = fmaxf(-127.0f, fminf(127.0f, roundf(__fmul_rn(finite_or_zero(v), inv))));   // half away from zero
+    return (int)r;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
-tensor_quant_kernel(const T* __restrict__ x, int8_t* __restrict__ q, const float* __restrict__ absmax, long long size) {
+tensor_quant_kernel(const T* __restrict__ x, int8_t* __restrict__ q, const float* __restrict__ absmax, long long size,
+                    long long n_vec) {
     const float a = *absmax;
     const float inv = (a > 1e-8f) ? __fdiv_rn(127.0f, a) : 0.0f;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < size; i += (long long)gridDim.x * blockDim.x) {
-        const float v = finite_or_zero(to_float<T>(x[i]));
-        const float r = fmaxf(-127.0f, fminf(127.0f, roundf(__fmul_rn(v, inv))));   // half away from zero
-        q[i] = (int8_t)r;
+    const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, stride = (long long)gridDim.x * blockDim.x;
+#pragma unroll 4
+    for (long long i = tid; i < n_vec; i += stride) {
+        float v[16];
+        load8<T>(x + i * 16, v);
+        load8<T>(x + i * 16 + 8, v + 8);
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            w[j] = pack4_s8(tensor_q8(v[4 * j], inv), tensor_q8(v[4 * j + 1], inv), tensor_q8(v[4 * j + 2], inv), tensor_q8(v[4 * j + 3], inv));
+        reinterpret_cast<uint4*>(q)[i] = make_uint4(w[0], w[1], w[2], w[3]);
     }
+    for (long long i = n_vec * 16 + tid; i < size; i += stride) q[i] = (int8_t)tensor_q8(to_float<T>(x[i]), inv);
 }
 
 template <typename T> __device__ __forceinline__ T from_float(float v);
@@ -344,12 +450,37 @@ template <> __device__ __forceinline__ float from_float<float>(float v) { return
 template <> __device__ __forceinline__ __half from_float<__half>(float v) { return __float2half_rn(v); }
 template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
+template <typename T> __device__ __forceinline__ void store8_scaled(T* out, uint32_t lo, uint32_t hi, float sc);
+template <> __device__ __forceinline__ void store8_scaled<float>(float* out, uint32_t lo, uint32_t hi, float sc) {
+    reinterpret_cast<float4*>(out)[0] = make_float4(__fmul_rn(s8_of(lo, 0), sc), __fmul_rn(s8_of(lo, 1), sc), __fmul_rn(s8_of(lo, 2), sc), __fmul_rn(s8_of(lo, 3), sc));
+    reinterpret_cast<float4*>(out)[1] = make_float4(__fmul_rn(s8_of(hi, 0), sc), __fmul_rn(s8_of(hi, 1), sc), __fmul_rn(s8_of(hi, 2), sc), __fmul_rn(s8_of(hi, 3), sc));
+}
+template <> __device__ __forceinline__ void store8_scaled<__nv_bfloat16>(__nv_bfloat16* out, uint32_t lo, uint32_t hi, float sc) {
+    *reinterpret_cast<uint4*>(out) = make_uint4(pack_bf16x2(__fmul_rn(s8_of(lo, 0), sc), __fmul_rn(s8_of(lo, 1), sc)),
+                                                pack_bf16x2(__fmul_rn(s8_of(lo, 2), sc), __fmul_rn(s8_of(lo, 3), sc)),
+                                                pack_bf16x2(__fmul_rn(s8_of(hi, 0), sc), __fmul_rn(s8_of(hi, 1), sc)),
+                                                pack_bf16x2(__fmul_rn(s8_of(hi, 2), sc), __fmul_rn(s8_of(hi, 3), sc)));
+}
+template <> __device__ __forceinline__ void store8_scaled<__half>(__half* out, uint32_t lo, uint32_t hi, float sc) {
+    *reinterpret_cast<uint4*>(out) = make_uint4(pack_f16x2(__fmul_rn(s8_of(lo, 0), sc), __fmul_rn(s8_of(lo, 1), sc)),
+                                                pack_f16x2(__fmul_rn(s8_of(lo, 2), sc), __fmul_rn(s8_of(lo, 3), sc)),
+                                                pack_f16x2(__fmul_rn(s8_of(hi, 0), sc), __fmul_rn(s8_of(hi, 1), sc)),
+                                                pack_f16x2(__fmul_rn(s8_of(hi, 2), sc), __fmul_rn(s8_of(hi, 3), sc)));
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
-tensor_dequant_kernel(const int8_t* __restrict__ q, const float* __restrict__ absmax, T* __restrict__ out, long long size) {
+tensor_dequant_kernel(const int8_t* __restrict__ q, const float* __restrict__ absmax, T* __restrict__ out, long long size,
+                      long long n_vec) {
     const float sc = __fdiv_rn(*absmax, 127.0f);
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < size; i += (long long)gridDim.x * blockDim.x)
-        out[i] = from_float<T>(__fmul_rn((float)q[i], sc));
+    const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, stride = (long long)gridDim.x * blockDim.x;
+#pragma unroll 4
+    for (long long i = tid; i < n_vec; i += stride) {
+        const uint4 w = __ldg(reinterpret_cast<const uint4*>(q) + i);
+        store8_scaled<T>(out + i * 16, w.x, w.y, sc);
+        store8_scaled<T>(out + i * 16 + 8, w.z, w.w, sc);
+    }
+    for (long long i = n_vec * 16 + tid; i < size; i += stride) out[i] = from_float<T>(__fmul_rn((float)q[i], sc));
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -465,6 +596,12 @@ int launch_pack(const void* src, bool from_float, float gamma, uint8_t* Wp, int 
     const int pK = (K + 3) / 4;
     const long long work = (long long)N * pK;
     if (work == 0) return EL_OK;
+    if (from_float && K % 16 == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+        int sms = 148;
+        device_sm_count(&sms);
+        ternarize_pack_vec_kernel<<<grid_for(work, 256 * 4, sms * 16), 256, 0, st>>>(static_cast<const float4*>(src), gamma, Wp, work);
+        return check_launch();
+    }
     if (from_float) pack_kernel<true><<<grid_for(work, 256), 256, 0, st>>>(src, gamma, Wp, N, K, pK, pad_code);
     else pack_kernel<false><<<grid_for(work, 256), 256, 0, st>>>(src, gamma, Wp, N, K, pK, pad_code);
     return check_launch();
@@ -474,6 +611,21 @@ int launch_unpack(const uint8_t* Wp, void* out, int out_dtype, int N, int K, cud
     const int pK = (K + 3) / 4;
     const long long work = (long long)N * pK;
     if (work == 0) return EL_OK;
+    if (K % 16 == 0 && (reinterpret_cast<uintptr_t>(Wp) & 3) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+        int sms = 148;
+        device_sm_count(&sms);
+        const long long n_words = work / 4;
+        const int gv = grid_for(n_words, 256 * 4, sms * 16);
+        const uint32_t* wp = reinterpret_cast<const uint32_t*>(Wp);
+        switch (out_dtype) {
+            case EL_F16: unpack_vec_kernel<__half><<<gv, 256, 0, st>>>(wp, (__half*)out, n_words); break;
+            case EL_BF16: unpack_vec_kernel<__nv_bfloat16><<<gv, 256, 0, st>>>(wp, (__nv_bfloat16*)out, n_words); break;
+            case EL_F32: unpack_vec_kernel<float><<<gv, 256, 0, st>>>(wp, (float*)out, n_words); break;
+            case EL_I32: unpack_vec_kernel<int8_t><<<gv, 256, 0, st>>>(wp, (int8_t*)out, n_words); break;
+            default: return EL_ERR_INVALID_ARG;
+        }
+        return check_launch();
+    }
     const int g = grid_for(work, 256);
     switch (out_dtype) {
         case EL_F16: unpack_kernel<__half><<<g, 256, 0, st>>>(Wp, (__half*)out, N, K, pK); break;
@@ -528,11 +680,13 @@ template <typename T>
 static int launch_quantize_tensor_t(const T* x, int8_t* q, float* absmax, long long size, cudaStream_t st) {
     int sms = 148;
     device_sm_count(&sms);
-    const int g = grid_for(size, 256, sms * 8);
-    tensor_absmax_kernel<T><<<g, 256, 0, st>>>(x, absmax, size);
+    const bool vec = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(q)) & 15) == 0;
+    const long long n_vec = vec ? size / 16 : 0;
+    const int g = grid_for(vec ? (size + 15) / 16 : size, 256, sms * 8);
+    tensor_absmax_kernel<T><<<g, 256, 0, st>>>(x, absmax, size, n_vec);
     int rc = check_launch();
     if (rc != EL_OK) return rc;
-    tensor_quant_kernel<T><<<g, 256, 0, st>>>(x, q, absmax, size);
+    tensor_quant_kernel<T><<<g, 256, 0, st>>>(x, q, absmax, size, n_vec);
     return check_launch();
 }
 
@@ -551,11 +705,13 @@ int launch_dequantize_tensor(const int8_t* q, const float* absmax, void* out, in
     if (size == 0) return EL_OK;
     int sms = 148;
     device_sm_count(&sms);
-    const int g = grid_for(size, 256, sms * 8);
+    const bool vec = ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(q)) & 15) == 0;
+    const long long n_vec = vec ? size / 16 : 0;
+    const int g = grid_for(vec ? (size + 15) / 16 : size, 256, sms * 8);
     switch (dt) {
-        case EL_F16: tensor_dequant_kernel<__half><<<g, 256, 0, st>>>(q, absmax, (__half*)out, size); break;
-        case EL_BF16: tensor_dequant_kernel<__nv_bfloat16><<<g, 256, 0, st>>>(q, absmax, (__nv_bfloat16*)out, size); break;
-        case EL_F32: tensor_dequant_kernel<float><<<g, 256, 0, st>>>(q, absmax, (float*)out, size); break;
+        case EL_F16: tensor_dequant_kernel<__half><<<g, 256, 0, st>>>(q, absmax, (__half*)out, size, n_vec); break;
+        case EL_BF16: tensor_dequant_kernel<__nv_bfloat16><<<g, 256, 0, st>>>(q, absmax, (__nv_bfloat16*)out, size, n_vec); break;
+        case EL_F32: tensor_dequant_kernel<float><<<g, 256, 0, st>>>(q, absmax, (float*)out, size, n_vec); break;
         default: return EL_ERR_INVALID_ARG;
     }
     return check_launch();
@@ -638,23 +794,46 @@ int launch_peer_put(const void* src, void* const* dst_all, int n_dst, size_t dst
     return check_launch();
 }
 
-// int32 sums -> scaled output, four columns per thread
+// int32 sums -> scaled output, four columns per thread; VEC: C % 4 == 0 and 16-byte aligned sums and 8-byte (16-bit types)
+// or 16-byte aligned output rows, so the four columns move as one load and one store
+template <bool VEC>
 __global__ void __launch_bounds__(256)
 scale_rows_kernel(const int* __restrict__ acc, EpiParams epi, int M, int C) {
-    const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const int cg = (C + 3) / 4;
-    if (t >= (long long)M * cg) return;
-    const int m = (int)(t / cg), c0 = (int)(t % cg) * 4;
-    const float sc = epi_row_scale(epi, m);
+    const long long work = (long long)M * cg, stride = (long long)gridDim.x * blockDim.x;
+#pragma unroll 4
+    for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < work; t += stride) {
+        const int m = (int)(t / cg), c0 = (int)(t % cg) * 4;
+        const float sc = epi_row_scale(epi, m);
+        if (VEC) {
+            const int4 a = __ldg(reinterpret_cast<const int4*>(acc + (size_t)m * C + c0));
+            const size_t o = (size_t)m * epi.ldo + c0;
+            const float f0 = __fmul_rn((float)a.x, sc), f1 = __fmul_rn((float)a.y, sc), f2 = __fmul_rn((float)a.z, sc), f3 = __fmul_rn((float)a.w, sc);
+            switch (epi.out_dtype) {
+                case EL_BF16: *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(epi.out) + o) = make_uint2(pack_bf16x2(f0, f1), pack_bf16x2(f2, f3)); break;
+                case EL_F16: *reinterpret_cast<uint2*>(static_cast<__half*>(epi.out) + o) = make_uint2(pack_f16x2(f0, f1), pack_f16x2(f2, f3)); break;
+                case EL_F32: *reinterpret_cast<float4*>(static_cast<float*>(epi.out) + o) = make_float4(f0, f1, f2, f3); break;
+                default: *reinterpret_cast<int4*>(static_cast<int*>(epi.out) + o) = a; break;
+            }
+        } else {
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
-        if (c0 + j < C) epi_store_one(epi, m, c0 + j, acc[(size_t)m * C + c0 + j], sc);
+            for (int j = 0; j < 4; ++j)
+                if (c0 + j < C) epi_store_one(epi, m, c0 + j, acc[(size_t)m * C + c0 + j], sc);
+        }
+    }
 }
 
 int launch_scale_rows(const int* acc, const EpiParams& epi, int M, int C, cudaStream_t st) {
     const long long work = (long long)M * ((C + 3) / 4);
     if (work == 0) return EL_OK;
-    scale_rows_kernel<<<(int)((work + 255) / 256), 256, 0, st>>>(acc, epi, M, C);
+    const size_t out_elem = (epi.out_dtype == EL_BF16 || epi.out_dtype == EL_F16) ? 2 : 4;
+    const bool vec = C % 4 == 0 && epi.ldo % 4 == 0 && (reinterpret_cast<uintptr_t>(acc) & 15) == 0 &&
+                     (reinterpret_cast<uintptr_t>(epi.out) & (4 * out_elem - 1)) == 0;
+    int sms = 148;
+    device_sm_count(&sms);
+    const int g = grid_for(work, 256 * 4, sms * 8);
+    if (vec) scale_rows_kernel<true><<<g, 256, 0, st>>>(acc, epi, M, C);
+    else scale_rows_kernel<false><<<g, 256, 0, st>>>(acc, epi, M, C);
     return check_launch();
 }
 

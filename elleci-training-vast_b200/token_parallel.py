@@ -103,9 +103,17 @@ def _forward_impl(layer: "TokenParallelInt2Linear", x: torch.Tensor):
         bufs = None
         Xq, ax = run("quantize_rows", ops.quantize_rows, x2, ACT_EPS)
     layer._weights_ready()                  # the other ranks' updated rows of W_packed have landed
-    if will_update and layer.world > 1:
-        layer._share_tokens(bufs, own, Ml)
+    # The GEMM is queued before the push that runs beside it: queued the other way round, the push kernel took the SMs
+    # first and the persistent GEMM's CTA pairs waited for them (the forward launch took three times its own time at
+    # eight ranks).  The push only has to start after the quantiser, which the event marks.
+    share = will_update and layer.world > 1
+    ready = None
+    if share and layer._use_fused():
+        ready = torch.cuda.Event()
+        ready.record()
     y = run("gemm_fwd", ops.matmul_rows, Xq, layer.W_packed, ax, layer.gamma_value(), io, layer.gemm_path)
+    if share:
+        layer._share_tokens(bufs, own, Ml, ready)
     return y, ((bufs, ax) if will_update else None), io
 
 
@@ -284,11 +292,16 @@ class TokenParallelInt2Linear(nn.Module):
         if self._use_fused() and self._peer is not None and self._peer.epoch < self._w_ready_epoch:
             self._run("barrier_weights", self._peer.barrier)
 
-    def _share_tokens(self, bufs: dict, own: torch.Tensor, Ml: int):
-        """All-gather of the int8 tokens; on the fused path a push to the peers on a side stream, beside the forward GEMM."""
+    def _share_tokens(self, bufs: dict, own: torch.Tensor, Ml: int, ready: Optional[torch.cuda.Event] = None):
+        """All-gather of the int8 tokens; on the fused path a push to the peers on a side stream, beside the forward GEMM
+        (`ready`: recorded on the main stream once the tokens were quantised; without it the push waits for all of the
+        main stream's queued work)."""
         if self._use_fused():
             main, side = torch.cuda.current_stream(), self._peer.side
-            side.wait_stream(main)
+            if ready is not None:
+                side.wait_event(ready)
+            else:
+                side.wait_stream(main)
             peers = [p for i, p in enumerate(bufs["hx"].buffer_ptrs) if i != self.rank]
             with torch.cuda.stream(side):
                 self._run("push_tokens", self.ops.peer_put, own, peers, self.rank * Ml * self.in_features, self.push_ctas)
@@ -435,13 +448,15 @@ class TokenParallelInt2Linear(nn.Module):
         if peer.epoch < self._w_ready_epoch:
             barrier("barrier_weights")
         side = peer.side
-        side.wait_stream(main)
+        ready = torch.cuda.Event()
+        ready.record(main)                  # tokens quantised, replica complete: the push may start here ...
+        call("gemm_fwd", lib.el_gemm_fwd_ws, P.own.data_ptr(), W, P.y.data_ptr(), P.dt, P.ax.data_ptr(), 1, gam, Ml, N, K,
+             self.gemm_path, P.ws.data_ptr(), P.ws_bytes, P.status, st)
+        side.wait_event(ready)              # ... but is queued after the GEMM, so that the GEMM's CTA pairs get their SMs first
         with torch.cuda.stream(side):
             call("push_tokens", lib.el_peer_put, P.own.data_ptr(), P.peers_x, g - 1, r * Ml * K, Ml * K, self.push_ctas, side.cuda_stream)
         peer.pending = torch.cuda.Event()
         peer.pending.record(side)
-        call("gemm_fwd", lib.el_gemm_fwd_ws, P.own.data_ptr(), W, P.y.data_ptr(), P.dt, P.ax.data_ptr(), 1, gam, Ml, N, K,
-             self.gemm_path, P.ws.data_ptr(), P.ws_bytes, P.status, st)
         # backward: quantise the gradient rows (with the fold that yields this rank's partial maximum)
         P.gloc.zero_()
         call("quantize_rows_dy", lib.el_quantize_rows, dY.data_ptr(), P.dt, N, P.dyq.data_ptr(), P.ady.data_ptr(), Ml, N, GRAD_EPS, 0,
