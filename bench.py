@@ -380,6 +380,12 @@ class StepBench:
     # ---- the measurement -----------------------------------------------------------------------------------------------
     def run(self, steps: int, warmup: int, sample_clocks: bool):
         env, torch, timer = self.env, self.env.torch, self.timer
+        # Token partition: the step is replayed from a recorded CUDA graph (one host launch per layer and step); the
+        # per-kernel pass below queues the same launches one by one, with an event pair around each.
+        self.graphed = self.partition == "tokens" and env.world > 1 and not env.args.no_graph
+        for lay in self.layers:
+            if hasattr(lay, "mod"):
+                lay.mod.graph_steps = self.graphed
         for _ in range(max(warmup, 3)):
             self.step()
         env.barrier()
@@ -390,10 +396,13 @@ class StepBench:
         env.barrier()
         if sampler:
             sampler.start()
+        host_s = 0.0
         for i in range(steps):
             env.flush.zero_()
             ev[i][0].record()
+            h0 = time.perf_counter()
             self.step()
+            host_s += time.perf_counter() - h0
             ev[i][1].record()
         env.barrier()
         clocks = sampler.stop() if sampler else None
@@ -404,6 +413,9 @@ class StepBench:
             # The per-kernel event pairs (roofline, breakdown) come from a second pass of the same K steps: inside the
             # headline region the extra event records per step cost about 5 % of it.
             timer.enabled = True
+            for lay in self.layers:
+                if hasattr(lay, "mod"):
+                    lay.mod.graph_steps = False
             for i in range(steps):
                 env.flush.zero_()
                 self.step()
@@ -412,7 +424,9 @@ class StepBench:
         totals = timer.totals()
         ms = total_ms / steps
         out = {"partition": self.partition, "ms_per_step": ms, "tokens_per_s": self.M / (ms * 1e-3), "steps": steps,
-               "clocks": clocks, "totals": totals}
+               "clocks": clocks, "totals": totals,
+               # host time spent queueing one step's launches: a step whose device time is close to it is bound by the host
+               "host_enqueue_ms_per_step": env.max_over_ranks(host_s * 1e3) / steps, "cuda_graph": self.graphed}
         out["gemm_modes"] = self.gemm_modes(totals, steps)
         out["kernels_ms_per_step"] = {n: t / steps for n, (t, c) in sorted(totals.items())}
         out["own_launches"] = sum(c for n, (t, c) in totals.items() if not n.startswith(LIBRARY_NAMES))
@@ -857,7 +871,8 @@ def run_ours(args, wl):
     par = {"single": "single GPU (order: forward, weight update, dX - the reference's hook order)",
            "tokens": (f"token-parallel x{world}: every rank runs forward and dX on {wl['M'] // world} tokens against a replica of "
                       "W_packed and updates N/g rows from all ranks' int8 tokens and gradient windows; exchanges are this "
-                      "library's peer stores + barrier (order: forward, dX, weight update)"),
+                      "library's peer stores + barrier (order: forward, dX, weight update)"
+                      + ("" if args.no_graph else "; each layer's step replayed from a recorded CUDA graph")),
            "features": (f"N-sharded x{world}, activations replicated: Y gathered and dX partial sums reduce-scattered by TMA "
                         "stores from the GEMM epilogues, dX rows summed and re-gathered by peer stores on a side stream")}
     line = {
@@ -870,12 +885,14 @@ def run_ours(args, wl):
         "clocks": res["clocks"], "e2e": e2e, "gpu_launches": res["own_launches"],
         "roofline": roofline, "gemm_modes": res["gemm_modes"], "hbm_kernels": hbm,
         "kernels_ms_per_step": res["kernels_ms_per_step"],
+        "host_enqueue_ms_per_step": res["host_enqueue_ms_per_step"],
     }
     if res["nvlink"]:
         line["nvlink"] = res["nvlink"]
     if len(results) > 1:
         line["partitions"] = {p: {"ms_per_step": r["ms_per_step"], "tokens_per_s": r["tokens_per_s"], "gemm_modes": r["gemm_modes"],
-                                  "kernels_ms_per_step": r["kernels_ms_per_step"], "nvlink": r["nvlink"], "parallelism": par[p]}
+                                  "kernels_ms_per_step": r["kernels_ms_per_step"], "nvlink": r["nvlink"], "parallelism": par[p],
+                                  "host_enqueue_ms_per_step": r["host_enqueue_ms_per_step"], "cuda_graph": r["cuda_graph"]}
                               for p, r in results.items()}
     if config4 is not None:
         line["config4"] = config4
@@ -1267,6 +1284,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg of the default run")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
     ap.add_argument("--no-config4", action="store_true", help="skip the config-4 sub-record of the default run")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="token partition: queue every launch of the step from the host instead of replaying a recorded CUDA graph")
     ap.add_argument("--brief", action="store_true",
                     help="skip the sub-records measured outside the step (int8 ceiling, configs 1 and 3, reference kernels)")
     ap.add_argument("--inline-kernel-events", action="store_true",

@@ -52,8 +52,9 @@ int launch_swiglu_quantize_rows(const void* gate, const void* up, int dt, long l
 int launch_swiglu_backward(const void* gy, const void* gate, const void* up, int dt, long long ld, const float* weight,
                            const float* rstd, void* d_gate, void* d_up, long long ld_d, float* dweight, void* workspace,
                            size_t workspace_bytes, int M, int H, cudaStream_t st);
-int launch_peer_barrier(unsigned int* const* flags_all, int n_ranks, int rank, unsigned int epoch, int32_t* status,
-                        cudaStream_t st, const void* put_src, void* const* put_dst_all, size_t put_offset);
+int launch_peer_barrier(unsigned int* const* flags_all, int n_ranks, int rank, unsigned int epoch, bool next_epoch,
+                        int32_t* status, cudaStream_t st, const void* put_src, void* const* put_dst_all, size_t put_offset);
+int launch_counter_add(int32_t* counter, int delta, cudaStream_t st);
 int set_peer_barrier_limit_us(long long us);
 int launch_quantize_grad_scatter(const void* dY, int dt, long long ld, const float* xa, const float* g_slots, int n_slots,
                                  float* g_out, void* const* Gq_all, int n_ranks, long long row_offset, int M, int N,
@@ -399,8 +400,24 @@ int el_peer_barrier(uint32_t* const* flags_all, int n_ranks, int rank, uint32_t 
     if (!flags_all) return EL_ERR_NULL_PTR;
     const int rc = require_sm100();
     if (rc != EL_OK) return rc;
-    return launch_peer_barrier(reinterpret_cast<unsigned int* const*>(flags_all), n_ranks, rank, epoch, dev_status,
+    return launch_peer_barrier(reinterpret_cast<unsigned int* const*>(flags_all), n_ranks, rank, epoch, false, dev_status,
                                (cudaStream_t)stream, nullptr, nullptr, 0);
+}
+
+int el_peer_barrier_next(uint32_t* const* flags_all, int n_ranks, int rank, int32_t* dev_status, const void* word,
+                         void* const* dst_all, size_t dst_offset, el_stream_t stream) {
+    if (!flags_all) return EL_ERR_NULL_PTR;
+    if ((word != nullptr) != (dst_all != nullptr)) return EL_ERR_INVALID_ARG;
+    const int rc = require_sm100();
+    if (rc != EL_OK) return rc;
+    return launch_peer_barrier(reinterpret_cast<unsigned int* const*>(flags_all), n_ranks, rank, 0, true, dev_status,
+                               (cudaStream_t)stream, word, dst_all, dst_offset);
+}
+
+int el_counter_add(int32_t* counter, int delta, el_stream_t stream) {
+    const int rc = require_sm100();
+    if (rc != EL_OK) return rc;
+    return launch_counter_add(counter, delta, (cudaStream_t)stream);
 }
 
 int el_peer_barrier_put(uint32_t* const* flags_all, int n_ranks, int rank, uint32_t epoch, int32_t* dev_status, const void* word,
@@ -408,7 +425,7 @@ int el_peer_barrier_put(uint32_t* const* flags_all, int n_ranks, int rank, uint3
     if (!flags_all || !word || !dst_all) return EL_ERR_NULL_PTR;
     const int rc = require_sm100();
     if (rc != EL_OK) return rc;
-    return launch_peer_barrier(reinterpret_cast<unsigned int* const*>(flags_all), n_ranks, rank, epoch, dev_status,
+    return launch_peer_barrier(reinterpret_cast<unsigned int* const*>(flags_all), n_ranks, rank, epoch, false, dev_status,
                                (cudaStream_t)stream, word, dst_all, dst_offset);
 }
 
@@ -456,6 +473,21 @@ int el_dw_hysteresis(const int8_t* Gq, const int8_t* Xq, const float* g_absmax, 
     if (N == 0 || K == 0) return EL_OK;
     if (!Gq || !Xq || !g_absmax || !W_packed || !H_packed) return EL_ERR_NULL_PTR;
     const HystParams hp = make_hyst_params(lr, lr_scale, threshold, decay_rate, (uint32_t)step, 1);
+    return launch_dw_hysteresis_tc(Gq, Xq, g_absmax, W_packed, H_packed, hp, idx_base, M, N, K, dev_status,
+                                   (cudaStream_t)stream);
+}
+
+int el_dw_hysteresis_step_ptr(const int8_t* Gq, const int8_t* Xq, const float* g_absmax, uint8_t* W_packed, uint8_t* H_packed,
+                              float lr, float lr_scale, int threshold, float decay_rate, const int32_t* step, uint32_t idx_base,
+                              int M, int N, int K, int32_t* dev_status, el_stream_t stream) {
+    if (M <= 0 || N < 0 || K < 0) return EL_ERR_INVALID_ARG;
+    if ((long long)N * K > 0x7FFFFFFFLL) return EL_ERR_UNSUPPORTED_SHAPE;
+    if (!step) return EL_ERR_NULL_PTR;
+    if (reinterpret_cast<uintptr_t>(step) & 3) return EL_ERR_ALIGNMENT;
+    if (N == 0 || K == 0) return EL_OK;
+    if (!Gq || !Xq || !g_absmax || !W_packed || !H_packed) return EL_ERR_NULL_PTR;
+    HystParams hp = make_hyst_params(lr, lr_scale, threshold, decay_rate, 0u, 1);
+    hp.step_ptr = step;
     return launch_dw_hysteresis_tc(Gq, Xq, g_absmax, W_packed, H_packed, hp, idx_base, M, N, K, dev_status,
                                    (cudaStream_t)stream);
 }

@@ -111,7 +111,20 @@ struct HystParams {
     int thr;             // clamp(threshold, 1, 7)
     uint32_t s1, s2;     // step*2654435761, step*2246822519 (uint32 wrap-around)
     int ftz;
+    const int32_t* step_ptr;   // when not null, the step is read from device memory by the kernel (hyst_resolve_step)
 };
+
+// The parameters with s1, s2 formed from the step in device memory, for kernels launched with a step pointer (a training
+// step recorded once and replayed cannot carry the step number as a launch argument).
+__device__ __forceinline__ HystParams hyst_resolve_step(const HystParams& p) {
+    HystParams r = p;
+    if (p.step_ptr != nullptr) {
+        const uint32_t step = (uint32_t)*p.step_ptr;
+        r.s1 = step * 2654435761u;
+        r.s2 = step * 2246822519u;
+    }
+    return r;
+}
 
 __device__ __forceinline__ uint32_t mix2(uint32_t h) {
     h = ((h >> 16) ^ h) * 0x45d9f3bu;
@@ -216,6 +229,7 @@ inline HystParams make_hyst_params(float lr, float lr_scale, int threshold, floa
     p.s1 = step * 2654435761u;
     p.s2 = step * 2246822519u;
     p.ftz = ftz;
+    p.step_ptr = nullptr;
     return p;
 }
 

@@ -189,6 +189,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int quarter = warp & 3;                 // the tensor-memory lanes this warp may read
         const int sub = (warp - 2) >> 2;              // 0 for warps 2-5, 1 for 6-9, 2 for 10-13, 3 for 14-17
         const int row_in_tile = quarter * 32 + lane;
+        HystParams hp;                                // with the step taken from device memory when the launch says so
+        if (EPI == EPI_HYST) hp = hyst_resolve_step(p.hp);
         int it = 0;
         for (int t = blockIdx.x; t < num_tiles && !failed; t += gridDim.x, ++it) {
             const int r0 = (t % p.tiles_r) * BM, c0 = (t / p.tiles_r) * BN;
@@ -240,8 +242,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         uint32_t w[2] = {w_pre[i].x, w_pre[i].y};
                         uint32_t h[4] = {h_pre[i].x, h_pre[i].y, h_pre[i].z, h_pre[i].w};
                         const uint32_t idx0 = p.idx_base + (uint32_t)row * (uint32_t)p.C + (uint32_t)col0;
-                        if ((p.idx_base & 31u) == 0) hyst_update_chunk32<true, true>(v, sc, w, h, idx0, p.hp);     // C % 32 == 0
-                        else hyst_update_chunk32<true, false>(v, sc, w, h, idx0, p.hp);
+                        if ((p.idx_base & 31u) == 0) hyst_update_chunk32<true, true>(v, sc, w, h, idx0, hp);     // C % 32 == 0
+                        else hyst_update_chunk32<true, false>(v, sc, w, h, idx0, hp);
                         *reinterpret_cast<uint2*>(p.Wp + (size_t)row * p.pK + (col0 >> 2)) = make_uint2(w[0], w[1]);
                         *reinterpret_cast<uint4*>(p.Hp + (size_t)row * p.pH + (col0 >> 1)) = make_uint4(h[0], h[1], h[2], h[3]);
                     }

@@ -23,10 +23,17 @@ struct PeerFlags {
     unsigned int* put_dst[PEER_MAX];     // optional payload: one 32-bit word delivered to every rank ahead of the flag
 };
 
+// next_epoch: the barrier's number is not given but taken from memory: one more than the number this rank published last,
+// which sits in its own slot of its own array.  A launch recorded once (a CUDA graph) can then be replayed, each replay
+// being the next barrier; the explicit form may be mixed in, since it leaves its number in the same slot.
 __global__ void __launch_bounds__(32)
-peer_barrier_kernel(PeerFlags flags, int n_ranks, int rank, unsigned int epoch, long long limit_cycles, int32_t* status,
-                    const unsigned int* put_src) {
+peer_barrier_kernel(PeerFlags flags, int n_ranks, int rank, unsigned int epoch, int next_epoch, long long limit_cycles,
+                    int32_t* status, const unsigned int* put_src) {
     const int i = threadIdx.x;
+    if (next_epoch) {
+        epoch = *reinterpret_cast<volatile unsigned int*>(flags.p[rank] + rank) + 1u;
+        __syncwarp();                    // every lane has read the old number before lane `rank` overwrites it
+    }
     if (i >= n_ranks) return;
     if (put_src != nullptr) *flags.put_dst[i] = *put_src;      // ordered before the flag by the fence and the release below
     __threadfence_system();
@@ -44,6 +51,9 @@ peer_barrier_kernel(PeerFlags flags, int n_ranks, int rank, unsigned int epoch, 
     }
 }
 
+// A step counter kept in device memory (the hysteresis step of a recorded training step): one thread adds `delta`.
+__global__ void counter_add_kernel(int32_t* counter, int delta) { *counter += delta; }
+
 }  // namespace
 
 int set_peer_barrier_limit_us(long long us) {
@@ -52,8 +62,15 @@ int set_peer_barrier_limit_us(long long us) {
     return EL_OK;
 }
 
-int launch_peer_barrier(unsigned int* const* flags_all, int n_ranks, int rank, unsigned int epoch, int32_t* status,
-                        cudaStream_t st, const void* put_src, void* const* put_dst_all, size_t put_offset) {
+int launch_counter_add(int32_t* counter, int delta, cudaStream_t st) {
+    if (counter == nullptr) return EL_ERR_NULL_PTR;
+    if (reinterpret_cast<uintptr_t>(counter) & 3) return EL_ERR_ALIGNMENT;
+    counter_add_kernel<<<1, 1, 0, st>>>(counter, delta);
+    return check_launch();
+}
+
+int launch_peer_barrier(unsigned int* const* flags_all, int n_ranks, int rank, unsigned int epoch, bool next_epoch,
+                        int32_t* status, cudaStream_t st, const void* put_src, void* const* put_dst_all, size_t put_offset) {
     if (n_ranks < 1 || n_ranks > PEER_MAX || rank < 0 || rank >= n_ranks) return EL_ERR_INVALID_ARG;
     if ((put_src != nullptr) != (put_dst_all != nullptr)) return EL_ERR_INVALID_ARG;
     if (put_src != nullptr && ((reinterpret_cast<uintptr_t>(put_src) | put_offset) & 3)) return EL_ERR_ALIGNMENT;
@@ -76,7 +93,8 @@ int launch_peer_barrier(unsigned int* const* flags_all, int n_ranks, int rank, u
         EL_CUDA_TRY(cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, dev));     // the SM clock's maximum, kHz
         limit = us * (long long)(khz > 0 ? khz : 2000000) / 1000;
     }
-    peer_barrier_kernel<<<1, 32, 0, st>>>(f, n_ranks, rank, epoch, limit, status, static_cast<const unsigned int*>(put_src));
+    peer_barrier_kernel<<<1, 32, 0, st>>>(f, n_ranks, rank, epoch, next_epoch ? 1 : 0, limit, status,
+                                          static_cast<const unsigned int*>(put_src));
     return check_launch();
 }
 

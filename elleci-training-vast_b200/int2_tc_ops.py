@@ -545,6 +545,29 @@ def peer_barrier_put(flag_ptrs, rank: int, epoch: int, device: torch.device, wor
          int(dst_offset_bytes), _stream())
 
 
+def peer_barrier_next(flag_ptrs, rank: int, device: torch.device, word: Optional[torch.Tensor] = None, dst_ptrs=None,
+                      dst_offset_bytes: int = 0) -> None:
+    """peer_barrier / peer_barrier_put whose epoch is one more than the epoch this rank published last (read by the kernel
+    from the rank's own flag array): a launch that can be recorded in a CUDA graph and replayed."""
+    keep, arr = _ptr_array(flag_ptrs)
+    st = device_status(device)
+    if word is None:
+        call("el_peer_barrier_next", arr, len(flag_ptrs), int(rank), st.data_ptr(), None, None, 0, _stream())
+        return
+    _cuda(word, "word")
+    _require(word.numel() * word.element_size() == 4, "word must hold exactly four bytes")
+    keep2, arr2 = _ptr_array(dst_ptrs)
+    call("el_peer_barrier_next", arr, len(flag_ptrs), int(rank), st.data_ptr(), word.data_ptr(), arr2, int(dst_offset_bytes),
+         _stream())
+
+
+def counter_add(counter: torch.Tensor, delta: int = 1) -> None:
+    """counter[0] += delta on the device, in stream order (int32 [1])."""
+    _cuda(counter, "counter")
+    _require(counter.dtype == torch.int32 and counter.numel() == 1, "counter must be int32 [1]")
+    call("el_counter_add", counter.data_ptr(), int(delta), _stream())
+
+
 def backward_input_rows(dYq: torch.Tensor, W_packed: torch.Tensor, row_absmax: torch.Tensor, gamma: float, K: int,
                         out_dtype: torch.dtype = torch.bfloat16, path: int = EL_PATH_AUTO) -> torch.Tensor:
     """dX[m,:] = (dYq[m,:] @ W) * (row_absmax[m]/127) * gamma: the dX GEMM with per-token scales."""
@@ -614,9 +637,10 @@ def dw_hysteresis_supported(N: int, K: int) -> bool:
 
 
 def dw_hysteresis(Gq: torch.Tensor, Xq: torch.Tensor, g_absmax: torch.Tensor, W_packed: torch.Tensor,
-                  H_packed: torch.Tensor, lr: float, lr_scale: float, threshold: int, decay: float, step: int,
+                  H_packed: torch.Tensor, lr: float, lr_scale: float, threshold: int, decay: float, step,
                   idx_base: int = 0) -> None:
-    """Fused weight-gradient GEMM + hysteresis update, in place on W_packed / H_packed."""
+    """Fused weight-gradient GEMM + hysteresis update, in place on W_packed / H_packed.  `step`: the step number, or an
+    int32 [1] CUDA tensor that holds it (for launches recorded in a CUDA graph; see counter_add)."""
     _cuda(Gq, "Gq"); _cuda(Xq, "Xq")
     _require(Gq.dtype == torch.int8 and Xq.dtype == torch.int8, "Gq and Xq must be int8")
     N, K = Gq.shape[-1], Xq.shape[-1]
@@ -626,9 +650,16 @@ def dw_hysteresis(Gq: torch.Tensor, Xq: torch.Tensor, g_absmax: torch.Tensor, W_
     _require(tuple(W_packed.shape) == (N, (K + 3) // 4) and tuple(H_packed.shape) == (N, (K + 1) // 2),
              "W_packed / H_packed shape mismatch")
     _require(W_packed.is_contiguous() and H_packed.is_contiguous(), "W_packed/H_packed must be contiguous")
+    st = device_status(Gq.device)
+    if isinstance(step, torch.Tensor):          # the step number is read from device memory when the kernel runs
+        _cuda(step, "step")
+        _require(step.dtype == torch.int32 and step.numel() == 1, "a step tensor must be int32 [1]")
+        call("el_dw_hysteresis_step_ptr", G2.data_ptr(), X2.data_ptr(), g_absmax.data_ptr(), W_packed.data_ptr(),
+             H_packed.data_ptr(), float(lr), float(lr_scale), int(threshold), float(decay), step.data_ptr(),
+             int(idx_base) & 0xFFFFFFFF, M, N, K, st.data_ptr(), _stream())
+        return
     step32 = int(step) & 0xFFFFFFFF
     step_i = step32 - (1 << 32) if step32 >= (1 << 31) else step32
-    st = device_status(Gq.device)
     call("el_dw_hysteresis", G2.data_ptr(), X2.data_ptr(), g_absmax.data_ptr(), W_packed.data_ptr(), H_packed.data_ptr(),
          float(lr), float(lr_scale), int(threshold), float(decay), step_i, int(idx_base) & 0xFFFFFFFF, M, N, K,
          st.data_ptr(), _stream())

@@ -169,7 +169,7 @@ class TokenParallelInt2Linear(nn.Module):
 
     def __init__(self, in_features: int, out_features: int, group: Optional[dist.ProcessGroup] = None, threshold: int = 7,
                  lr_scale: float = 5.0, decay_rate: float = 0.001, hysteresis_order: str = "after_dx", ops=None,
-                 fused: bool = False, push_ctas: int = 296):
+                 fused: bool = False, push_ctas: int = 148, graph_steps: bool = False):
         super().__init__()
         if ops is None:
             from . import int2_tc_ops as ops_mod
@@ -188,8 +188,12 @@ class TokenParallelInt2Linear(nn.Module):
         self.fused = fused
         # CTAs of the pushes that run on a side stream beside the GEMMs.  They hold no shared memory, so they sit on the SMs
         # next to the GEMM's CTAs; NVLink needs a few megabytes of stores in flight to run at rate (32 CTAs moved 140-310
-        # GB/s, a fifth of the link), hence two CTAs per SM.
+        # GB/s, a fifth of the link).  One CTA per SM: the register-lean GEMM leaves 16 K registers per SM and a push CTA
+        # takes 12 K, so with two per SM a GEMM CTA that arrives second finds no room and waits for the whole push.
         self.push_ctas = push_ctas
+        # train_step on the fused path replays a recorded CUDA graph per (input buffers, settings) instead of queueing its
+        # launches one by one; for callers that pass the same x and dY buffers every step (see _replayed_step).
+        self.graph_steps = graph_steps
         # From four ranks on, the pushes are a large enough share of the step that they must overlap with the GEMMs: the
         # forward and dX GEMMs then run in their register-lean form (EL_FLAG_LEAN), which leaves room on the SMs for the
         # push kernel of the side stream.  With two ranks the faster form wins (measured).
@@ -394,6 +398,10 @@ class TokenParallelInt2Linear(nn.Module):
         P.ady = torch.empty(Ml, dtype=torch.float32, device=dev)
         P.dyq = torch.empty(Ml, N, dtype=torch.int8, device=dev)
         P.gloc = torch.zeros(1, dtype=torch.float32, device=dev)
+        P.step_dev = torch.zeros(1, dtype=torch.int32, device=dev)      # the hysteresis step, for recorded steps
+        P.step_dev_value = 0
+        P.graphs = {}
+        P.warm = False
         P.own = bufs["xq_all"][r * Ml:(r + 1) * Ml]
         P.status = ops.device_status(dev).data_ptr()
         # scratch for the split reduction of GEMMs with few output tiles (a rank's share of a small batch): see el_gemm_fwd_ws
@@ -421,6 +429,47 @@ class TokenParallelInt2Linear(nn.Module):
         P = self._plans.get(key)
         if P is None:
             P = self._plans[key] = self._make_plan(Ml, x.dtype)
+        if self.graph_steps and P.warm:
+            return self._replayed_step(P, x, dY, need_dx)
+        P.warm = True        # a plan's first step is always queued launch by launch: first-call set-up cannot be recorded
+        return self._issue_step(P, x, dY, need_dx, recorded=False)
+
+    def _replayed_step(self, P, x: torch.Tensor, dY: torch.Tensor, need_dx: bool):
+        """The planned step as one CUDA graph per (inputs, settings): recorded on first use, replayed afterwards, so that
+        the host queues one launch per step instead of about twenty (at eight ranks and 512 tokens per rank the host
+        needed as long to queue a step as the GPU to run it).  What changes from step to step lives in device memory: the
+        barriers take their number from the flag array (el_peer_barrier_next), the weight update reads its step from a
+        counter that a one-thread kernel advances.  The host mirrors both so that unrecorded calls can be mixed in."""
+        peer = self._peer
+        need_wbar = peer.epoch < self._w_ready_epoch
+        key = (x.data_ptr(), dY.data_ptr(), need_dx, need_wbar, self.gamma_value(), float(self._lr), float(self.lr_scale),
+               int(self.threshold), float(self.decay_rate), self.hysteresis_order)
+        G = P.graphs.get(key)
+        if G is None:
+            from types import SimpleNamespace
+            peer.join_side()                # nothing recorded waits on work queued before the recording
+            saved = (peer.epoch, self._step_py, self._w_ready_epoch, self._step_dirty)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                y, dx = self._issue_step(P, x, dY, need_dx, recorded=True)
+                peer.join_side()            # the side stream's pushes end inside the recording
+            G = SimpleNamespace(graph=graph, y=y, dx=dx, barriers=peer.epoch - saved[0], w_ready=self._w_ready_epoch - saved[0])
+            peer.epoch, self._step_py, self._w_ready_epoch, self._step_dirty = saved      # recording ran nothing
+            P.graphs[key] = G
+        if P.step_dev_value != self._step_py:
+            P.step_dev.fill_(self._step_py)
+            P.step_dev_value = self._step_py
+        peer.join_side()
+        G.graph.replay()
+        self._step_py += 1
+        P.step_dev_value += 1
+        self._step_dirty = True
+        self._w_ready_epoch = peer.epoch + G.w_ready
+        peer.epoch += G.barriers
+        return G.y, G.dx
+
+    def _issue_step(self, P, x: torch.Tensor, dY: torch.Tensor, need_dx: bool, recorded: bool):
+        Ml = x.shape[0]
         lib, run, peer, bufs = P.lib, self._run, self._peer, P.bufs
         g, r, K, N, Nl = self.world, self.rank, self.in_features, self.out_features, self.local_out_features
         gam = self.gamma_value()
@@ -436,7 +485,12 @@ class TokenParallelInt2Linear(nn.Module):
         def barrier(name, with_gmax=False):
             peer.join_side()
             peer.epoch += 1
-            if with_gmax:       # the barrier carries this rank's partial maximum to slot r of every rank
+            if recorded:        # the barrier's number comes from the flag array: nothing in the launch changes per step
+                if with_gmax:
+                    call(name, lib.el_peer_barrier_next, P.flags, g, r, P.status, P.gloc.data_ptr(), P.all_slots, 4 * r, st)
+                else:
+                    call(name, lib.el_peer_barrier_next, P.flags, g, r, P.status, None, None, 0, st)
+            elif with_gmax:     # the barrier carries this rank's partial maximum to slot r of every rank
                 call(name, lib.el_peer_barrier_put, P.flags, g, r, peer.epoch & 0xFFFFFFFF, P.status, P.gloc.data_ptr(),
                      P.all_slots, 4 * r, st)
             else:
@@ -475,10 +529,17 @@ class TokenParallelInt2Linear(nn.Module):
                  bufs["gmax"].data_ptr(), P.all_gq, g, r * Ml, Ml, N, st)
             barrier("barrier_grad")
             step32 = self._step_py & 0xFFFFFFFF
-            call("gemm_dw_hysteresis", lib.el_dw_hysteresis, bufs["gq_recv"].data_ptr(), bufs["xq_all"].data_ptr(),
-                 bufs["gmax"].data_ptr(), own_w, self.H_packed.data_ptr(), float(self._lr), float(self.lr_scale), int(self.threshold),
-                 float(self.decay_rate), step32 - (1 << 32) if step32 >= (1 << 31) else step32,
-                 (self.row_start * K) & 0xFFFFFFFF, g * Ml, Nl, K, P.status, st)
+            if recorded:
+                call("step_counter", lib.el_counter_add, P.step_dev.data_ptr(), 1, st)
+                call("gemm_dw_hysteresis", lib.el_dw_hysteresis_step_ptr, bufs["gq_recv"].data_ptr(), bufs["xq_all"].data_ptr(),
+                     bufs["gmax"].data_ptr(), own_w, self.H_packed.data_ptr(), float(self._lr), float(self.lr_scale),
+                     int(self.threshold), float(self.decay_rate), P.step_dev.data_ptr(), (self.row_start * K) & 0xFFFFFFFF,
+                     g * Ml, Nl, K, P.status, st)
+            else:
+                call("gemm_dw_hysteresis", lib.el_dw_hysteresis, bufs["gq_recv"].data_ptr(), bufs["xq_all"].data_ptr(),
+                     bufs["gmax"].data_ptr(), own_w, self.H_packed.data_ptr(), float(self._lr), float(self.lr_scale),
+                     int(self.threshold), float(self.decay_rate), step32 - (1 << 32) if step32 >= (1 << 31) else step32,
+                     (self.row_start * K) & 0xFFFFFFFF, g * Ml, Nl, K, P.status, st)
             side.wait_stream(main)          # the updated rows go out on the side stream, under the main stream's next work
             with torch.cuda.stream(side):
                 call("push_weights", lib.el_peer_put, own_w, P.peers_w, g - 1, self.row_start * self.W_packed.shape[1],

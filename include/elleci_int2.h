@@ -271,6 +271,17 @@ EL_API int el_peer_barrier(uint32_t* const* flags_all, int n_ranks, int rank, ui
  * way, in the barrier it needs anyway, instead of with a launch of its own.  No counterpart in the reference. */
 EL_API int el_peer_barrier_put(uint32_t* const* flags_all, int n_ranks, int rank, uint32_t epoch, int32_t* dev_status,
                                const void* word, void* const* dst_all, size_t dst_offset, el_stream_t stream);
+/* el_peer_barrier (word == dst_all == NULL) or el_peer_barrier_put whose epoch is not passed but taken from memory: one
+ * more than the epoch this rank published last, which every form of the barrier leaves in slot `rank` of the rank's own
+ * flag array.  The launch therefore has no argument that changes from barrier to barrier, so a sequence of launches
+ * recorded once (CUDA stream capture) can be replayed, each replay being the next barriers; explicit-epoch calls may be
+ * mixed in as long as the host keeps counting.  Every rank must use the same sequence of barriers, as before.  No
+ * counterpart in the reference. */
+EL_API int el_peer_barrier_next(uint32_t* const* flags_all, int n_ranks, int rank, int32_t* dev_status, const void* word,
+                                void* const* dst_all, size_t dst_offset, el_stream_t stream);
+/* *counter += delta on the device, in stream order (one thread).  Keeps a step counter that kernels read from memory
+ * (el_dw_hysteresis_step_ptr) in step with the recorded launches that use it.  No counterpart in the reference. */
+EL_API int el_counter_add(int32_t* counter, int delta, el_stream_t stream);
 /* Bound of el_peer_barrier's wait, process-wide, for barriers queued from now on: microseconds > 0 sets it, 0 restores
  * the default of a few seconds.  A health check (or a test) that wants a missing rank reported within a millisecond
  * instead of seconds sets it; the barrier then returns with code 40 + rank in *dev_status and the device stays usable. */
@@ -321,6 +332,14 @@ EL_API int el_hysteresis_from_dw(const float* dW, uint8_t* W_packed, uint8_t* H_
 EL_API int el_dw_hysteresis(const int8_t* Gq, const int8_t* Xq, const float* g_absmax, uint8_t* W_packed,
                      uint8_t* H_packed, float lr, float lr_scale, int threshold, float decay_rate, int step,
                      uint32_t idx_base, int M, int N, int K, int32_t* dev_status, el_stream_t stream);
+/* el_dw_hysteresis with the step number read from device memory (`step`, one int32, read by the kernel when it runs)
+ * instead of passed by value: the launch then has no argument that changes from step to step and can be recorded once
+ * and replayed; el_counter_add advances the number between replays.  Same update, bit for bit, as el_dw_hysteresis with
+ * the value found there.  No counterpart in the reference. */
+EL_API int el_dw_hysteresis_step_ptr(const int8_t* Gq, const int8_t* Xq, const float* g_absmax, uint8_t* W_packed,
+                                     uint8_t* H_packed, float lr, float lr_scale, int threshold, float decay_rate,
+                                     const int32_t* step, uint32_t idx_base, int M, int N, int K, int32_t* dev_status,
+                                     el_stream_t stream);
 
 /* ---- small-M ("decode") layer -------------------------------------------------------------------------------- */
 

@@ -795,3 +795,50 @@ def test_register_lean_pair_kernels_bit_exact(ops, pkg, M, N, K):
     assert np.array_equal(t2n(ops.backward_input_rows(ddY, dWp, day, gamma, K, torch.bfloat16, path)),
                           O.to_bf16(O.scale_rows(acc_x, ay, gamma)))
     ops.check_device_status(torch.device(DEV))
+
+
+def test_barrier_and_weight_update_replayed_from_a_cuda_graph(ops, pkg):
+    """What a recorded training step needs: a barrier whose number comes from the flag array and a weight update whose
+    step number comes from a device counter.  One rank on one device: three replays of a graph holding
+    [barrier_next + word, counter_add, dW + hysteresis with the step pointer] must leave the flag at the right epoch,
+    mix with an explicitly numbered barrier, and update the weights exactly as three ordinary calls with steps 6, 7, 8."""
+    dev = torch.device(DEV)
+    M, N, K = 256, 128, 128
+    g = torch.Generator().manual_seed(77)
+    Gq = torch.randint(-127, 128, (M, N), generator=g, dtype=torch.int8).to(DEV)
+    Xq = torch.randint(-127, 128, (M, K), generator=g, dtype=torch.int8).to(DEV)
+    gmax = torch.tensor([3.0e-3], dtype=torch.float32, device=DEV)
+    Wp, _ = random_packed(N, K, seed=9)
+    W_ref, W_rec = _cuda(Wp).clone(), _cuda(Wp).clone()
+    H_ref = torch.zeros(N, K // 2, dtype=torch.uint8, device=DEV)
+    H_rec = H_ref.clone()
+    for step in (6, 7, 8):
+        ops.dw_hysteresis(Gq, Xq, gmax, W_ref, H_ref, 0.8, 5.0, 2, 0.01, step, 64)
+    flags = torch.zeros(8, dtype=torch.int32, device=DEV)
+    slots = torch.zeros(8, dtype=torch.float32, device=DEV)
+    word = torch.tensor([1.5], dtype=torch.float32, device=DEV)
+    counter = torch.tensor([5], dtype=torch.int32, device=DEV)
+    ops.peer_barrier([flags.data_ptr()], 0, 1, dev)                  # explicit epochs 1 and 2 first
+    ops.peer_barrier([flags.data_ptr()], 0, 2, dev)
+    ops.peer_barrier_next([flags.data_ptr()], 0, dev)                # 3, queued directly
+    torch.cuda.synchronize()
+    assert flags[0].item() == 3
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        ops.peer_barrier_next([flags.data_ptr()], 0, dev, word, [slots.data_ptr()], 4 * 2)
+        ops.counter_add(counter, 1)
+        ops.dw_hysteresis(Gq, Xq, gmax, W_rec, H_rec, 0.8, 5.0, 2, 0.01, counter, 64)
+    torch.cuda.synchronize()
+    assert flags[0].item() == 3 and counter.item() == 5 and torch.equal(W_rec, _cuda(Wp))     # recording ran nothing
+    for i in range(3):
+        word.fill_(2.0 + i)
+        graph.replay()
+    torch.cuda.synchronize()
+    assert flags[0].item() == 6 and counter.item() == 8 and slots[2].item() == 4.0
+    assert torch.equal(W_rec, W_ref) and torch.equal(H_rec, H_ref)
+    assert not torch.equal(W_rec, _cuda(Wp))
+    ops.peer_barrier([flags.data_ptr()], 0, 7, dev)                  # the host kept counting: explicit 7, then next = 8
+    ops.peer_barrier_next([flags.data_ptr()], 0, dev)
+    torch.cuda.synchronize()
+    assert flags[0].item() == 8
+    ops.check_device_status(dev)

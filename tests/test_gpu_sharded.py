@@ -15,7 +15,7 @@ from helpers import make_layer_inputs
 pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 M, K, N = 512, 1024, 2048
-STEPS = 3
+STEPS = 4
 
 
 def _free_port():
@@ -104,7 +104,8 @@ def _tp_worker(rank, world, port, order, out_dir, fused):
         d = make_layer_inputs(M, K, N, seed=3, dtype=torch.bfloat16, dy_std=1e-2, counters=1)
         layers = []
         for li in range(2):                              # two layers share the barrier group (and each other's barriers)
-            layer = pkg.token_parallel.TokenParallelInt2Linear(K, N, threshold=2, hysteresis_order=order, fused=fused).to(dev)
+            layer = pkg.token_parallel.TokenParallelInt2Linear(K, N, threshold=2, hysteresis_order=order, fused=bool(fused),
+                                                               graph_steps=(fused == "graph")).to(dev)
             layer.load_full(torch.from_numpy(d["Wp"]), torch.from_numpy(d["Hp"]), d["gamma"])
             layer.set_lr(0.5 + li)
             layers.append(layer.train())
@@ -137,12 +138,15 @@ def _tp_worker(rank, world, port, order, out_dir, fused):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("fused", [False, True])
+@pytest.mark.parametrize("fused", [False, True, "graph"])
 @pytest.mark.parametrize("order", ["reference", "after_dx"])
 def test_token_parallel_steps_on_gpus_equal_single_gpu(tmp_path, order, fused):
     """Every rank runs forward and dX on its own tokens against its replica of the weights and updates its own rows from
-    all ranks' tokens; after three steps each rank's rows of Y and dX, every replica of W_packed and the owners' counters
-    must equal the single-GPU layer's.  fused: the exchanges are the library's own peer stores and barrier."""
+    all ranks' tokens; after the steps each rank's rows of Y and dX, every replica of W_packed and the owners' counters
+    must equal the single-GPU layer's.  fused: the exchanges are the library's own peer stores and barrier.  "graph": the
+    directly issued layer also replays its step from a recorded CUDA graph from the second step on (barrier numbers and
+    the hysteresis step then come from device memory), next to a layer that queues its launches one by one and shares
+    the barrier group with it."""
     world = min(torch.cuda.device_count(), 8)
     if world < 2:
         pytest.skip("needs at least two GPUs")
