@@ -292,7 +292,8 @@ class StepBench:
                 lay.dY = dY[rank * Ml:(rank + 1) * Ml].contiguous()
                 del x, dY
                 mod = pkg.token_parallel.TokenParallelInt2Linear(K, N, threshold=thr, lr_scale=LR_SCALE, decay_rate=DECAY,
-                                                                 hysteresis_order="after_dx", fused=True).to(dev)
+                                                                 hysteresis_order="after_dx", fused=True,
+                                                                 push_ctas=env.args.push_ctas).to(dev)
                 mod.load_full(Wfull, Hfull, lay.gamma)
                 mod.set_lr(LR)
                 mod.train()
@@ -1284,6 +1285,9 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg of the default run")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
     ap.add_argument("--no-config4", action="store_true", help="skip the config-4 sub-record of the default run")
+    ap.add_argument("--push-ctas", type=int, default=0,
+                    help="token partition: CTAs of the peer-store kernel that pushes tokens and weight rows "
+                         "(negative: copy engines; 0: the layer's choice by size)")
     ap.add_argument("--no-graph", action="store_true",
                     help="token partition: queue every launch of the step from the host instead of replaying a recorded CUDA graph")
     ap.add_argument("--brief", action="store_true",

@@ -68,6 +68,7 @@ SIGNATURES = {
     "el_dw_hysteresis_step_ptr": [_vp, _vp, _vp, _vp, _vp, _f, _f, _i, _f, _vp, _u32, _i, _i, _i, _vp, _vp],
     "el_peer_barrier_next": [_vp, _i, _i, _vp, _vp, _vp, C.c_size_t, _vp],
     "el_counter_add": [_vp, _i, _vp],
+    "el_peer_put_dma": [_vp, _vp, _i, C.c_size_t, C.c_size_t, _vp],
 }
 
 

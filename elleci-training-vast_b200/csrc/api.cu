@@ -444,6 +444,19 @@ int el_peer_put(const void* src, void* const* dst, int n_dst, size_t dst_offset,
     return launch_peer_put(src, dst, n_dst, dst_offset, bytes, max_ctas, (cudaStream_t)stream);
 }
 
+int el_peer_put_dma(const void* src, void* const* dst, int n_dst, size_t dst_offset, size_t bytes, el_stream_t stream) {
+    if (n_dst < 0 || n_dst > 8) return EL_ERR_INVALID_ARG;
+    if (bytes == 0 || n_dst == 0) return EL_OK;
+    if (!src || !dst) return EL_ERR_NULL_PTR;
+    for (int d = 0; d < n_dst; ++d)
+        if (dst[d] == nullptr) return EL_ERR_NULL_PTR;
+    // one copy per destination, in the caller's order, each through a copy engine: no SM is involved
+    for (int d = 0; d < n_dst; ++d)
+        EL_CUDA_TRY(cudaMemcpyAsync(static_cast<char*>(dst[d]) + dst_offset, src, bytes, cudaMemcpyDeviceToDevice,
+                                    (cudaStream_t)stream));
+    return EL_OK;
+}
+
 int el_set_peer_barrier_limit_us(long long microseconds) { return set_peer_barrier_limit_us(microseconds); }
 
 int el_gemm_dw(const int8_t* Gq, const int8_t* Xq, void* dW, int out_dtype, const float* g_absmax, int M, int N, int K,

@@ -603,12 +603,18 @@ def quantize_grad_scatter(dY: torch.Tensor, x_absmax: torch.Tensor, g_slots: tor
 
 def peer_put(src: torch.Tensor, dst_ptrs, dst_offset_bytes: int, max_ctas: int = 0) -> None:
     """Copies the contiguous tensor `src` to byte offset `dst_offset_bytes` of every buffer in `dst_ptrs` (device
-    addresses of peer mappings): one rank's push of an all-gather, as plain stores over NVLink from one kernel."""
+    addresses of peer mappings): one rank's push of an all-gather, as plain stores over NVLink from one kernel
+    (`max_ctas` >= 0: its grid limit, 0 = as many as saturate the links) or, with `max_ctas` < 0, as one copy-engine
+    copy per destination in the order given."""
     _cuda(src, "src")
     _require(src.is_contiguous(), "src must be contiguous")
     if len(dst_ptrs) == 0 or src.numel() == 0:
         return
     keep, arr = _ptr_array(dst_ptrs)
+    if max_ctas < 0:
+        call("el_peer_put_dma", src.data_ptr(), arr, len(dst_ptrs), int(dst_offset_bytes), src.numel() * src.element_size(),
+             _stream())
+        return
     call("el_peer_put", src.data_ptr(), arr, len(dst_ptrs), int(dst_offset_bytes), src.numel() * src.element_size(),
          int(max_ctas), _stream())
 

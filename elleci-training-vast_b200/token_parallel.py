@@ -37,6 +37,7 @@ from .int2_tc_ops import ACT_EPS, GRAD_EPS
 from .sharded import shard_rows
 
 _FLOAT_IO = (torch.float16, torch.bfloat16, torch.float32)
+PUSH_DMA_MIN_BYTES = 8 << 20      # pushes of at least this many bytes per destination go through the copy engines
 
 
 class PeerGroup:
@@ -111,7 +112,7 @@ def _forward_impl(layer: "TokenParallelInt2Linear", x: torch.Tensor):
     if share and layer._use_fused():
         ready = torch.cuda.Event()
         ready.record()
-    y = run("gemm_fwd", ops.matmul_rows, Xq, layer.W_packed, ax, layer.gamma_value(), io, layer.gemm_path)
+    y = run("gemm_fwd", ops.matmul_rows, Xq, layer.W_packed, ax, layer.gamma_value(), io, layer._gemm_flags(Ml))
     if share:
         layer._share_tokens(bufs, own, Ml, ready)
     return y, ((bufs, ax) if will_update else None), io
@@ -137,7 +138,7 @@ def _backward_impl(layer: "TokenParallelInt2Linear", saved, dY: torch.Tensor, io
     def input_grad():
         if not need_dx:
             return None
-        return run("gemm_dx", ops.backward_input_rows, dYq, layer.W_packed, ady, layer.gamma_value(), K, io, layer.gemm_path)
+        return run("gemm_dx", ops.backward_input_rows, dYq, layer.W_packed, ady, layer.gamma_value(), K, io, layer._gemm_flags(dYq.shape[0]))
 
     if do_update and layer.hysteresis_order == "reference":
         layer._update(bufs, dY2, ax, gloc)             # as the reference's hook: before dX ...
@@ -169,7 +170,7 @@ class TokenParallelInt2Linear(nn.Module):
 
     def __init__(self, in_features: int, out_features: int, group: Optional[dist.ProcessGroup] = None, threshold: int = 7,
                  lr_scale: float = 5.0, decay_rate: float = 0.001, hysteresis_order: str = "after_dx", ops=None,
-                 fused: bool = False, push_ctas: int = 148, graph_steps: bool = False):
+                 fused: bool = False, push_ctas: int = 0, graph_steps: bool = False):
         super().__init__()
         if ops is None:
             from . import int2_tc_ops as ops_mod
@@ -186,18 +187,24 @@ class TokenParallelInt2Linear(nn.Module):
         self.hysteresis_order = hysteresis_order
         self.hysteresis_enabled = True
         self.fused = fused
-        # CTAs of the pushes that run on a side stream beside the GEMMs.  They hold no shared memory, so they sit on the SMs
-        # next to the GEMM's CTAs; NVLink needs a few megabytes of stores in flight to run at rate (32 CTAs moved 140-310
-        # GB/s, a fifth of the link).  One CTA per SM: the register-lean GEMM leaves 16 K registers per SM and a push CTA
-        # takes 12 K, so with two per SM a GEMM CTA that arrives second finds no room and waits for the whole push.
+        # How the pushes that run on a side stream beside the GEMMs move their bytes.  push_ctas > 0: a peer-store kernel of
+        # that many CTAs.  It holds no shared memory, so it sits on the SMs next to the GEMM's CTAs; NVLink needs a few
+        # megabytes of stores in flight to run at rate (32 CTAs moved 140-310 GB/s, a fifth of the link), and one CTA per
+        # SM is the most that fits: the register-lean GEMM leaves 16 K registers per SM, a push CTA takes 12 K, and with
+        # two per SM a GEMM CTA that arrives second finds no room and waits for the whole push.  push_ctas < 0: the copy
+        # engines, one copy per destination (el_peer_put_dma): no SM takes part and the GEMM beside it keeps its faster
+        # form, but the copies run one after the other at about 10 us each plus their bytes.  0 (default): by size -
+        # copy engines from PUSH_DMA_MIN_BYTES per destination on, the kernel with one CTA per SM below.  Measured at
+        # eight ranks: 33 MB per destination (65536 tokens): step 1.92 -> 1.64 ms with the copy engines; 2-6 MB per
+        # destination (4096 tokens): 0.436 ms with the kernel, 0.463 ms with the copy engines.
         self.push_ctas = push_ctas
+        # From four ranks on, the pushes are a large enough share of the step that they must overlap with the GEMMs: next
+        # to a push kernel the forward and dX GEMMs run in their register-lean form (EL_FLAG_LEAN), which leaves room on
+        # the SMs for it.  With two ranks the faster form wins (measured).
+        self._lean = getattr(ops, "EL_FLAG_LEAN", 0) if (fused and self.world >= 4) else 0
         # train_step on the fused path replays a recorded CUDA graph per (input buffers, settings) instead of queueing its
         # launches one by one; for callers that pass the same x and dY buffers every step (see _replayed_step).
         self.graph_steps = graph_steps
-        # From four ranks on, the pushes are a large enough share of the step that they must overlap with the GEMMs: the
-        # forward and dX GEMMs then run in their register-lean form (EL_FLAG_LEAN), which leaves room on the SMs for the
-        # push kernel of the side stream.  With two ranks the faster form wins (measured).
-        self.gemm_path = getattr(ops, "EL_FLAG_LEAN", 0) if (fused and self.world >= 4) else 0
         self._lr = 0.001
         self._step_py = 0
         self._gamma_cached: Optional[float] = None
@@ -253,6 +260,21 @@ class TokenParallelInt2Linear(nn.Module):
         return self.W_packed[self.row_start:self.row_stop]
 
     # ---- exchange plumbing ---------------------------------------------------------------------------------------------
+    def _push_mode(self, bytes_per_destination: int) -> int:
+        """The max_ctas argument of ops.peer_put for a push of that size: negative = copy engines."""
+        if self.push_ctas != 0:
+            return self.push_ctas
+        return -1 if bytes_per_destination >= PUSH_DMA_MIN_BYTES else 148
+
+    def _gemm_flags(self, Ml: int) -> int:
+        """Path flags of the forward and dX GEMMs for Ml local tokens: register-lean only beside a push kernel."""
+        return self._lean if self._push_mode(Ml * self.in_features) > 0 else 0
+
+    def _successors(self, ptrs):
+        """The peers' entries of `ptrs`, starting with this rank's successor: when every rank pushes in this order, each
+        GPU receives from one sender at a time (copy-engine pushes run one destination after the other)."""
+        return [ptrs[(self.rank + j) % self.world] for j in range(1, self.world)]
+
     def _use_fused(self) -> bool:
         return self.fused and self.world > 1 and self.W_packed.is_cuda
 
@@ -306,9 +328,10 @@ class TokenParallelInt2Linear(nn.Module):
                 side.wait_event(ready)
             else:
                 side.wait_stream(main)
-            peers = [p for i, p in enumerate(bufs["hx"].buffer_ptrs) if i != self.rank]
+            peers = self._successors(bufs["hx"].buffer_ptrs)
             with torch.cuda.stream(side):
-                self._run("push_tokens", self.ops.peer_put, own, peers, self.rank * Ml * self.in_features, self.push_ctas)
+                self._run("push_tokens", self.ops.peer_put, own, peers, self.rank * Ml * self.in_features,
+                          self._push_mode(Ml * self.in_features))
                 self._peer.pending = torch.cuda.Event()
                 self._peer.pending.record(side)
         else:
@@ -353,11 +376,12 @@ class TokenParallelInt2Linear(nn.Module):
             return
         if self._use_fused():
             # the updated rows go out on the side stream, under whatever the main stream does until the next barrier
-            peers = [p for i, p in enumerate(self._w_handle.buffer_ptrs) if i != r]
+            peers = self._successors(self._w_handle.buffer_ptrs)
             main, side = torch.cuda.current_stream(), self._peer.side
             side.wait_stream(main)
             with torch.cuda.stream(side):
-                run("push_weights", ops.peer_put, own, peers, self.row_start * self.W_packed.shape[1], self.push_ctas)
+                run("push_weights", ops.peer_put, own, peers, self.row_start * self.W_packed.shape[1],
+                    self._push_mode(own.numel()))
                 self._peer.pending = torch.cuda.Event()
                 self._peer.pending.record(side)
             self._w_ready_epoch = self._peer.epoch + 1          # complete after the next barrier, whoever queues it
@@ -402,6 +426,8 @@ class TokenParallelInt2Linear(nn.Module):
         P.step_dev_value = 0
         P.graphs = {}
         P.warm = False
+        P.push_x, P.push_w = self._push_mode(Ml * K), self._push_mode(Nl * self.W_packed.shape[1])
+        P.gemm_path = self._gemm_flags(Ml)
         P.own = bufs["xq_all"][r * Ml:(r + 1) * Ml]
         P.status = ops.device_status(dev).data_ptr()
         # scratch for the split reduction of GEMMs with few output tiles (a rank's share of a small batch): see el_gemm_fwd_ws
@@ -414,9 +440,9 @@ class TokenParallelInt2Linear(nn.Module):
             return a, ctypes.cast(a, ctypes.c_void_p)
 
         P.keep = []
-        for name, ptrs in (("peers_x", [p for i, p in enumerate(bufs["hx"].buffer_ptrs) if i != r]),
+        for name, ptrs in (("peers_x", self._successors(bufs["hx"].buffer_ptrs)),
                            ("all_slots", list(bufs["hs"].buffer_ptrs)), ("all_gq", list(bufs["hg"].buffer_ptrs)),
-                           ("peers_w", [p for i, p in enumerate(self._w_handle.buffer_ptrs) if i != r]),
+                           ("peers_w", self._successors(self._w_handle.buffer_ptrs)),
                            ("flags", list(self._peer.handle.buffer_ptrs))):
             a, c = arr(ptrs)
             P.keep.append(a)
@@ -505,10 +531,14 @@ class TokenParallelInt2Linear(nn.Module):
         ready = torch.cuda.Event()
         ready.record(main)                  # tokens quantised, replica complete: the push may start here ...
         call("gemm_fwd", lib.el_gemm_fwd_ws, P.own.data_ptr(), W, P.y.data_ptr(), P.dt, P.ax.data_ptr(), 1, gam, Ml, N, K,
-             self.gemm_path, P.ws.data_ptr(), P.ws_bytes, P.status, st)
+             P.gemm_path, P.ws.data_ptr(), P.ws_bytes, P.status, st)
         side.wait_event(ready)              # ... but is queued after the GEMM, so that the GEMM's CTA pairs get their SMs first
         with torch.cuda.stream(side):
-            call("push_tokens", lib.el_peer_put, P.own.data_ptr(), P.peers_x, g - 1, r * Ml * K, Ml * K, self.push_ctas, side.cuda_stream)
+            if P.push_x < 0:
+                call("push_tokens", lib.el_peer_put_dma, P.own.data_ptr(), P.peers_x, g - 1, r * Ml * K, Ml * K, side.cuda_stream)
+            else:
+                call("push_tokens", lib.el_peer_put, P.own.data_ptr(), P.peers_x, g - 1, r * Ml * K, Ml * K, P.push_x,
+                     side.cuda_stream)
         peer.pending = torch.cuda.Event()
         peer.pending.record(side)
         # backward: quantise the gradient rows (with the fold that yields this rank's partial maximum)
@@ -519,7 +549,7 @@ class TokenParallelInt2Linear(nn.Module):
         def input_grad():
             if need_dx:
                 call("gemm_dx", lib.el_gemm_dx_ws, P.dyq.data_ptr(), W, P.dx.data_ptr(), P.dt, P.ady.data_ptr(), 1, gam, Ml, N, K,
-                     self.gemm_path, P.ws.data_ptr(), P.ws_bytes, P.status, st)
+                     P.gemm_path, P.ws.data_ptr(), P.ws_bytes, P.status, st)
 
         def update():
             self._step_py += 1
@@ -542,8 +572,12 @@ class TokenParallelInt2Linear(nn.Module):
                      (self.row_start * K) & 0xFFFFFFFF, g * Ml, Nl, K, P.status, st)
             side.wait_stream(main)          # the updated rows go out on the side stream, under the main stream's next work
             with torch.cuda.stream(side):
-                call("push_weights", lib.el_peer_put, own_w, P.peers_w, g - 1, self.row_start * self.W_packed.shape[1],
-                     Nl * self.W_packed.shape[1], self.push_ctas, side.cuda_stream)
+                if P.push_w < 0:
+                    call("push_weights", lib.el_peer_put_dma, own_w, P.peers_w, g - 1, self.row_start * self.W_packed.shape[1],
+                         Nl * self.W_packed.shape[1], side.cuda_stream)
+                else:
+                    call("push_weights", lib.el_peer_put, own_w, P.peers_w, g - 1, self.row_start * self.W_packed.shape[1],
+                         Nl * self.W_packed.shape[1], P.push_w, side.cuda_stream)
             peer.pending = torch.cuda.Event()
             peer.pending.record(side)
             self._w_ready_epoch = peer.epoch + 1

@@ -297,6 +297,11 @@ EL_API int el_set_peer_barrier_limit_us(long long microseconds);
  * takes few SMs; 0 picks a size that saturates the links.  No counterpart in the reference (single-GPU, README.md:58). */
 EL_API int el_peer_put(const void* src, void* const* dst, int n_dst, size_t dst_offset, size_t bytes, int max_ctas,
                        el_stream_t stream);
+/* The same push through the copy engines: one asynchronous device-to-device copy per destination, queued on `stream` in
+ * the order of dst[] (a rank should list its peers starting with its successor, so that at any moment every GPU receives
+ * from one sender).  No SM takes part, so a GEMM running beside the push keeps all of its SMs and registers; any
+ * alignment.  No counterpart in the reference. */
+EL_API int el_peer_put_dma(const void* src, void* const* dst, int n_dst, size_t dst_offset, size_t bytes, el_stream_t stream);
 
 /* el_quantize_grad for a token-sharded layer, fused with the all-to-all of its result: this rank's M gradient rows
  * dY[M,N] are quantised exactly as el_quantize_grad does, and the column window [d*N/n_ranks, (d+1)*N/n_ranks) of row m is
