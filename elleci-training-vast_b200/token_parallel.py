@@ -22,7 +22,10 @@ Int2LinearTCFunction's (core/bitnet/int2_linear_tc.py:255-305) with the hook's u
 Two data paths.  `fused=False`: torch.distributed collectives (NCCL on GPUs; gloo in the CPU tests, where a stand-in for
 the operator module is injected).  `fused=True` (CUDA): no collective kernel moves data; all buffers that peers write
 live in symmetric memory and the library's own kernels store into them over NVLink (el_peer_put, el_quantize_grad_scatter),
-ordered by el_peer_barrier.  Only stores cross NVLink; nothing loads from a peer.
+ordered by el_peer_barrier; pushes of 8 MiB and more per destination go through the copy engines instead
+(el_peer_put_dma), so that the GEMM beside them keeps every SM.  Only stores and copies cross NVLink; no kernel loads
+from a peer.  `train_step` issues the fused step from a prepared plan and, with `graph_steps=True`, replays it from a
+recorded CUDA graph (what changes per step - barrier numbers, the hysteresis step - then lives in device memory).
 """
 from __future__ import annotations
 
@@ -38,6 +41,7 @@ from .sharded import shard_rows
 
 _FLOAT_IO = (torch.float16, torch.bfloat16, torch.float32)
 PUSH_DMA_MIN_BYTES = 8 << 20      # pushes of at least this many bytes per destination go through the copy engines
+MAX_RECORDED_STEPS = 8            # recorded CUDA graphs kept per (layer, token count): one per distinct (x, dY, settings)
 
 
 class PeerGroup:
@@ -472,15 +476,23 @@ class TokenParallelInt2Linear(nn.Module):
                int(self.threshold), float(self.decay_rate), self.hysteresis_order)
         G = P.graphs.get(key)
         if G is None:
+            if len(P.graphs) >= MAX_RECORDED_STEPS:
+                # The caller's buffers keep changing (every step a new x or dY address): recording a graph per address
+                # would only pile graphs up, so such steps are queued launch by launch.
+                return self._issue_step(P, x, dY, need_dx, recorded=False)
             from types import SimpleNamespace
             peer.join_side()                # nothing recorded waits on work queued before the recording
             saved = (peer.epoch, self._step_py, self._w_ready_epoch, self._step_dirty)
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
-                y, dx = self._issue_step(P, x, dY, need_dx, recorded=True)
-                peer.join_side()            # the side stream's pushes end inside the recording
-            G = SimpleNamespace(graph=graph, y=y, dx=dx, barriers=peer.epoch - saved[0], w_ready=self._w_ready_epoch - saved[0])
-            peer.epoch, self._step_py, self._w_ready_epoch, self._step_dirty = saved      # recording ran nothing
+            try:
+                with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                    y, dx = self._issue_step(P, x, dY, need_dx, recorded=True)
+                    peer.join_side()        # the side stream's pushes end inside the recording
+                G = SimpleNamespace(graph=graph, y=y, dx=dx, barriers=peer.epoch - saved[0],
+                                    w_ready=self._w_ready_epoch - saved[0])
+            finally:                        # recording ran nothing: the host's mirrors go back to where they were
+                peer.epoch, self._step_py, self._w_ready_epoch, self._step_dirty = saved
+                peer.pending = None
             P.graphs[key] = G
         if P.step_dev_value != self._step_py:
             P.step_dev.fill_(self._step_py)
