@@ -210,7 +210,8 @@ class Timer:
 
 
 GEMM_NAMES = ("gemm_fwd", "gemm_dx", "gemm_dw_hysteresis")
-LIBRARY_NAMES = ("all_", "barrier_post", "barrier_dx", "permute_y")     # torch / NCCL work, not this library's launches
+# torch / NCCL work and copy-engine copies: not this library's kernel launches
+LIBRARY_NAMES = ("all_", "barrier_post", "barrier_dx", "permute_y", "push_tokens_dma", "push_weights_dma")
 
 
 class Env:

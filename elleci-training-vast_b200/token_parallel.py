@@ -41,6 +41,7 @@ from .sharded import shard_rows
 
 _FLOAT_IO = (torch.float16, torch.bfloat16, torch.float32)
 PUSH_DMA_MIN_BYTES = 8 << 20      # pushes of at least this many bytes per destination go through the copy engines
+PUSH_STREAMS = 4                  # side streams a copy-engine push spreads its destinations over
 MAX_RECORDED_STEPS = 8            # recorded CUDA graphs kept per (layer, token count): one per distinct (x, dY, settings)
 
 
@@ -61,8 +62,11 @@ class PeerGroup:
         self.handle = symm_mem.rendezvous(self.flags, self.group)
         self.handle.barrier(channel=0)              # every rank's flags are zero before anybody signals
         self.epoch = 0
-        self.side = torch.cuda.Stream(device=device)
-        self.pending = None             # event of the last push queued on the side stream and not yet joined
+        # Side streams for the pushes.  A peer-store kernel runs on the first; copy-engine pushes spread their
+        # destinations over all of them, so that several copy engines work at once instead of one copy after the other.
+        self.sides = [torch.cuda.Stream(device=device) for _ in range(PUSH_STREAMS)]
+        self.side = self.sides[0]
+        self.pending = []               # events of the pushes queued on side streams and not yet joined
 
     @classmethod
     def get(cls, group, device: torch.device, ops) -> "PeerGroup":
@@ -73,9 +77,11 @@ class PeerGroup:
 
     def join_side(self) -> None:
         """Pushes queued on the side stream are ordered before whatever the main stream does next (a barrier)."""
-        if self.pending is not None:
-            torch.cuda.current_stream().wait_event(self.pending)
-            self.pending = None
+        if self.pending:
+            main = torch.cuda.current_stream()
+            for ev in self.pending:
+                main.wait_event(ev)
+            self.pending = []
 
     def barrier(self, word: Optional[torch.Tensor] = None, dst_ptrs=None, dst_offset: int = 0) -> None:
         """All ranks have finished the work queued on their main streams so far - and on the side stream before this
@@ -274,6 +280,27 @@ class TokenParallelInt2Linear(nn.Module):
         """Path flags of the forward and dX GEMMs for Ml local tokens: register-lean only beside a push kernel."""
         return self._lean if self._push_mode(Ml * self.in_features) > 0 else 0
 
+    def _queue_push(self, name: str, src: torch.Tensor, dst_ptrs, dst_offset: int, after: Optional[torch.cuda.Event]):
+        """Queues the push of the contiguous tensor `src` to `dst_offset` of every buffer in `dst_ptrs` (peers, from the
+        successor on) on the side stream(s), after `after` (an event of the main stream; None: after everything queued
+        on the main stream so far), and notes the events a later barrier has to wait for."""
+        peer, main = self._peer, torch.cuda.current_stream()
+        mode = self._push_mode(src.numel() * src.element_size())
+        if mode < 0:            # copy engines: destination j goes to side stream j mod PUSH_STREAMS
+            groups = [(peer.sides[j], dst_ptrs[j::PUSH_STREAMS]) for j in range(min(PUSH_STREAMS, len(dst_ptrs)))]
+        else:
+            groups = [(peer.side, list(dst_ptrs))]
+        for stream, ptrs in groups:
+            if after is not None:
+                stream.wait_event(after)
+            else:
+                stream.wait_stream(main)
+            with torch.cuda.stream(stream):
+                self._run(name if mode >= 0 else name + "_dma", self.ops.peer_put, src, ptrs, dst_offset, mode)
+                ev = torch.cuda.Event()
+                ev.record(stream)
+            peer.pending.append(ev)
+
     def _successors(self, ptrs):
         """The peers' entries of `ptrs`, starting with this rank's successor: when every rank pushes in this order, each
         GPU receives from one sender at a time (copy-engine pushes run one destination after the other)."""
@@ -327,17 +354,7 @@ class TokenParallelInt2Linear(nn.Module):
         (`ready`: recorded on the main stream once the tokens were quantised; without it the push waits for all of the
         main stream's queued work)."""
         if self._use_fused():
-            main, side = torch.cuda.current_stream(), self._peer.side
-            if ready is not None:
-                side.wait_event(ready)
-            else:
-                side.wait_stream(main)
-            peers = self._successors(bufs["hx"].buffer_ptrs)
-            with torch.cuda.stream(side):
-                self._run("push_tokens", self.ops.peer_put, own, peers, self.rank * Ml * self.in_features,
-                          self._push_mode(Ml * self.in_features))
-                self._peer.pending = torch.cuda.Event()
-                self._peer.pending.record(side)
+            self._queue_push("push_tokens", own, self._successors(bufs["hx"].buffer_ptrs), self.rank * Ml * self.in_features, ready)
         else:
             self._run("all_gather_tokens", dist.all_gather_into_tensor, bufs["xq_all"], own.clone(), group=self.group)
 
@@ -380,14 +397,8 @@ class TokenParallelInt2Linear(nn.Module):
             return
         if self._use_fused():
             # the updated rows go out on the side stream, under whatever the main stream does until the next barrier
-            peers = self._successors(self._w_handle.buffer_ptrs)
-            main, side = torch.cuda.current_stream(), self._peer.side
-            side.wait_stream(main)
-            with torch.cuda.stream(side):
-                run("push_weights", ops.peer_put, own, peers, self.row_start * self.W_packed.shape[1],
-                    self._push_mode(own.numel()))
-                self._peer.pending = torch.cuda.Event()
-                self._peer.pending.record(side)
+            self._queue_push("push_weights", own, self._successors(self._w_handle.buffer_ptrs),
+                             self.row_start * self.W_packed.shape[1], None)
             self._w_ready_epoch = self._peer.epoch + 1          # complete after the next barrier, whoever queues it
         else:
             run("all_gather_weights", dist.all_gather_into_tensor, self.W_packed, own.clone(), group=self.group)
@@ -430,7 +441,7 @@ class TokenParallelInt2Linear(nn.Module):
         P.step_dev_value = 0
         P.graphs = {}
         P.warm = False
-        P.push_x, P.push_w = self._push_mode(Ml * K), self._push_mode(Nl * self.W_packed.shape[1])
+        P.succ_x, P.succ_w = self._successors(bufs["hx"].buffer_ptrs), self._successors(self._w_handle.buffer_ptrs)
         P.gemm_path = self._gemm_flags(Ml)
         P.own = bufs["xq_all"][r * Ml:(r + 1) * Ml]
         P.status = ops.device_status(dev).data_ptr()
@@ -444,9 +455,7 @@ class TokenParallelInt2Linear(nn.Module):
             return a, ctypes.cast(a, ctypes.c_void_p)
 
         P.keep = []
-        for name, ptrs in (("peers_x", self._successors(bufs["hx"].buffer_ptrs)),
-                           ("all_slots", list(bufs["hs"].buffer_ptrs)), ("all_gq", list(bufs["hg"].buffer_ptrs)),
-                           ("peers_w", self._successors(self._w_handle.buffer_ptrs)),
+        for name, ptrs in (("all_slots", list(bufs["hs"].buffer_ptrs)), ("all_gq", list(bufs["hg"].buffer_ptrs)),
                            ("flags", list(self._peer.handle.buffer_ptrs))):
             a, c = arr(ptrs)
             P.keep.append(a)
@@ -492,7 +501,7 @@ class TokenParallelInt2Linear(nn.Module):
                                     w_ready=self._w_ready_epoch - saved[0])
             finally:                        # recording ran nothing: the host's mirrors go back to where they were
                 peer.epoch, self._step_py, self._w_ready_epoch, self._step_dirty = saved
-                peer.pending = None
+                peer.pending = []
             P.graphs[key] = G
         if P.step_dev_value != self._step_py:
             P.step_dev.fill_(self._step_py)
@@ -539,20 +548,12 @@ class TokenParallelInt2Linear(nn.Module):
              None, None, st)
         if peer.epoch < self._w_ready_epoch:
             barrier("barrier_weights")
-        side = peer.side
         ready = torch.cuda.Event()
         ready.record(main)                  # tokens quantised, replica complete: the push may start here ...
         call("gemm_fwd", lib.el_gemm_fwd_ws, P.own.data_ptr(), W, P.y.data_ptr(), P.dt, P.ax.data_ptr(), 1, gam, Ml, N, K,
              P.gemm_path, P.ws.data_ptr(), P.ws_bytes, P.status, st)
-        side.wait_event(ready)              # ... but is queued after the GEMM, so that the GEMM's CTA pairs get their SMs first
-        with torch.cuda.stream(side):
-            if P.push_x < 0:
-                call("push_tokens", lib.el_peer_put_dma, P.own.data_ptr(), P.peers_x, g - 1, r * Ml * K, Ml * K, side.cuda_stream)
-            else:
-                call("push_tokens", lib.el_peer_put, P.own.data_ptr(), P.peers_x, g - 1, r * Ml * K, Ml * K, P.push_x,
-                     side.cuda_stream)
-        peer.pending = torch.cuda.Event()
-        peer.pending.record(side)
+        # ... but is queued after the GEMM, so that the GEMM's CTA pairs get their SMs first
+        self._queue_push("push_tokens", P.own, P.succ_x, r * Ml * K, ready)
         # backward: quantise the gradient rows (with the fold that yields this rank's partial maximum)
         P.gloc.zero_()
         call("quantize_rows_dy", lib.el_quantize_rows, dY.data_ptr(), P.dt, N, P.dyq.data_ptr(), P.ady.data_ptr(), Ml, N, GRAD_EPS, 0,
@@ -582,16 +583,8 @@ class TokenParallelInt2Linear(nn.Module):
                      bufs["gmax"].data_ptr(), own_w, self.H_packed.data_ptr(), float(self._lr), float(self.lr_scale),
                      int(self.threshold), float(self.decay_rate), step32 - (1 << 32) if step32 >= (1 << 31) else step32,
                      (self.row_start * K) & 0xFFFFFFFF, g * Ml, Nl, K, P.status, st)
-            side.wait_stream(main)          # the updated rows go out on the side stream, under the main stream's next work
-            with torch.cuda.stream(side):
-                if P.push_w < 0:
-                    call("push_weights", lib.el_peer_put_dma, own_w, P.peers_w, g - 1, self.row_start * self.W_packed.shape[1],
-                         Nl * self.W_packed.shape[1], side.cuda_stream)
-                else:
-                    call("push_weights", lib.el_peer_put, own_w, P.peers_w, g - 1, self.row_start * self.W_packed.shape[1],
-                         Nl * self.W_packed.shape[1], P.push_w, side.cuda_stream)
-            peer.pending = torch.cuda.Event()
-            peer.pending.record(side)
+            # the updated rows go out on the side stream(s), under the main stream's next work
+            self._queue_push("push_weights", self.owned_rows(), P.succ_w, self.row_start * self.W_packed.shape[1], None)
             self._w_ready_epoch = peer.epoch + 1
 
         if self.hysteresis_order == "reference":
