@@ -667,6 +667,22 @@ def test_peer_put_copies_the_block_into_every_destination(ops, nbytes, offset):
         assert bool((d[:offset] == 7).all()) and bool((d[offset + nbytes:] == 7).all())
 
 
+@pytest.mark.parametrize("nbytes,offset", [(4096, 0), (70001, 13), (3 << 20, 4096)])
+def test_peer_put_through_the_copy_engines(ops, nbytes, offset):
+    """The same push as one copy-engine copy per destination (max_ctas < 0): any size and alignment, the same bytes in
+    every destination, nothing around them touched; ordered with kernels of the stream (the source is written by a
+    kernel queued just before, and a kernel queued after reads the destinations)."""
+    src = torch.empty(nbytes, dtype=torch.uint8, device=DEV)
+    dsts = [torch.full((offset + nbytes + 64,), 7, dtype=torch.uint8, device=DEV) for _ in range(3)]
+    src.copy_(torch.arange(nbytes, device=DEV, dtype=torch.int64).remainder(251).to(torch.uint8))
+    ops.peer_put(src, [d.data_ptr() for d in dsts], offset, max_ctas=-1)
+    sums = [int(d[offset:offset + nbytes].to(torch.int64).sum().item()) for d in dsts]
+    want = int(src.to(torch.int64).sum().item())
+    for d, s_ in zip(dsts, sums):
+        assert s_ == want and torch.equal(d[offset:offset + nbytes], src)
+        assert bool((d[:offset] == 7).all()) and bool((d[offset + nbytes:] == 7).all())
+
+
 def test_peer_put_rejects_misaligned_blocks(ops, pkg):
     src = torch.zeros(64, dtype=torch.uint8, device=DEV)
     dst = torch.zeros(64, dtype=torch.uint8, device=DEV)
