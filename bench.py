@@ -716,10 +716,51 @@ def measure_e2e(env: Env, bench: StepBench, steps: int):
     copy_in, copy_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
 
     def e2e_step():
-        # the host->device copies of all layers go out on a copy stream at the start of the step, so a later layer's
-        # inputs cross PCIe while an earlier layer computes; results leave on a second copy stream as they appear
+        # A training step's order: forward through the layers, backward through them in reverse.  The host->device
+        # copies go out on a copy stream in the order the step needs them (inputs first, then the output gradients,
+        # last layer's first), results leave on a second copy stream as they appear; PCIe is full duplex, so Y of the
+        # first layer already travels back while the later inputs still arrive.  What arrives last (the first layer's
+        # gradient) feeds the smallest result (its dX), which keeps the tail after the last arrival short.
         main = torch.cuda.current_stream()
         copy_in.wait_stream(main)                  # copies start inside the timed region
+        xs, dys = [], {}
+        with torch.cuda.stream(copy_in):
+            for i, (m, xh, dyh, yh, dxh) in enumerate(mods):
+                x = xh.to(dev, non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(copy_in)
+                xs.append((x, ev))
+            for i in reversed(range(len(mods))):
+                dy = mods[i][2].to(dev, non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(copy_in)
+                dys[i] = (dy, ev)
+        ys = []
+        for (m, xh, dyh, yh, dxh), (x, ev) in zip(mods, xs):
+            main.wait_event(ev)
+            x.record_stream(main)
+            x.requires_grad_(True)
+            y = m(x)
+            copy_out.wait_stream(main)
+            with torch.cuda.stream(copy_out):
+                yh.copy_(y.detach(), non_blocking=True)
+            y.record_stream(copy_out)
+            ys.append(y)
+        for i in reversed(range(len(mods))):
+            (m, xh, dyh, yh, dxh), (x, _), (dy, ev) = mods[i], xs[i], dys[i]
+            main.wait_event(ev)
+            dy.record_stream(main)
+            ys[i].backward(dy)
+            copy_out.wait_stream(main)
+            with torch.cuda.stream(copy_out):
+                dxh.copy_(x.grad, non_blocking=True)
+            x.grad.record_stream(copy_out)
+        main.wait_stream(copy_out)                 # the step ends when its results are on the host
+
+    def e2e_step_per_layer():
+        # the other order (--e2e-order layer): each layer's forward and backward back to back, all inputs copied first
+        main = torch.cuda.current_stream()
+        copy_in.wait_stream(main)
         staged = []
         with torch.cuda.stream(copy_in):
             for m, xh, dyh, yh, dxh in mods:
@@ -743,8 +784,10 @@ def measure_e2e(env: Env, bench: StepBench, steps: int):
             with torch.cuda.stream(copy_out):
                 dxh.copy_(x.grad, non_blocking=True)
             x.grad.record_stream(copy_out)
-        main.wait_stream(copy_out)                 # the step ends when its results are on the host
+        main.wait_stream(copy_out)
 
+    if env.args.e2e_order == "layer":
+        e2e_step = e2e_step_per_layer
     e_steps = max(3, min(steps, 20))
     for _ in range(3):
         e2e_step()
@@ -1285,6 +1328,9 @@ def main():
                     help="N > 1: which partition(s) of the step to measure (value = the faster of those measured)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg of the default run")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
+    ap.add_argument("--e2e-order", default="step", choices=["step", "layer"],
+                    help="end-to-end leg: forward through all layers then backward in reverse (a training step), or each "
+                         "layer's forward and backward back to back")
     ap.add_argument("--no-config4", action="store_true", help="skip the config-4 sub-record of the default run")
     ap.add_argument("--push-ctas", type=int, default=0,
                     help="token partition: CTAs of the peer-store kernel that pushes tokens and weight rows "
