@@ -124,3 +124,31 @@ def test_token_parallel_single_rank_equals_the_n_sharded_single_rank_layer():
         assert torch.equal(y.detach(), ys1[i]) and torch.equal(x.grad, dxs1[i])
     assert torch.equal(ref.W_packed, W1) and torch.equal(ref.H_packed, H1)
     assert int(ref._step.item()) == STEPS
+
+
+def test_push_policy_and_peer_order():
+    """Host-side choices of the fused path that need no GPU: the peers are listed from the rank's successor on (so that
+    copy-engine pushes of all ranks never meet at one destination), pushes of 8 MiB and more per destination go through
+    the copy engines, smaller ones through the peer-store kernel with one CTA per SM, and the register-lean GEMM form is
+    only chosen beside a push kernel, from four ranks on."""
+    import oracle_ops
+    pkg = load_package()
+    tp = pkg.token_parallel
+    layer = tp.TokenParallelInt2Linear(4096, 11008, threshold=2, ops=oracle_ops)
+    layer.world, layer.rank = 8, 5
+    assert layer._successors(list("abcdefgh")) == list("ghabcde")
+    # every rank r sends to (r + j) mod g at position j: at a given position all destinations differ
+    for j in range(1, 8):
+        dests = set()
+        for r in range(8):
+            layer.rank = r
+            dests.add(layer._successors(list(range(8)))[j - 1])
+        assert dests == set(range(8))
+    assert layer._push_mode(tp.PUSH_DMA_MIN_BYTES) < 0 and layer._push_mode(tp.PUSH_DMA_MIN_BYTES - 1) == 148
+    layer.push_ctas = 37
+    assert layer._push_mode(1) == 37 and layer._push_mode(1 << 30) == 37
+    layer.push_ctas = -1
+    assert layer._push_mode(1) < 0
+    layer.push_ctas, layer._lean = 0, 0x100
+    assert layer._gemm_flags(512) == 0x100            # 512 x 4096 = 2 MiB per destination: kernel push, lean GEMM beside it
+    assert layer._gemm_flags(8192) == 0               # 32 MiB: copy engines, the GEMM keeps its faster form
