@@ -687,6 +687,27 @@ def measure_ref_cuda(env: Env):
             "rows": rows}
 
 
+def gpu_local_cpus(torch, index: int):
+    """The CPUs on the NUMA node the GPU's PCIe slot hangs off (from sysfs), restricted to those this process may use;
+    None when the system does not say."""
+    try:
+        pr = torch.cuda.get_device_properties(index)
+        path = f"/sys/bus/pci/devices/{pr.pci_domain_id:04x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0/local_cpulist"
+        with open(path) as f:
+            text = f.read().strip()
+        cpus = set()
+        for part in text.split(","):
+            if "-" in part:
+                a, b = part.split("-")
+                cpus.update(range(int(a), int(b) + 1))
+            elif part:
+                cpus.add(int(part))
+        cpus &= os.sched_getaffinity(0)
+        return cpus or None
+    except (OSError, ValueError, AttributeError):
+        return None
+
+
 def measure_e2e(env: Env, bench: StepBench, steps: int):
     """The same step through the module API with HOST buffers: every step copies the layers' inputs (X and dY of each
     layer) from pinned host memory to the device and copies each layer's results (Y and dX) back to pinned host memory,
@@ -694,6 +715,13 @@ def measure_e2e(env: Env, bench: StepBench, steps: int):
     torch, pkg, dev = env.torch, env.pkg, env.dev
     wl, thr = bench.wl, bench.wl["threshold"]
     mods = []
+    # The pinned host buffers are allocated from a thread that runs on the GPU's own NUMA node, so that their pages sit
+    # next to the GPU's PCIe root: on a two-socket host, pages on the other socket put the inter-socket link into every
+    # copy.  (What a trainer's data loader does with its staging buffers.)  The affinity is put back afterwards.
+    old_affinity = os.sched_getaffinity(0)
+    local = gpu_local_cpus(torch, dev.index)
+    if local:
+        os.sched_setaffinity(0, local)
     for lay in bench.layers:
         if bench.partition == "tokens":
             m = lay.mod
@@ -711,6 +739,8 @@ def measure_e2e(env: Env, bench: StepBench, steps: int):
         yh = torch.empty(xh.shape[0], lay.N, dtype=torch.bfloat16).pin_memory()
         dxh = torch.empty(xh.shape[0], lay.K, dtype=torch.bfloat16).pin_memory()
         mods.append((m, xh, dyh, yh, dxh))
+    if local:
+        os.sched_setaffinity(0, old_affinity)
     h2d = sum(x.numel() * 2 + dy.numel() * 2 for _, x, dy, _, _ in mods)
     d2h = sum(y.numel() * 2 + dx.numel() * 2 for _, _, _, y, dx in mods)
     copy_in, copy_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
@@ -807,7 +837,8 @@ def measure_e2e(env: Env, bench: StepBench, steps: int):
             "bound": (f"host link: {(h2d + d2h) / 1e6:.0f} MB{per_rank} cross PCIe per step (X, dY in; Y, dX out); "
                       f"the link moved {max(h2d, d2h) / (e_ms * 1e-3) / 1e9:.1f} GB/s in its busier direction"),
             "api": "token_parallel.TokenParallelInt2Linear (autograd)" if bench.partition == "tokens"
-                   else "Int2LinearTCWithGradHook (autograd, gradient hook)"}
+                   else "Int2LinearTCWithGradHook (autograd, gradient hook)",
+            "host_buffers": ("pinned, allocated on the GPU's NUMA node" if local else "pinned (the GPU's NUMA node is not known)")}
 
 
 def run_ours(args, wl):
